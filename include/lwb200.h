@@ -1,0 +1,132 @@
+/* C ABI of liblwb200: Huffman-coded llama.cpp block weights decoded on the GPU (sm_100a), fused with block
+ * dequantisation and the matrix-vector / small-M matrix product.
+ *
+ * The rt_* entry points keep the names, argument meaning and return conventions of the reference runtime's
+ * `extern "C"` block (kernels/llmrt.cu:1916-2575) for the per-matrix path, so that a ctypes caller such as
+ * scripts/a2_act8_ppl.py:56-77 binds them unchanged.  The lw_* entry points are additions: device-pointer
+ * variants for callers that already hold activations on the GPU, the host-side codec, and error reporting.
+ *
+ * Conventions: plain pointers and sizes only; a handle is an opaque pointer owned by the library and released by
+ * rt_close; the library owns all device memory it allocates; callers own every buffer they
+ * pass.  One handle is driven by one host thread at a time.  Where the reference prints and exits on a CUDA error
+ * or a malformed bundle, these functions return a negative status (or NULL) and leave a message for
+ * lw_last_error().  Without a CUDA device every function that needs one fails with LW_ERR_NO_DEVICE: there is no
+ * CPU fallback for the GPU path.
+ */
+#ifndef LWB200_H
+#define LWB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  LW_OK = 0,
+  LW_ERR = -1,           /* not found / not resident (the reference's -1) */
+  LW_ERR_ARG = -2,
+  LW_ERR_FORMAT = -3,    /* malformed bundle or blob, rejected on the host before anything is launched */
+  LW_ERR_CUDA = -4,
+  LW_ERR_TOO_LARGE = -5,
+  LW_ERR_NO_DEVICE = -6
+};
+
+/* Block formats (side-tensor encodings kq_Q4_K, kq_Q5_K, kq_Q6_K, kq_IQ4_XS; kernels/llmrt.cu:113-121). */
+enum { LW_FMT_NONE = 0, LW_FMT_Q4_K = 1, LW_FMT_Q5_K = 2, LW_FMT_Q6_K = 3, LW_FMT_IQ4_XS = 4 };
+
+/* ---- bundle handle ------------------------------------------------------------------------------------- */
+
+/* Opens a bundle directory (manifest.txt + weights.bin, lazyweights/bundle.py:10-21) on the current CUDA device:
+ * validates every coded matrix on the host, re-lays it out and uploads it with its `.kqs` side tensor.
+ * Replaces rt_open, kernels/llmrt.cu:1921.  budget_mb and floor_mb are accepted for signature compatibility;
+ * every matrix is made resident (no streaming on a 180 GB device).  Returns NULL on failure. */
+void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, int floor_mb, int verbose);
+
+/* Frees the handle and all device memory it owns.  Replaces rt_close, kernels/llmrt.cu:2239. */
+void rt_close(void* handle);
+
+/* Y[m, N] = X[m, K] . dequant(W)^T with host fp32 buffers; path 0 auto, 1 fused decode+product per chunk of up to
+ * eight rows, 2 decode to fp16 weights then GEMM.  Returns -1 if the matrix is unknown.
+ * Replaces rt_test_matmul, kernels/llmrt.cu:2441. */
+int rt_test_matmul(void* handle, const char* name, const float* X, int m, float* Y, int path);
+
+/* Decodes a matrix on the GPU to host codes, one code per byte [N, K].  Replaces rt_test_decode,
+ * kernels/llmrt.cu:2461. */
+int rt_test_decode(void* handle, const char* name, uint8_t* out);
+
+/* Decodes a matrix on `threads` host threads to symbols [N, K / (8 / bits)].  Replaces rt_test_cpu_decode,
+ * kernels/llmrt.cu:2543. */
+int rt_test_cpu_decode(void* handle, const char* name, int threads, uint8_t* out);
+
+/* GPU decode of every coded matrix into scratch, median seconds per pass over `reps` passes.  Replaces
+ * rt_gpu_decode_all, kernels/llmrt.cu:2482. */
+double rt_gpu_decode_all(void* handle, int reps);
+
+/* Host decode of every coded matrix on `threads` threads; returns seconds and the symbol count.  Replaces
+ * rt_cpu_decode_all, kernels/llmrt.cu:2558. */
+double rt_cpu_decode_all(void* handle, int threads, long long* symbols);
+
+/* Counters by name ("resident_bytes", "coded_bytes", "side_bytes", "n_matrices", ...); -1 for an unknown key.
+ * Replaces rt_stat, kernels/llmrt.cu:2276. */
+double rt_stat(void* handle, const char* key);
+
+/* ---- per-matrix entry points on device pointers (additions) ---------------------------------------------- */
+
+/* Index of a matrix in the handle (>= 0) or -1.  The *_id variants below skip the name lookup. */
+int lw_matrix_id(void* handle, const char* name);
+
+/* Shape and sizes of matrix `id`: N rows, K weights per row, block format, coded blob bytes and side bytes as in
+ * the manifest (the algorithmic bytes of one product), and the bytes the device layout occupies. */
+int lw_matrix_info(void* handle, int id, int* N, int* K, int* fmt, long long* blob_bytes, long long* side_bytes,
+                   long long* device_bytes);
+
+/* y[m, N] (fp32, row stride N) = x[m, K] . W^T for 1 <= m <= 8; x is fp16 (x_is_half != 0) or fp32, row-major, on
+ * the device.  Launches on `stream` (a cudaStream_t) and does not synchronise.  This is the device-pointer form of
+ * the reference's internal matmul(), kernels/llmrt.cu:1794-1826. */
+int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
+
+/* Decoded and dequantised weights as fp16 [N, K] on the device: float32 block arithmetic (scale * f(q) - offset,
+ * each operation rounded) rounded once to fp16. */
+int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream);
+
+/* Decoded codes on the device, one per byte [N, K] (expand != 0) or symbols [N, K / (8 / bits)] (expand == 0). */
+int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* stream);
+
+/* ---- single matrices without a bundle directory (additions) ---------------------------------------------- */
+
+/* Builds a one-matrix handle from a blob in host memory (N rows, Ks symbols per row), an optional side tensor and
+ * its block format.  The matrix has id 0.  Released by rt_close. */
+void* lw_matrix_create(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
+                       long long side_bytes);
+
+/* ---- host-side codec (no GPU needed; additions mirroring lazyweights/bundle.py:57-106) -------------------- */
+
+/* Encodes symbols [N, Ks] into a blob.  Returns the blob size in bytes; if out is NULL or cap is too small only the
+ * size is returned.  nbits receives the payload bits. */
+long long lw_encode_huf8(const uint8_t* sym, int N, int Ks, uint8_t* out, long long cap, long long* nbits);
+
+/* Full host-side validation of a blob: canonical table, every lane decodes and ends where the next begins. */
+int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks);
+
+/* Threaded host decode of a blob to symbols [N, Ks] (the algorithm of cpu_decode, kernels/llmrt.cu:2513-2541). */
+int lw_cpu_decode(const uint8_t* blob, long long blob_bytes, int N, int Ks, int threads, uint8_t* out);
+
+/* ---- diagnostics ------------------------------------------------------------------------------------------ */
+
+/* Message of the last failure on the calling thread. */
+const char* lw_last_error(void);
+
+/* Status code of the last rt_open / lw_matrix_create on the calling thread (they can only return NULL). */
+int lw_last_status(void);
+
+/* Reads and clears the device error word (bit 0: a bounded wait on a bulk copy gave up). */
+int lw_kernel_error(void);
+
+/* Number of kernels this library has launched since it was loaded. */
+long long lw_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

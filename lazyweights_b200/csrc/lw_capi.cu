@@ -1,0 +1,507 @@
+// The extern "C" surface (include/lwb200.h): bundle handles, per-matrix products and decodes, the host codec.
+#include <fcntl.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/lwb200.h"
+#include "lw_host.h"
+#include "lw_kernels.h"
+
+namespace lw {
+
+void set_kernel_error_text(const char* what, const char* detail) { set_error("%s: %s", what, detail); }
+
+struct Matrix {
+  std::string name;
+  int N = 0, K = 0, Ks = 0, fmt = kFmtNone;
+  bool paired = false;
+  long long blob_bytes = 0, side_bytes = 0, file_offset = -1;
+  size_t device_bytes = 0;
+  void* d_block = nullptr;   // one allocation: table, group bases, words, side bytes
+  MatDev dev{};
+};
+
+struct Model {
+  std::string dir;
+  Manifest man;
+  int fd = -1;
+  int device = 0;
+  bool verbose = false;
+  std::vector<Matrix> mats;
+  std::map<std::string, int> by_name;
+  float* d_partials = nullptr;   // split-K partial sums, sized for the largest matrix at m = 8
+  size_t partial_floats = 0;
+  size_t resident_bytes = 0;
+  long long coded_bytes = 0, side_bytes = 0;
+  ~Model() {
+    for (auto& m : mats)
+      if (m.d_block) cudaFree(m.d_block);
+    if (d_partials) cudaFree(d_partials);
+    if (fd >= 0) close(fd);
+  }
+};
+
+static int cuda_fail(const char* what, cudaError_t e) {
+  set_error("%s: %s", what, cudaGetErrorString(e));
+  return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? kErrNoDevice : kErrCuda;
+}
+
+static int require_device(int* dev) {
+  int n = 0;
+  const cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0) {
+    cudaGetLastError();
+    set_error("no CUDA device: this library has no CPU path for GPU entry points");
+    return kErrNoDevice;
+  }
+  if (cudaGetDevice(dev) != cudaSuccess) return cuda_fail("cudaGetDevice", cudaGetLastError());
+  return kOk;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Validates, indexes, re-lays out and uploads one blob.  Ks = symbols per row.
+static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uint8_t* side, size_t side_nbytes,
+                       int threads) {
+  BlobView v;
+  int rc = make_view(blob, nbytes, mx.N, mx.Ks, v);
+  if (rc) return rc;
+  auto tab = std::make_unique<HuffTable>();
+  if ((rc = table_from_lut(v.lut(), *tab))) return rc;
+  if (mx.fmt != kFmtNone) {
+    const size_t want = static_cast<size_t>(mx.N) * (mx.K / 256) * side_bytes(mx.fmt);
+    if (mx.K % 256 || side_nbytes != want || !side) {
+      set_error("%s: side tensor of %zu bytes, expected %zu", mx.name.c_str(), side_nbytes, want);
+      return kErrFormat;
+    }
+  }
+  const int split = 1;
+  std::vector<uint32_t> chain_start, lane_end, group_base, words;
+  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr))) return rc;
+  uint32_t max_group = 0, max_tile = 0;
+  if ((rc = relayout(v, split, chain_start, lane_end, threads, group_base, words, &max_group, &max_tile))) return rc;
+
+  const size_t off_gb = align_up(2 * kLutSize, 256);
+  const size_t off_words = align_up(off_gb + group_base.size() * 4, 256);
+  const size_t off_side = align_up(off_words + words.size() * 4, 256);
+  const size_t total = off_side + align_up(side_nbytes, 256);
+  cudaError_t e = cudaMalloc(&mx.d_block, total);
+  if (e != cudaSuccess) return cuda_fail("cudaMalloc (matrix)", e);
+  uint8_t* d = static_cast<uint8_t*>(mx.d_block);
+  if ((e = cudaMemcpy(d, v.lut(), 2 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_gb, group_base.data(), group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_words, words.data(), words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (side_nbytes && (e = cudaMemcpy(d + off_side, side, side_nbytes, cudaMemcpyHostToDevice)) != cudaSuccess))
+    return cuda_fail("cudaMemcpy (matrix)", e);
+  mx.device_bytes = total;
+  mx.dev.lut = reinterpret_cast<const uint16_t*>(d);
+  mx.dev.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
+  mx.dev.words = reinterpret_cast<const uint32_t*>(d + off_words);
+  mx.dev.side = side_nbytes ? d + off_side : nullptr;
+  mx.dev.N = mx.N;
+  mx.dev.K = mx.K;
+  mx.dev.Ks = mx.Ks;
+  mx.dev.KT = v.KT;
+  mx.dev.T = v.T;
+  mx.dev.fmt = mx.fmt;
+  mx.dev.split = split;
+  mx.dev.max_tile_words = max_tile;
+  return kOk;
+}
+
+static int finish_model(Model* M) {
+  size_t need = 0;
+  for (auto& m : M->mats) {
+    if (m.fmt != kFmtNone) need = std::max(need, gemv_partial_floats(m.dev, 8));
+    M->resident_bytes += m.device_bytes;
+    M->coded_bytes += m.blob_bytes;
+    M->side_bytes += m.side_bytes;
+  }
+  if (need) {
+    const cudaError_t e = cudaMalloc(&M->d_partials, need * sizeof(float));
+    if (e != cudaSuccess) return cuda_fail("cudaMalloc (partials)", e);
+    M->partial_floats = need;
+  }
+  return kOk;
+}
+
+static Matrix* matrix_by_id(void* h, int id) {
+  Model* M = static_cast<Model*>(h);
+  if (!M || id < 0 || id >= static_cast<int>(M->mats.size())) {
+    set_error("no matrix with id %d", id);
+    return nullptr;
+  }
+  return &M->mats[id];
+}
+
+static int matrix_id(Model* M, const char* name) {
+  if (!M || !name) return -1;
+  auto it = M->by_name.find(name);
+  if (it == M->by_name.end()) {
+    set_error("no coded matrix named %s", name);
+    return -1;
+  }
+  return it->second;
+}
+
+static int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy,
+                         cudaStream_t st) {
+  if (mx.fmt == kFmtNone) {
+    set_error("%s has no side tensor: products need a block format", mx.name.c_str());
+    return kErrArg;
+  }
+  const size_t xe = x_half ? 2 : 4;
+  for (int r0 = 0; r0 < m; r0 += 8) {
+    const int mm = std::min(8, m - r0);
+    const int rc = launch_gemv(mx.dev, static_cast<const uint8_t*>(x) + static_cast<size_t>(r0) * mx.K * xe, x_half,
+                               mm, y + static_cast<size_t>(r0) * ldy, ldy, M->d_partials, st);
+    if (rc) return rc;
+  }
+  return kOk;
+}
+
+}  // namespace lw
+
+using namespace lw;
+
+extern "C" {
+
+const char* lw_last_error(void) { return last_error(); }
+
+int lw_last_status(void) { return last_status(); }
+
+int lw_kernel_error(void) {
+  unsigned int v = 0;
+  if (read_kernel_error(&v, true)) return kErrCuda;
+  return static_cast<int>(v);
+}
+
+long long lw_launch_count(void) { return launch_count(); }
+
+void rt_close(void* handle) { delete static_cast<Model*>(handle); }
+
+void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, int floor_mb, int verbose) {
+  (void)max_ctx; (void)max_batch; (void)budget_mb; (void)floor_mb;
+  note_status(kOk);
+  if (!dir) {
+    set_error("rt_open: null directory");
+    note_status(kErrArg);
+    return nullptr;
+  }
+  auto M = std::make_unique<Model>();
+  M->dir = dir;
+  M->verbose = verbose != 0;
+  if (note_status(read_manifest(M->dir, M->man))) return nullptr;
+  M->fd = open((M->dir + "/weights.bin").c_str(), O_RDONLY);
+  if (M->fd < 0) {
+    set_error("cannot open %s/weights.bin", dir);
+    note_status(kErrGeneric);
+    return nullptr;
+  }
+  if (note_status(require_device(&M->device))) return nullptr;
+  const auto t0 = std::chrono::steady_clock::now();
+  const int threads = default_threads();
+  std::vector<uint8_t> blob, side;
+  for (const TensorEntry& t : M->man.tensors) {
+    if (t.enc != "huf8" && t.enc != "huf4p") continue;
+    Matrix mx;
+    mx.name = t.name;
+    mx.N = t.N;
+    mx.K = t.K;
+    mx.paired = t.enc == "huf4p";
+    mx.Ks = mx.paired ? t.K / 2 : t.K;
+    mx.blob_bytes = t.nbytes;
+    mx.file_offset = t.offset;
+    if (mx.paired && t.K % 2) {
+      set_error("%s: odd K for a paired matrix", t.name.c_str());
+      note_status(kErrFormat);
+      return nullptr;
+    }
+    if (note_status(read_blob(M->fd, t, blob))) return nullptr;
+    const TensorEntry* s = M->man.find(t.name + ".kqs");
+    size_t sbytes = 0;
+    if (s) {
+      mx.fmt = format_of_side_enc(s->enc);
+      if (mx.fmt == kFmtNone || is_paired(mx.fmt) != mx.paired || s->N != t.N) {
+        set_error("%s: side tensor %s does not fit a %s matrix", t.name.c_str(), s->enc.c_str(), t.enc.c_str());
+        note_status(kErrFormat);
+        return nullptr;
+      }
+      if (note_status(read_blob(M->fd, *s, side))) return nullptr;
+      sbytes = static_cast<size_t>(s->nbytes);
+      mx.side_bytes = s->nbytes;
+    }
+    if (note_status(load_matrix(mx, blob.data(), static_cast<size_t>(t.nbytes), s ? side.data() : nullptr, sbytes,
+                                threads))) {
+      if (mx.d_block) cudaFree(mx.d_block);
+      return nullptr;
+    }
+    M->by_name[mx.name] = static_cast<int>(M->mats.size());
+    M->mats.push_back(std::move(mx));
+  }
+  if (note_status(finish_model(M.get()))) return nullptr;
+  if (verbose) {
+    const double s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    fprintf(stderr, "[lwb200] %s: %zu coded matrices, %.1f MB coded + %.1f MB side, %.1f MB on device, load %.2f s\n",
+            dir, M->mats.size(), M->coded_bytes / 1e6, M->side_bytes / 1e6, M->resident_bytes / 1e6, s);
+  }
+  return M.release();
+}
+
+void* lw_matrix_create(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
+                       long long side_bytes) {
+  if (!blob || blob_bytes <= 0 || fmt < kFmtNone || fmt > kFmtIQ4XS) {
+    set_error("lw_matrix_create: bad argument");
+    note_status(kErrArg);
+    return nullptr;
+  }
+  note_status(kOk);
+  auto M = std::make_unique<Model>();
+  if (note_status(require_device(&M->device))) return nullptr;
+  Matrix mx;
+  mx.name = "m";
+  mx.N = N;
+  mx.Ks = Ks;
+  mx.fmt = fmt;
+  mx.paired = fmt != kFmtNone && is_paired(fmt);
+  mx.K = mx.paired ? 2 * Ks : Ks;
+  mx.blob_bytes = blob_bytes;
+  mx.side_bytes = fmt != kFmtNone ? side_bytes : 0;
+  std::vector<uint8_t> copy(static_cast<size_t>(blob_bytes) + 16, 0);   // the walker reads 8 bytes at a time
+  std::memcpy(copy.data(), blob, static_cast<size_t>(blob_bytes));
+  if (note_status(load_matrix(mx, copy.data(), static_cast<size_t>(blob_bytes), fmt != kFmtNone ? side : nullptr,
+                              fmt != kFmtNone ? static_cast<size_t>(side_bytes) : 0, default_threads()))) {
+    if (mx.d_block) cudaFree(mx.d_block);
+    return nullptr;
+  }
+  M->by_name[mx.name] = 0;
+  M->mats.push_back(std::move(mx));
+  if (note_status(finish_model(M.get()))) return nullptr;
+  return M.release();
+}
+
+int lw_matrix_id(void* handle, const char* name) { return matrix_id(static_cast<Model*>(handle), name); }
+
+int lw_matrix_info(void* handle, int id, int* N, int* K, int* fmt, long long* blob_bytes, long long* side_bytes,
+                   long long* device_bytes) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (N) *N = mx->N;
+  if (K) *K = mx->K;
+  if (fmt) *fmt = mx->fmt;
+  if (blob_bytes) *blob_bytes = mx->blob_bytes;
+  if (side_bytes) *side_bytes = mx->side_bytes;
+  if (device_bytes) *device_bytes = static_cast<long long>(mx->device_bytes);
+  return kOk;
+}
+
+int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (!x_dev || !y_dev || m < 1) {
+    set_error("lw_linear: bad argument");
+    return kErrArg;
+  }
+  return linear_device(static_cast<Model*>(handle), *mx, x_dev, x_is_half != 0, m, y_dev, mx->N,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (!w_half_dev) return kErrArg;
+  return launch_decode_weights(mx->dev, static_cast<__half*>(w_half_dev), static_cast<cudaStream_t>(stream));
+}
+
+int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* stream) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (!out_dev) return kErrArg;
+  return launch_decode_codes(mx->dev, out_dev, expand != 0 && mx->paired, static_cast<cudaStream_t>(stream));
+}
+
+int rt_test_matmul(void* handle, const char* name, const float* X, int m, float* Y, int path) {
+  Model* M = static_cast<Model*>(handle);
+  const int id = matrix_id(M, name);
+  if (id < 0) return -1;
+  Matrix& mx = M->mats[id];
+  if (!X || !Y || m < 1 || path < 0 || path > 2) {
+    set_error("rt_test_matmul: bad argument");
+    return kErrArg;
+  }
+  float *dx = nullptr, *dy = nullptr;
+  cudaError_t e;
+  int rc = kOk;
+  if ((e = cudaMalloc(&dx, static_cast<size_t>(m) * mx.K * 4)) != cudaSuccess ||
+      (e = cudaMalloc(&dy, static_cast<size_t>(m) * mx.N * 4)) != cudaSuccess ||
+      (e = cudaMemcpy(dx, X, static_cast<size_t>(m) * mx.K * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
+    rc = cuda_fail("rt_test_matmul buffers", e);
+  } else {
+    rc = linear_device(M, mx, dx, false, m, dy, mx.N, nullptr);
+    if (!rc && (e = cudaMemcpy(Y, dy, static_cast<size_t>(m) * mx.N * 4, cudaMemcpyDeviceToHost)) != cudaSuccess)
+      rc = cuda_fail("rt_test_matmul copy back", e);
+  }
+  cudaFree(dx);
+  cudaFree(dy);
+  return rc;
+}
+
+int rt_test_decode(void* handle, const char* name, uint8_t* out) {
+  Model* M = static_cast<Model*>(handle);
+  const int id = matrix_id(M, name);
+  if (id < 0) return -1;
+  Matrix& mx = M->mats[id];
+  if (!out) return kErrArg;
+  const size_t n = static_cast<size_t>(mx.N) * mx.K;
+  uint8_t* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, n);
+  if (e != cudaSuccess) return cuda_fail("rt_test_decode buffer", e);
+  int rc = launch_decode_codes(mx.dev, d, mx.paired, nullptr);
+  if (!rc && (e = cudaMemcpy(out, d, n, cudaMemcpyDeviceToHost)) != cudaSuccess) rc = cuda_fail("rt_test_decode copy", e);
+  cudaFree(d);
+  return rc;
+}
+
+static int cpu_decode_entry(Model* M, const Matrix& mx, int threads, uint8_t* out, double* seconds) {
+  const TensorEntry* t = M->man.find(mx.name);
+  if (!t) {
+    set_error("%s was not loaded from a bundle directory", mx.name.c_str());
+    return kErrGeneric;
+  }
+  std::vector<uint8_t> blob;
+  int rc = read_blob(M->fd, *t, blob);
+  if (rc) return rc;
+  BlobView v;
+  if ((rc = make_view(blob.data(), static_cast<size_t>(t->nbytes), mx.N, mx.Ks, v))) return rc;
+  auto tab = std::make_unique<HuffTable>();
+  if ((rc = table_from_lut(v.lut(), *tab))) return rc;
+  const auto t0 = std::chrono::steady_clock::now();
+  rc = walk_blob(v, *tab, 1, std::max(1, threads), nullptr, nullptr, out);
+  if (seconds) *seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+  return rc;
+}
+
+int rt_test_cpu_decode(void* handle, const char* name, int threads, uint8_t* out) {
+  Model* M = static_cast<Model*>(handle);
+  const int id = matrix_id(M, name);
+  if (id < 0) return -1;
+  if (!out) return kErrArg;
+  return cpu_decode_entry(M, M->mats[id], threads, out, nullptr);
+}
+
+double rt_cpu_decode_all(void* handle, int threads, long long* symbols) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M) return -1;
+  double total = 0;
+  long long nsym = 0;
+  std::vector<uint8_t> out;
+  for (auto& mx : M->mats) {
+    out.resize(static_cast<size_t>(mx.N) * mx.Ks);
+    double s = 0;
+    if (cpu_decode_entry(M, mx, threads, out.data(), &s)) return -1;
+    total += s;
+    nsym += static_cast<long long>(mx.N) * mx.Ks;
+  }
+  if (symbols) *symbols = nsym;
+  return total;
+}
+
+double rt_gpu_decode_all(void* handle, int reps) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || reps < 1) return -1;
+  size_t cap = 0;
+  for (auto& mx : M->mats) cap = std::max(cap, static_cast<size_t>(mx.N) * mx.K);
+  uint8_t* scratch = nullptr;
+  if (cudaMalloc(&scratch, std::max<size_t>(cap, 16)) != cudaSuccess) {
+    cuda_fail("rt_gpu_decode_all scratch", cudaGetLastError());
+    return -1;
+  }
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  std::vector<double> secs;
+  bool ok = true;
+  for (int r = 0; r < reps && ok; ++r) {
+    cudaEventRecord(e0);
+    for (auto& mx : M->mats)
+      if (launch_decode_codes(mx.dev, scratch, mx.paired, nullptr)) ok = false;
+    cudaEventRecord(e1);
+    if (cudaEventSynchronize(e1) != cudaSuccess) ok = false;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    secs.push_back(ms / 1e3);
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(scratch);
+  if (!ok) return -1;
+  std::sort(secs.begin(), secs.end());
+  return secs[secs.size() / 2];
+}
+
+double rt_stat(void* handle, const char* key) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !key) return -1;
+  const std::string k(key);
+  if (k == "resident_bytes") return static_cast<double>(M->resident_bytes);
+  if (k == "coded_bytes") return static_cast<double>(M->coded_bytes);
+  if (k == "side_bytes") return static_cast<double>(M->side_bytes);
+  if (k == "n_matrices") return static_cast<double>(M->mats.size());
+  if (k == "streamed_bytes" || k == "n_streamed" || k == "stream_wait_s" || k == "stream_bytes_moved") return 0;
+  return -1;
+}
+
+long long lw_encode_huf8(const uint8_t* sym, int N, int Ks, uint8_t* out, long long cap, long long* nbits) {
+  if (!sym) {
+    set_error("lw_encode_huf8: null input");
+    return kErrArg;
+  }
+  std::vector<uint8_t> blob;
+  int64_t bits = 0;
+  const int rc = encode_huf8(sym, N, Ks, blob, &bits);
+  if (rc) return rc;
+  if (nbits) *nbits = bits;
+  if (out && cap >= static_cast<long long>(blob.size())) std::memcpy(out, blob.data(), blob.size());
+  return static_cast<long long>(blob.size());
+}
+
+static int host_view(const uint8_t* blob, long long nbytes, int N, int Ks, std::vector<uint8_t>& copy, BlobView& v,
+                     HuffTable& tab) {
+  if (!blob || nbytes <= 0) {
+    set_error("null or empty blob");
+    return kErrArg;
+  }
+  copy.assign(static_cast<size_t>(nbytes) + 16, 0);
+  std::memcpy(copy.data(), blob, static_cast<size_t>(nbytes));
+  int rc = make_view(copy.data(), static_cast<size_t>(nbytes), N, Ks, v);
+  if (rc) return rc;
+  return table_from_lut(v.lut(), tab);
+}
+
+int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks) {
+  std::vector<uint8_t> copy;
+  BlobView v;
+  auto tab = std::make_unique<HuffTable>();
+  int rc = host_view(blob, blob_bytes, N, Ks, copy, v, *tab);
+  if (rc) return rc;
+  return walk_blob(v, *tab, 1, default_threads(), nullptr, nullptr, nullptr);
+}
+
+int lw_cpu_decode(const uint8_t* blob, long long blob_bytes, int N, int Ks, int threads, uint8_t* out) {
+  if (!out) return kErrArg;
+  std::vector<uint8_t> copy;
+  BlobView v;
+  auto tab = std::make_unique<HuffTable>();
+  int rc = host_view(blob, blob_bytes, N, Ks, copy, v, *tab);
+  if (rc) return rc;
+  return walk_blob(v, *tab, 1, std::max(1, threads), nullptr, nullptr, out);
+}
+
+}  // extern "C"

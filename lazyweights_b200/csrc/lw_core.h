@@ -1,0 +1,83 @@
+// Shared definitions of the coded-weight library: formats, the Huffman table, the host-side view of a blob and
+// the device layout of a matrix.  Host and device code both include this file.
+//
+// On-disk blob (reference: lazyweights/bundle.py:16-21), little-endian:
+//   uint16 lut[2048]          index = next 11 stream bits, LSB first -> symbol | length << 8
+//   uint32 lane_start[T][32]  absolute bit offset of lane l of tile t; T = (N / 64) * (Ks / 256)
+//   uint32 payload[W + 2]     bit b = (payload[b >> 5] >> (b & 31)) & 1
+// A tile is 64 rows x 256 symbols; lane l carries tile row l and then tile row l + 32, 256 symbols each.
+//
+// Device layout (built once at load, lw::relayout): every lane is cut into "chains" of 256 / SPLIT symbols
+// (its two rows, each optionally cut into SPLIT column segments).  The 32 chains that cover the same rows half
+// and the same column segment form a group; each chain of a group is re-based to bit 0 and the group's words are
+// interleaved: word i of chain c (= lane) sits at group_base + 32 i + c, so one warp reads its 32 next words as
+// one 128-byte line.  A group is padded to its longest chain.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace lw {
+
+constexpr int kTileRows = 64;
+constexpr int kTileSyms = 256;
+constexpr int kMaxLen = 11;
+constexpr int kLanes = 32;
+constexpr int kLutSize = 1 << kMaxLen;
+constexpr int kBlobAlign = 256;
+constexpr int kTailWords = 256;   // zero words after the last group: read-ahead of the last chains lands here
+
+// Block formats of the side bytes (reference: kernels/llmrt.cu:113-121, scripts/a2_kq_bundle.py:41-42).
+enum Format : int { kFmtNone = 0, kFmtQ4K = 1, kFmtQ5K = 2, kFmtQ6K = 3, kFmtIQ4XS = 4 };
+
+constexpr int side_bytes(int f) { return f == kFmtQ6K ? 18 : f == kFmtIQ4XS ? 8 : 16; }
+constexpr int sub_width(int f) { return f == kFmtQ6K ? 16 : 32; }
+constexpr bool is_paired(int f) { return f == kFmtQ4K || f == kFmtIQ4XS; }
+
+// Status codes of the C ABI (0 = success; the reference's -1 / nullptr conventions are kept where it has them).
+enum Status : int {
+  kOk = 0,
+  kErrGeneric = -1,     // not found / not resident (the reference's -1)
+  kErrArg = -2,
+  kErrFormat = -3,      // malformed bundle or blob
+  kErrCuda = -4,
+  kErrTooLarge = -5,
+  kErrNoDevice = -6,
+};
+
+struct HuffTable {
+  uint16_t lut[kLutSize];     // as stored in the blob
+  uint8_t len[256];           // code length per symbol (0 = unused)
+  int nsym = 0;               // symbols in use
+  int max_len = 0;
+  // canonical comparator form (reference: hw/huff/huff_engine.h:39-52): codes of length l are the MSB-first values
+  // first[l] .. first[l] + count[l] - 1; limit[l] = (first[l] + count[l]) << (11 - l); sorted[] lists symbols by
+  // (length, symbol); base[l] = index in sorted[] of the first symbol of length l.
+  uint32_t limit[kMaxLen + 1];
+  uint32_t first[kMaxLen + 1];
+  uint32_t base[kMaxLen + 1];
+  uint8_t sorted[256];
+};
+
+struct BlobView {
+  const uint8_t* data = nullptr;
+  size_t nbytes = 0;
+  int N = 0, Ks = 0;          // rows, symbols per row
+  int KT = 0, T = 0;          // tile columns, tiles
+  const uint16_t* lut() const { return reinterpret_cast<const uint16_t*>(data); }
+  const uint32_t* lane_start() const { return reinterpret_cast<const uint32_t*>(data + 2 * kLutSize); }
+  const uint32_t* payload() const { return lane_start() + static_cast<size_t>(T) * kLanes; }
+  size_t payload_words() const { return (nbytes - 2 * kLutSize - static_cast<size_t>(T) * kLanes * 4) / 4; }
+};
+
+// Device layout of one coded matrix, as host-side arrays ready for upload.
+struct DeviceImage {
+  int split = 1;                        // chains per row
+  int groups_per_tile = 2;              // 2 * split
+  std::size_t n_words = 0;              // length of words (incl. tail)
+  uint32_t* group_base = nullptr;       // [T * groups_per_tile + 1] word offset of each group (multiple of 32)
+  uint32_t* words = nullptr;            // interleaved chain words
+  uint32_t max_group_words = 0;         // longest group, in words per chain
+  uint32_t max_tile_words = 0;          // largest tile, in words (all groups, all chains)
+};
+
+}  // namespace lw

@@ -1,0 +1,451 @@
+#include "lw_host.h"
+
+#include <fcntl.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <queue>
+#include <sstream>
+#include <thread>
+
+namespace lw {
+
+// ------------------------------------------------------------------------------------------------ errors
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+}
+
+const char* last_error() { return g_err; }
+
+static thread_local int g_status = 0;
+int note_status(int rc) {
+  g_status = rc;
+  return rc;
+}
+int last_status() { return g_status; }
+
+int default_threads() {
+  unsigned n = std::thread::hardware_concurrency();
+  return n ? static_cast<int>(n) : 1;
+}
+
+template <class F>
+static void parallel_for(int n, int threads, F&& body) {
+  threads = std::max(1, std::min(threads, n));
+  if (threads == 1) {
+    for (int i = 0; i < n; ++i) body(i);
+    return;
+  }
+  std::atomic<int> next(0);
+  std::vector<std::thread> pool;
+  for (int w = 0; w < threads; ++w)
+    pool.emplace_back([&] {
+      for (int i; (i = next.fetch_add(1)) < n;) body(i);
+    });
+  for (auto& t : pool) t.join();
+}
+
+// ------------------------------------------------------------------------------------------------ tables
+
+// Depth of every used symbol in the Huffman tree.  Two nodes of equal weight are taken in creation order (leaves in
+// symbol order, then merged nodes as they are made); that rule decides the lengths, so it must be kept.
+void huffman_depths(const int64_t counts[256], int depth[256]) {
+  struct Node {
+    int64_t w;
+    int serial;
+    bool operator>(const Node& o) const { return w != o.w ? w > o.w : serial > o.serial; }
+  };
+  std::fill(depth, depth + 256, 0);
+  std::vector<int> leaf_sym;
+  for (int s = 0; s < 256; ++s)
+    if (counts[s] > 0) leaf_sym.push_back(s);
+  const int n = static_cast<int>(leaf_sym.size());
+  if (n == 0) return;
+  if (n == 1) {
+    depth[leaf_sym[0]] = 1;
+    return;
+  }
+  std::priority_queue<Node, std::vector<Node>, std::greater<Node>> heap;
+  std::vector<int> parent(2 * n, -1);
+  for (int i = 0; i < n; ++i) heap.push({counts[leaf_sym[i]], i});
+  int serial = n;
+  while (heap.size() > 1) {
+    Node a = heap.top();
+    heap.pop();
+    Node b = heap.top();
+    heap.pop();
+    parent[a.serial] = parent[b.serial] = serial;
+    heap.push({a.w + b.w, serial});
+    ++serial;
+  }
+  for (int i = 0; i < n; ++i) {
+    int d = 0;
+    for (int v = i; parent[v] >= 0; v = parent[v]) ++d;
+    depth[leaf_sym[i]] = d;
+  }
+}
+
+void limited_lengths(const int64_t counts[256], uint8_t len[256]) {
+  int depth[256];
+  for (int shift = 0;; ++shift) {
+    int64_t scaled[256];
+    for (int s = 0; s < 256; ++s) scaled[s] = counts[s] > 0 ? std::max<int64_t>(counts[s] >> shift, 1) : 0;
+    huffman_depths(scaled, depth);
+    if (*std::max_element(depth, depth + 256) <= kMaxLen) break;
+  }
+  for (int s = 0; s < 256; ++s) len[s] = static_cast<uint8_t>(depth[s]);
+}
+
+static uint32_t reverse_bits(uint32_t v, int n) {
+  uint32_t r = 0;
+  for (int i = 0; i < n; ++i) r |= ((v >> i) & 1u) << (n - 1 - i);
+  return r;
+}
+
+void table_from_lengths(const uint8_t len[256], HuffTable& t) {
+  std::memset(&t, 0, sizeof t);
+  std::memcpy(t.len, len, 256);
+  uint32_t code = 0, filled = 0;
+  for (int l = 1; l <= kMaxLen; ++l) {
+    t.first[l] = code;
+    t.base[l] = filled;
+    for (int s = 0; s < 256; ++s) {
+      if (len[s] != l) continue;
+      t.sorted[filled++] = static_cast<uint8_t>(s);
+      const uint32_t rev = reverse_bits(code, l);
+      for (uint32_t hi = 0; hi < (1u << (kMaxLen - l)); ++hi)
+        t.lut[rev | (hi << l)] = static_cast<uint16_t>(s | (l << 8));
+      ++code;
+      t.max_len = l;
+    }
+    t.limit[l] = code << (kMaxLen - l);
+    code <<= 1;
+  }
+  t.nsym = static_cast<int>(filled);
+}
+
+int table_from_lut(const uint16_t* lut, HuffTable& t) {
+  uint8_t len[256] = {0};
+  for (int i = 0; i < kLutSize; ++i) {
+    const int l = lut[i] >> 8, s = lut[i] & 255;
+    if (l > kMaxLen) {
+      set_error("table entry %d has length %d", i, l);
+      return kErrFormat;
+    }
+    if (l == 0) continue;
+    if (len[s] && len[s] != l) {
+      set_error("table gives symbol %d two lengths (%d, %d)", s, len[s], l);
+      return kErrFormat;
+    }
+    len[s] = static_cast<uint8_t>(l);
+  }
+  table_from_lengths(len, t);
+  if (t.nsym == 0) {
+    set_error("table has no symbols");
+    return kErrFormat;
+  }
+  // Kraft: a complete code unless it is the one-symbol table (a single length-1 code)
+  uint32_t kraft = 0;
+  for (int s = 0; s < 256; ++s)
+    if (len[s]) kraft += 1u << (kMaxLen - len[s]);
+  const bool single = t.nsym == 1 && t.max_len == 1;
+  if (!single && kraft != (1u << kMaxLen)) {
+    set_error("table is not a complete prefix code (Kraft sum %u / 2048)", kraft);
+    return kErrFormat;
+  }
+  if (std::memcmp(t.lut, lut, sizeof t.lut) != 0) {
+    set_error("table is not the canonical table of its code lengths");
+    return kErrFormat;
+  }
+  return kOk;
+}
+
+// ------------------------------------------------------------------------------------------------ blob
+
+int make_view(const uint8_t* blob, size_t nbytes, int N, int Ks, BlobView& v) {
+  if (N <= 0 || Ks <= 0 || N % kTileRows || Ks % kTileSyms) {
+    set_error("matrix of %d x %d symbols is not a multiple of 64 x 256", N, Ks);
+    return kErrArg;
+  }
+  v.data = blob;
+  v.nbytes = nbytes;
+  v.N = N;
+  v.Ks = Ks;
+  v.KT = Ks / kTileSyms;
+  v.T = (N / kTileRows) * v.KT;
+  const size_t head = 2 * kLutSize + static_cast<size_t>(v.T) * kLanes * 4;
+  if (nbytes < head + 12 || (nbytes - head) % 4) {
+    set_error("blob of %zu bytes is too short for %d tiles", nbytes, v.T);
+    return kErrFormat;
+  }
+  return kOk;
+}
+
+int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits) {
+  if (N <= 0 || Ks <= 0 || N % kTileRows || Ks % kTileSyms) {
+    set_error("matrix of %d x %d symbols is not a multiple of 64 x 256", N, Ks);
+    return kErrArg;
+  }
+  int64_t hist[256] = {0};
+  const size_t total_sym = static_cast<size_t>(N) * Ks;
+  for (size_t i = 0; i < total_sym; ++i) ++hist[sym[i]];
+  uint8_t len[256];
+  limited_lengths(hist, len);
+  HuffTable tab;
+  table_from_lengths(len, tab);
+  uint32_t rcode[256] = {0};
+  {
+    uint32_t code = 0;
+    for (int l = 1; l <= kMaxLen; ++l) {
+      for (int s = 0; s < 256; ++s)
+        if (len[s] == l) rcode[s] = reverse_bits(code++, l);
+      code <<= 1;
+    }
+  }
+  uint64_t total = 0;
+  for (int s = 0; s < 256; ++s) total += static_cast<uint64_t>(hist[s]) * len[s];
+  if (total >= (1ull << 32)) {
+    set_error("payload of %llu bits does not fit 32-bit lane offsets", static_cast<unsigned long long>(total));
+    return kErrTooLarge;
+  }
+  const int KT = Ks / kTileSyms, NT = N / kTileRows, T = NT * KT;
+  const size_t nwords = (total + 31) / 32 + 2;
+  const size_t head = 2 * kLutSize + static_cast<size_t>(T) * kLanes * 4;
+  blob.assign(head + nwords * 4, 0);
+  std::memcpy(blob.data(), tab.lut, 2 * kLutSize);
+  uint32_t* starts = reinterpret_cast<uint32_t*>(blob.data() + 2 * kLutSize);
+  uint32_t* words = reinterpret_cast<uint32_t*>(blob.data() + head);
+  uint64_t acc = 0, pos = 0;   // acc holds the bits of the current 32-bit word and beyond
+  size_t wi = 0;
+  int fill = 0;
+  for (int tr = 0; tr < NT; ++tr)
+    for (int tc = 0; tc < KT; ++tc)
+      for (int lane = 0; lane < kLanes; ++lane) {
+        starts[(static_cast<size_t>(tr) * KT + tc) * kLanes + lane] = static_cast<uint32_t>(pos);
+        for (int half = 0; half < 2; ++half) {
+          const uint8_t* row = sym + (static_cast<size_t>(tr) * kTileRows + half * 32 + lane) * Ks + tc * kTileSyms;
+          for (int c = 0; c < kTileSyms; ++c) {
+            const int s = row[c], l = len[s];
+            acc |= static_cast<uint64_t>(rcode[s]) << fill;
+            fill += l;
+            pos += l;
+            if (fill >= 32) {
+              words[wi++] = static_cast<uint32_t>(acc);
+              acc >>= 32;
+              fill -= 32;
+            }
+          }
+        }
+      }
+  if (fill) words[wi++] = static_cast<uint32_t>(acc);
+  if (nbits) *nbits = static_cast<int64_t>(total);
+  return kOk;
+}
+
+int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, std::vector<uint32_t>* chain_start,
+              std::vector<uint32_t>* lane_end, uint8_t* out) {
+  if (split != 1 && split != 2 && split != 4) {
+    set_error("split must be 1, 2 or 4");
+    return kErrArg;
+  }
+  const int G = 2 * split, seg = kTileSyms / split;
+  const size_t nl = static_cast<size_t>(v.T) * kLanes;
+  if (chain_start) chain_start->assign(nl * G, 0);
+  std::vector<uint32_t> ends_local;
+  std::vector<uint32_t>& ends = lane_end ? *lane_end : ends_local;
+  ends.assign(nl, 0);
+  const uint32_t* starts = v.lane_start();
+  const uint8_t* pay = reinterpret_cast<const uint8_t*>(v.payload());
+  const uint64_t pay_bits = static_cast<uint64_t>(v.payload_words() - 2) * 32;   // the two tail words are padding
+  std::atomic<int> bad(0);
+  parallel_for(v.T, threads, [&](int t) {
+    if (bad.load(std::memory_order_relaxed)) return;
+    const int tr = t / v.KT, tc = t % v.KT;
+    for (int lane = 0; lane < kLanes; ++lane) {
+      uint64_t bp = starts[static_cast<size_t>(t) * kLanes + lane];
+      for (int half = 0; half < 2; ++half) {
+        uint8_t* row = out ? out + (static_cast<size_t>(tr) * kTileRows + half * 32 + lane) * v.Ks + tc * kTileSyms
+                           : nullptr;
+        for (int c = 0; c < kTileSyms; ++c) {
+          if (chain_start && c % seg == 0)
+            (*chain_start)[(static_cast<size_t>(t) * kLanes + lane) * G + half * split + c / seg] =
+                static_cast<uint32_t>(bp);
+          if (bp >= pay_bits) {
+            bad.store(1);
+            return;
+          }
+          uint64_t w;
+          std::memcpy(&w, pay + ((bp >> 5) << 2), 8);
+          const uint16_t e = tab.lut[(w >> (bp & 31)) & (kLutSize - 1)];
+          if ((e >> 8) == 0) {
+            bad.store(2);
+            return;
+          }
+          if (row) row[c] = static_cast<uint8_t>(e);
+          bp += e >> 8;
+        }
+      }
+      ends[static_cast<size_t>(t) * kLanes + lane] = static_cast<uint32_t>(bp);
+      if (bp > pay_bits) {
+        bad.store(1);
+        return;
+      }
+    }
+  });
+  if (bad.load() == 1) {
+    set_error("a lane runs past the end of the payload");
+    return kErrFormat;
+  }
+  if (bad.load() == 2) {
+    set_error("the payload holds a bit pattern the table does not resolve");
+    return kErrFormat;
+  }
+  if (starts[0] != 0) {
+    set_error("first lane does not start at bit 0");
+    return kErrFormat;
+  }
+  for (size_t i = 0; i + 1 < nl; ++i)
+    if (ends[i] != starts[i + 1]) {
+      set_error("lane %zu ends at bit %u but the next lane starts at bit %u", i, ends[i], starts[i + 1]);
+      return kErrFormat;
+    }
+  if ((static_cast<uint64_t>(ends[nl - 1]) + 31) / 32 + 2 != v.payload_words()) {
+    set_error("payload has %zu words but the lanes cover %u bits", v.payload_words(), ends[nl - 1]);
+    return kErrFormat;
+  }
+  return kOk;
+}
+
+int relayout(const BlobView& v, int split, const std::vector<uint32_t>& chain_start,
+             const std::vector<uint32_t>& lane_end, int threads, std::vector<uint32_t>& group_base,
+             std::vector<uint32_t>& words, uint32_t* max_group_words, uint32_t* max_tile_words) {
+  const int G = 2 * split;
+  const size_t ngroups = static_cast<size_t>(v.T) * G;
+  group_base.assign(ngroups + 1, 0);
+  auto chain_bits = [&](size_t t, int lane, int g, uint32_t* begin) {
+    const size_t li = t * kLanes + lane;
+    const uint32_t b = chain_start[li * G + g];
+    const uint32_t e = g + 1 < G ? chain_start[li * G + g + 1] : lane_end[li];
+    *begin = b;
+    return e - b;
+  };
+  // pass 1: words per chain of every group (its longest chain), then the running base
+  std::vector<uint32_t> gw(ngroups);
+  uint32_t mg = 0, mt = 0;
+  uint64_t total = 0;
+  for (size_t t = 0; t < static_cast<size_t>(v.T); ++t) {
+    uint32_t tile_words = 0;
+    for (int g = 0; g < G; ++g) {
+      uint32_t w = 0, b;
+      for (int lane = 0; lane < kLanes; ++lane) w = std::max(w, (chain_bits(t, lane, g, &b) + 31) / 32);
+      gw[t * G + g] = w;
+      mg = std::max(mg, w);
+      tile_words += w * kLanes;
+    }
+    mt = std::max(mt, tile_words);
+    for (int g = 0; g < G; ++g) {
+      if (total > 0xFFFFFFFFull) {
+        set_error("matrix needs more than 2^32 device words");
+        return kErrTooLarge;
+      }
+      group_base[t * G + g] = static_cast<uint32_t>(total);
+      total += static_cast<uint64_t>(gw[t * G + g]) * kLanes;
+    }
+  }
+  if (total > 0xFFFFFFFFull) {
+    set_error("matrix needs more than 2^32 device words");
+    return kErrTooLarge;
+  }
+  group_base[ngroups] = static_cast<uint32_t>(total);
+  words.assign(total + kTailWords, 0);
+  const uint32_t* pay = v.payload();
+  parallel_for(v.T, threads, [&](int t) {
+    for (int g = 0; g < G; ++g) {
+      uint32_t* dst = words.data() + group_base[static_cast<size_t>(t) * G + g];
+      for (int lane = 0; lane < kLanes; ++lane) {
+        uint32_t b;
+        const uint32_t nbits = chain_bits(t, lane, g, &b);
+        for (uint32_t i = 0; i * 32 < nbits; ++i) {
+          const uint64_t p = static_cast<uint64_t>(b) + i * 32ull;
+          const uint64_t x = pay[p >> 5] | (static_cast<uint64_t>(pay[(p >> 5) + 1]) << 32);
+          uint32_t w = static_cast<uint32_t>(x >> (p & 31));
+          const uint32_t left = nbits - i * 32;
+          if (left < 32) w &= (1u << left) - 1;
+          dst[static_cast<size_t>(i) * kLanes + lane] = w;
+        }
+      }
+    }
+  });
+  if (max_group_words) *max_group_words = mg;
+  if (max_tile_words) *max_tile_words = mt;
+  return kOk;
+}
+
+// ------------------------------------------------------------------------------------------------ bundle
+
+int read_manifest(const std::string& dir, Manifest& m) {
+  std::ifstream f(dir + "/manifest.txt");
+  if (!f) {
+    set_error("cannot open %s/manifest.txt", dir.c_str());
+    return kErrGeneric;
+  }
+  std::string line;
+  while (std::getline(f, line)) {
+    std::istringstream is(line);
+    std::string tag;
+    if (!(is >> tag)) continue;
+    if (tag == "cfg") {
+      std::string k, val;
+      if (is >> k >> val) m.cfg[k] = val;
+    } else if (tag == "t") {
+      TensorEntry t;
+      if (!(is >> t.name >> t.enc >> t.N >> t.K >> t.scale >> t.zp >> t.offset >> t.nbytes)) {
+        set_error("bad manifest line: %s", line.c_str());
+        return kErrFormat;
+      }
+      if (t.N < 0 || t.K < 0 || t.offset < 0 || t.nbytes < 0 || t.offset % kBlobAlign) {
+        set_error("tensor %s: bad shape, size or alignment", t.name.c_str());
+        return kErrFormat;
+      }
+      m.by_name[t.name] = static_cast<int>(m.tensors.size());
+      m.tensors.push_back(t);
+    }
+  }
+  return kOk;
+}
+
+int read_blob(int fd, const TensorEntry& t, std::vector<uint8_t>& out) {
+  out.resize(static_cast<size_t>(t.nbytes) + 16);   // slack: the decoder reads 8 bytes at a time
+  size_t done = 0;
+  while (done < static_cast<size_t>(t.nbytes)) {
+    const ssize_t r = pread(fd, out.data() + done, t.nbytes - done, t.offset + done);
+    if (r <= 0) {
+      set_error("tensor %s: weights.bin is shorter than the manifest says", t.name.c_str());
+      return kErrFormat;
+    }
+    done += static_cast<size_t>(r);
+  }
+  std::memset(out.data() + t.nbytes, 0, 16);
+  return kOk;
+}
+
+int format_of_side_enc(const std::string& enc) {
+  if (enc == "kq_Q4_K") return kFmtQ4K;
+  if (enc == "kq_Q5_K") return kFmtQ5K;
+  if (enc == "kq_Q6_K") return kFmtQ6K;
+  if (enc == "kq_IQ4_XS") return kFmtIQ4XS;
+  return kFmtNone;
+}
+
+}  // namespace lw

@@ -1,0 +1,67 @@
+// Host-side (CPU, no CUDA) part of the library: Huffman tables, the blob encoder, blob validation and indexing,
+// the load-time re-layout into the device image, the threaded CPU decoder and the bundle directory reader/writer.
+#pragma once
+#include <cstdint>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "lw_core.h"
+
+namespace lw {
+
+// Thread-local text of the last failure, returned by lw_last_error().
+void set_error(const char* fmt, ...);
+const char* last_error();
+// Status of the last call that could only report failure as NULL (handle constructors).
+int note_status(int rc);
+int last_status();
+
+// ---- tables (reference: lazyweights/huffman.py:8-26, lazyweights/lanecodecs.py:28-62, lazyweights/bundle.py:46-54)
+void huffman_depths(const int64_t counts[256], int depth[256]);
+void limited_lengths(const int64_t counts[256], uint8_t len[256]);
+void table_from_lengths(const uint8_t len[256], HuffTable& t);
+// Recovers lengths from a stored table and checks that the table is exactly the canonical one for those lengths.
+int table_from_lut(const uint16_t* lut, HuffTable& t);
+
+// ---- blob (reference: lazyweights/bundle.py:57-106, kernels/llmrt.cu:2513-2541)
+int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits);
+int make_view(const uint8_t* blob, size_t nbytes, int N, int Ks, BlobView& v);
+
+// Walks every lane once.  chain_start[(t * 32 + l) * (2 * split) + g] = absolute bit offset at which chain g of the
+// lane starts; lane_end[t * 32 + l] = bit offset after its 512th symbol.  Checks that every window resolves, that
+// each lane ends where the next begins and that the last one ends inside the payload.  If `out` is not null the
+// decoded symbols are written to it as [N, Ks].
+int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, std::vector<uint32_t>* chain_start,
+              std::vector<uint32_t>* lane_end, uint8_t* out);
+
+// Re-layout into interleaved chain groups (the role of interleave_huf8, kernels/llmrt.cu:1208-1257).
+int relayout(const BlobView& v, int split, const std::vector<uint32_t>& chain_start,
+             const std::vector<uint32_t>& lane_end, int threads, std::vector<uint32_t>& group_base,
+             std::vector<uint32_t>& words, uint32_t* max_group_words, uint32_t* max_tile_words);
+
+// ---- bundle directory (reference: lazyweights/bundle.py:114-148)
+struct TensorEntry {
+  std::string name, enc;
+  int N = 0, K = 0;
+  double scale = 1.0;
+  long long zp = 0;
+  long long offset = 0, nbytes = 0;
+};
+
+struct Manifest {
+  std::map<std::string, std::string> cfg;
+  std::vector<TensorEntry> tensors;
+  std::map<std::string, int> by_name;
+  const TensorEntry* find(const std::string& n) const {
+    auto it = by_name.find(n);
+    return it == by_name.end() ? nullptr : &tensors[it->second];
+  }
+};
+
+int read_manifest(const std::string& dir, Manifest& m);
+int read_blob(int fd, const TensorEntry& t, std::vector<uint8_t>& out);
+int format_of_side_enc(const std::string& enc);   // "kq_Q4_K" -> kFmtQ4K, ... ; 0 if unknown
+int default_threads();
+
+}  // namespace lw

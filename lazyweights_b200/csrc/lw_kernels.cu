@@ -1,0 +1,415 @@
+// CUDA kernels (sm_100a) of the coded-weight path and their launchers.
+//
+//   k_decode_codes    chain groups -> uint8 codes [N, K]           (role of k_decode_hufi, kernels/llmrt.cu:767-806)
+//   k_decode_weights  chain groups + side bytes -> fp16 [N, K]     (decode fused with the block dequantisation)
+//   k_gemv_fused      decode + dequant + product for m <= 8 rows   (role of k_gemvm_kq, kernels/llmrt.cu:896-1033)
+//   k_sum_partials    ordered sum over tile columns                (role of k_sum_kt, kernels/llmrt.cu:1173-1180)
+//
+// Common shape: one warp owns one 64 x 256-symbol tile.  Lane l decodes tile rows l and l + 32 as two independent
+// chains.  The tile's interleaved words are staged into shared memory by one bulk copy (cp.async.bulk, completion
+// on an mbarrier) issued by lane 0; the lanes then read their next words from shared memory, bank = lane.
+#include "lw_kernels.h"
+
+#include <atomic>
+#include <cstdio>
+
+#include "lw_device.cuh"
+
+namespace lw {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kSlackWords = 96;   // read-ahead of the last chains of a tile lands here
+
+__host__ __device__ constexpr uint32_t tile_buf_words(uint32_t max_tile_words) {
+  return (max_tile_words + kSlackWords + 31u) & ~31u;
+}
+
+// Stages tile t into `buf` and returns false if the copy did not land in time.
+__device__ __forceinline__ bool stage_tile(const MatDev& M, int t, uint32_t* buf, uint64_t* bar, int lane,
+                                           uint32_t* tile_base) {
+  const int G = 2 * M.split;
+  const uint32_t b0 = __ldg(M.group_base + static_cast<size_t>(t) * G);
+  const uint32_t b1 = __ldg(M.group_base + static_cast<size_t>(t + 1) * G);
+  *tile_base = b0;
+  const uint32_t bar_a = smem_addr(bar);
+  if (lane == 0) {
+    mbar_init(bar_a, 1);
+    bulk_load(smem_addr(buf), M.words + b0, (b1 - b0) * 4u, bar_a);
+  }
+  __syncwarp();
+  return mbar_wait(bar_a, 0);
+}
+
+// ------------------------------------------------------------------------------------------------ decode to codes
+
+template <bool EXPAND>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_codes(MatDev M, uint8_t* __restrict__ out) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint16_t* lut = reinterpret_cast<uint16_t*>(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kLutSize);
+  uint32_t* bufs = reinterpret_cast<uint32_t*>(smem + 2 * kLutSize + 128);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kLutSize / 2; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(lut)[i] = __ldg(reinterpret_cast<const uint32_t*>(M.lut) + i);
+  __syncthreads();
+  const int t = blockIdx.x * kWarpsPerBlock + warp;
+  if (t >= M.T) return;
+  uint32_t* buf = bufs + static_cast<size_t>(warp) * tile_buf_words(M.max_tile_words);
+  uint32_t base;
+  if (!stage_tile(M, t, buf, bars + warp, lane, &base)) return;
+  const int tr = t / M.KT, tc = t - tr * M.KT;
+  const int row_bytes = EXPAND ? 2 * M.Ks : M.Ks;
+  const int tile_bytes = EXPAND ? 2 * kTileSyms : kTileSyms;
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    Chain ch;
+    ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * 2 + half) - base) + lane);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(tr * kTileRows + half * 32 + lane) * row_bytes +
+                                          static_cast<size_t>(tc) * tile_bytes);
+#pragma unroll 1
+    for (int c = 0; c < tile_bytes / 16; ++c) {
+      uint32_t v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (EXPAND) {
+          const uint32_t e0 = ch.next(lut), e1 = ch.next(lut);
+          v[j] = (e0 & 15u) | ((e0 & 0xF0u) << 4) | ((e1 & 15u) << 16) | ((e1 & 0xF0u) << 20);
+        } else {
+          v[j] = ch.next(lut) & 255u;
+          v[j] |= (ch.next(lut) & 255u) << 8;
+          v[j] |= (ch.next(lut) & 255u) << 16;
+          v[j] |= (ch.next(lut) & 255u) << 24;
+        }
+      }
+      dst[c] = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- decode to weights
+
+template <int FMT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_weights(MatDev M, __half* __restrict__ out) {
+  constexpr bool PAIR = is_paired(FMT);
+  constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;   // weights per tile row
+  constexpr int GW = sub_width(FMT), SB = side_bytes(FMT);
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint16_t* lut = reinterpret_cast<uint16_t*>(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kLutSize);
+  float* iq4 = reinterpret_cast<float*>(smem + 2 * kLutSize + 64);
+  uint32_t* bufs = reinterpret_cast<uint32_t*>(smem + 2 * kLutSize + 128);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kLutSize / 2; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(lut)[i] = __ldg(reinterpret_cast<const uint32_t*>(M.lut) + i);
+  if (threadIdx.x < 16) iq4[threadIdx.x] = c_iq4_grid[threadIdx.x];
+  __syncthreads();
+  const int t = blockIdx.x * kWarpsPerBlock + warp;
+  if (t >= M.T) return;
+  uint32_t* buf = bufs + static_cast<size_t>(warp) * tile_buf_words(M.max_tile_words);
+  uint32_t base;
+  if (!stage_tile(M, t, buf, bars + warp, lane, &base)) return;
+  const int tr = t / M.KT, tc = t - tr * M.KT;
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    const int n = tr * kTileRows + half * 32 + lane;
+    Chain ch;
+    ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * 2 + half) - base) + lane);
+    const uint8_t* srow = M.side + (static_cast<size_t>(n) * (M.K / 256) + static_cast<size_t>(tc) * (TW / 256)) * SB;
+    __half* orow = out + static_cast<size_t>(n) * M.K + static_cast<size_t>(tc) * TW;
+#pragma unroll 1
+    for (int sb = 0; sb < TW / 256; ++sb) {
+      SideRegs<FMT> sr;
+      sr.load(srow + sb * SB);
+#pragma unroll
+      for (int jj = 0; jj < 256 / GW; ++jj) {
+        float s, o;
+        sr.sub(jj, s, o);
+#pragma unroll
+        for (int c = 0; c < GW / 8; ++c) {   // 8 weights -> one 16-byte store
+          __half h[8];
+          if (PAIR) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t e = ch.next(lut);
+              h[2 * i] = __float2half_rn(__fsub_rn(__fmul_rn(s, grid_value<FMT>(e & 15u, iq4)), o));
+              h[2 * i + 1] = __float2half_rn(__fsub_rn(__fmul_rn(s, grid_value<FMT>((e >> 4) & 15u, iq4)), o));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              h[i] = __float2half_rn(__fsub_rn(__fmul_rn(s, grid_value<FMT>(ch.next(lut) & 255u, iq4)), o));
+          }
+          *reinterpret_cast<uint4*>(orow + sb * 256 + jj * GW + c * 8) = *reinterpret_cast<const uint4*>(h);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- fused decode + GEMV
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+// P[tc, j, n] = sum over the tile column's sub-blocks g of  s_ng * sum_(k in g) X[j, k] f(q[n, k]) - o_ng * sum_(k in g) X[j, k]
+// A block's warps share one tile column (x staged once); warp w handles tile row blockIdx.y * 8 + w.
+template <int FMT, int MT, typename XT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+    k_gemv_fused(MatDev M, const XT* __restrict__ X, float* __restrict__ P, int m) {
+  constexpr bool PAIR = is_paired(FMT);
+  constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;
+  constexpr int GW = sub_width(FMT), NG = TW / GW, SPG = PAIR ? GW / 2 : GW, SB = side_bytes(FMT);
+  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint16_t* lut = reinterpret_cast<uint16_t*>(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kLutSize);
+  float* iq4 = reinterpret_cast<float*>(smem + 2 * kLutSize + 64);
+  float* xs = reinterpret_cast<float*>(smem + 2 * kLutSize + 128);   // [TW][MT]
+  float* xg = xs + TW * MT;                                          // [NG][MT]
+  uint32_t* bufs = reinterpret_cast<uint32_t*>(xg + NG * MT);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tc = blockIdx.x, tr = blockIdx.y * kWarpsPerBlock + warp;
+  const int NT = M.N / kTileRows;
+  const bool active = tr < NT;
+  const int t = tr * M.KT + tc;
+  uint32_t* buf = bufs + static_cast<size_t>(warp) * tile_buf_words(M.max_tile_words);
+  uint32_t base = 0;
+  const uint32_t bar_a = smem_addr(bars + warp);
+  if (active) {   // start the tile's copy first: it overlaps the table and activation staging below
+    const uint32_t b0 = __ldg(M.group_base + static_cast<size_t>(t) * 2);
+    const uint32_t b1 = __ldg(M.group_base + static_cast<size_t>(t + 1) * 2);
+    base = b0;
+    if (lane == 0) {
+      mbar_init(bar_a, 1);
+      bulk_load(smem_addr(buf), M.words + b0, (b1 - b0) * 4u, bar_a);
+    }
+  }
+  for (int i = threadIdx.x; i < kLutSize / 2; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(lut)[i] = __ldg(reinterpret_cast<const uint32_t*>(M.lut) + i);
+  if (threadIdx.x < 16) iq4[threadIdx.x] = c_iq4_grid[threadIdx.x];
+  for (int i = threadIdx.x; i < TW * MT; i += blockDim.x) {
+    const int j = i / TW, k = i - j * TW;
+    xs[k * MT + j] = j < m ? to_f32(X[static_cast<size_t>(j) * M.K + static_cast<size_t>(tc) * TW + k]) : 0.f;
+  }
+  __syncthreads();
+  if (HAS_OFFSET) {
+    for (int i = threadIdx.x; i < NG * MT; i += blockDim.x) {
+      const int g = i / MT, j = i - g * MT;
+      float a = 0.f;
+      for (int k = g * GW; k < (g + 1) * GW; ++k) a += xs[k * MT + j];
+      xg[i] = a;
+    }
+    __syncthreads();
+  }
+  if (!active) return;
+  __syncwarp();
+  if (!mbar_wait(bar_a, 0)) return;
+
+  Chain ca, cb;
+  ca.init(buf + lane);
+  cb.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * 2 + 1) - base) + lane);
+  const int na = tr * kTileRows + lane, nb = na + 32;
+  const size_t side_row = static_cast<size_t>(M.K / 256) * SB;
+  const uint8_t* sa = M.side + na * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
+  const uint8_t* sbp = M.side + nb * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
+  float tot_a[MT], tot_b[MT];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) tot_a[j] = tot_b[j] = 0.f;
+#pragma unroll 1
+  for (int sb = 0; sb < TW / 256; ++sb) {
+    SideRegs<FMT> ra, rb;
+    ra.load(sa + sb * SB);
+    rb.load(sbp + sb * SB);
+#pragma unroll
+    for (int jj = 0; jj < 256 / GW; ++jj) {
+      const int g = sb * (256 / GW) + jj;
+      float s_a, o_a, s_b, o_b;
+      ra.sub(jj, s_a, o_a);
+      rb.sub(jj, s_b, o_b);
+      float acc_a[MT], acc_b[MT];
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc_a[j] = acc_b[j] = 0.f;
+      const float* xp = xs + static_cast<size_t>(g) * GW * MT;
+#pragma unroll 4
+      for (int c = 0; c < SPG; ++c) {
+        const uint32_t ea = ca.next(lut), eb = cb.next(lut);
+        if (PAIR) {
+          const float fa0 = grid_value<FMT>(ea & 15u, iq4), fa1 = grid_value<FMT>((ea >> 4) & 15u, iq4);
+          const float fb0 = grid_value<FMT>(eb & 15u, iq4), fb1 = grid_value<FMT>((eb >> 4) & 15u, iq4);
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            const float x0 = xp[(2 * c) * MT + j], x1 = xp[(2 * c + 1) * MT + j];
+            acc_a[j] = fmaf(x0, fa0, acc_a[j]);
+            acc_b[j] = fmaf(x0, fb0, acc_b[j]);
+            acc_a[j] = fmaf(x1, fa1, acc_a[j]);
+            acc_b[j] = fmaf(x1, fb1, acc_b[j]);
+          }
+        } else {
+          const float fa = grid_value<FMT>(ea & 255u, iq4), fb = grid_value<FMT>(eb & 255u, iq4);
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            const float x0 = xp[c * MT + j];
+            acc_a[j] = fmaf(x0, fa, acc_a[j]);
+            acc_b[j] = fmaf(x0, fb, acc_b[j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        if (HAS_OFFSET) {
+          const float gx = xg[g * MT + j];
+          tot_a[j] += s_a * acc_a[j] - o_a * gx;
+          tot_b[j] += s_b * acc_b[j] - o_b * gx;
+        } else {
+          tot_a[j] = fmaf(s_a, acc_a[j], tot_a[j]);
+          tot_b[j] = fmaf(s_b, acc_b[j], tot_b[j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < MT; ++j)
+    if (j < m) {
+      P[(static_cast<size_t>(tc) * m + j) * M.N + na] = tot_a[j];
+      P[(static_cast<size_t>(tc) * m + j) * M.N + nb] = tot_b[j];
+    }
+}
+
+__global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int KT) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m * N) return;
+  const int j = i / N, n = i - j * N;
+  float a = 0.f;
+  for (int tc = 0; tc < KT; ++tc) a += P[(static_cast<size_t>(tc) * m + j) * N + n];
+  Y[static_cast<size_t>(j) * ldy + n] = a;
+}
+
+// ------------------------------------------------------------------------------------------------------ launchers
+
+static std::atomic<long long> g_launches{0};
+long long launch_count() { return g_launches.load(); }
+
+static int check_cuda(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_kernel_error_text(what, cudaGetErrorString(e));
+    return kErrCuda;
+  }
+  return kOk;
+}
+
+static int check_launch(const char* what) {
+  g_launches.fetch_add(1);
+  return check_cuda(what);
+}
+
+static size_t stage_bytes(const MatDev& M) { return static_cast<size_t>(tile_buf_words(M.max_tile_words)) * 4; }
+
+template <class K>
+static int prepare(K kernel, size_t smem) {
+  if (smem > 227 * 1024) {
+    set_kernel_error_text("launch", "tile staging does not fit shared memory");
+    return kErrTooLarge;
+  }
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+      cudaSuccess)
+    return check_cuda("cudaFuncSetAttribute");
+  return kOk;
+}
+
+int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaStream_t st) {
+  const size_t smem = 2 * kLutSize + 128 + kWarpsPerBlock * stage_bytes(M);
+  const int blocks = (M.T + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  int rc;
+  if (expand_pairs) {
+    if ((rc = prepare(k_decode_codes<true>, smem))) return rc;
+    k_decode_codes<true><<<blocks, kWarpsPerBlock * 32, smem, st>>>(M, out);
+  } else {
+    if ((rc = prepare(k_decode_codes<false>, smem))) return rc;
+    k_decode_codes<false><<<blocks, kWarpsPerBlock * 32, smem, st>>>(M, out);
+  }
+  return check_launch("k_decode_codes");
+}
+
+int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
+  const size_t smem = 2 * kLutSize + 128 + kWarpsPerBlock * stage_bytes(M);
+  const int blocks = (M.T + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  int rc = kErrArg;
+#define LW_CASE(F)                                                              \
+  case F:                                                                       \
+    if ((rc = prepare(k_decode_weights<F>, smem))) return rc;                   \
+    k_decode_weights<F><<<blocks, kWarpsPerBlock * 32, smem, st>>>(M, out);     \
+    break;
+  switch (M.fmt) {
+    LW_CASE(kFmtQ4K)
+    LW_CASE(kFmtQ5K)
+    LW_CASE(kFmtQ6K)
+    LW_CASE(kFmtIQ4XS)
+    default:
+      set_kernel_error_text("decode_weights", "matrix has no block format");
+      return kErrArg;
+  }
+#undef LW_CASE
+  return check_launch("k_decode_weights");
+}
+
+size_t gemv_partial_floats(const MatDev& M, int m) { return static_cast<size_t>(M.KT) * m * M.N; }
+
+template <int FMT, int MT, typename XT>
+static int launch_gemv_t(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
+  constexpr int TW = is_paired(FMT) ? 512 : 256;
+  constexpr int NG = TW / sub_width(FMT);
+  const size_t smem = 2 * kLutSize + 128 + (TW + NG) * MT * sizeof(float) + kWarpsPerBlock * stage_bytes(M);
+  int rc;
+  if ((rc = prepare(k_gemv_fused<FMT, MT, XT>, smem))) return rc;
+  const int NT = M.N / kTileRows;
+  dim3 grid(M.KT, (NT + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  k_gemv_fused<FMT, MT, XT><<<grid, kWarpsPerBlock * 32, smem, st>>>(M, X, P, m);
+  return check_launch("k_gemv_fused");
+}
+
+template <int FMT, typename XT>
+static int launch_gemv_m(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
+  if (m == 1) return launch_gemv_t<FMT, 1, XT>(M, X, m, P, st);
+  if (m == 2) return launch_gemv_t<FMT, 2, XT>(M, X, m, P, st);
+  if (m <= 4) return launch_gemv_t<FMT, 4, XT>(M, X, m, P, st);
+  return launch_gemv_t<FMT, 8, XT>(M, X, m, P, st);
+}
+
+template <typename XT>
+static int launch_gemv_f(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
+  switch (M.fmt) {
+    case kFmtQ4K: return launch_gemv_m<kFmtQ4K, XT>(M, X, m, P, st);
+    case kFmtQ5K: return launch_gemv_m<kFmtQ5K, XT>(M, X, m, P, st);
+    case kFmtQ6K: return launch_gemv_m<kFmtQ6K, XT>(M, X, m, P, st);
+    case kFmtIQ4XS: return launch_gemv_m<kFmtIQ4XS, XT>(M, X, m, P, st);
+  }
+  set_kernel_error_text("gemv", "matrix has no block format");
+  return kErrArg;
+}
+
+int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
+                cudaStream_t st) {
+  if (m < 1 || m > 8) {
+    set_kernel_error_text("gemv", "m must be 1..8");
+    return kErrArg;
+  }
+  int rc = x_is_half ? launch_gemv_f<__half>(M, static_cast<const __half*>(X), m, partials, st)
+                     : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
+  if (rc) return rc;
+  k_sum_partials<<<(m * M.N + 255) / 256, 256, 0, st>>>(partials, Y, m, M.N, ldy, M.KT);
+  return check_launch("k_sum_partials");
+}
+
+int read_kernel_error(unsigned int* value, bool clear) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_kernel_error, sizeof v) != cudaSuccess) return check_cuda("read error word");
+  if (clear && v) {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_kernel_error, &z, sizeof z);
+  }
+  *value = v;
+  return kOk;
+}
+
+}  // namespace lw

@@ -1,0 +1,41 @@
+// Launchers of the CUDA kernels (implemented in lw_kernels.cu).  All take device pointers and a stream; none
+// allocates.  They return lw::Status codes and leave a message for lw_last_error() on failure.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "lw_core.h"
+
+namespace lw {
+
+// One coded matrix on the device (all pointers are device pointers; passed to kernels by value).
+struct MatDev {
+  const uint16_t* lut;          // [2048] symbol | length << 8
+  const uint32_t* group_base;   // [T * groups + 1] word offset of every chain group
+  const uint32_t* words;        // interleaved chain words (+ zero tail)
+  const uint8_t* side;          // [N, K / 256 * side_bytes] or null (symbols only)
+  int N, K, Ks, KT, T;
+  int fmt, split;
+  uint32_t max_tile_words;
+};
+
+// uint8 [N, K] (expand_pairs: each paired symbol becomes two bytes, low nibble first) or symbols [N, Ks].
+int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaStream_t st);
+// fp16 [N, K], bit-exact float32 block arithmetic rounded once to fp16.
+int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st);
+// Y[j, n] (row stride ldy) = sum_k X[j, k] W[n, k] for m <= 8 rows of X (fp16 or fp32, row-major [m, K]).
+// `partials` must hold gemv_partial_floats(M, m) floats.
+size_t gemv_partial_floats(const MatDev& M, int m);
+int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
+                cudaStream_t st);
+// Reads (and optionally clears) the device error word that kernels set when a bounded wait gives up.
+int read_kernel_error(unsigned int* value, bool clear);
+
+void set_kernel_error_text(const char* what, const char* detail);
+// Kernels launched by this library since it was loaded.
+long long launch_count();
+
+}  // namespace lw

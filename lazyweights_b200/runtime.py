@@ -1,0 +1,161 @@
+"""Handles on coded matrices: a whole bundle directory (`Bundle`, the counterpart of the reference runtime's
+rt_open handle, kernels/llmrt.cu:1921) or a single blob (`CodedMatrix`).
+
+Host-buffer methods (`matmul`, `decode`, `cpu_decode`) go through the reference-named rt_test_* entry points;
+`linear`, `decode_weights` and `decode_codes` take and return CUDA torch tensors and call the device-pointer
+entry points on torch's current stream.  torch is only used for device memory and streams.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import _native as nat
+
+
+def _torch():
+    import torch
+    return torch
+
+
+class _Handle:
+    def __init__(self, ptr):
+        if not ptr:
+            raise nat.LwError(nat.lib().lw_last_status() or -1, nat.last_error())
+        self._h = C.c_void_p(ptr)
+        self._ids = {}
+
+    # ---- lifetime
+    def close(self):
+        if self._h:
+            nat.lib().rt_close(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- lookup
+    def matrix_id(self, name):
+        if name not in self._ids:
+            i = nat.lib().lw_matrix_id(self._h, name.encode())
+            if i < 0:
+                raise KeyError(name)
+            self._ids[name] = i
+        return self._ids[name]
+
+    def info(self, name):
+        n, k, fmt = C.c_int(), C.c_int(), C.c_int()
+        bb, sb, db = C.c_longlong(), C.c_longlong(), C.c_longlong()
+        nat.check(nat.lib().lw_matrix_info(self._h, self.matrix_id(name), C.byref(n), C.byref(k), C.byref(fmt),
+                                           C.byref(bb), C.byref(sb), C.byref(db)))
+        return dict(N=n.value, K=k.value, fmt=nat.FMT_NAME[fmt.value], blob_bytes=bb.value, side_bytes=sb.value,
+                    device_bytes=db.value, paired=fmt.value in (1, 4))
+
+    # ---- device-pointer path
+    def linear(self, name, x, out=None):
+        """x: CUDA tensor [m, K] or [K], fp16 or fp32 -> fp32 [m, N] (or [N])."""
+        torch = _torch()
+        inf = self.info(name)
+        squeeze = x.dim() == 1
+        x2 = x.reshape(1, -1) if squeeze else x
+        if not x2.is_cuda or x2.dtype not in (torch.float16, torch.float32) or x2.shape[1] != inf["K"]:
+            raise ValueError("linear wants a CUDA fp16/fp32 tensor with %d columns" % inf["K"])
+        x2 = x2.contiguous()
+        m = x2.shape[0]
+        y = out if out is not None else torch.empty((m, inf["N"]), dtype=torch.float32, device=x2.device)
+        st = torch.cuda.current_stream(x2.device).cuda_stream
+        nat.check(nat.lib().lw_linear(self._h, self.matrix_id(name), C.c_void_p(x2.data_ptr()),
+                                      int(x2.dtype == torch.float16), m, C.c_void_p(y.data_ptr()), C.c_void_p(st)))
+        return y[0] if squeeze and out is None else y
+
+    def decode_weights(self, name):
+        """fp16 CUDA tensor [N, K] of the dequantised weights."""
+        torch = _torch()
+        inf = self.info(name)
+        w = torch.empty((inf["N"], inf["K"]), dtype=torch.float16, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+        nat.check(nat.lib().lw_decode_weights(self._h, self.matrix_id(name), C.c_void_p(w.data_ptr()), C.c_void_p(st)))
+        return w
+
+    def decode_codes(self, name, expand=True):
+        """uint8 CUDA tensor: codes [N, K] (expand) or symbols [N, K / 2] of a paired matrix."""
+        torch = _torch()
+        inf = self.info(name)
+        cols = inf["K"] if (expand or not inf["paired"]) else inf["K"] // 2
+        out = torch.empty((inf["N"], cols), dtype=torch.uint8, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+        nat.check(nat.lib().lw_decode_codes(self._h, self.matrix_id(name), C.c_void_p(out.data_ptr()), int(expand),
+                                            C.c_void_p(st)))
+        return out
+
+    # ---- host-buffer path (reference-named entry points)
+    def matmul(self, name, X, path=0):
+        """Y[m, N] = X[m, K] . W^T with host float32 arrays (rt_test_matmul)."""
+        X = np.ascontiguousarray(np.atleast_2d(X), np.float32)
+        inf = self.info(name)
+        if X.shape[1] != inf["K"]:
+            raise ValueError("X has %d columns, the matrix %d" % (X.shape[1], inf["K"]))
+        Y = np.empty((X.shape[0], inf["N"]), np.float32)
+        nat.check(nat.lib().rt_test_matmul(self._h, name.encode(), X.ctypes.data_as(C.c_void_p), X.shape[0],
+                                           Y.ctypes.data_as(C.c_void_p), path))
+        return Y
+
+    def decode(self, name):
+        """uint8 [N, K] codes on the host (rt_test_decode)."""
+        inf = self.info(name)
+        out = np.empty((inf["N"], inf["K"]), np.uint8)
+        nat.check(nat.lib().rt_test_decode(self._h, name.encode(), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def kernel_error(self):
+        return nat.lib().lw_kernel_error()
+
+
+class Bundle(_Handle):
+    """A bundle directory opened on the current CUDA device."""
+
+    def __init__(self, path, max_ctx=4096, max_batch=8, verbose=False):
+        self.path = path
+        super().__init__(nat.lib().rt_open(os.fsencode(path), max_ctx, max_batch, -1, 0, int(verbose)))
+
+    def cpu_decode(self, name, threads=0):
+        inf = self.info(name)
+        cols = inf["K"] // 2 if inf["paired"] else inf["K"]
+        out = np.empty((inf["N"], cols), np.uint8)
+        nat.check(nat.lib().rt_test_cpu_decode(self._h, name.encode(), threads or (os.cpu_count() or 1),
+                                               out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def stat(self, key):
+        return nat.lib().rt_stat(self._h, key.encode())
+
+    def gpu_decode_all(self, reps=3):
+        return nat.lib().rt_gpu_decode_all(self._h, reps)
+
+    def cpu_decode_all(self, threads=0):
+        n = C.c_longlong(0)
+        s = nat.lib().rt_cpu_decode_all(self._h, threads or (os.cpu_count() or 1), C.byref(n))
+        return s, n.value
+
+
+class CodedMatrix(_Handle):
+    """One blob (N rows, Ks symbols per row) with an optional side tensor of block format `fmt`."""
+    NAME = "m"
+
+    def __init__(self, blob, N, Ks, fmt="none", side=None):
+        b = np.frombuffer(blob, np.uint8)
+        s = np.ascontiguousarray(side, np.uint8).reshape(-1) if side is not None else np.zeros(0, np.uint8)
+        super().__init__(nat.lib().lw_matrix_create(b.ctypes.data_as(C.c_void_p), b.size, N, Ks, nat.FMT[fmt],
+                                                    s.ctypes.data_as(C.c_void_p) if s.size else None, s.size))
+
+    def decode_symbols(self):
+        return self.decode_codes(self.NAME, expand=False).cpu().numpy()

@@ -1,0 +1,156 @@
+"""Parity of the CUDA path with the reference, through the C ABI, on a real GPU.
+
+Three layers of evidence: (1) golden vectors written by the reference's own Python code, (2) the CPU oracle on
+seeded inputs at sizes it handles in seconds, (3) size-independent properties at the benchmark's full sizes.
+Integer results (symbols, codes) and fp16 weights must match bit for bit; products are held to
+max|y - y_ref| / max|y_ref| <= 1e-3 against a float64 product of the exact float32 weights.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import lw_oracle as orc
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lw():
+    helpers.build_library()
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import lazyweights_b200 as pkg
+    yield pkg
+    assert pkg.lib().lw_kernel_error() == 0
+
+
+def _bits16(a):
+    return np.ascontiguousarray(a).view(np.uint16)
+
+
+@pytest.mark.parametrize("ty", helpers.FORMATS)
+def test_golden_decode_and_weights(lw, golden_dir, ty):
+    g = helpers.golden(golden_dir, ty)
+    n, ks = g["sym"].shape
+    blob = g["blob"].tobytes()
+    assert np.array_equal(lw.bundle.decode_huf8(blob, n, ks), g["decoded"])          # drop-in for decode_huf8
+    with lw.CodedMatrix(blob, n, ks, ty, g["side"]) as m:
+        assert np.array_equal(m.decode_codes("m", expand=True).cpu().numpy(), g["q"])
+        w = m.decode_weights("m").cpu().numpy()
+        assert np.array_equal(_bits16(w), _bits16(g["w"].astype(np.float16)))          # bit-exact fp16 weights
+
+
+@pytest.mark.parametrize("ty", helpers.FORMATS)
+@pytest.mark.parametrize("m_rows", [1, 2, 3, 4, 5, 8])
+def test_golden_products(lw, golden_dir, ty, m_rows):
+    import torch
+    g = helpers.golden(golden_dir, ty)
+    n, ks = g["sym"].shape
+    with lw.CodedMatrix(g["blob"].tobytes(), n, ks, ty, g["side"]) as mat:
+        x16 = torch.from_numpy(g["x"][:m_rows]).cuda()
+        y = mat.linear("m", x16).cpu().numpy()
+        assert helpers.rel_err(y, g["y"][:m_rows]) <= helpers.GEMV_TOL
+        y32 = mat.linear("m", x16.float()).cpu().numpy()
+        assert np.array_equal(y, y32)                                                 # fp16 x is widened exactly
+        if m_rows == 1:
+            y1 = mat.linear("m", x16[0]).cpu().numpy()
+            assert y1.shape == (n,) and np.array_equal(y1, y[0])
+
+
+@pytest.mark.parametrize("name", ["single", "uniform256", "two", "skewed"])
+def test_golden_edge_blobs(lw, golden_dir, name):
+    g = np.load(os.path.join(golden_dir, "edge_%s.npz" % name))
+    assert np.array_equal(lw.bundle.decode_huf8(g["blob"].tobytes(), *g["sym"].shape), g["sym"])
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q4_K", 256, 2048), ("Q5_K", 192, 1024), ("Q6_K", 320, 1024),
+                                     ("IQ4_XS", 128, 2560), ("Q6_K", 64, 256), ("Q4_K", 64, 512)])
+def test_oracle_parity_seeded(lw, ty, n, k):
+    import torch
+    q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=n + k)
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    assert np.array_equal(orc.decode_huf8(blob, *sym.shape), sym)                     # oracle reads the product's blob
+    with lw.CodedMatrix(blob, n, sym.shape[1], ty, side) as mat:
+        assert np.array_equal(mat.decode_codes("m", expand=False).cpu().numpy(), sym)
+        assert np.array_equal(mat.decode_codes("m", expand=True).cpu().numpy(), q)
+        got = mat.decode_weights("m").cpu().numpy()
+        assert np.array_equal(_bits16(got), _bits16(w.astype(np.float16)))
+        x = rng.standard_normal((8, k)).astype(np.float16)
+        y = mat.linear("m", torch.from_numpy(x).cuda()).cpu().numpy()
+        assert helpers.rel_err(y, orc.gemv_f64(w, x.astype(np.float32))) <= helpers.GEMV_TOL
+
+
+def test_bundle_directory_host_api(lw, tmp_path):
+    """The reference-named host-buffer entry points on a bundle directory with all four formats."""
+    rng = np.random.default_rng(77)
+    cases = {}
+    wr = lw.bundle.Writer(str(tmp_path / "b"))
+    wr.cfg("hidden", 1024)
+    for i, ty in enumerate(helpers.FORMATS):
+        n, k = 128 + 64 * i, 1024
+        q, side = orc.synth_codes(ty, n, k, rng), orc.synth_side(ty, n, k, rng)
+        wr.add_kquant("l%d.up" % i, ty, q, side)
+        cases["l%d.up" % i] = (ty, q, side)
+    wr.close()
+    with lw.Bundle(str(tmp_path / "b")) as b:
+        assert b.stat("n_matrices") == 4 and b.stat("nope") == -1
+        for name, (ty, q, side) in cases.items():
+            inf = b.info(name)
+            assert (inf["N"], inf["K"], inf["fmt"]) == (q.shape[0], q.shape[1], ty)
+            assert np.array_equal(b.decode(name), q)                                   # rt_test_decode
+            assert np.array_equal(b.cpu_decode(name, 4), orc.symbols_of(ty, q))        # rt_test_cpu_decode
+            w = orc.dequant(ty, q, side)
+            X = (rng.random((11, q.shape[1])) - 0.5).astype(np.float32)                # m > 8: chunks of eight rows
+            for path in (0, 1):
+                Y = b.matmul(name, X, path)
+                assert helpers.rel_err(Y, orc.gemv_f64(w, X)) <= helpers.GEMV_TOL
+        with pytest.raises(KeyError):
+            b.matmul("missing", np.zeros((1, 1024), np.float32))
+        assert b.gpu_decode_all(2) > 0
+        secs, nsym = b.cpu_decode_all(4)
+        assert secs > 0 and nsym == sum(q.shape[0] * q.shape[1] // (2 if ty in ("Q4_K", "IQ4_XS") else 1)
+                                        for ty, q, _ in cases.values())
+
+
+def test_worst_case_code_lengths(lw):
+    """Every symbol 11 bits long is the largest tile the format allows; the staging buffers must take it."""
+    rng = np.random.default_rng(5)
+    # 2047 equiprobable-ish symbols are impossible with 256 symbols; force long codes with a geometric tail
+    p = 0.5 ** np.arange(1, 60)
+    sym = rng.choice(59, (128, 512), p=p / p.sum()).astype(np.uint8)
+    sym[:64, :256] = rng.integers(40, 59, (64, 256))                                   # one tile of rare (long) symbols
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    assert (np.frombuffer(blob, np.uint16, 2048) >> 8).max() == 11
+    assert np.array_equal(lw.bundle.decode_huf8(blob, 128, 512), sym)
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q6_K", 14336, 4096), ("Q4_K", 4096, 4096)])
+def test_full_size_properties(lw, ty, n, k):
+    """Benchmark-size matrices: round trip, agreement with the library's own host decoder, row sums, linearity."""
+    import torch
+    rng = np.random.default_rng(1)
+    q = orc.synth_codes(ty, n, k, rng)
+    side = orc.synth_side(ty, n, k, rng)
+    sym = orc.symbols_of(ty, q)
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    with lw.CodedMatrix(blob, n, sym.shape[1], ty, side) as mat:
+        assert np.array_equal(mat.decode_codes("m", expand=True).cpu().numpy(), q)    # encode -> GPU decode round trip
+        w16 = mat.decode_weights("m")
+        rows = rng.choice(n, 96, replace=False)
+        w_ref = orc.dequant(ty, q[rows], side[rows])
+        assert np.array_equal(_bits16(w16[torch.from_numpy(rows).cuda()].cpu().numpy()),
+                              _bits16(w_ref.astype(np.float16)))
+        x1 = torch.from_numpy(rng.standard_normal(k).astype(np.float16)).cuda()
+        x2 = torch.from_numpy(rng.standard_normal(k).astype(np.float16)).cuda()
+        y1, y2 = mat.linear("m", x1), mat.linear("m", x2)
+        y12 = mat.linear("m", x1.float() + x2.float())
+        scale = float(y12.abs().max())
+        assert float((y12 - (y1 + y2)).abs().max()) <= 1e-4 * scale                   # linearity in x
+        # the fused product against the decoded fp16 weights (fp64 on the host for a subset of rows)
+        yr = w_ref.astype(np.float64) @ x1.float().cpu().numpy().astype(np.float64)
+        assert np.abs(y1.cpu().numpy()[rows] - yr).max() <= helpers.GEMV_TOL * np.abs(yr).max()
+        ones = torch.ones(k, dtype=torch.float16, device="cuda")
+        rs = mat.linear("m", ones).cpu().numpy()[rows]
+        assert np.abs(rs - w_ref.astype(np.float64).sum(1)).max() <= helpers.GEMV_TOL * np.abs(rs).max()
