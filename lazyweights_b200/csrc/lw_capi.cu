@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -82,13 +83,23 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
       return kErrFormat;
     }
   }
-  const int split = 1;
-  std::vector<uint32_t> chain_start, lane_end, group_base, words;
+  // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
+  // table (7: 1024 windows x 32 copies, codes <= 10 bits; 6: 2048 windows x 16 copies).  LW_PAD overrides (2 = the
+  // single-copy table of the staged kernel).
+  int split = 2;
+  if (const char* e = getenv("LW_SPLIT")) split = atoi(e) == 1 ? 1 : 2;
+  if (mx.fmt == kFmtNone) split = 1;
+  int pad = tab->max_len <= 10 ? 7 : 6;
+  if (const char* e = getenv("LW_PAD")) pad = std::max(0, std::min(7, atoi(e)));
+  if (pad == 7 && tab->max_len > 10) pad = 6;
+  std::vector<uint32_t> chain_start, lane_end, group_base, words, fat(kLutSize);
+  fat_table(*tab, mx.fmt, fat.data());
   if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr))) return rc;
   uint32_t max_group = 0, max_tile = 0;
-  if ((rc = relayout(v, split, chain_start, lane_end, threads, group_base, words, &max_group, &max_tile))) return rc;
+  if ((rc = relayout(v, split, pad, chain_start, lane_end, threads, group_base, words, &max_group, &max_tile))) return rc;
 
-  const size_t off_gb = align_up(2 * kLutSize, 256);
+  const size_t off_fat = align_up(2 * kLutSize, 256);
+  const size_t off_gb = align_up(off_fat + 4 * kLutSize, 256);
   const size_t off_words = align_up(off_gb + group_base.size() * 4, 256);
   const size_t off_side = align_up(off_words + words.size() * 4, 256);
   const size_t total = off_side + align_up(side_nbytes, 256);
@@ -96,12 +107,16 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
   if (e != cudaSuccess) return cuda_fail("cudaMalloc (matrix)", e);
   uint8_t* d = static_cast<uint8_t*>(mx.d_block);
   if ((e = cudaMemcpy(d, v.lut(), 2 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_fat, fat.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_gb, group_base.data(), group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_words, words.data(), words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (side_nbytes && (e = cudaMemcpy(d + off_side, side, side_nbytes, cudaMemcpyHostToDevice)) != cudaSuccess))
     return cuda_fail("cudaMemcpy (matrix)", e);
   mx.device_bytes = total;
   mx.dev.lut = reinterpret_cast<const uint16_t*>(d);
+  mx.dev.tab32 = reinterpret_cast<const uint32_t*>(d + off_fat);
+  mx.dev.pad = pad;
+  mx.dev.max_len = tab->max_len;
   mx.dev.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
   mx.dev.words = reinterpret_cast<const uint32_t*>(d + off_words);
   mx.dev.side = side_nbytes ? d + off_side : nullptr;
@@ -113,6 +128,7 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
   mx.dev.fmt = mx.fmt;
   mx.dev.split = split;
   mx.dev.max_tile_words = max_tile;
+  mx.dev.max_unit_words = max_group;
   return kOk;
 }
 

@@ -9,9 +9,10 @@
 //
 // Device layout (built once at load, lw::relayout): every lane is cut into "chains" of 256 / SPLIT symbols
 // (its two rows, each optionally cut into SPLIT column segments).  The 32 chains that cover the same rows half
-// and the same column segment form a group; each chain of a group is re-based to bit 0 and the group's words are
-// interleaved: word i of chain c (= lane) sits at group_base + 32 i + c, so one warp reads its 32 next words as
-// one 128-byte line.  A group is padded to its longest chain.
+// and the same column segment form a group; each chain of a group is re-based (it starts with `pad` zero bits, then
+// its code bits) and the group's words are interleaved: word i of chain c (= lane) sits at group_base + 32 i + c, so
+// one warp reads its 32 next words as one 128-byte line.  A group is padded to its longest chain.  Groups of a tile
+// are stored segment-major: group 2 s + h holds rows half h (rows 32 h .. 32 h + 31) over column segment s.
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -24,7 +25,7 @@ constexpr int kMaxLen = 11;
 constexpr int kLanes = 32;
 constexpr int kLutSize = 1 << kMaxLen;
 constexpr int kBlobAlign = 256;
-constexpr int kTailWords = 256;   // zero words after the last group: read-ahead of the last chains lands here
+constexpr int kTailWords = 512;   // zero words after the last group: read-ahead of the last chains lands here
 
 // Block formats of the side bytes (reference: kernels/llmrt.cu:113-121, scripts/a2_kq_bundle.py:41-42).
 enum Format : int { kFmtNone = 0, kFmtQ4K = 1, kFmtQ5K = 2, kFmtQ6K = 3, kFmtIQ4XS = 4 };

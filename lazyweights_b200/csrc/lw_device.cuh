@@ -63,12 +63,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 struct Chain {
   const uint32_t* p;
   uint32_t w0, w1, w2, bp;
-  __device__ __forceinline__ void init(const uint32_t* chain_words) {
+  __device__ __forceinline__ void init(const uint32_t* chain_words, int pad) {
     w0 = chain_words[0];
     w1 = chain_words[32];
     w2 = chain_words[64];
     p = chain_words + 96;
-    bp = 0;
+    bp = pad;
   }
   __device__ __forceinline__ uint32_t next(const uint16_t* lut) {
     const uint32_t e = lut[__funnelshift_r(w0, w1, bp) & (kLutSize - 1)];

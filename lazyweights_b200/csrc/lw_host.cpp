@@ -171,6 +171,36 @@ int table_from_lut(const uint16_t* lut, HuffTable& t) {
   return kOk;
 }
 
+static uint32_t bf16_bits(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  return u >> 16;   // exact for the small integers of the block formats' grids
+}
+
+static float grid_of(int fmt, int q) {
+  static const float iq4[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+  if (fmt == kFmtIQ4XS) return iq4[q & 15];
+  return static_cast<float>(q) - (fmt == kFmtQ6K ? 32.f : 0.f);
+}
+
+// 32-bit decode table for the fused kernels: bits 28-31 = code length; unpaired formats keep f(symbol) as bf16 in
+// bits 0-15; Q4_K keeps f(low nibble) as the top 12 bits of its bf16 in bits 16-27 and f(high nibble) as bf16 in
+// bits 0-15.  A float is recovered by a shift (and one mask), the length by a multiply-high.
+void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]) {
+  for (int i = 0; i < kLutSize; ++i) {
+    const uint32_t sym = t.lut[i] & 255u, len = t.lut[i] >> 8;
+    uint32_t e = len << 28;
+    if (fmt == kFmtQ4K) {
+      e |= ((bf16_bits(grid_of(fmt, sym & 15)) >> 4) << 16) | bf16_bits(grid_of(fmt, sym >> 4));
+    } else if (fmt == kFmtQ5K || fmt == kFmtQ6K) {
+      e |= bf16_bits(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)));
+    } else {
+      e |= sym;
+    }
+    out[i] = e;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ blob
 
 int make_view(const uint8_t* blob, size_t nbytes, int N, int Ks, BlobView& v) {
@@ -327,16 +357,20 @@ int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, s
   return kOk;
 }
 
-int relayout(const BlobView& v, int split, const std::vector<uint32_t>& chain_start,
+int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>& chain_start,
              const std::vector<uint32_t>& lane_end, int threads, std::vector<uint32_t>& group_base,
              std::vector<uint32_t>& words, uint32_t* max_group_words, uint32_t* max_tile_words) {
   const int G = 2 * split;
   const size_t ngroups = static_cast<size_t>(v.T) * G;
   group_base.assign(ngroups + 1, 0);
-  auto chain_bits = [&](size_t t, int lane, int g, uint32_t* begin) {
+  // group gi of a tile = (column segment gi / 2, rows half gi % 2): the two halves of a segment are adjacent, so a
+  // warp that decodes rows l and l + 32 over one segment stages one contiguous piece.  In stream order the lane's
+  // chains run half-major (row l: all segments, then row l + 32).
+  auto chain_bits = [&](size_t t, int lane, int gi, uint32_t* begin) {
     const size_t li = t * kLanes + lane;
-    const uint32_t b = chain_start[li * G + g];
-    const uint32_t e = g + 1 < G ? chain_start[li * G + g + 1] : lane_end[li];
+    const int ci = (gi & 1) * split + (gi >> 1);
+    const uint32_t b = chain_start[li * G + ci];
+    const uint32_t e = ci + 1 < G ? chain_start[li * G + ci + 1] : lane_end[li];
     *begin = b;
     return e - b;
   };
@@ -348,12 +382,13 @@ int relayout(const BlobView& v, int split, const std::vector<uint32_t>& chain_st
     uint32_t tile_words = 0;
     for (int g = 0; g < G; ++g) {
       uint32_t w = 0, b;
-      for (int lane = 0; lane < kLanes; ++lane) w = std::max(w, (chain_bits(t, lane, g, &b) + 31) / 32);
+      for (int lane = 0; lane < kLanes; ++lane) w = std::max(w, (chain_bits(t, lane, g, &b) + pad + 31) / 32);
       gw[t * G + g] = w;
-      mg = std::max(mg, w);
       tile_words += w * kLanes;
     }
     mt = std::max(mt, tile_words);
+    for (int seg = 0; seg < split; ++seg)
+      mg = std::max(mg, (gw[t * G + 2 * seg] + gw[t * G + 2 * seg + 1]) * kLanes);
     for (int g = 0; g < G; ++g) {
       if (total > 0xFFFFFFFFull) {
         set_error("matrix needs more than 2^32 device words");
@@ -375,11 +410,17 @@ int relayout(const BlobView& v, int split, const std::vector<uint32_t>& chain_st
       uint32_t* dst = words.data() + group_base[static_cast<size_t>(t) * G + g];
       for (int lane = 0; lane < kLanes; ++lane) {
         uint32_t b;
-        const uint32_t nbits = chain_bits(t, lane, g, &b);
+        const uint32_t nbits = chain_bits(t, lane, g, &b) + pad;   // the chain starts with `pad` zero bits
         for (uint32_t i = 0; i * 32 < nbits; ++i) {
-          const uint64_t p = static_cast<uint64_t>(b) + i * 32ull;
-          const uint64_t x = pay[p >> 5] | (static_cast<uint64_t>(pay[(p >> 5) + 1]) << 32);
-          uint32_t w = static_cast<uint32_t>(x >> (p & 31));
+          uint32_t w;
+          if (i == 0) {
+            const uint64_t x = pay[b >> 5] | (static_cast<uint64_t>(pay[(b >> 5) + 1]) << 32);
+            w = static_cast<uint32_t>(x >> (b & 31)) << pad;
+          } else {
+            const uint64_t p = static_cast<uint64_t>(b) + i * 32ull - pad;
+            const uint64_t x = pay[p >> 5] | (static_cast<uint64_t>(pay[(p >> 5) + 1]) << 32);
+            w = static_cast<uint32_t>(x >> (p & 31));
+          }
           const uint32_t left = nbits - i * 32;
           if (left < 32) w &= (1u << left) - 1;
           dst[static_cast<size_t>(i) * kLanes + lane] = w;

@@ -23,6 +23,7 @@ void limited_lengths(const int64_t counts[256], uint8_t len[256]);
 void table_from_lengths(const uint8_t len[256], HuffTable& t);
 // Recovers lengths from a stored table and checks that the table is exactly the canonical one for those lengths.
 int table_from_lut(const uint16_t* lut, HuffTable& t);
+void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]);
 
 // ---- blob (reference: lazyweights/bundle.py:57-106, kernels/llmrt.cu:2513-2541)
 int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits);
@@ -36,9 +37,10 @@ int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, s
               std::vector<uint32_t>* lane_end, uint8_t* out);
 
 // Re-layout into interleaved chain groups (the role of interleave_huf8, kernels/llmrt.cu:1208-1257).
-int relayout(const BlobView& v, int split, const std::vector<uint32_t>& chain_start,
+// Every chain starts with `pad` zero bits (the fused kernels fold the table's entry size into the shift).
+int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>& chain_start,
              const std::vector<uint32_t>& lane_end, int threads, std::vector<uint32_t>& group_base,
-             std::vector<uint32_t>& words, uint32_t* max_group_words, uint32_t* max_tile_words);
+             std::vector<uint32_t>& words, uint32_t* max_unit_words, uint32_t* max_tile_words);
 
 // ---- bundle directory (reference: lazyweights/bundle.py:114-148)
 struct TensorEntry {

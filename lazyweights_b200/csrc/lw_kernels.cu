@@ -10,8 +10,10 @@
 // on an mbarrier) issued by lane 0; the lanes then read their next words from shared memory, bank = lane.
 #include "lw_kernels.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 
 #include "lw_device.cuh"
 
@@ -61,13 +63,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_codes(MatDev M, 
   const int row_bytes = EXPAND ? 2 * M.Ks : M.Ks;
   const int tile_bytes = EXPAND ? 2 * kTileSyms : kTileSyms;
 #pragma unroll 1
+  const int G = 2 * M.split, per_seg = tile_bytes / 16 / M.split;
   for (int half = 0; half < 2; ++half) {
     Chain ch;
-    ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * 2 + half) - base) + lane);
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(tr * kTileRows + half * 32 + lane) * row_bytes +
                                           static_cast<size_t>(tc) * tile_bytes);
 #pragma unroll 1
     for (int c = 0; c < tile_bytes / 16; ++c) {
+      if (c % per_seg == 0)   // next column segment: its own chain
+        ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * G + 2 * (c / per_seg) + half) - base) + lane, M.pad);
       uint32_t v[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -113,7 +117,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_weights(MatDev M
   for (int half = 0; half < 2; ++half) {
     const int n = tr * kTileRows + half * 32 + lane;
     Chain ch;
-    ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * 2 + half) - base) + lane);
+    const int G = 2 * M.split, sub_per_seg = (TW / GW) / M.split;
     const uint8_t* srow = M.side + (static_cast<size_t>(n) * (M.K / 256) + static_cast<size_t>(tc) * (TW / 256)) * SB;
     __half* orow = out + static_cast<size_t>(n) * M.K + static_cast<size_t>(tc) * TW;
 #pragma unroll 1
@@ -124,6 +128,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_weights(MatDev M
       for (int jj = 0; jj < 256 / GW; ++jj) {
         float s, o;
         sr.sub(jj, s, o);
+        const int g = sb * (256 / GW) + jj;
+        if (g % sub_per_seg == 0)   // next column segment: its own chain
+          ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * G + 2 * (g / sub_per_seg) + half) - base) + lane,
+                  M.pad);
 #pragma unroll
         for (int c = 0; c < GW / 8; ++c) {   // 8 weights -> one 16-byte store
           __half h[8];
@@ -176,8 +184,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   uint32_t base = 0;
   const uint32_t bar_a = smem_addr(bars + warp);
   if (active) {   // start the tile's copy first: it overlaps the table and activation staging below
-    const uint32_t b0 = __ldg(M.group_base + static_cast<size_t>(t) * 2);
-    const uint32_t b1 = __ldg(M.group_base + static_cast<size_t>(t + 1) * 2);
+    const uint32_t b0 = __ldg(M.group_base + static_cast<size_t>(t) * 2 * M.split);
+    const uint32_t b1 = __ldg(M.group_base + static_cast<size_t>(t + 1) * 2 * M.split);
     base = b0;
     if (lane == 0) {
       mbar_init(bar_a, 1);
@@ -206,8 +214,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   if (!mbar_wait(bar_a, 0)) return;
 
   Chain ca, cb;
-  ca.init(buf + lane);
-  cb.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * 2 + 1) - base) + lane);
+  const int G = 2 * M.split, sub_per_seg = NG / M.split;
   const int na = tr * kTileRows + lane, nb = na + 32;
   const size_t side_row = static_cast<size_t>(M.K / 256) * SB;
   const uint8_t* sa = M.side + na * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
@@ -223,6 +230,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 #pragma unroll
     for (int jj = 0; jj < 256 / GW; ++jj) {
       const int g = sb * (256 / GW) + jj;
+      if (g % sub_per_seg == 0) {   // next column segment: its own pair of chains
+        const uint32_t* gb = M.group_base + static_cast<size_t>(t) * G + 2 * (g / sub_per_seg);
+        ca.init(buf + (__ldg(gb) - base) + lane, M.pad);
+        cb.init(buf + (__ldg(gb + 1) - base) + lane, M.pad);
+      }
       float s_a, o_a, s_b, o_b;
       ra.sub(jj, s_a, o_a);
       rb.sub(jj, s_b, o_b);
@@ -274,6 +286,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
       P[(static_cast<size_t>(tc) * m + j) * M.N + nb] = tot_b[j];
     }
 }
+
+}  // namespace lw
+#include "lw_gemv1.cuh"
+namespace lw {
 
 __global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int KT) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -353,7 +369,9 @@ int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
   return check_launch("k_decode_weights");
 }
 
-size_t gemv_partial_floats(const MatDev& M, int m) { return static_cast<size_t>(M.KT) * m * M.N; }
+size_t gemv_partial_floats(const MatDev& M, int m) {
+  return static_cast<size_t>(M.KT) * std::max(m, M.split) * M.N;
+}
 
 template <int FMT, int MT, typename XT>
 static int launch_gemv_t(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
@@ -388,16 +406,132 @@ static int launch_gemv_f(const MatDev& M, const XT* X, int m, float* P, cudaStre
   return kErrArg;
 }
 
+static int sm_count() {
+  static const int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 1;
+  }();
+  return n;
+}
+
+// ---- batch-1 kernel: one persistent block per SM; see lw_gemv1.cuh
+constexpr size_t kSmemLimit = 227 * 1024;
+constexpr int kMaxStagedColumns = 16;   // tile columns whose activations one block keeps in shared memory
+
+struct Gemv1Plan {
+  int warps, nsets, cols_per_set, blocks;
+  uint32_t buf_words;
+  size_t smem;
+};
+
+template <int FMT, int SPLIT>
+static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
+  constexpr int TW = is_paired(FMT) ? 512 : 256;
+  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
+  p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
+  p.buf_words = (M.max_unit_words + kSlackWords + 31u) & ~31u;
+  const size_t fixed = kReplicatedTableBytes +
+                       static_cast<size_t>(p.cols_per_set) * (TW + (has_offset ? TW / sub_width(FMT) : 0)) * 4 +
+                       kGemv1MaxWarps * 8;
+  const int units = (M.N / kTileRows) * M.KT * SPLIT;
+  p.blocks = std::max(p.nsets, std::min(sm_count(), units));
+  const double per_block = static_cast<double>(units) / p.blocks;
+  // warps per block: as many as fit, but prefer a count that leaves no nearly-empty last round of units
+  int best = 0;
+  double best_score = -1;
+  for (int w = 1; w <= kGemv1MaxWarps; ++w) {
+    if (fixed + static_cast<size_t>(w) * p.buf_words * 4 > kSmemLimit) break;
+    const double rounds = per_block / w;
+    const double eff = rounds / std::max(1.0, std::ceil(rounds - 1e-9));
+    const double score = eff * std::min<double>(w, 12) / 12.0;   // beyond ~12 warps latency is hidden anyway
+    if (score > best_score + 1e-9) {
+      best_score = score;
+      best = w;
+    }
+  }
+  if (!best) return false;
+  p.warps = best;
+  p.smem = fixed + static_cast<size_t>(best) * p.buf_words * 4;
+  return true;
+}
+
+template <int FMT, int G, int IDXBITS, int SPLIT>
+static int launch_gemv1_t(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
+  Gemv1Plan p;
+  if (!plan_gemv1<FMT, SPLIT>(M, p)) {
+    set_kernel_error_text("gemv1", "work unit does not fit shared memory");
+    return kErrTooLarge;
+  }
+  int rc;
+  if ((rc = prepare(k_gemv1<FMT, G, IDXBITS, SPLIT>, p.smem))) return rc;
+  Gemv1Args a;
+  a.x = X;
+  a.partials = P;
+  a.x_is_half = x_is_half;
+  a.warps = p.warps;
+  a.buf_words = p.buf_words;
+  a.nsets = p.nsets;
+  a.cols_per_set = p.cols_per_set;
+  k_gemv1<FMT, G, IDXBITS, SPLIT><<<p.blocks, p.warps * 32, p.smem, st>>>(M, a);
+  return check_launch("k_gemv1");
+}
+
+template <int FMT, int SPLIT>
+static int launch_gemv1_g(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
+  if (M.pad == 7) {
+    if (M.max_len <= 8) return launch_gemv1_t<FMT, 4, 10, SPLIT>(M, X, x_is_half, P, st);
+    return launch_gemv1_t<FMT, 3, 10, SPLIT>(M, X, x_is_half, P, st);
+  }
+  return launch_gemv1_t<FMT, 2, 11, SPLIT>(M, X, x_is_half, P, st);
+}
+
+template <int FMT>
+static int launch_gemv1_s(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
+  if (M.split == 2) return launch_gemv1_g<FMT, 2>(M, X, x_is_half, P, st);
+  return launch_gemv1_g<FMT, 1>(M, X, x_is_half, P, st);
+}
+
+static int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
+  switch (M.fmt) {
+    case kFmtQ4K: return launch_gemv1_s<kFmtQ4K>(M, X, x_is_half, P, st);
+    case kFmtQ5K: return launch_gemv1_s<kFmtQ5K>(M, X, x_is_half, P, st);
+    default: return launch_gemv1_s<kFmtQ6K>(M, X, x_is_half, P, st);
+  }
+}
+
+static bool gemv1_usable(const MatDev& M) {
+  const bool pad_ok = (M.pad == 7 && M.max_len <= 10) || M.pad == 6;
+  const bool fmt_ok = M.fmt == kFmtQ4K || M.fmt == kFmtQ5K || M.fmt == kFmtQ6K;
+  return pad_ok && fmt_ok && (M.split == 1 || M.split == 2);
+}
+
+static int gemv1_variant() {
+  static const int v = [] {
+    const char* e = getenv("LW_GEMV1");
+    return e ? atoi(e) : 1;
+  }();
+  return v;
+}
+
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
                 cudaStream_t st) {
   if (m < 1 || m > 8) {
     set_kernel_error_text("gemv", "m must be 1..8");
     return kErrArg;
   }
-  int rc = x_is_half ? launch_gemv_f<__half>(M, static_cast<const __half*>(X), m, partials, st)
-                     : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
+  int rc, terms = M.KT;
+  if (m == 1 && gemv1_variant() != 0 && gemv1_usable(M)) {
+    rc = launch_gemv1(M, X, x_is_half, partials, st);
+    terms = M.KT * M.split;
+  } else {
+    rc = x_is_half ? launch_gemv_f<__half>(M, static_cast<const __half*>(X), m, partials, st)
+                   : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
+  }
   if (rc) return rc;
-  k_sum_partials<<<(m * M.N + 255) / 256, 256, 0, st>>>(partials, Y, m, M.N, ldy, M.KT);
+  k_sum_partials<<<(m * M.N + 255) / 256, 256, 0, st>>>(partials, Y, m, M.N, ldy, terms);
   return check_launch("k_sum_partials");
 }
 
