@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblwb200.so")
+LIB_PATH = os.environ.get("LWB200_LIB") or os.path.join(_HERE, "liblwb200.so")
 
 LW_OK, LW_ERR, LW_ERR_ARG, LW_ERR_FORMAT, LW_ERR_CUDA, LW_ERR_TOO_LARGE, LW_ERR_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6
 FMT = {"none": 0, "Q4_K": 1, "Q5_K": 2, "Q6_K": 3, "IQ4_XS": 4}

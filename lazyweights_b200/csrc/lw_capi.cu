@@ -86,8 +86,12 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
   // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
   // table (7: 1024 windows x 32 copies, codes <= 10 bits; 6: 2048 windows x 16 copies).  LW_PAD overrides (2 = the
   // single-copy table of the staged kernel).
-  int split = 2;
-  if (const char* e = getenv("LW_SPLIT")) split = atoi(e) == 1 ? 1 : 2;
+  // Column segments per tile row: more segments = shorter chains = more of them in flight for the same staging memory.
+  int split = mx.fmt == kFmtQ5K ? 2 : 4;
+  if (const char* e = getenv("LW_SPLIT")) {
+    const int v = atoi(e);
+    if (v == 1 || v == 2 || (v == 4 && mx.fmt != kFmtQ5K)) split = v;
+  }
   if (mx.fmt == kFmtNone) split = 1;
   int pad = tab->max_len <= 10 ? 7 : 6;
   if (const char* e = getenv("LW_PAD")) pad = std::max(0, std::min(7, atoi(e)));

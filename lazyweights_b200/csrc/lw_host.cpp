@@ -171,29 +171,24 @@ int table_from_lut(const uint16_t* lut, HuffTable& t) {
   return kOk;
 }
 
-static uint32_t bf16_bits(float f) {
-  uint32_t u;
-  std::memcpy(&u, &f, 4);
-  return u >> 16;   // exact for the small integers of the block formats' grids
-}
-
 static float grid_of(int fmt, int q) {
   static const float iq4[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
   if (fmt == kFmtIQ4XS) return iq4[q & 15];
   return static_cast<float>(q) - (fmt == kFmtQ6K ? 32.f : 0.f);
 }
 
-// 32-bit decode table for the fused kernels: bits 28-31 = code length; unpaired formats keep f(symbol) as bf16 in
-// bits 0-15; Q4_K keeps f(low nibble) as the top 12 bits of its bf16 in bits 16-27 and f(high nibble) as bf16 in
-// bits 0-15.  A float is recovered by a shift (and one mask), the length by a multiply-high.
+// 32-bit decode table of the batch-1 kernel: bits 28-31 = code length (recovered by one multiply-high); byte 0 =
+// the grid value of the symbol (of its low nibble for paired formats) as a signed 8-bit integer, byte 1 = the grid
+// value of the high nibble (0 for unpaired formats).  The two bytes are the multiplier operand of a dp2a instruction.
 void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]) {
   for (int i = 0; i < kLutSize; ++i) {
     const uint32_t sym = t.lut[i] & 255u, len = t.lut[i] >> 8;
     uint32_t e = len << 28;
-    if (fmt == kFmtQ4K) {
-      e |= ((bf16_bits(grid_of(fmt, sym & 15)) >> 4) << 16) | bf16_bits(grid_of(fmt, sym >> 4));
+    if (is_paired(fmt)) {
+      const int v0 = static_cast<int>(grid_of(fmt, sym & 15)), v1 = static_cast<int>(grid_of(fmt, sym >> 4));
+      e |= (static_cast<uint32_t>(v0) & 255u) | ((static_cast<uint32_t>(v1) & 255u) << 8);
     } else if (fmt == kFmtQ5K || fmt == kFmtQ6K) {
-      e |= bf16_bits(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)));
+      e |= static_cast<uint32_t>(static_cast<int>(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)))) & 255u;
     } else {
       e |= sym;
     }

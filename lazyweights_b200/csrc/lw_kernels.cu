@@ -421,7 +421,7 @@ constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kMaxStagedColumns = 16;   // tile columns whose activations one block keeps in shared memory
 
 struct Gemv1Plan {
-  int warps, nsets, cols_per_set, blocks;
+  int warps, producers, prefetch, slots, nsets, cols_per_set, blocks;
   uint32_t buf_words;
   size_t smem;
 };
@@ -434,27 +434,21 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
   p.buf_words = (M.max_unit_words + kSlackWords + 31u) & ~31u;
   const size_t fixed = kReplicatedTableBytes +
-                       static_cast<size_t>(p.cols_per_set) * (TW + (has_offset ? TW / sub_width(FMT) : 0)) * 4 +
-                       kGemv1MaxWarps * 8;
+                       static_cast<size_t>(p.cols_per_set) * (TW / 2 + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
+                       2 * kGemv1MaxSlots * 8 + kGemv1MaxUnits * sizeof(UnitMeta);
+  if (fixed + static_cast<size_t>(p.buf_words) * 4 > kSmemLimit) return false;
   const int units = (M.N / kTileRows) * M.KT * SPLIT;
   p.blocks = std::max(p.nsets, std::min(sm_count(), units));
-  const double per_block = static_cast<double>(units) / p.blocks;
-  // warps per block: as many as fit, but prefer a count that leaves no nearly-empty last round of units
-  int best = 0;
-  double best_score = -1;
-  for (int w = 1; w <= kGemv1MaxWarps; ++w) {
-    if (fixed + static_cast<size_t>(w) * p.buf_words * 4 > kSmemLimit) break;
-    const double rounds = per_block / w;
-    const double eff = rounds / std::max(1.0, std::ceil(rounds - 1e-9));
-    const double score = eff * std::min<double>(w, 12) / 12.0;   // beyond ~12 warps latency is hidden anyway
-    if (score > best_score + 1e-9) {
-      best_score = score;
-      best = w;
-    }
-  }
-  if (!best) return false;
-  p.warps = best;
-  p.smem = fixed + static_cast<size_t>(best) * p.buf_words * 4;
+  if ((units + p.blocks - 1) / p.blocks + 1 > kGemv1MaxUnits) return false;
+  // as many staging buffers as fit; about three consumers per four buffers, so that copies run ahead of the decoding
+  p.slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));
+  p.warps = std::max(1, std::min(kGemv1MaxWarps, p.slots * 3 / 4));
+  if (const char* e = getenv("LW_GEMV1_WARPS")) p.warps = std::max(1, std::min(std::min(kGemv1MaxWarps, p.slots), atoi(e)));
+  p.producers = 2;
+  p.prefetch = 0;
+  if (const char* e = getenv("LW_GEMV1_PRODUCERS")) p.producers = std::max(1, std::min(4, atoi(e)));
+  if (const char* e = getenv("LW_GEMV1_PREFETCH")) p.prefetch = std::max(0, atoi(e));
+  p.smem = fixed + static_cast<size_t>(p.slots) * p.buf_words * 4;
   return true;
 }
 
@@ -472,10 +466,13 @@ static int launch_gemv1_t(const MatDev& M, const void* X, bool x_is_half, float*
   a.partials = P;
   a.x_is_half = x_is_half;
   a.warps = p.warps;
+  a.slots = p.slots;
+  a.producers = p.producers;
+  a.prefetch = p.prefetch;
   a.buf_words = p.buf_words;
   a.nsets = p.nsets;
   a.cols_per_set = p.cols_per_set;
-  k_gemv1<FMT, G, IDXBITS, SPLIT><<<p.blocks, p.warps * 32, p.smem, st>>>(M, a);
+  k_gemv1<FMT, G, IDXBITS, SPLIT><<<p.blocks, (p.warps + p.producers) * 32, p.smem, st>>>(M, a);
   return check_launch("k_gemv1");
 }
 
@@ -490,6 +487,7 @@ static int launch_gemv1_g(const MatDev& M, const void* X, bool x_is_half, float*
 
 template <int FMT>
 static int launch_gemv1_s(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
+  if (M.split == 4 && FMT != kFmtQ5K) return launch_gemv1_g<FMT, (FMT == kFmtQ5K ? 2 : 4)>(M, X, x_is_half, P, st);
   if (M.split == 2) return launch_gemv1_g<FMT, 2>(M, X, x_is_half, P, st);
   return launch_gemv1_g<FMT, 1>(M, X, x_is_half, P, st);
 }
@@ -498,14 +496,15 @@ static int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P
   switch (M.fmt) {
     case kFmtQ4K: return launch_gemv1_s<kFmtQ4K>(M, X, x_is_half, P, st);
     case kFmtQ5K: return launch_gemv1_s<kFmtQ5K>(M, X, x_is_half, P, st);
+    case kFmtIQ4XS: return launch_gemv1_s<kFmtIQ4XS>(M, X, x_is_half, P, st);
     default: return launch_gemv1_s<kFmtQ6K>(M, X, x_is_half, P, st);
   }
 }
 
 static bool gemv1_usable(const MatDev& M) {
   const bool pad_ok = (M.pad == 7 && M.max_len <= 10) || M.pad == 6;
-  const bool fmt_ok = M.fmt == kFmtQ4K || M.fmt == kFmtQ5K || M.fmt == kFmtQ6K;
-  return pad_ok && fmt_ok && (M.split == 1 || M.split == 2);
+  const bool fmt_ok = M.fmt >= kFmtQ4K && M.fmt <= kFmtIQ4XS;
+  return pad_ok && fmt_ok && (M.split == 1 || M.split == 2 || (M.split == 4 && M.fmt != kFmtQ5K));
 }
 
 static int gemv1_variant() {

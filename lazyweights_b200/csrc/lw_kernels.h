@@ -14,7 +14,7 @@ namespace lw {
 // One coded matrix on the device (all pointers are device pointers; passed to kernels by value).
 struct MatDev {
   const uint16_t* lut;          // [2048] symbol | length << 8
-  const uint32_t* tab32;        // [2048] length << 28 | grid value(s) as bf16 (see lw::fat_table)
+  const uint32_t* tab32;        // [2048] length << 28 | grid value(s) as int8 (see lw::fat_table)
   const uint32_t* group_base;   // [T * groups + 1] word offset of every chain group
   const uint32_t* words;        // interleaved chain words (+ zero tail)
   const uint8_t* side;          // [N, K / 256 * side_bytes] or null (symbols only)
