@@ -39,12 +39,16 @@ struct Model {
   std::map<std::string, int> by_name;
   float* d_partials = nullptr;   // split-K partial sums, sized for the largest matrix at m = 8
   size_t partial_floats = 0;
+  float *d_x = nullptr, *d_y = nullptr;   // staging of rt_test_matmul's host buffers (grown on demand, kept)
+  size_t x_floats = 0, y_floats = 0;
   size_t resident_bytes = 0;
   long long coded_bytes = 0, side_bytes = 0;
   ~Model() {
     for (auto& m : mats)
       if (m.d_block) cudaFree(m.d_block);
     if (d_partials) cudaFree(d_partials);
+    if (d_x) cudaFree(d_x);
+    if (d_y) cudaFree(d_y);
     if (fd >= 0) close(fd);
   }
 };
@@ -356,20 +360,27 @@ int rt_test_matmul(void* handle, const char* name, const float* X, int m, float*
     set_error("rt_test_matmul: bad argument");
     return kErrArg;
   }
-  float *dx = nullptr, *dy = nullptr;
   cudaError_t e;
-  int rc = kOk;
-  if ((e = cudaMalloc(&dx, static_cast<size_t>(m) * mx.K * 4)) != cudaSuccess ||
-      (e = cudaMalloc(&dy, static_cast<size_t>(m) * mx.N * 4)) != cudaSuccess ||
-      (e = cudaMemcpy(dx, X, static_cast<size_t>(m) * mx.K * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
-    rc = cuda_fail("rt_test_matmul buffers", e);
-  } else {
-    rc = linear_device(M, mx, dx, false, m, dy, mx.N, nullptr);
-    if (!rc && (e = cudaMemcpy(Y, dy, static_cast<size_t>(m) * mx.N * 4, cudaMemcpyDeviceToHost)) != cudaSuccess)
-      rc = cuda_fail("rt_test_matmul copy back", e);
+  const size_t nx = static_cast<size_t>(m) * mx.K, ny = static_cast<size_t>(m) * mx.N;
+  if (nx > M->x_floats) {
+    if (M->d_x) cudaFree(M->d_x);
+    M->d_x = nullptr;
+    M->x_floats = 0;
+    if ((e = cudaMalloc(&M->d_x, nx * 4)) != cudaSuccess) return cuda_fail("rt_test_matmul buffers", e);
+    M->x_floats = nx;
   }
-  cudaFree(dx);
-  cudaFree(dy);
+  if (ny > M->y_floats) {
+    if (M->d_y) cudaFree(M->d_y);
+    M->d_y = nullptr;
+    M->y_floats = 0;
+    if ((e = cudaMalloc(&M->d_y, ny * 4)) != cudaSuccess) return cuda_fail("rt_test_matmul buffers", e);
+    M->y_floats = ny;
+  }
+  if ((e = cudaMemcpy(M->d_x, X, nx * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+    return cuda_fail("rt_test_matmul copy in", e);
+  int rc = linear_device(M, mx, M->d_x, false, m, M->d_y, mx.N, nullptr);
+  if (!rc && (e = cudaMemcpy(Y, M->d_y, ny * 4, cudaMemcpyDeviceToHost)) != cudaSuccess)
+    rc = cuda_fail("rt_test_matmul copy back", e);
   return rc;
 }
 

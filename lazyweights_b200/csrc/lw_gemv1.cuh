@@ -286,40 +286,73 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       }
     }
   }
-  // activations -> 16-bit fixed point with one scale per sub-block (GW consecutive weights sit in GW consecutive lanes)
-#pragma unroll 2
-  for (int i = threadIdx.x; i < ncol * TW; i += nthr) {
-    const int j = i / TW, k = i - j * TW;
-    const size_t src = static_cast<size_t>(set + A.nsets * j) * TW + k;
-    const float v = A.x_is_half ? __half2float(static_cast<const __half*>(A.x)[src]) : static_cast<const float*>(A.x)[src];
-    float amax = fabsf(v), sum = v;
+  // activations -> 16-bit fixed point with one scale per sub-block (GW consecutive weights sit in GW consecutive
+  // lanes).  Loads go out eight at a time so that their global-memory latencies overlap.
+  constexpr int XB = 8;
+  for (int base = 0; base < ncol * TW; base += XB * nthr) {
+    float v[XB];
 #pragma unroll
-    for (int o = 1; o < GW; o <<= 1) {
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    for (int u = 0; u < XB; ++u) {
+      const int i = base + u * nthr + threadIdx.x;
+      v[u] = 0.f;
+      if (i < ncol * TW) {
+        const int j = i / TW, k = i - j * TW;
+        const size_t src = static_cast<size_t>(set + A.nsets * j) * TW + k;
+        v[u] = A.x_is_half ? __half2float(static_cast<const __half*>(A.x)[src]) : static_cast<const float*>(A.x)[src];
+      }
     }
-    const int q = __float2int_rn(v * (amax > 0.f ? 32767.f / amax : 0.f));
-    const int qn = __shfl_down_sync(0xffffffffu, q, 1);
-    if ((lane & 1) == 0) xq[i >> 1] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
-    if ((lane & (GW - 1)) == 0) {
-      xscale[i / GW] = amax * (1.f / 32767.f);
-      if (HAS_OFFSET) xg[i / GW] = sum;
+#pragma unroll
+    for (int u = 0; u < XB; ++u) {
+      const int i = base + u * nthr + threadIdx.x;
+      if (i < ncol * TW) {   // whole warps take this branch together: sizes are multiples of 32
+        float amax = fabsf(v[u]), sum = v[u];
+#pragma unroll
+        for (int o = 1; o < GW; o <<= 1) {
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          if (HAS_OFFSET) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        const int q = __float2int_rn(v[u] * (amax > 0.f ? 32767.f / amax : 0.f));
+        const int qn = __shfl_down_sync(0xffffffffu, q, 1);
+        if ((lane & 1) == 0) xq[i >> 1] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
+        if ((lane & (GW - 1)) == 0) {
+          xscale[i / GW] = amax * (1.f / 32767.f);
+          if (HAS_OFFSET) xg[i / GW] = sum;
+        }
+      }
     }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
   const uint8_t* tab_lane = smem + ((lane & ((1 << LOG_R) - 1)) << 2);
   const size_t side_row = static_cast<size_t>(M.K / 256) * SB;
+  // side bytes of a unit's two rows: fetched one unit ahead (they come from DRAM in small strided pieces)
+  auto side_ptrs = [&](int k, const uint8_t*& pa, const uint8_t*& pb, int& seg) {
+    int tr, j;
+    coords(bi + k * nb_set, tr, j, seg);
+    const size_t col = static_cast<size_t>(set + A.nsets * j) * (TW / 256) * SB;
+    pa = M.side + static_cast<size_t>(tr * kTileRows + lane) * side_row + col;
+    pb = pa + 32 * side_row;
+  };
+  UnitSide<FMT, NQ> side_a, side_b, next_a, next_b;
+  if (warp < nmine) {
+    const uint8_t *pa, *pb;
+    int sg;
+    side_ptrs(warp, pa, pb, sg);
+    side_a.load(pa, sg * NQ);
+    side_b.load(pb, sg * NQ);
+  }
 #pragma unroll 1
   for (int k = warp; k < nmine; k += A.warps) {
     int tr, j, seg;
     coords(bi + k * nb_set, tr, j, seg);
     const int tc = set + A.nsets * j;
     const int na = tr * kTileRows + lane, nb = na + 32;
-    const uint8_t* sa = M.side + na * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
-    const uint8_t* sb_ = M.side + nb * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
-    UnitSide<FMT, NQ> side_a, side_b;
-    side_a.load(sa, seg * NQ);
-    side_b.load(sb_, seg * NQ);
+    if (k + A.warps < nmine) {
+      const uint8_t *pa, *pb;
+      int sg;
+      side_ptrs(k + A.warps, pa, pb, sg);
+      next_a.load(pa, sg * NQ);
+      next_b.load(pb, sg * NQ);
+    }
     const uint32_t* xt = xq + static_cast<size_t>(j) * (TW / 2) + seg * (TW / SPLIT / 2);
     const float* xst = xscale + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
     const float* xgt = xg + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
@@ -361,6 +394,8 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     float* prow = A.partials + static_cast<size_t>(tc * SPLIT + seg) * M.N;
     prow[na] = tot_a;
     prow[nb] = tot_b;
+    side_a = next_a;
+    side_b = next_b;
   }
 }
 

@@ -291,13 +291,22 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 #include "lw_gemv1.cuh"
 namespace lw {
 
-__global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int KT) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= m * N) return;
-  const int j = i / N, n = i - j * N;
+// Y[j, n] = sum over the `terms` partial rows of P[term, j, n], in a fixed order (no atomics: results do not depend on
+// scheduling).  Four threads share one output: thread q adds terms q, q + 4, ... and the four sums are then combined
+// in lane order, so there are enough threads in flight to cover the loads' latency.
+__global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int terms) {
+  const int i = blockIdx.x * (blockDim.x / 4) + (threadIdx.x >> 2), q = threadIdx.x & 3;
   float a = 0.f;
-  for (int tc = 0; tc < KT; ++tc) a += P[(static_cast<size_t>(tc) * m + j) * N + n];
-  Y[static_cast<size_t>(j) * ldy + n] = a;
+  if (i < m * N) {
+    const int j = i / N, n = i - j * N;
+    for (int t = q; t < terms; t += 4) a += P[(static_cast<size_t>(t) * m + j) * N + n];
+  }
+  a += __shfl_xor_sync(0xffffffffu, a, 1);
+  a += __shfl_xor_sync(0xffffffffu, a, 2);
+  if (q == 0 && i < m * N) {
+    const int j = i / N, n = i - j * N;
+    Y[static_cast<size_t>(j) * ldy + n] = a;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------ launchers
@@ -432,10 +441,13 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
   p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
   p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
-  p.buf_words = (M.max_unit_words + kSlackWords + 31u) & ~31u;
-  const size_t fixed = kReplicatedTableBytes +
-                       static_cast<size_t>(p.cols_per_set) * (TW / 2 + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
+  // a chain reader looks up to three words past its chain; for all buffers but the last that lands in the next buffer
+  // (harmless: those bits are never used), so only the end of the ring needs slack
+  p.buf_words = (M.max_unit_words + 31u) & ~31u;
+  const size_t fixed0 = kReplicatedTableBytes +
+                        static_cast<size_t>(p.cols_per_set) * (TW / 2 + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
                        2 * kGemv1MaxSlots * 8 + kGemv1MaxUnits * sizeof(UnitMeta);
+  const size_t fixed = fixed0 + kSlackWords * 4;
   if (fixed + static_cast<size_t>(p.buf_words) * 4 > kSmemLimit) return false;
   const int units = (M.N / kTileRows) * M.KT * SPLIT;
   p.blocks = std::max(p.nsets, std::min(sm_count(), units));
@@ -444,7 +456,7 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   p.slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));
   p.warps = std::max(1, std::min(kGemv1MaxWarps, p.slots * 3 / 4));
   if (const char* e = getenv("LW_GEMV1_WARPS")) p.warps = std::max(1, std::min(std::min(kGemv1MaxWarps, p.slots), atoi(e)));
-  p.producers = 2;
+  p.producers = 3;
   p.prefetch = 0;
   if (const char* e = getenv("LW_GEMV1_PRODUCERS")) p.producers = std::max(1, std::min(4, atoi(e)));
   if (const char* e = getenv("LW_GEMV1_PREFETCH")) p.prefetch = std::max(0, atoi(e));
@@ -530,7 +542,7 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
                    : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
   }
   if (rc) return rc;
-  k_sum_partials<<<(m * M.N + 255) / 256, 256, 0, st>>>(partials, Y, m, M.N, ldy, terms);
+  k_sum_partials<<<(m * M.N + 63) / 64, 256, 0, st>>>(partials, Y, m, M.N, ldy, terms);
   return check_launch("k_sum_partials");
 }
 

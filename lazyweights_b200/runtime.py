@@ -24,6 +24,7 @@ class _Handle:
             raise nat.LwError(nat.lib().lw_last_status() or -1, nat.last_error())
         self._h = C.c_void_p(ptr)
         self._ids = {}
+        self._info = {}
 
     # ---- lifetime
     def close(self):
@@ -53,12 +54,15 @@ class _Handle:
         return self._ids[name]
 
     def info(self, name):
+        if name in self._info:
+            return self._info[name]
         n, k, fmt = C.c_int(), C.c_int(), C.c_int()
         bb, sb, db = C.c_longlong(), C.c_longlong(), C.c_longlong()
         nat.check(nat.lib().lw_matrix_info(self._h, self.matrix_id(name), C.byref(n), C.byref(k), C.byref(fmt),
                                            C.byref(bb), C.byref(sb), C.byref(db)))
-        return dict(N=n.value, K=k.value, fmt=nat.FMT_NAME[fmt.value], blob_bytes=bb.value, side_bytes=sb.value,
-                    device_bytes=db.value, paired=fmt.value in (1, 4))
+        self._info[name] = dict(N=n.value, K=k.value, fmt=nat.FMT_NAME[fmt.value], blob_bytes=bb.value,
+                                side_bytes=sb.value, device_bytes=db.value, paired=fmt.value in (1, 4))
+        return self._info[name]
 
     # ---- device-pointer path
     def linear(self, name, x, out=None):
