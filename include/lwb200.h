@@ -86,6 +86,23 @@ int lw_matrix_info(void* handle, int id, int* N, int* K, int* fmt, long long* bl
  * the reference's internal matmul(), kernels/llmrt.cu:1794-1826. */
 int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
 
+/* The same product as lw_linear for callers that must not allocate device memory while they run: code that executes
+ * inside a region where the allocator is off limits (a latency-critical serving loop that has already handed all of
+ * its memory budget out, a plug-in running under a host framework that owns the device heap, a handle that was opened
+ * by someone else and must not grow).  lw_linear draws its split-K scratch from the handle, which rt_open /
+ * lw_matrix_create allocated; this entry point uses a fixed 16 MiB scratch array that is part of the library image
+ * instead, so nothing is allocated or freed here, by this library or by any library it calls.
+ *   - Limit: (K / tile width) x max(m, column segments) x N <= 4,194,304 partial sums and m <= 8; larger products are
+ *     refused with LW_ERR_TOO_LARGE and a message (use lw_linear for those).
+ *   - The first call on a device looks the array's device address up (once per device, with that device current); make
+ *     that first call before any stream capture begins.
+ *   - All calls share the one array and it keeps whatever the previous call left.  Nothing needs clearing (a call
+ *     overwrites every partial sum it later reads), but two calls whose kernels overlap on the GPU - different streams,
+ *     or different handles on one device - race on it: serialise them on one stream.
+ *   - The 16 MiB stay resident on every GPU that loads the library, until the process ends.
+ * No counterpart in the reference (its runtime always allocates through cudaMalloc in rt_open / rt_test_matmul). */
+int lw_linear_static(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
+
 /* Decoded and dequantised weights as fp16 [N, K] on the device: float32 block arithmetic (scale * f(q) - offset,
  * each operation rounded) rounded once to fp16. */
 int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream);

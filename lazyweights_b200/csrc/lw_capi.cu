@@ -165,6 +165,11 @@ static Matrix* matrix_by_id(void* h, int id) {
   return &M->mats[id];
 }
 
+const MatDev* matrix_descriptor(void* handle, int id) {
+  Matrix* mx = matrix_by_id(handle, id);
+  return mx ? &mx->dev : nullptr;
+}
+
 static int matrix_id(Model* M, const char* name) {
   if (!M || !name) return -1;
   auto it = M->by_name.find(name);

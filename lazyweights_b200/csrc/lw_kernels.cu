@@ -14,6 +14,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 #include "lw_device.cuh"
 
@@ -545,6 +546,69 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
   k_sum_partials<<<(m * M.N + 63) / 64, 256, 0, st>>>(partials, Y, m, M.N, ldy, terms);
   return check_launch("k_sum_partials");
 }
+
+// ---------------------------------------------------------------------------------- product without any allocation
+//
+// Scratch for the split-K partial sums of lw_linear_static, built into the library image: every GPU that loads the
+// library holds these 16 MiB until the process exits.  In host code `g_static_partials` is only a handle for the
+// runtime; the device address is looked up once per device with cudaGetSymbolAddress and passed to the kernels.
+constexpr size_t kStaticPartialFloats = size_t(4) << 20;
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+
+static int static_partials(float** out) {
+  static std::mutex mu;
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda("cudaGetDevice");
+  if (dev < 0 || dev >= 64) {
+    set_kernel_error_text("lw_linear_static", "device index out of range");
+    return kErrArg;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev]) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      set_kernel_error_text("cudaGetSymbolAddress(static scratch)", cudaGetErrorString(e));
+      return kErrCuda;
+    }
+    per_device[dev] = p;
+  }
+  *out = per_device[dev];
+  return kOk;
+}
+
+}  // namespace lw
+
+// Declared in include/lwb200.h.  Lives in this file because the scratch array, the look-up of its device address and
+// the kernels that receive that address must share one translation unit.
+extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev,
+                                void* stream) {
+  using namespace lw;
+  const MatDev* M = matrix_descriptor(handle, id);
+  if (!M) return kErrGeneric;
+  if (!x_dev || !y_dev || m < 1 || m > 8) {
+    set_kernel_error_text("lw_linear_static", "bad argument (m must be 1..8)");
+    return kErrArg;
+  }
+  if (M->fmt == kFmtNone) {
+    set_kernel_error_text("lw_linear_static", "matrix has no block format");
+    return kErrArg;
+  }
+  if (gemv_partial_floats(*M, m) > kStaticPartialFloats) {
+    set_kernel_error_text("lw_linear_static",
+                          "this product needs more partial sums than the built-in scratch holds "
+                          "(tile columns x max(m, segments) x N must be <= 4194304); use lw_linear");
+    return kErrTooLarge;
+  }
+  float* scratch = nullptr;
+  const int rc = static_partials(&scratch);
+  if (rc) return rc;
+  return launch_gemv(*M, x_dev, x_is_half != 0, m, y_dev, M->N, scratch, static_cast<cudaStream_t>(stream));
+}
+
+namespace lw {
 
 int read_kernel_error(unsigned int* value, bool clear) {
   unsigned int v = 0;

@@ -39,6 +39,8 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
 int read_kernel_error(unsigned int* value, bool clear);
 
 void set_kernel_error_text(const char* what, const char* detail);
+// Device descriptor of matrix `id` of a handle (implemented next to the handle type), or null.
+const MatDev* matrix_descriptor(void* handle, int id);
 // Kernels launched by this library since it was loaded.
 long long launch_count();
 

@@ -81,6 +81,22 @@ class _Handle:
                                       int(x2.dtype == torch.float16), m, C.c_void_p(y.data_ptr()), C.c_void_p(st)))
         return y[0] if squeeze and out is None else y
 
+    def linear_static(self, name, x, out):
+        """lw_linear_static: the same product with the library's built-in scratch; `out` must be preallocated
+        (fp32 [m, N], CUDA) so that the call itself allocates nothing."""
+        torch = _torch()
+        inf = self.info(name)
+        x2 = x.reshape(1, -1) if x.dim() == 1 else x
+        if not (x2.is_cuda and x2.is_contiguous() and x2.dtype in (torch.float16, torch.float32)):
+            raise ValueError("linear_static wants a contiguous CUDA fp16/fp32 tensor")
+        if x2.shape[1] != inf["K"] or tuple(out.shape) != (x2.shape[0], inf["N"]) or out.dtype != torch.float32:
+            raise ValueError("shape or dtype mismatch")
+        st = torch.cuda.current_stream(x2.device).cuda_stream
+        nat.check(nat.lib().lw_linear_static(self._h, self.matrix_id(name), C.c_void_p(x2.data_ptr()),
+                                             int(x2.dtype == torch.float16), x2.shape[0], C.c_void_p(out.data_ptr()),
+                                             C.c_void_p(st)))
+        return out
+
     def decode_weights(self, name):
         """fp16 CUDA tensor [N, K] of the dequantised weights."""
         torch = _torch()
