@@ -71,6 +71,30 @@ double rt_cpu_decode_all(void* handle, int threads, long long* symbols);
  * Replaces rt_stat, kernels/llmrt.cu:2276. */
 double rt_stat(void* handle, const char* key);
 
+/* ---- decoder runtime (bundles whose cfg describes a model: n_layers, hidden, n_heads, ...) ------------------- */
+
+/* Runs n tokens at the current position through the decoder (chunks of max_batch): embedding, per layer RMSNorm,
+ * coded qkv / o / gate / up / down products, rotate-half RoPE, fp16 KV cache, causal grouped-query attention, SwiGLU;
+ * final norm and lm_head.  logits (host): n x vocab if all_logits, else vocab values of the last token; may be NULL.
+ * Returns 0, -1 on context overflow, or a negative status.  Replaces rt_forward, kernels/llmrt.cu:2291. */
+int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logits);
+
+/* Position bookkeeping.  Replace rt_reset, rt_set_window, rt_set_pos, rt_pos, rt_vocab, kernels/llmrt.cu:2269-2274:
+ * rt_set_pos only rewinds (the KV cache below the new position is kept); rt_set_window sets a sliding attention
+ * window (0 = none). */
+void rt_reset(void* handle);
+void rt_set_window(void* handle, int w);
+void rt_set_pos(void* handle, int p);
+int rt_pos(void* handle);
+int rt_vocab(void* handle);
+
+/* Tensor parallelism over NCCL (additions; the reference is single-GPU).  Every rank opens its own shard bundle (cfg
+ * tp_world / tp_rank; n_heads, n_kv_heads, inter and vocab are the shard's sizes), rank 0 obtains an id with
+ * lw_tp_unique_id, all ranks call rt_tp_init with it.  rt_forward then all-reduces the partial outputs of `o` and
+ * `down` and gathers the logits slices into the full vocabulary. */
+int lw_tp_unique_id(uint8_t* out128);
+int rt_tp_init(void* handle, int rank, int world, const uint8_t* id128);
+
 /* ---- per-matrix entry points on device pointers (additions) ---------------------------------------------- */
 
 /* Index of a matrix in the handle (>= 0) or -1.  The *_id variants below skip the name lookup. */

@@ -24,6 +24,14 @@ _SIGNATURES = {
     "rt_gpu_decode_all": (C.c_double, [C.c_void_p, C.c_int]),
     "rt_cpu_decode_all": (C.c_double, [C.c_void_p, C.c_int, C.POINTER(C.c_longlong)]),
     "rt_stat": (C.c_double, [C.c_void_p, C.c_char_p]),
+    "rt_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
+    "rt_reset": (None, [C.c_void_p]),
+    "rt_set_window": (None, [C.c_void_p, C.c_int]),
+    "rt_set_pos": (None, [C.c_void_p, C.c_int]),
+    "rt_pos": (C.c_int, [C.c_void_p]),
+    "rt_vocab": (C.c_int, [C.c_void_p]),
+    "lw_tp_unique_id": (C.c_int, [C.c_void_p]),
+    "rt_tp_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "lw_matrix_id": (C.c_int, [C.c_void_p, C.c_char_p]),
     "lw_matrix_info": (C.c_int, [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 3 + [C.POINTER(C.c_longlong)] * 3),
     "lw_linear": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

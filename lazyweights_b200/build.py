@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblwb200.so")
-SOURCES = ["lw_host.cpp", "lw_kernels.cu", "lw_capi.cu"]
+SOURCES = ["lw_host.cpp", "lw_kernels.cu", "lw_capi.cu", "lw_runtime.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC,-O3,-Wall,-pthread", "-Xptxas", "-v"]
 
@@ -54,7 +54,7 @@ def build(force=False, verbose=False):
         if verbose:
             sys.stderr.write(r.stderr)
         objs.append(obj)
-    r = subprocess.run([nvcc, "-shared", "-o", LIB] + objs + ["-lcudart", "-lpthread"], capture_output=True, text=True)
+    r = subprocess.run([nvcc, "-shared", "-o", LIB] + objs + ["-lcudart", "-lpthread", "-ldl"], capture_output=True, text=True)
     if r.returncode:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link failed")

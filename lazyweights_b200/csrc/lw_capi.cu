@@ -14,46 +14,13 @@
 #include "../../include/lwb200.h"
 #include "lw_host.h"
 #include "lw_kernels.h"
+#include "lw_model.h"
 
 namespace lw {
 
 void set_kernel_error_text(const char* what, const char* detail) { set_error("%s: %s", what, detail); }
 
-struct Matrix {
-  std::string name;
-  int N = 0, K = 0, Ks = 0, fmt = kFmtNone;
-  bool paired = false;
-  long long blob_bytes = 0, side_bytes = 0, file_offset = -1;
-  size_t device_bytes = 0;
-  void* d_block = nullptr;   // one allocation: table, group bases, words, side bytes
-  MatDev dev{};
-};
-
-struct Model {
-  std::string dir;
-  Manifest man;
-  int fd = -1;
-  int device = 0;
-  bool verbose = false;
-  std::vector<Matrix> mats;
-  std::map<std::string, int> by_name;
-  float* d_partials = nullptr;   // split-K partial sums, sized for the largest matrix at m = 8
-  size_t partial_floats = 0;
-  float *d_x = nullptr, *d_y = nullptr;   // staging of rt_test_matmul's host buffers (grown on demand, kept)
-  size_t x_floats = 0, y_floats = 0;
-  size_t resident_bytes = 0;
-  long long coded_bytes = 0, side_bytes = 0;
-  ~Model() {
-    for (auto& m : mats)
-      if (m.d_block) cudaFree(m.d_block);
-    if (d_partials) cudaFree(d_partials);
-    if (d_x) cudaFree(d_x);
-    if (d_y) cudaFree(d_y);
-    if (fd >= 0) close(fd);
-  }
-};
-
-static int cuda_fail(const char* what, cudaError_t e) {
+int cuda_fail(const char* what, cudaError_t e) {
   set_error("%s: %s", what, cudaGetErrorString(e));
   return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? kErrNoDevice : kErrCuda;
 }
@@ -180,7 +147,7 @@ static int matrix_id(Model* M, const char* name) {
   return it->second;
 }
 
-static int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy,
+int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy,
                          cudaStream_t st) {
   if (mx.fmt == kFmtNone) {
     set_error("%s has no side tensor: products need a block format", mx.name.c_str());
@@ -214,7 +181,11 @@ int lw_kernel_error(void) {
 
 long long lw_launch_count(void) { return launch_count(); }
 
-void rt_close(void* handle) { delete static_cast<Model*>(handle); }
+void rt_close(void* handle) {
+  Model* M = static_cast<Model*>(handle);
+  if (M) runtime_free(M);
+  delete M;
+}
 
 void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, int floor_mb, int verbose) {
   (void)max_ctx; (void)max_batch; (void)budget_mb; (void)floor_mb;
@@ -281,6 +252,8 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
     fprintf(stderr, "[lwb200] %s: %zu coded matrices, %.1f MB coded + %.1f MB side, %.1f MB on device, load %.2f s\n",
             dir, M->mats.size(), M->coded_bytes / 1e6, M->side_bytes / 1e6, M->resident_bytes / 1e6, s);
   }
+  // a bundle with model configuration also gets the decoder runtime (activations, KV cache, norms, rotary tables)
+  if (M->man.cfg.count("n_layers") && note_status(runtime_init(M.get(), max_ctx, max_batch))) return nullptr;
   return M.release();
 }
 

@@ -1,0 +1,59 @@
+// The handle type behind the C ABI: a bundle's coded matrices on one GPU and, when the bundle carries a model
+// configuration, the decoder runtime state (lw_runtime.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "lw_host.h"
+#include "lw_kernels.h"
+
+namespace lw {
+
+struct Matrix {
+  std::string name;
+  int N = 0, K = 0, Ks = 0, fmt = kFmtNone;
+  bool paired = false;
+  long long blob_bytes = 0, side_bytes = 0, file_offset = -1;
+  size_t device_bytes = 0;
+  void* d_block = nullptr;   // one allocation: table, group bases, words, side bytes
+  MatDev dev{};
+};
+
+struct Runtime;   // decoder state, defined in lw_runtime.cu
+
+struct Model {
+  std::string dir;
+  Manifest man;
+  int fd = -1;
+  int device = 0;
+  bool verbose = false;
+  std::vector<Matrix> mats;
+  std::map<std::string, int> by_name;
+  float* d_partials = nullptr;   // split-K partial sums, sized for the largest matrix at m = 8
+  size_t partial_floats = 0;
+  float *d_x = nullptr, *d_y = nullptr;   // staging of rt_test_matmul's host buffers (grown on demand, kept)
+  size_t x_floats = 0, y_floats = 0;
+  size_t resident_bytes = 0;
+  long long coded_bytes = 0, side_bytes = 0;
+  Runtime* rt = nullptr;
+  ~Model() {
+    for (auto& m : mats)
+      if (m.d_block) cudaFree(m.d_block);
+    if (d_partials) cudaFree(d_partials);
+    if (d_x) cudaFree(d_x);
+    if (d_y) cudaFree(d_y);
+    if (fd >= 0) close(fd);
+  }
+};
+
+int cuda_fail(const char* what, cudaError_t e);
+int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st);
+int runtime_init(Model* M, int max_ctx, int max_batch);
+void runtime_free(Model* M);
+
+}  // namespace lw

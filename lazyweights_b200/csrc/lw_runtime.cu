@@ -1,0 +1,525 @@
+// Decoder runtime around the coded matrices (the "next" rows of the path: what rt_forward needs).
+//
+// Mirrors the token step of the reference runtime (kernels/llmrt.cu:2291-2436): embedding gather, RMSNorm with the
+// residual add folded in (:1288-1301), rotate-half RoPE + fp16 KV-cache write (:1305-1332), causal grouped-query
+// attention with per-query arithmetic that does not depend on the number of tokens in the pass (:1336-1498), SwiGLU
+// (:1500-1505), coded matrices through the fused decode + product kernels.  Activations fp32, KV cache fp16
+// [layer][kv head][position][head dim].  Tensor parallelism: a rank opens ITS shard of the model as a bundle whose
+// cfg carries the local head / FFN / vocabulary sizes; partial outputs of `o` and `down` are summed with NCCL
+// all-reduce and the logits are gathered (rt_tp_init).
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <sstream>
+
+#include "../../include/lwb200.h"
+#include "lw_model.h"
+
+namespace lw {
+
+// ------------------------------------------------------------------------------------------------ NCCL by dlopen
+// The process (PyTorch) already carries an NCCL; binding it at run time avoids a second copy at link time.
+struct Nccl {
+  void* lib = nullptr;
+  int (*GetUniqueId)(void*) = nullptr;
+  int (*CommInitRank)(void**, int, const void*, int) = nullptr;   // ncclUniqueId is passed by value: see init()
+  int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  int (*CommDestroy)(void*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  void* init_rank_sym = nullptr;
+  bool load() {
+    if (lib) return true;
+    for (const char* n : {"libnccl.so.2", "libnccl.so"}) {
+      lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      if (lib) break;
+    }
+    if (!lib) return false;
+    GetUniqueId = reinterpret_cast<int (*)(void*)>(dlsym(lib, "ncclGetUniqueId"));
+    init_rank_sym = dlsym(lib, "ncclCommInitRank");
+    AllReduce = reinterpret_cast<decltype(AllReduce)>(dlsym(lib, "ncclAllReduce"));
+    AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(lib, "ncclAllGather"));
+    CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+    GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+    return GetUniqueId && init_rank_sym && AllReduce && AllGather && CommDestroy;
+  }
+};
+static Nccl g_nccl;
+struct UniqueId { char bytes[128]; };
+constexpr int kNcclFloat = 7, kNcclSum = 0;
+
+struct Runtime {
+  int L = 0, D = 0, H = 0, Hk = 0, Dh = 0, I = 0, V = 0;   // heads, FFN width and vocabulary are the LOCAL sizes
+  int Tmax = 0, max_batch = 0, pos = 0, window = 0;
+  int tp_rank = 0, tp_world = 1;
+  float eps = 1e-5f, attn_scale = 1.f;
+  void* comm = nullptr;
+  float *h = nullptr, *xn = nullptr, *att = nullptr, *o = nullptr, *qkv = nullptr, *g = nullptr, *u = nullptr;
+  float *logits = nullptr, *logits_all = nullptr, *cosv = nullptr, *sinv = nullptr, *lnf = nullptr;
+  int* ids = nullptr;
+  __half *kc = nullptr, *vc = nullptr, *embed16 = nullptr;
+  uint8_t* embed8 = nullptr;
+  float *embed_rs = nullptr, *embed_rsub = nullptr;
+  int embed_groups = 0;
+  std::vector<float*> ln1, ln2;
+  std::vector<int> m_qkv, m_q, m_k, m_v, m_o, m_gate, m_up, m_down;
+  int m_head = -1;
+  std::vector<void*> owned;   // device allocations to free
+  std::vector<int> eos;
+};
+
+// ----------------------------------------------------------------------------------------------------- kernels
+
+__global__ void k_embed16(const int* __restrict__ ids, const __half* __restrict__ E, float* __restrict__ h, int D) {
+  const __half* row = E + static_cast<size_t>(ids[blockIdx.x]) * D;
+  for (int k = threadIdx.x; k < D; k += blockDim.x) h[static_cast<size_t>(blockIdx.x) * D + k] = __half2float(row[k]);
+}
+
+// raw8 embedding with per-group scale / offset, rounded to fp16 like the reference's gather (kernels/llmrt.cu:1261-1274)
+__global__ void k_embed8(const int* __restrict__ ids, const uint8_t* __restrict__ E, const float* __restrict__ rs,
+                         const float* __restrict__ rsub, float* __restrict__ h, int D, int G) {
+  const int id = ids[blockIdx.x], sub = D / G;
+  for (int k = threadIdx.x; k < D; k += blockDim.x) {
+    const float v = (static_cast<float>(E[static_cast<size_t>(id) * D + k]) - rsub[static_cast<size_t>(id) * G + k / sub]) *
+                    rs[static_cast<size_t>(id) * G + k / sub];
+    h[static_cast<size_t>(blockIdx.x) * D + k] = __half2float(__float2half_rn(v));
+  }
+}
+
+// h += res (if res), out = h * rsqrt(mean(h^2) + eps) * g.  One block per token.
+__global__ void k_rmsnorm(float* __restrict__ h, const float* __restrict__ res, const float* __restrict__ g,
+                          float* __restrict__ out, int D, float eps) {
+  __shared__ float red[32];
+  float* hr = h + static_cast<size_t>(blockIdx.x) * D;
+  const float* rr = res ? res + static_cast<size_t>(blockIdx.x) * D : nullptr;
+  float ss = 0.f;
+  for (int k = threadIdx.x; k < D; k += blockDim.x) {
+    float v = hr[k];
+    if (rr) {
+      v += rr[k];
+      hr[k] = v;
+    }
+    ss += v * v;
+  }
+  for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) red[0] = rsqrtf(v / D + eps);
+  }
+  __syncthreads();
+  const float r = red[0];
+  for (int k = threadIdx.x; k < D; k += blockDim.x) out[static_cast<size_t>(blockIdx.x) * D + k] = hr[k] * r * g[k];
+}
+
+// rotate-half RoPE on q (in place) and k (into the cache), v into the cache.  grid (heads + 2 kv heads, tokens).
+__global__ void k_rope_cache(float* __restrict__ qkv, const float* __restrict__ cosv, const float* __restrict__ sinv,
+                             __half* __restrict__ kc, __half* __restrict__ vc, int pos0, int H, int Hk, int Dh, int Tmax) {
+  const int head = blockIdx.x, j = blockIdx.y, p = pos0 + j, half = Dh / 2;
+  float* row = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head) * Dh;
+  if (head < H + Hk) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float c = cosv[static_cast<size_t>(p) * half + i], s = sinv[static_cast<size_t>(p) * half + i];
+      const float a = row[i], b = row[i + half];
+      const float ra = a * c - b * s, rb = b * c + a * s;
+      if (head < H) {
+        row[i] = ra;
+        row[i + half] = rb;
+      } else {
+        __half* dst = kc + (static_cast<size_t>(head - H) * Tmax + p) * Dh;
+        dst[i] = __float2half_rn(ra);
+        dst[i + half] = __float2half_rn(rb);
+      }
+    }
+  } else {
+    __half* dst = vc + (static_cast<size_t>(head - H - Hk) * Tmax + p) * Dh;
+    for (int i = threadIdx.x; i < Dh; i += blockDim.x) dst[i] = __float2half_rn(row[i]);
+  }
+}
+
+// Causal attention of query head blockIdx.x, token blockIdx.y over positions lo .. pos0 + j.  Scores in dynamic
+// shared memory; one warp per position for the dot products, one thread per output dimension for the weighted sum.
+__global__ void k_attn(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
+                       float* __restrict__ att, int pos0, int H, int Hk, int Dh, int Tmax, float scale, int window) {
+  extern __shared__ float sc[];
+  __shared__ float red[33];
+  const int head = blockIdx.x, j = blockIdx.y, kh = head / (H / Hk), last = pos0 + j;
+  const int lo = window > 0 ? max(0, last - window + 1) : 0, n = last - lo + 1;
+  const float* q = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head) * Dh;
+  const __half* K = kc + static_cast<size_t>(kh) * Tmax * Dh;
+  const __half* Vv = vc + static_cast<size_t>(kh) * Tmax * Dh;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float mx = -INFINITY;
+  for (int t = warp; t < n; t += nw) {
+    const __half* kr = K + static_cast<size_t>(lo + t) * Dh;
+    float a = 0.f;
+    for (int i = lane; i < Dh; i += 32) a += q[i] * __half2float(kr[i]);
+    for (int o = 16; o; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    a *= scale;
+    if (lane == 0) sc[t] = a;
+    mx = fmaxf(mx, a);
+  }
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m2 = -INFINITY;
+    for (int w = 0; w < nw; ++w) m2 = fmaxf(m2, red[w]);
+    red[32] = m2;
+  }
+  __syncthreads();
+  mx = red[32];
+  float sum = 0.f;
+  for (int t = threadIdx.x; t < n; t += blockDim.x) {
+    const float e = __expf(sc[t] - mx);
+    sc[t] = e;
+    sum += e;
+  }
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s2 = 0.f;
+    for (int w = 0; w < nw; ++w) s2 += red[w];
+    red[32] = 1.f / s2;
+  }
+  __syncthreads();
+  const float inv = red[32];
+  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+    float a = 0.f;
+    for (int t = 0; t < n; ++t) a += sc[t] * __half2float(Vv[static_cast<size_t>(lo + t) * Dh + d]);
+    att[static_cast<size_t>(j) * H * Dh + static_cast<size_t>(head) * Dh + d] = a * inv;
+  }
+}
+
+__global__ void k_silu_mul(float* __restrict__ g, const float* __restrict__ u, size_t n) {
+  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i < n) {
+    const float v = g[i];
+    g[i] = v / (1.f + __expf(-v)) * u[i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------- host side
+
+static int cfg_int(const Model* M, const char* k, int def) {
+  auto it = M->man.cfg.find(k);
+  return it == M->man.cfg.end() ? def : atoi(it->second.c_str());
+}
+static double cfg_f(const Model* M, const char* k, double def) {
+  auto it = M->man.cfg.find(k);
+  return it == M->man.cfg.end() ? def : atof(it->second.c_str());
+}
+
+template <class T>
+static int dalloc(Runtime* R, T** p, size_t count) {
+  const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(p), std::max<size_t>(count, 1) * sizeof(T));
+  if (e != cudaSuccess) return cuda_fail("cudaMalloc (runtime)", e);
+  R->owned.push_back(*p);
+  return kOk;
+}
+
+// an uncoded tensor of the bundle -> device memory (f32 / f16 / raw8 as stored)
+static int upload(Model* M, Runtime* R, const char* name, const char* enc, size_t elem, void** out, const TensorEntry** te) {
+  const TensorEntry* t = M->man.find(name);
+  if (!t || t->enc != enc) {
+    set_error("bundle has no %s tensor %s", enc, name);
+    return kErrFormat;
+  }
+  if (static_cast<size_t>(t->nbytes) != static_cast<size_t>(t->N) * t->K * elem) {
+    set_error("tensor %s: %lld bytes do not match its shape", name, t->nbytes);
+    return kErrFormat;
+  }
+  std::vector<uint8_t> host;
+  int rc = read_blob(M->fd, *t, host);
+  if (rc) return rc;
+  uint8_t* d = nullptr;
+  if ((rc = dalloc(R, &d, static_cast<size_t>(t->nbytes)))) return rc;
+  const cudaError_t e = cudaMemcpy(d, host.data(), t->nbytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return cuda_fail("cudaMemcpy (runtime tensor)", e);
+  *out = d;
+  if (te) *te = t;
+  return kOk;
+}
+
+static int find_matrix(Model* M, const std::string& n) {
+  auto it = M->by_name.find(n);
+  return it == M->by_name.end() ? -1 : it->second;
+}
+
+int runtime_init(Model* M, int max_ctx, int max_batch) {
+  auto R = new Runtime();
+  M->rt = R;
+  R->L = cfg_int(M, "n_layers", 0);
+  R->D = cfg_int(M, "hidden", 0);
+  R->H = cfg_int(M, "n_heads", 0);
+  R->Hk = cfg_int(M, "n_kv_heads", R->H);
+  R->Dh = cfg_int(M, "head_dim", R->H ? R->D / R->H : 0);
+  R->I = cfg_int(M, "inter", 0);
+  R->V = cfg_int(M, "vocab", 0);
+  R->eps = static_cast<float>(cfg_f(M, "eps", 1e-5));
+  R->attn_scale = static_cast<float>(cfg_f(M, "attn_scale", R->Dh ? 1.0 / std::sqrt(static_cast<double>(R->Dh)) : 1.0));
+  const int rope_rows = cfg_int(M, "rope_rows", 4096);
+  R->Tmax = std::max(1, std::min(max_ctx > 0 ? max_ctx : rope_rows, rope_rows));
+  R->max_batch = std::max(1, max_batch);
+  R->tp_world = cfg_int(M, "tp_world", 1);
+  R->tp_rank = cfg_int(M, "tp_rank", 0);
+  {
+    auto it = M->man.cfg.find("eos");
+    std::stringstream es(it == M->man.cfg.end() ? "" : it->second);
+    std::string x;
+    while (std::getline(es, x, ',')) R->eos.push_back(atoi(x.c_str()));
+  }
+  if (R->L <= 0 || R->D <= 0 || R->H <= 0 || R->Hk <= 0 || R->Dh <= 0 || R->I <= 0 || R->V <= 0 || R->H % R->Hk ||
+      R->Dh % 2 || R->Dh > 256) {
+    set_error("bundle cfg: bad model shape");
+    return kErrFormat;
+  }
+  int rc;
+  const size_t B = R->max_batch, QKV = static_cast<size_t>(R->H + 2 * R->Hk) * R->Dh;
+  if ((rc = dalloc(R, &R->h, B * R->D)) || (rc = dalloc(R, &R->xn, B * R->D)) ||
+      (rc = dalloc(R, &R->att, B * R->H * R->Dh)) || (rc = dalloc(R, &R->o, B * R->D)) ||
+      (rc = dalloc(R, &R->qkv, B * QKV)) || (rc = dalloc(R, &R->g, B * R->I)) || (rc = dalloc(R, &R->u, B * R->I)) ||
+      (rc = dalloc(R, &R->logits, B * R->V)) || (rc = dalloc(R, &R->logits_all, B * R->V * R->tp_world)) ||
+      (rc = dalloc(R, &R->ids, B)) ||
+      (rc = dalloc(R, &R->kc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)) ||
+      (rc = dalloc(R, &R->vc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)))
+    return rc;
+  const TensorEntry* te = nullptr;
+  void* p = nullptr;
+  if (M->man.find("embed") && M->man.find("embed")->enc == "f16") {
+    if ((rc = upload(M, R, "embed", "f16", 2, &p, &te))) return rc;
+    R->embed16 = static_cast<__half*>(p);
+  } else {
+    if ((rc = upload(M, R, "embed", "raw8", 1, &p, &te))) return rc;
+    R->embed8 = static_cast<uint8_t*>(p);
+    const TensorEntry* ts = nullptr;
+    if ((rc = upload(M, R, "embed.rs", "f32", 4, &p, &ts))) return rc;
+    R->embed_rs = static_cast<float*>(p);
+    R->embed_groups = ts->K;
+    if ((rc = upload(M, R, "embed.rsub", "f32", 4, &p, nullptr))) return rc;
+    R->embed_rsub = static_cast<float*>(p);
+  }
+  if (te->K != R->D) {
+    set_error("embed has %d columns, hidden is %d", te->K, R->D);
+    return kErrFormat;
+  }
+  if ((rc = upload(M, R, "cos", "f32", 4, &p, &te))) return rc;
+  R->cosv = static_cast<float*>(p);
+  if (te->K != R->Dh / 2 || te->N < R->Tmax) {
+    set_error("rotary table has the wrong shape");
+    return kErrFormat;
+  }
+  if ((rc = upload(M, R, "sin", "f32", 4, &p, nullptr))) return rc;
+  R->sinv = static_cast<float*>(p);
+  if ((rc = upload(M, R, "lnf", "f32", 4, &p, nullptr))) return rc;
+  R->lnf = static_cast<float*>(p);
+  for (int l = 0; l < R->L; ++l) {
+    const std::string pre = "l" + std::to_string(l) + ".";
+    if ((rc = upload(M, R, (pre + "ln1").c_str(), "f32", 4, &p, nullptr))) return rc;
+    R->ln1.push_back(static_cast<float*>(p));
+    if ((rc = upload(M, R, (pre + "ln2").c_str(), "f32", 4, &p, nullptr))) return rc;
+    R->ln2.push_back(static_cast<float*>(p));
+    R->m_qkv.push_back(find_matrix(M, pre + "qkv"));
+    R->m_q.push_back(find_matrix(M, pre + "q"));
+    R->m_k.push_back(find_matrix(M, pre + "k"));
+    R->m_v.push_back(find_matrix(M, pre + "v"));
+    R->m_o.push_back(find_matrix(M, pre + "o"));
+    R->m_gate.push_back(find_matrix(M, pre + "gate"));
+    R->m_up.push_back(find_matrix(M, pre + "up"));
+    R->m_down.push_back(find_matrix(M, pre + "down"));
+    const bool attn_ok = R->m_qkv[l] >= 0 || (R->m_q[l] >= 0 && R->m_k[l] >= 0 && R->m_v[l] >= 0);
+    if (!attn_ok || R->m_o[l] < 0 || R->m_gate[l] < 0 || R->m_up[l] < 0 || R->m_down[l] < 0) {
+      set_error("layer %d: a coded matrix is missing", l);
+      return kErrFormat;
+    }
+  }
+  R->m_head = find_matrix(M, "lm_head");
+  if (R->m_head < 0) {
+    set_error("bundle has no lm_head");
+    return kErrFormat;
+  }
+  return kOk;
+}
+
+void runtime_free(Model* M) {
+  Runtime* R = M->rt;
+  if (!R) return;
+  if (R->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(R->comm);
+  for (void* p : R->owned) cudaFree(p);
+  delete R;
+  M->rt = nullptr;
+}
+
+static int nccl_check(int r, const char* what) {
+  if (r == 0) return kOk;
+  set_error("%s: %s", what, g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "NCCL error");
+  return kErrCuda;
+}
+
+// One pass over m <= max_batch tokens at positions pos .. pos + m - 1.  Leaves logits of the last token (or of all).
+static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool all_logits) {
+  cudaStream_t st = nullptr;
+  cudaError_t e = cudaMemcpyAsync(R->ids, ids_host, m * sizeof(int), cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return cuda_fail("ids upload", e);
+  if (R->embed16) k_embed16<<<m, 256, 0, st>>>(R->ids, R->embed16, R->h, R->D);
+  else k_embed8<<<m, 256, 0, st>>>(R->ids, R->embed8, R->embed_rs, R->embed_rsub, R->h, R->D, R->embed_groups);
+  const size_t QKV = static_cast<size_t>(R->H + 2 * R->Hk) * R->Dh;
+  const float* pending = nullptr;   // output of the previous block, added to h by the next norm
+  int rc;
+  for (int l = 0; l < R->L; ++l) {
+    k_rmsnorm<<<m, 256, 0, st>>>(R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
+    if (R->m_qkv[l] >= 0) {
+      if ((rc = linear_device(M, M->mats[R->m_qkv[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st))) return rc;
+    } else {
+      if ((rc = linear_device(M, M->mats[R->m_q[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st)) ||
+          (rc = linear_device(M, M->mats[R->m_k[l]], R->xn, false, m, R->qkv + R->H * R->Dh, static_cast<int>(QKV), st)) ||
+          (rc = linear_device(M, M->mats[R->m_v[l]], R->xn, false, m, R->qkv + (R->H + R->Hk) * R->Dh,
+                              static_cast<int>(QKV), st)))
+        return rc;
+    }
+    __half* kc = R->kc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
+    __half* vc = R->vc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
+    k_rope_cache<<<dim3(R->H + 2 * R->Hk, m), 64, 0, st>>>(R->qkv, R->cosv, R->sinv, kc, vc, R->pos, R->H, R->Hk, R->Dh,
+                                                          R->Tmax);
+    k_attn<<<dim3(R->H, m), 128, static_cast<size_t>(R->pos + m) * sizeof(float), st>>>(
+        R->qkv, kc, vc, R->att, R->pos, R->H, R->Hk, R->Dh, R->Tmax, R->attn_scale, R->window);
+    if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
+    if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
+                                                     R->comm, st), "all-reduce (o)")))
+      return rc;
+    k_rmsnorm<<<m, 256, 0, st>>>(R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
+    if ((rc = linear_device(M, M->mats[R->m_gate[l]], R->xn, false, m, R->g, R->I, st)) ||
+        (rc = linear_device(M, M->mats[R->m_up[l]], R->xn, false, m, R->u, R->I, st)))
+      return rc;
+    const size_t ng = static_cast<size_t>(m) * R->I;
+    k_silu_mul<<<static_cast<unsigned>((ng + 255) / 256), 256, 0, st>>>(R->g, R->u, ng);
+    if ((rc = linear_device(M, M->mats[R->m_down[l]], R->g, false, m, R->o, R->D, st))) return rc;
+    if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
+                                                     R->comm, st), "all-reduce (down)")))
+      return rc;
+    pending = R->o;
+  }
+  k_rmsnorm<<<m, 256, 0, st>>>(R->h, pending, R->lnf, R->xn, R->D, R->eps);
+  const int rows = all_logits ? m : 1;
+  const float* xlast = all_logits ? R->xn : R->xn + static_cast<size_t>(m - 1) * R->D;
+  if ((rc = linear_device(M, M->mats[R->m_head], xlast, false, rows, R->logits, R->V, st))) return rc;
+  if (R->comm) {
+    // ranks hold consecutive slices of the vocabulary: gathered rank-major [world][rows][V], reordered by the caller
+    if ((rc = nccl_check(g_nccl.AllGather(R->logits, R->logits_all, static_cast<size_t>(rows) * R->V, kNcclFloat,
+                                          R->comm, st), "all-gather (logits)")))
+      return rc;
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("forward", e);
+  R->pos += m;
+  return kOk;
+}
+
+}  // namespace lw
+
+using namespace lw;
+
+extern "C" {
+
+int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logits) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt || !ids || n < 1) {
+    set_error("rt_forward: no model runtime in this handle, or bad argument");
+    return kErrArg;
+  }
+  Runtime* R = M->rt;
+  if (R->pos + n > R->Tmax) return -1;   // context overflow (the reference's -1, kernels/llmrt.cu:2293)
+  const int W = R->tp_world, Vfull = R->V * W;
+  std::vector<float> stage;
+  for (int i0 = 0; i0 < n; i0 += R->max_batch) {
+    const int m = std::min(R->max_batch, n - i0);
+    const bool last = i0 + m == n;
+    const int rc = forward_chunk(M, R, ids + i0, m, all_logits != 0);
+    if (rc) return rc;
+    if (!logits || (!all_logits && !last)) continue;
+    const int rows = all_logits ? m : 1;
+    float* dst = all_logits ? logits + static_cast<size_t>(i0) * Vfull : logits;
+    cudaError_t e;
+    if (W == 1) {
+      e = cudaMemcpy(dst, R->logits, static_cast<size_t>(rows) * R->V * 4, cudaMemcpyDeviceToHost);
+    } else {
+      stage.resize(static_cast<size_t>(W) * rows * R->V);
+      e = cudaMemcpy(stage.data(), R->logits_all, stage.size() * 4, cudaMemcpyDeviceToHost);
+      for (int r = 0; r < W && e == cudaSuccess; ++r)
+        for (int j = 0; j < rows; ++j)
+          std::memcpy(dst + static_cast<size_t>(j) * Vfull + static_cast<size_t>(r) * R->V,
+                      stage.data() + (static_cast<size_t>(r) * rows + j) * R->V, static_cast<size_t>(R->V) * 4);
+    }
+    if (e != cudaSuccess) return cuda_fail("logits copy", e);
+  }
+  if (!logits) cudaStreamSynchronize(nullptr);
+  return 0;
+}
+
+void rt_reset(void* handle) {
+  Model* M = static_cast<Model*>(handle);
+  if (M && M->rt) M->rt->pos = 0;
+}
+void rt_set_window(void* handle, int w) {
+  Model* M = static_cast<Model*>(handle);
+  if (M && M->rt) M->rt->window = std::max(0, w);
+}
+void rt_set_pos(void* handle, int p) {
+  Model* M = static_cast<Model*>(handle);
+  if (M && M->rt) M->rt->pos = std::max(0, std::min(p, M->rt->pos));
+}
+int rt_pos(void* handle) {
+  Model* M = static_cast<Model*>(handle);
+  return M && M->rt ? M->rt->pos : -1;
+}
+int rt_vocab(void* handle) {
+  Model* M = static_cast<Model*>(handle);
+  return M && M->rt ? M->rt->V * M->rt->tp_world : -1;
+}
+
+int lw_tp_unique_id(uint8_t* out128) {
+  if (!out128 || !g_nccl.load()) {
+    set_error("NCCL is not available in this process");
+    return kErrGeneric;
+  }
+  UniqueId id;
+  std::memset(&id, 0, sizeof id);
+  const int rc = nccl_check(g_nccl.GetUniqueId(&id), "ncclGetUniqueId");
+  if (rc) return rc;
+  std::memcpy(out128, id.bytes, 128);
+  return kOk;
+}
+
+int rt_tp_init(void* handle, int rank, int world, const uint8_t* id128) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt || !id128 || world < 1 || rank < 0 || rank >= world) {
+    set_error("rt_tp_init: bad argument");
+    return kErrArg;
+  }
+  Runtime* R = M->rt;
+  if (world != R->tp_world) {
+    set_error("bundle was sharded for %d ranks, not %d", R->tp_world, world);
+    return kErrArg;
+  }
+  if (world == 1) return kOk;
+  if (!g_nccl.load()) {
+    set_error("NCCL is not available in this process");
+    return kErrGeneric;
+  }
+  UniqueId id;
+  std::memcpy(id.bytes, id128, 128);
+  auto init = reinterpret_cast<int (*)(void**, int, UniqueId, int)>(g_nccl.init_rank_sym);
+  const int rc = nccl_check(init(&R->comm, world, id, rank), "ncclCommInitRank");
+  if (rc) return rc;
+  R->tp_rank = rank;
+  return kOk;
+}
+
+}  // extern "C"

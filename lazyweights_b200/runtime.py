@@ -147,6 +147,39 @@ class Bundle(_Handle):
         self.path = path
         super().__init__(nat.lib().rt_open(os.fsencode(path), max_ctx, max_batch, -1, 0, int(verbose)))
 
+    # ---- decoder runtime (bundles with a model cfg)
+    def forward(self, ids, all_logits=False):
+        """rt_forward: logits of the last token [vocab] or of every token [n, vocab] (host float32)."""
+        ids = np.ascontiguousarray(ids, np.int32).reshape(-1)
+        v = nat.lib().rt_vocab(self._h)
+        out = np.empty((ids.size, v) if all_logits else (v,), np.float32)
+        rc = nat.lib().rt_forward(self._h, ids.ctypes.data_as(C.c_void_p), ids.size, out.ctypes.data_as(C.c_void_p),
+                                  int(all_logits))
+        if rc == -1:
+            raise IndexError("context overflow")
+        nat.check(rc)
+        return out
+
+    def reset(self):
+        nat.lib().rt_reset(self._h)
+
+    def set_pos(self, p):
+        nat.lib().rt_set_pos(self._h, p)
+
+    def set_window(self, w):
+        nat.lib().rt_set_window(self._h, w)
+
+    @property
+    def pos(self):
+        return nat.lib().rt_pos(self._h)
+
+    @property
+    def vocab(self):
+        return nat.lib().rt_vocab(self._h)
+
+    def tp_init(self, rank, world, unique_id):
+        nat.check(nat.lib().rt_tp_init(self._h, rank, world, (C.c_uint8 * 128).from_buffer_copy(unique_id)))
+
     def cpu_decode(self, name, threads=0):
         inf = self.info(name)
         cols = inf["K"] // 2 if inf["paired"] else inf["K"]
@@ -165,6 +198,12 @@ class Bundle(_Handle):
         n = C.c_longlong(0)
         s = nat.lib().rt_cpu_decode_all(self._h, threads or (os.cpu_count() or 1), C.byref(n))
         return s, n.value
+
+
+def tp_unique_id():
+    buf = (C.c_uint8 * 128)()
+    nat.check(nat.lib().lw_tp_unique_id(buf))
+    return bytes(buf)
 
 
 class CodedMatrix(_Handle):

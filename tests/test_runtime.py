@@ -1,0 +1,79 @@
+"""The decoder runtime around the coded matrices (rt_forward and friends) against a float64 NumPy model built from
+the oracle's dequantised weights: same architecture as the reference runtime's token step (RMSNorm with folded
+residual, rotate-half RoPE, fp16 KV cache, grouped-query causal attention, SwiGLU)."""
+import numpy as np
+import pytest
+
+from oracle import lw_oracle as orc
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = dict(n_layers=2, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, inter=1024, vocab=512, eps=1e-5, theta=1e4)
+
+
+def ref_forward(W, ids, shape, hk_round=True):
+    """All-positions logits [n, V] in float64; k and v rounded to fp16 as the cache stores them."""
+    L, D, H, Hk, Dh, I = (shape[k] for k in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "inter"))
+    emb, norms, (cos, sin) = W["__embed__"], W["__norms__"], W["__rope__"]
+    deq = lambda name: orc.dequant(W[name][0], W[name][1], W[name][2]).astype(np.float64)
+    h = emb[ids].astype(np.float64)
+    n = len(ids)
+
+    def rms(x, g):
+        return x / np.sqrt((x * x).mean(-1, keepdims=True) + shape["eps"]) * g
+
+    def rope(x, p):   # x [heads, Dh]
+        half = Dh // 2
+        a, b = x[:, :half], x[:, half:]
+        c, s = cos[p][None].astype(np.float64), sin[p][None].astype(np.float64)
+        return np.concatenate([a * c - b * s, b * c + a * s], 1)
+
+    for l in range(L):
+        xn = rms(h, norms["l%d.ln1" % l])
+        qkv = xn @ deq("l%d.qkv" % l).T
+        q = qkv[:, :H * Dh].reshape(n, H, Dh)
+        k = qkv[:, H * Dh:(H + Hk) * Dh].reshape(n, Hk, Dh)
+        v = qkv[:, (H + Hk) * Dh:].reshape(n, Hk, Dh)
+        q = np.stack([rope(q[p], p) for p in range(n)])
+        k = np.stack([rope(k[p], p) for p in range(n)]).astype(np.float16).astype(np.float64)
+        v = v.astype(np.float16).astype(np.float64)
+        att = np.zeros((n, H, Dh))
+        for p in range(n):
+            for hd in range(H):
+                kh = hd // (H // Hk)
+                s = (k[:p + 1, kh] @ q[p, hd]) * Dh ** -0.5
+                e = np.exp(s - s.max())
+                att[p, hd] = (e / e.sum()) @ v[:p + 1, kh]
+        h = h + att.reshape(n, H * Dh) @ deq("l%d.o" % l).T
+        xn = rms(h, norms["l%d.ln2" % l])
+        g, u = xn @ deq("l%d.gate" % l).T, xn @ deq("l%d.up" % l).T
+        h = h + (g / (1 + np.exp(-g)) * u) @ deq("l%d.down" % l).T
+    return rms(h, norms["lnf"]) @ deq("lm_head").T
+
+
+@pytest.mark.parametrize("fmt_attn,fmt_ffn", [("Q4_K", "Q4_K"), ("Q5_K", "Q6_K")])
+def test_forward_matches_numpy_model(tmp_path, fmt_attn, fmt_ffn):
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    from lazyweights_b200 import modelgen
+    W = modelgen.write_model(str(tmp_path / "m"), SHAPE, fmt_attn, fmt_ffn, seed=3, return_weights=True)
+    ids = np.random.default_rng(1).integers(0, SHAPE["vocab"], 11).astype(np.int32)
+    ref = ref_forward(W, ids, SHAPE)
+    with lw.Bundle(str(tmp_path / "m"), max_ctx=64, max_batch=8) as b:
+        assert b.vocab == SHAPE["vocab"] and b.pos == 0
+        full = b.forward(ids, all_logits=True)                       # two passes: 8 + 3 tokens
+        assert b.pos == 11 and full.shape == ref.shape
+        assert helpers.rel_err(full, ref) <= 5e-3
+        assert (full.argmax(1) == ref.argmax(1)).mean() >= 0.9
+        b.reset()
+        step = np.stack([b.forward(ids[i:i + 1]) for i in range(len(ids))])   # token by token
+        assert helpers.rel_err(step, full) <= 1e-4                   # per-query arithmetic does not depend on m
+        b.set_pos(5)                                                 # rewind: the cache below 5 is kept
+        assert b.pos == 5
+        again = b.forward(ids[5:], all_logits=True)
+        assert helpers.rel_err(again, full[5:]) <= 1e-4
+        b.reset()
+        with pytest.raises(IndexError):
+            b.forward(np.zeros(65, np.int32))                        # context overflow: the reference's -1
+        assert b.kernel_error() == 0
