@@ -1,0 +1,78 @@
+"""Tensor parallelism.  CPU part (gloo, world size 2): shards of the seeded model tile the full model exactly and the
+id rendezvous delivers rank 0's bytes.  GPU part (needs two GPUs): a 2-rank run gives the single-GPU logits."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from tests import helpers
+from tests.tp_worker import SHAPE
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gloo_worker(rank, world, port, tmp):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    from lazyweights_b200 import modelgen
+    W = modelgen.write_model(os.path.join(tmp, "s%d" % rank), SHAPE, "Q4_K", "Q6_K", seed=9, tp=(rank, world),
+                             return_weights=True)
+    # the rendezvous used for the NCCL id: rank 0's 128 bytes must arrive everywhere
+    buf = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf.copy_(torch.arange(128, dtype=torch.uint8))
+    dist.broadcast(buf, src=0)
+    assert buf.tolist() == list(range(128))
+    np.savez(os.path.join(tmp, "w%d.npz" % rank), **{k: v[1] for k, v in W.items() if not k.startswith("__")})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_shards_tile_the_full_model(tmp_path):
+    import torch.multiprocessing as mp
+    helpers.build_library()
+    mp.spawn(_gloo_worker, args=(2, 29731, str(tmp_path)), nprocs=2, join=True)
+    from lazyweights_b200 import modelgen
+    full = modelgen.write_model(str(tmp_path / "full"), SHAPE, "Q4_K", "Q6_K", seed=9, return_weights=True)
+    s = [np.load(tmp_path / ("w%d.npz" % r)) for r in range(2)]
+    H, Hk, Dh = SHAPE["n_heads"], SHAPE["n_kv_heads"], SHAPE["head_dim"]
+    for l in range(SHAPE["n_layers"]):
+        q = full["l%d.qkv" % l][1]
+        parts = [s[r]["l%d.qkv" % l] for r in range(2)]
+        hq, hk = H // 2 * Dh, Hk // 2 * Dh
+        rebuilt = np.concatenate([parts[0][:hq], parts[1][:hq], parts[0][hq:hq + hk], parts[1][hq:hq + hk],
+                                  parts[0][hq + hk:], parts[1][hq + hk:]])
+        assert np.array_equal(rebuilt, q)
+        for name, axis in (("o", 1), ("gate", 0), ("up", 0), ("down", 1)):
+            key = "l%d.%s" % (l, name)
+            assert np.array_equal(np.concatenate([s[0][key], s[1][key]], axis), full[key][1])
+    assert np.array_equal(np.concatenate([s[0]["lm_head"], s[1]["lm_head"]]), full["lm_head"][1])
+
+
+@pytest.mark.gpu
+def test_two_rank_forward_matches_one_gpu(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    from lazyweights_b200 import modelgen
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29741", WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(tmp_path)],
+                              env=dict(env, RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+             for r in range(2)]
+    outs = [p.communicate(timeout=600)[0].decode() for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    modelgen.write_model(str(tmp_path / "full"), SHAPE, "Q4_K", "Q6_K", seed=9)
+    ids = np.random.default_rng(2).integers(0, SHAPE["vocab"], 10).astype(np.int32)
+    with lw.Bundle(str(tmp_path / "full"), max_ctx=64, max_batch=8) as b:
+        ref = b.forward(ids, all_logits=True)
+        ref_step = b.forward(ids[:1])
+    for r in range(2):
+        assert helpers.rel_err(np.load(tmp_path / ("logits%d.npy" % r)), ref) <= 1e-3
+        assert helpers.rel_err(np.load(tmp_path / ("step%d.npy" % r)), ref_step) <= 1e-3
