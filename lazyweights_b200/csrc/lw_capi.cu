@@ -8,7 +8,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <map>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/lwb200.h"
@@ -39,14 +41,48 @@ static int require_device(int* dev) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Validates, indexes, re-lays out and uploads one blob.  Ks = symbols per row.
-static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uint8_t* side, size_t side_nbytes,
-                       int threads) {
+// Host-side result of validating, indexing and re-laying out one blob: everything that goes to the device.
+struct HostImage {
+  std::vector<uint16_t> lut;
+  std::vector<uint32_t> fat, group_base, words;
+  int KT = 0, T = 0, split = 1, pad = 0, max_len = 0;
+  uint32_t max_unit = 0, max_tile = 0;
+};
+
+static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, int threads, HostImage& im) {
   BlobView v;
   int rc = make_view(blob, nbytes, mx.N, mx.Ks, v);
   if (rc) return rc;
   auto tab = std::make_unique<HuffTable>();
   if ((rc = table_from_lut(v.lut(), *tab))) return rc;
+  // Column segments per tile row: more segments = shorter chains = more of them in flight for the same staging memory.
+  int split = mx.fmt == kFmtQ5K ? 2 : 4;
+  if (const char* e = getenv("LW_SPLIT")) {
+    const int s = atoi(e);
+    if (s == 1 || s == 2 || (s == 4 && mx.fmt != kFmtQ5K)) split = s;
+  }
+  if (mx.fmt == kFmtNone) split = 1;
+  // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
+  // table (7: 1024 windows x 32 copies, codes <= 10 bits; 6: 2048 windows x 16 copies).  LW_PAD overrides.
+  int pad = tab->max_len <= 10 ? 7 : 6;
+  if (const char* e = getenv("LW_PAD")) pad = std::max(0, std::min(7, atoi(e)));
+  if (pad == 7 && tab->max_len > 10) pad = 6;
+  std::vector<uint32_t> chain_start, lane_end;
+  im.fat.resize(kLutSize);
+  fat_table(*tab, mx.fmt, im.fat.data());
+  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr))) return rc;
+  if ((rc = relayout(v, split, pad, chain_start, lane_end, threads, im.group_base, im.words, &im.max_unit, &im.max_tile)))
+    return rc;
+  im.lut.assign(v.lut(), v.lut() + kLutSize);
+  im.KT = v.KT;
+  im.T = v.T;
+  im.split = split;
+  im.pad = pad;
+  im.max_len = tab->max_len;
+  return kOk;
+}
+
+static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, size_t side_nbytes) {
   if (mx.fmt != kFmtNone) {
     const size_t want = static_cast<size_t>(mx.N) * (mx.K / 256) * side_bytes(mx.fmt);
     if (mx.K % 256 || side_nbytes != want || !side) {
@@ -54,57 +90,46 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
       return kErrFormat;
     }
   }
-  // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
-  // table (7: 1024 windows x 32 copies, codes <= 10 bits; 6: 2048 windows x 16 copies).  LW_PAD overrides (2 = the
-  // single-copy table of the staged kernel).
-  // Column segments per tile row: more segments = shorter chains = more of them in flight for the same staging memory.
-  int split = mx.fmt == kFmtQ5K ? 2 : 4;
-  if (const char* e = getenv("LW_SPLIT")) {
-    const int v = atoi(e);
-    if (v == 1 || v == 2 || (v == 4 && mx.fmt != kFmtQ5K)) split = v;
-  }
-  if (mx.fmt == kFmtNone) split = 1;
-  int pad = tab->max_len <= 10 ? 7 : 6;
-  if (const char* e = getenv("LW_PAD")) pad = std::max(0, std::min(7, atoi(e)));
-  if (pad == 7 && tab->max_len > 10) pad = 6;
-  std::vector<uint32_t> chain_start, lane_end, group_base, words, fat(kLutSize);
-  fat_table(*tab, mx.fmt, fat.data());
-  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr))) return rc;
-  uint32_t max_group = 0, max_tile = 0;
-  if ((rc = relayout(v, split, pad, chain_start, lane_end, threads, group_base, words, &max_group, &max_tile))) return rc;
-
   const size_t off_fat = align_up(2 * kLutSize, 256);
   const size_t off_gb = align_up(off_fat + 4 * kLutSize, 256);
-  const size_t off_words = align_up(off_gb + group_base.size() * 4, 256);
-  const size_t off_side = align_up(off_words + words.size() * 4, 256);
+  const size_t off_words = align_up(off_gb + im.group_base.size() * 4, 256);
+  const size_t off_side = align_up(off_words + im.words.size() * 4, 256);
   const size_t total = off_side + align_up(side_nbytes, 256);
   cudaError_t e = cudaMalloc(&mx.d_block, total);
   if (e != cudaSuccess) return cuda_fail("cudaMalloc (matrix)", e);
   uint8_t* d = static_cast<uint8_t*>(mx.d_block);
-  if ((e = cudaMemcpy(d, v.lut(), 2 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
-      (e = cudaMemcpy(d + off_fat, fat.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
-      (e = cudaMemcpy(d + off_gb, group_base.data(), group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
-      (e = cudaMemcpy(d + off_words, words.data(), words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+  if ((e = cudaMemcpy(d, im.lut.data(), 2 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_fat, im.fat.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_gb, im.group_base.data(), im.group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_words, im.words.data(), im.words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (side_nbytes && (e = cudaMemcpy(d + off_side, side, side_nbytes, cudaMemcpyHostToDevice)) != cudaSuccess))
     return cuda_fail("cudaMemcpy (matrix)", e);
   mx.device_bytes = total;
   mx.dev.lut = reinterpret_cast<const uint16_t*>(d);
   mx.dev.tab32 = reinterpret_cast<const uint32_t*>(d + off_fat);
-  mx.dev.pad = pad;
-  mx.dev.max_len = tab->max_len;
+  mx.dev.pad = im.pad;
+  mx.dev.max_len = im.max_len;
   mx.dev.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
   mx.dev.words = reinterpret_cast<const uint32_t*>(d + off_words);
   mx.dev.side = side_nbytes ? d + off_side : nullptr;
   mx.dev.N = mx.N;
   mx.dev.K = mx.K;
   mx.dev.Ks = mx.Ks;
-  mx.dev.KT = v.KT;
-  mx.dev.T = v.T;
+  mx.dev.KT = im.KT;
+  mx.dev.T = im.T;
   mx.dev.fmt = mx.fmt;
-  mx.dev.split = split;
-  mx.dev.max_tile_words = max_tile;
-  mx.dev.max_unit_words = max_group;
+  mx.dev.split = im.split;
+  mx.dev.max_tile_words = im.max_tile;
+  mx.dev.max_unit_words = im.max_unit;
   return kOk;
+}
+
+// Validates, indexes, re-lays out and uploads one blob.  Ks = symbols per row.
+static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uint8_t* side, size_t side_nbytes,
+                       int threads) {
+  HostImage im;
+  const int rc = prepare_matrix(mx, blob, nbytes, threads, im);
+  return rc ? rc : upload_matrix(mx, im, side, side_nbytes);
 }
 
 static int finish_model(Model* M) {
@@ -209,6 +234,7 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
   const auto t0 = std::chrono::steady_clock::now();
   const int threads = default_threads();
   std::vector<uint8_t> blob, side;
+  std::map<std::tuple<long long, long long, int>, HostImage> images;
   for (const TensorEntry& t : M->man.tensors) {
     if (t.enc != "huf8" && t.enc != "huf4p") continue;
     Matrix mx;
@@ -238,8 +264,16 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
       sbytes = static_cast<size_t>(s->nbytes);
       mx.side_bytes = s->nbytes;
     }
-    if (note_status(load_matrix(mx, blob.data(), static_cast<size_t>(t.nbytes), s ? side.data() : nullptr, sbytes,
-                                threads))) {
+    // several tensors may share one blob in the file (synthetic models reuse a layer): prepare it once
+    const auto key = std::make_tuple(t.offset, t.nbytes, mx.fmt);
+    auto hit = images.find(key);
+    if (hit == images.end()) {
+      HostImage im;
+      if (note_status(prepare_matrix(mx, blob.data(), static_cast<size_t>(t.nbytes), threads, im))) return nullptr;
+      if (images.size() >= 16) images.clear();
+      hit = images.emplace(key, std::move(im)).first;
+    }
+    if (note_status(upload_matrix(mx, hit->second, s ? side.data() : nullptr, sbytes))) {
       if (mx.d_block) cudaFree(mx.d_block);
       return nullptr;
     }

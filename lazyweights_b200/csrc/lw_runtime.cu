@@ -60,6 +60,8 @@ struct Runtime {
   void* comm = nullptr;
   float *h = nullptr, *xn = nullptr, *att = nullptr, *o = nullptr, *qkv = nullptr, *g = nullptr, *u = nullptr;
   float *logits = nullptr, *logits_all = nullptr, *cosv = nullptr, *sinv = nullptr, *lnf = nullptr;
+  float* attn_part = nullptr;   // [max_batch][H][max_chunks][Dh + 2]
+  int max_chunks = 1;
   int* ids = nullptr;
   __half *kc = nullptr, *vc = nullptr, *embed16 = nullptr;
   uint8_t* embed8 = nullptr;
@@ -143,23 +145,42 @@ __global__ void k_rope_cache(float* __restrict__ qkv, const float* __restrict__ 
   }
 }
 
-// Causal attention of query head blockIdx.x, token blockIdx.y over positions lo .. pos0 + j.  Scores in dynamic
-// shared memory; one warp per position for the dot products, one thread per output dimension for the weighted sum.
-__global__ void k_attn(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
-                       float* __restrict__ att, int pos0, int H, int Hk, int Dh, int Tmax, float scale, int window) {
-  extern __shared__ float sc[];
-  __shared__ float red[33];
-  const int head = blockIdx.x, j = blockIdx.y, kh = head / (H / Hk), last = pos0 + j;
-  const int lo = window > 0 ? max(0, last - window + 1) : 0, n = last - lo + 1;
+// Causal attention, split over the context so that a long context fills the GPU (one query token of one head is a
+// single reduction otherwise).  k_attn_part: block (head, token, chunk of kAttnChunk positions) -> the chunk's score
+// maximum, its sum of exponentials and the unnormalised weighted sum of v; k_attn_combine merges the chunks of one
+// (head, token) with the usual running-maximum rescaling.  Per-query arithmetic does not depend on how many tokens the
+// pass carries.
+constexpr int kAttnChunk = 128;
+
+__global__ void __launch_bounds__(128)
+    k_attn_part(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
+                float* __restrict__ part, int pos0, int H, int Hk, int Dh, int Tmax, float scale, int window,
+                int max_chunks) {
+  __shared__ float sc[kAttnChunk];
+  __shared__ float red[8];
+  const int head = blockIdx.x, j = blockIdx.y, c = blockIdx.z, kh = head / (H / Hk), last = pos0 + j;
+  const int lo = window > 0 ? max(0, last - window + 1) : 0;
+  const int p0 = lo + c * kAttnChunk, n = min(kAttnChunk, last + 1 - p0);
+  float* out = part + ((static_cast<size_t>(j) * H + head) * max_chunks + c) * (Dh + 2);
+  if (n <= 0) {   // chunk beyond this token's causal range
+    if (threadIdx.x == 0) {
+      out[0] = -INFINITY;
+      out[1] = 0.f;
+    }
+    return;
+  }
   const float* q = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head) * Dh;
-  const __half* K = kc + static_cast<size_t>(kh) * Tmax * Dh;
-  const __half* Vv = vc + static_cast<size_t>(kh) * Tmax * Dh;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const __half* K = kc + (static_cast<size_t>(kh) * Tmax + p0) * Dh;
+  const __half* Vv = vc + (static_cast<size_t>(kh) * Tmax + p0) * Dh;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float mx = -INFINITY;
-  for (int t = warp; t < n; t += nw) {
-    const __half* kr = K + static_cast<size_t>(lo + t) * Dh;
+  for (int t = warp; t < n; t += 4) {
+    const __half* kr = K + static_cast<size_t>(t) * Dh;
     float a = 0.f;
-    for (int i = lane; i < Dh; i += 32) a += q[i] * __half2float(kr[i]);
+    for (int i = 2 * lane; i < Dh; i += 64) {
+      const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kr + i));
+      a += q[i] * kk.x + q[i + 1] * kk.y;
+    }
     for (int o = 16; o; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
     a *= scale;
     if (lane == 0) sc[t] = a;
@@ -167,13 +188,7 @@ __global__ void k_attn(const float* __restrict__ qkv, const __half* __restrict__
   }
   if (lane == 0) red[warp] = mx;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float m2 = -INFINITY;
-    for (int w = 0; w < nw; ++w) m2 = fmaxf(m2, red[w]);
-    red[32] = m2;
-  }
-  __syncthreads();
-  mx = red[32];
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   float sum = 0.f;
   for (int t = threadIdx.x; t < n; t += blockDim.x) {
     const float e = __expf(sc[t] - mx);
@@ -181,19 +196,37 @@ __global__ void k_attn(const float* __restrict__ qkv, const __half* __restrict__
     sum += e;
   }
   for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  __syncthreads();
-  if (lane == 0) red[warp] = sum;
+  if (lane == 0) red[4 + warp] = sum;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float s2 = 0.f;
-    for (int w = 0; w < nw; ++w) s2 += red[w];
-    red[32] = 1.f / s2;
+    out[0] = mx;
+    out[1] = red[4] + red[5] + red[6] + red[7];
   }
-  __syncthreads();
-  const float inv = red[32];
   for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
     float a = 0.f;
-    for (int t = 0; t < n; ++t) a += sc[t] * __half2float(Vv[static_cast<size_t>(lo + t) * Dh + d]);
+    for (int t = 0; t < n; ++t) a += sc[t] * __half2float(Vv[static_cast<size_t>(t) * Dh + d]);
+    out[2 + d] = a;
+  }
+}
+
+__global__ void k_attn_combine(const float* __restrict__ part, float* __restrict__ att, int H, int Dh, int nchunks,
+                               int max_chunks) {
+  const int head = blockIdx.x, j = blockIdx.y;
+  const float* p = part + (static_cast<size_t>(j) * H + head) * max_chunks * (Dh + 2);
+  float mx = -INFINITY;
+  for (int c = 0; c < nchunks; ++c) mx = fmaxf(mx, p[static_cast<size_t>(c) * (Dh + 2)]);
+  float tot = 0.f;
+  for (int c = 0; c < nchunks; ++c) {
+    const float* pc = p + static_cast<size_t>(c) * (Dh + 2);
+    tot += pc[1] * __expf(pc[0] - mx);
+  }
+  const float inv = 1.f / tot;
+  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+    float a = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+      const float* pc = p + static_cast<size_t>(c) * (Dh + 2);
+      if (pc[1] > 0.f) a += pc[2 + d] * __expf(pc[0] - mx);
+    }
     att[static_cast<size_t>(j) * H * Dh + static_cast<size_t>(head) * Dh + d] = a * inv;
   }
 }
@@ -268,6 +301,7 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
   const int rope_rows = cfg_int(M, "rope_rows", 4096);
   R->Tmax = std::max(1, std::min(max_ctx > 0 ? max_ctx : rope_rows, rope_rows));
   R->max_batch = std::max(1, max_batch);
+  R->max_chunks = (R->Tmax + kAttnChunk - 1) / kAttnChunk;
   R->tp_world = cfg_int(M, "tp_world", 1);
   R->tp_rank = cfg_int(M, "tp_rank", 0);
   {
@@ -288,6 +322,7 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
       (rc = dalloc(R, &R->qkv, B * QKV)) || (rc = dalloc(R, &R->g, B * R->I)) || (rc = dalloc(R, &R->u, B * R->I)) ||
       (rc = dalloc(R, &R->logits, B * R->V)) || (rc = dalloc(R, &R->logits_all, B * R->V * R->tp_world)) ||
       (rc = dalloc(R, &R->ids, B)) ||
+      (rc = dalloc(R, &R->attn_part, B * R->H * ((R->Tmax + kAttnChunk - 1) / kAttnChunk) * (R->Dh + 2))) ||
       (rc = dalloc(R, &R->kc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)) ||
       (rc = dalloc(R, &R->vc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)))
     return rc;
@@ -388,8 +423,13 @@ static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool 
     __half* vc = R->vc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
     k_rope_cache<<<dim3(R->H + 2 * R->Hk, m), 64, 0, st>>>(R->qkv, R->cosv, R->sinv, kc, vc, R->pos, R->H, R->Hk, R->Dh,
                                                           R->Tmax);
-    k_attn<<<dim3(R->H, m), 128, static_cast<size_t>(R->pos + m) * sizeof(float), st>>>(
-        R->qkv, kc, vc, R->att, R->pos, R->H, R->Hk, R->Dh, R->Tmax, R->attn_scale, R->window);
+    {
+      const int span = R->window > 0 ? std::min(R->window, R->pos + m) : R->pos + m;
+      const int nchunks = (span + kAttnChunk - 1) / kAttnChunk;
+      k_attn_part<<<dim3(R->H, m, nchunks), 128, 0, st>>>(R->qkv, kc, vc, R->attn_part, R->pos, R->H, R->Hk, R->Dh,
+                                                          R->Tmax, R->attn_scale, R->window, R->max_chunks);
+      k_attn_combine<<<dim3(R->H, m), 128, 0, st>>>(R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
+    }
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
     if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
                                                      R->comm, st), "all-reduce (o)")))
