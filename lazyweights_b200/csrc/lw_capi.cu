@@ -172,12 +172,55 @@ static int matrix_id(Model* M, const char* name) {
   return it->second;
 }
 
-int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy,
-                         cudaStream_t st) {
+template <class T>
+static int grow(T** buf, size_t* have, size_t want, const char* what) {
+  if (want <= *have) return kOk;
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr;
+  *have = 0;
+  const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(buf), want * sizeof(T));
+  if (e != cudaSuccess) return cuda_fail(what, e);
+  *have = want;
+  return kOk;
+}
+
+// Decode + GEMM (the reference's path for more than eight rows, kernels/llmrt.cu:1827-1841): tile rows are decoded to
+// fp16 weights in chunks that fit the scratch (grown on first use, at most kDecodeScratchBytes) and multiplied on the
+// tensor cores.
+constexpr size_t kDecodeScratchBytes = size_t(64) << 20;
+
+static int linear_decode_gemm(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy,
+                              cudaStream_t st) {
+  int rc;
+  const __half* x16 = static_cast<const __half*>(x);
+  if (!x_half) {
+    if ((rc = grow(&M->d_x16, &M->x16_halfs, static_cast<size_t>(m) * mx.K, "cudaMalloc (fp16 activations)"))) return rc;
+    if ((rc = launch_to_half(static_cast<const float*>(x), M->d_x16, static_cast<size_t>(m) * mx.K, st))) return rc;
+    x16 = M->d_x16;
+  }
+  const int NT = mx.N / kTileRows;
+  const size_t row_halfs = static_cast<size_t>(kTileRows) * mx.K;
+  const int fit = static_cast<int>(std::max<size_t>(1, kDecodeScratchBytes / 2 / row_halfs));
+  const int chunk = std::min(NT, fit);
+  if ((rc = grow(&M->d_w16, &M->w16_halfs, static_cast<size_t>(chunk) * row_halfs, "cudaMalloc (decoded weights)")))
+    return rc;
+  for (int tr0 = 0; tr0 < NT; tr0 += chunk) {
+    const int tr1 = std::min(NT, tr0 + chunk);
+    if ((rc = launch_decode_weights_rows(mx.dev, M->d_w16, tr0, tr1, st))) return rc;
+    if ((rc = launch_gemm_tc(x16, M->d_w16, y + static_cast<size_t>(tr0) * kTileRows, m, (tr1 - tr0) * kTileRows, mx.K,
+                             ldy, st)))
+      return rc;
+  }
+  return kOk;
+}
+
+int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
+                  int path) {
   if (mx.fmt == kFmtNone) {
     set_error("%s has no side tensor: products need a block format", mx.name.c_str());
     return kErrArg;
   }
+  if (path == 2 || (path == 0 && m > 8)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);
   const size_t xe = x_half ? 2 : 4;
   for (int r0 = 0; r0 < m; r0 += 8) {
     const int mm = std::min(8, m - r0);
@@ -390,7 +433,7 @@ int rt_test_matmul(void* handle, const char* name, const float* X, int m, float*
   }
   if ((e = cudaMemcpy(M->d_x, X, nx * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
     return cuda_fail("rt_test_matmul copy in", e);
-  int rc = linear_device(M, mx, M->d_x, false, m, M->d_y, mx.N, nullptr);
+  int rc = linear_device(M, mx, M->d_x, false, m, M->d_y, mx.N, nullptr, path);
   if (!rc && (e = cudaMemcpy(Y, M->d_y, ny * 4, cudaMemcpyDeviceToHost)) != cudaSuccess)
     rc = cuda_fail("rt_test_matmul copy back", e);
   return rc;

@@ -94,7 +94,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_codes(MatDev M, 
 // ---------------------------------------------------------------------------------------------- decode to weights
 
 template <int FMT>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_weights(MatDev M, __half* __restrict__ out) {
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+    k_decode_weights(MatDev M, __half* __restrict__ out, int tr0, int tr1) {
   constexpr bool PAIR = is_paired(FMT);
   constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;   // weights per tile row
   constexpr int GW = sub_width(FMT), SB = side_bytes(FMT);
@@ -108,12 +109,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_weights(MatDev M
     reinterpret_cast<uint32_t*>(lut)[i] = __ldg(reinterpret_cast<const uint32_t*>(M.lut) + i);
   if (threadIdx.x < 16) iq4[threadIdx.x] = c_iq4_grid[threadIdx.x];
   __syncthreads();
-  const int t = blockIdx.x * kWarpsPerBlock + warp;
-  if (t >= M.T) return;
+  const int t = tr0 * M.KT + blockIdx.x * kWarpsPerBlock + warp;   // tiles of tile rows tr0 .. tr1 - 1
+  if (t >= tr1 * M.KT) return;
   uint32_t* buf = bufs + static_cast<size_t>(warp) * tile_buf_words(M.max_tile_words);
   uint32_t base;
   if (!stage_tile(M, t, buf, bars + warp, lane, &base)) return;
   const int tr = t / M.KT, tc = t - tr * M.KT;
+  out -= static_cast<size_t>(tr0) * kTileRows * M.K;               // `out` holds rows from tile row tr0 on
 #pragma unroll 1
   for (int half = 0; half < 2; ++half) {
     const int n = tr * kTileRows + half * 32 + lane;
@@ -290,6 +292,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 
 }  // namespace lw
 #include "lw_gemv1.cuh"
+#include "lw_gemm_tc.cuh"
 namespace lw {
 
 // Y[j, n] = sum over the `terms` partial rows of P[term, j, n], in a fixed order (no atomics: results do not depend on
@@ -357,14 +360,19 @@ int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaSt
   return check_launch("k_decode_codes");
 }
 
-int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
+int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st) {
   const size_t smem = 2 * kLutSize + 128 + kWarpsPerBlock * stage_bytes(M);
-  const int blocks = (M.T + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const int tiles = (tr1 - tr0) * M.KT;
+  const int blocks = (tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (tr0 < 0 || tr1 > M.N / kTileRows || tiles <= 0) {
+    set_kernel_error_text("decode_weights", "bad tile-row range");
+    return kErrArg;
+  }
   int rc = kErrArg;
-#define LW_CASE(F)                                                              \
-  case F:                                                                       \
-    if ((rc = prepare(k_decode_weights<F>, smem))) return rc;                   \
-    k_decode_weights<F><<<blocks, kWarpsPerBlock * 32, smem, st>>>(M, out);     \
+#define LW_CASE(F)                                                                      \
+  case F:                                                                               \
+    if ((rc = prepare(k_decode_weights<F>, smem))) return rc;                           \
+    k_decode_weights<F><<<blocks, kWarpsPerBlock * 32, smem, st>>>(M, out, tr0, tr1);   \
     break;
   switch (M.fmt) {
     LW_CASE(kFmtQ4K)
@@ -377,6 +385,10 @@ int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
   }
 #undef LW_CASE
   return check_launch("k_decode_weights");
+}
+
+int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
+  return launch_decode_weights_rows(M, out, 0, M.N / kTileRows, st);
 }
 
 size_t gemv_partial_floats(const MatDev& M, int m) {
@@ -609,6 +621,22 @@ extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_i
 }
 
 namespace lw {
+
+int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st) {
+  k_to_half<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(src, dst, n);
+  return check_launch("k_to_half");
+}
+
+// Y[m, rows] (row stride ldy, starting at column col0) = X[m, K] . W[rows, K]^T on the tensor cores
+int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, cudaStream_t st) {
+  if (m < 1 || rows % kGemmRows || K % kGemmK) {
+    set_kernel_error_text("gemm_tc", "shape must be a multiple of 64 rows x 64 columns");
+    return kErrArg;
+  }
+  dim3 grid(rows / kGemmRows, (m + kGemmTokens - 1) / kGemmTokens);
+  k_gemm_tc<<<grid, 128, 0, st>>>(X, W, Y, m, K, ldy);
+  return check_launch("k_gemm_tc");
+}
 
 int read_kernel_error(unsigned int* value, bool clear) {
   unsigned int v = 0;

@@ -30,6 +30,11 @@ struct MatDev {
 int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaStream_t st);
 // fp16 [N, K], bit-exact float32 block arithmetic rounded once to fp16.
 int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st);
+// Only tile rows tr0 .. tr1 - 1 (64 matrix rows each); `out` receives those rows, [ (tr1 - tr0) * 64, K ].
+int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st);
+// fp32 -> fp16 copy, and Y[m, rows] = X[m, K] . W[rows, K]^T (fp16 in, fp32 out, tensor cores) for the decode + GEMM path.
+int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st);
+int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, cudaStream_t st);
 // Y[j, n] (row stride ldy) = sum_k X[j, k] W[n, k] for m <= 8 rows of X (fp16 or fp32, row-major [m, K]).
 // `partials` must hold gemv_partial_floats(M, m) floats.
 size_t gemv_partial_floats(const MatDev& M, int m);

@@ -38,6 +38,8 @@ struct Model {
   size_t partial_floats = 0;
   float *d_x = nullptr, *d_y = nullptr;   // staging of rt_test_matmul's host buffers (grown on demand, kept)
   size_t x_floats = 0, y_floats = 0;
+  __half *d_w16 = nullptr, *d_x16 = nullptr;   // decode + GEMM path: decoded weights of a chunk of tile rows, fp16 x
+  size_t w16_halfs = 0, x16_halfs = 0;
   size_t resident_bytes = 0;
   long long coded_bytes = 0, side_bytes = 0;
   Runtime* rt = nullptr;
@@ -47,12 +49,17 @@ struct Model {
     if (d_partials) cudaFree(d_partials);
     if (d_x) cudaFree(d_x);
     if (d_y) cudaFree(d_y);
+    if (d_w16) cudaFree(d_w16);
+    if (d_x16) cudaFree(d_x16);
     if (fd >= 0) close(fd);
   }
 };
 
 int cuda_fail(const char* what, cudaError_t e);
-int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st);
+// path 0: fused decode + product for up to eight rows, decode + tensor-core GEMM above; 1: fused in chunks of eight
+// rows; 2: decode + GEMM.
+int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
+                  int path = 0);
 int runtime_init(Model* M, int max_ctx, int max_batch);
 void runtime_free(Model* M);
 

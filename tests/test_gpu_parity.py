@@ -102,16 +102,32 @@ def test_bundle_directory_host_api(lw, tmp_path):
             assert np.array_equal(b.decode(name), q)                                   # rt_test_decode
             assert np.array_equal(b.cpu_decode(name, 4), orc.symbols_of(ty, q))        # rt_test_cpu_decode
             w = orc.dequant(ty, q, side)
-            X = (rng.random((11, q.shape[1])) - 0.5).astype(np.float32)                # m > 8: chunks of eight rows
-            for path in (0, 1):
+            X = (rng.random((11, q.shape[1])) - 0.5).astype(np.float32)
+            # m > 8: path 0 = decode to fp16 weights + tensor-core GEMM, 1 = fused in chunks of eight rows, 2 = the
+            # decode + GEMM path forced; the reference's check compares exactly these against each other
+            # (kernels/llmrt.cu:2864-2876)
+            for path in (0, 1, 2):
                 Y = b.matmul(name, X, path)
                 assert helpers.rel_err(Y, orc.gemv_f64(w, X)) <= helpers.GEMV_TOL
+            Y2 = b.matmul(name, X[:3], 2)
+            assert helpers.rel_err(Y2, orc.gemv_f64(w, X[:3])) <= helpers.GEMV_TOL
         with pytest.raises(KeyError):
             b.matmul("missing", np.zeros((1, 1024), np.float32))
         assert b.gpu_decode_all(2) > 0
         secs, nsym = b.cpu_decode_all(4)
         assert secs > 0 and nsym == sum(q.shape[0] * q.shape[1] // (2 if ty in ("Q4_K", "IQ4_XS") else 1)
                                         for ty, q, _ in cases.values())
+
+
+def test_many_rows_tensor_core_path(lw):
+    """33 activation rows (more than one token block of the GEMM) on the device-pointer entry point."""
+    import torch
+    q, side, sym, w, rng = helpers.seeded_case("Q6_K", 192, 1024, seed=99)
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    with lw.CodedMatrix(blob, 192, sym.shape[1], "Q6_K", side) as mat:
+        x = rng.standard_normal((33, 1024)).astype(np.float16)
+        y = mat.linear("m", torch.from_numpy(x).cuda()).cpu().numpy()
+        assert helpers.rel_err(y, orc.gemv_f64(w, x.astype(np.float32))) <= helpers.GEMV_TOL
 
 
 def test_worst_case_code_lengths(lw):
