@@ -540,6 +540,7 @@ double rt_stat(void* handle, const char* key) {
   if (k == "coded_bytes") return static_cast<double>(M->coded_bytes);
   if (k == "side_bytes") return static_cast<double>(M->side_bytes);
   if (k == "n_matrices") return static_cast<double>(M->mats.size());
+  if (k == "graph_launches" || k == "graph_captures") return runtime_stat(M, k.c_str());
   if (k == "streamed_bytes" || k == "n_streamed" || k == "stream_wait_s" || k == "stream_bytes_moved") return 0;
   return -1;
 }

@@ -62,5 +62,6 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
                   int path = 0);
 int runtime_init(Model* M, int max_ctx, int max_batch);
 void runtime_free(Model* M);
+double runtime_stat(const Model* M, const char* key);
 
 }  // namespace lw

@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <sstream>
 
 #include "../../include/lwb200.h"
@@ -62,7 +63,14 @@ struct Runtime {
   float *logits = nullptr, *logits_all = nullptr, *cosv = nullptr, *sinv = nullptr, *lnf = nullptr;
   float* attn_part = nullptr;   // [max_batch][H][max_chunks][Dh + 2]
   int max_chunks = 1;
-  int* ids = nullptr;
+  int* ids = nullptr;          // device: max_batch token ids, then the position of the pass (read by the kernels, so
+                               // that a captured graph replays at any position, as kernels/llmrt.cu:1308 does)
+  int* h_ids = nullptr;        // pinned host copy of the same
+  cudaStream_t stream = nullptr;
+  bool graphs = true;
+  std::map<long long, cudaGraphExec_t> graph_exec;
+  std::map<long long, int> graph_seen;
+  long long graph_launches = 0, graph_captures = 0;
   __half *kc = nullptr, *vc = nullptr, *embed16 = nullptr;
   uint8_t* embed8 = nullptr;
   float *embed_rs = nullptr, *embed_rsub = nullptr;
@@ -122,8 +130,9 @@ __global__ void k_rmsnorm(float* __restrict__ h, const float* __restrict__ res, 
 
 // rotate-half RoPE on q (in place) and k (into the cache), v into the cache.  grid (heads + 2 kv heads, tokens).
 __global__ void k_rope_cache(float* __restrict__ qkv, const float* __restrict__ cosv, const float* __restrict__ sinv,
-                             __half* __restrict__ kc, __half* __restrict__ vc, int pos0, int H, int Hk, int Dh, int Tmax) {
-  const int head = blockIdx.x, j = blockIdx.y, p = pos0 + j, half = Dh / 2;
+                             __half* __restrict__ kc, __half* __restrict__ vc, const int* __restrict__ posp, int H, int Hk,
+                             int Dh, int Tmax) {
+  const int head = blockIdx.x, j = blockIdx.y, p = *posp + j, half = Dh / 2;
   float* row = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head) * Dh;
   if (head < H + Hk) {
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -154,11 +163,11 @@ constexpr int kAttnChunk = 128;
 
 __global__ void __launch_bounds__(128)
     k_attn_part(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
-                float* __restrict__ part, int pos0, int H, int Hk, int Dh, int Tmax, float scale, int window,
-                int max_chunks) {
+                float* __restrict__ part, const int* __restrict__ posp, int H, int Hk, int Dh, int Tmax, float scale,
+                int window, int max_chunks) {
   __shared__ float sc[kAttnChunk];
   __shared__ float red[8];
-  const int head = blockIdx.x, j = blockIdx.y, c = blockIdx.z, kh = head / (H / Hk), last = pos0 + j;
+  const int head = blockIdx.x, j = blockIdx.y, c = blockIdx.z, kh = head / (H / Hk), last = *posp + j;
   const int lo = window > 0 ? max(0, last - window + 1) : 0;
   const int p0 = lo + c * kAttnChunk, n = min(kAttnChunk, last + 1 - p0);
   float* out = part + ((static_cast<size_t>(j) * H + head) * max_chunks + c) * (Dh + 2);
@@ -321,11 +330,16 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
       (rc = dalloc(R, &R->att, B * R->H * R->Dh)) || (rc = dalloc(R, &R->o, B * R->D)) ||
       (rc = dalloc(R, &R->qkv, B * QKV)) || (rc = dalloc(R, &R->g, B * R->I)) || (rc = dalloc(R, &R->u, B * R->I)) ||
       (rc = dalloc(R, &R->logits, B * R->V)) || (rc = dalloc(R, &R->logits_all, B * R->V * R->tp_world)) ||
-      (rc = dalloc(R, &R->ids, B)) ||
+      (rc = dalloc(R, &R->ids, B + 1)) ||
       (rc = dalloc(R, &R->attn_part, B * R->H * ((R->Tmax + kAttnChunk - 1) / kAttnChunk) * (R->Dh + 2))) ||
       (rc = dalloc(R, &R->kc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)) ||
       (rc = dalloc(R, &R->vc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)))
     return rc;
+  if (cudaMallocHost(reinterpret_cast<void**>(&R->h_ids), (B + 1) * sizeof(int)) != cudaSuccess)
+    return cuda_fail("cudaMallocHost (ids)", cudaGetLastError());
+  if (cudaStreamCreateWithFlags(&R->stream, cudaStreamNonBlocking) != cudaSuccess)
+    return cuda_fail("cudaStreamCreate", cudaGetLastError());
+  if (const char* e = getenv("LW_GRAPHS")) R->graphs = atoi(e) != 0;
   const TensorEntry* te = nullptr;
   void* p = nullptr;
   if (M->man.find("embed") && M->man.find("embed")->enc == "f16") {
@@ -386,10 +400,20 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
 void runtime_free(Model* M) {
   Runtime* R = M->rt;
   if (!R) return;
+  if (R->stream) cudaStreamSynchronize(R->stream);
+  for (auto& kv : R->graph_exec) cudaGraphExecDestroy(kv.second);
   if (R->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(R->comm);
+  if (R->stream) cudaStreamDestroy(R->stream);
+  if (R->h_ids) cudaFreeHost(R->h_ids);
   for (void* p : R->owned) cudaFree(p);
   delete R;
   M->rt = nullptr;
+}
+
+double runtime_stat(const Model* M, const char* key) {
+  if (!M->rt) return 0;
+  return std::strcmp(key, "graph_launches") == 0 ? static_cast<double>(M->rt->graph_launches)
+                                                  : static_cast<double>(M->rt->graph_captures);
 }
 
 static int nccl_check(int r, const char* what) {
@@ -398,11 +422,12 @@ static int nccl_check(int r, const char* what) {
   return kErrCuda;
 }
 
-// One pass over m <= max_batch tokens at positions pos .. pos + m - 1.  Leaves logits of the last token (or of all).
-static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool all_logits) {
-  cudaStream_t st = nullptr;
-  cudaError_t e = cudaMemcpyAsync(R->ids, ids_host, m * sizeof(int), cudaMemcpyHostToDevice, st);
+// The device work of one pass over m <= max_batch tokens (ids and position already in R->h_ids): everything is
+// enqueued on `st`, nothing here depends on host-side values that change from pass to pass except `nchunks`.
+static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunks, cudaStream_t st) {
+  cudaError_t e = cudaMemcpyAsync(R->ids, R->h_ids, (R->max_batch + 1) * sizeof(int), cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) return cuda_fail("ids upload", e);
+  const int* posp = R->ids + R->max_batch;
   if (R->embed16) k_embed16<<<m, 256, 0, st>>>(R->ids, R->embed16, R->h, R->D);
   else k_embed8<<<m, 256, 0, st>>>(R->ids, R->embed8, R->embed_rs, R->embed_rsub, R->h, R->D, R->embed_groups);
   const size_t QKV = static_cast<size_t>(R->H + 2 * R->Hk) * R->Dh;
@@ -421,15 +446,11 @@ static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool 
     }
     __half* kc = R->kc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
     __half* vc = R->vc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
-    k_rope_cache<<<dim3(R->H + 2 * R->Hk, m), 64, 0, st>>>(R->qkv, R->cosv, R->sinv, kc, vc, R->pos, R->H, R->Hk, R->Dh,
+    k_rope_cache<<<dim3(R->H + 2 * R->Hk, m), 64, 0, st>>>(R->qkv, R->cosv, R->sinv, kc, vc, posp, R->H, R->Hk, R->Dh,
                                                           R->Tmax);
-    {
-      const int span = R->window > 0 ? std::min(R->window, R->pos + m) : R->pos + m;
-      const int nchunks = (span + kAttnChunk - 1) / kAttnChunk;
-      k_attn_part<<<dim3(R->H, m, nchunks), 128, 0, st>>>(R->qkv, kc, vc, R->attn_part, R->pos, R->H, R->Hk, R->Dh,
-                                                          R->Tmax, R->attn_scale, R->window, R->max_chunks);
-      k_attn_combine<<<dim3(R->H, m), 128, 0, st>>>(R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
-    }
+    k_attn_part<<<dim3(R->H, m, nchunks), 128, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk, R->Dh, R->Tmax,
+                                                        R->attn_scale, R->window, R->max_chunks);
+    k_attn_combine<<<dim3(R->H, m), 128, 0, st>>>(R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
     if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
                                                      R->comm, st), "all-reduce (o)")))
@@ -458,6 +479,50 @@ static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool 
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("forward", e);
+  return kOk;
+}
+
+// One pass: direct launches the first time a shape (tokens, context bucket, all_logits) occurs, captured into a CUDA
+// graph the second time, replayed afterwards (the reference's policy, kernels/llmrt.cu:2294-2341).  The decode + GEMM
+// path (more than eight rows) may allocate scratch, so those passes are never captured.
+static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool all_logits) {
+  cudaStream_t st = R->stream;
+  cudaStreamSynchronize(st);   // the pinned id buffer is reused
+  std::memcpy(R->h_ids, ids_host, m * sizeof(int));
+  R->h_ids[R->max_batch] = R->pos;
+  const int span = R->window > 0 ? std::min(R->window, R->pos + m) : R->pos + m;
+  const int nchunks = (span + kAttnChunk - 1) / kAttnChunk;
+  const long long key = (static_cast<long long>(nchunks) << 8) | (m << 1) | (all_logits ? 1 : 0);
+  int rc = kOk;
+  auto it = R->graph_exec.find(key);
+  if (it != R->graph_exec.end()) {
+    const cudaError_t e = cudaGraphLaunch(it->second, st);
+    if (e != cudaSuccess) return cuda_fail("cudaGraphLaunch", e);
+    ++R->graph_launches;
+  } else if (R->graphs && m <= 8 && ++R->graph_seen[key] >= 2) {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed);
+    if (e != cudaSuccess) return cuda_fail("cudaStreamBeginCapture", e);
+    rc = enqueue_pass(M, R, m, all_logits, nchunks, st);
+    e = cudaStreamEndCapture(st, &graph);
+    if (rc == kOk && e == cudaSuccess && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+      R->graph_exec[key] = exec;
+      ++R->graph_captures;
+      e = cudaGraphLaunch(exec, st);
+      if (e != cudaSuccess) rc = cuda_fail("cudaGraphLaunch", e);
+      ++R->graph_launches;
+    } else {
+      // capture is not possible here (for instance a collective that cannot be captured): run directly from now on
+      cudaGetLastError();
+      R->graphs = false;
+      rc = enqueue_pass(M, R, m, all_logits, nchunks, st);
+    }
+    if (graph) cudaGraphDestroy(graph);
+  } else {
+    rc = enqueue_pass(M, R, m, all_logits, nchunks, st);
+  }
+  if (rc) return rc;
   R->pos += m;
   return kOk;
 }
@@ -488,10 +553,12 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
     float* dst = all_logits ? logits + static_cast<size_t>(i0) * Vfull : logits;
     cudaError_t e;
     if (W == 1) {
-      e = cudaMemcpy(dst, R->logits, static_cast<size_t>(rows) * R->V * 4, cudaMemcpyDeviceToHost);
+      e = cudaMemcpyAsync(dst, R->logits, static_cast<size_t>(rows) * R->V * 4, cudaMemcpyDeviceToHost, R->stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(R->stream);
     } else {
       stage.resize(static_cast<size_t>(W) * rows * R->V);
-      e = cudaMemcpy(stage.data(), R->logits_all, stage.size() * 4, cudaMemcpyDeviceToHost);
+      e = cudaMemcpyAsync(stage.data(), R->logits_all, stage.size() * 4, cudaMemcpyDeviceToHost, R->stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(R->stream);
       for (int r = 0; r < W && e == cudaSuccess; ++r)
         for (int j = 0; j < rows; ++j)
           std::memcpy(dst + static_cast<size_t>(j) * Vfull + static_cast<size_t>(r) * R->V,
@@ -499,7 +566,7 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
     }
     if (e != cudaSuccess) return cuda_fail("logits copy", e);
   }
-  if (!logits) cudaStreamSynchronize(nullptr);
+  if (!logits) cudaStreamSynchronize(R->stream);
   return 0;
 }
 
@@ -509,7 +576,14 @@ void rt_reset(void* handle) {
 }
 void rt_set_window(void* handle, int w) {
   Model* M = static_cast<Model*>(handle);
-  if (M && M->rt) M->rt->window = std::max(0, w);
+  if (M && M->rt && M->rt->window != std::max(0, w)) {
+    Runtime* R = M->rt;
+    cudaStreamSynchronize(R->stream);
+    for (auto& kv : R->graph_exec) cudaGraphExecDestroy(kv.second);   // the window is baked into captured passes
+    R->graph_exec.clear();
+    R->graph_seen.clear();
+    R->window = std::max(0, w);
+  }
 }
 void rt_set_pos(void* handle, int p) {
   Model* M = static_cast<Model*>(handle);

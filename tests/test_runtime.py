@@ -69,6 +69,7 @@ def test_forward_matches_numpy_model(tmp_path, fmt_attn, fmt_ffn):
         b.reset()
         step = np.stack([b.forward(ids[i:i + 1]) for i in range(len(ids))])   # token by token
         assert helpers.rel_err(step, full) <= 1e-4                   # per-query arithmetic does not depend on m
+        assert b.stat("graph_captures") >= 1 and b.stat("graph_launches") >= 9   # replayed CUDA graphs, same logits
         b.set_pos(5)                                                 # rewind: the cache below 5 is kept
         assert b.pos == 5
         again = b.forward(ids[5:], all_logits=True)
