@@ -56,8 +56,8 @@ struct Model {
 };
 
 int cuda_fail(const char* what, cudaError_t e);
-// path 0: fused decode + product for up to eight rows, decode + tensor-core GEMM above; 1: fused in chunks of eight
-// rows; 2: decode + GEMM.
+// path 0: fused decode + product in chunks of eight rows up to 24 rows, decode + tensor-core GEMM above; 1: always
+// fused; 2: always decode + GEMM.
 int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
                   int path = 0);
 int runtime_init(Model* M, int max_ctx, int max_batch);

@@ -102,8 +102,8 @@ def test_bundle_directory_host_api(lw, tmp_path):
             assert np.array_equal(b.decode(name), q)                                   # rt_test_decode
             assert np.array_equal(b.cpu_decode(name, 4), orc.symbols_of(ty, q))        # rt_test_cpu_decode
             w = orc.dequant(ty, q, side)
-            X = (rng.random((11, q.shape[1])) - 0.5).astype(np.float32)
-            # m > 8: path 0 = decode to fp16 weights + tensor-core GEMM, 1 = fused in chunks of eight rows, 2 = the
+            X = (rng.random((27, q.shape[1])) - 0.5).astype(np.float32)
+            # m > 24: path 0 = decode to fp16 weights + tensor-core GEMM, 1 = fused in chunks of eight rows, 2 = the
             # decode + GEMM path forced; the reference's check compares exactly these against each other
             # (kernels/llmrt.cu:2864-2876)
             for path in (0, 1, 2):

@@ -78,3 +78,21 @@ def test_forward_matches_numpy_model(tmp_path, fmt_attn, fmt_ffn):
         with pytest.raises(IndexError):
             b.forward(np.zeros(65, np.int32))                        # context overflow: the reference's -1
         assert b.kernel_error() == 0
+
+
+def test_prompt_lookup_equals_greedy(tmp_path):
+    """Speculation must not change the output: drafts are only accepted where they equal the greedy choice."""
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    from lazyweights_b200 import modelgen, speculate
+    modelgen.write_model(str(tmp_path / "m"), SHAPE, "IQ4_XS", "IQ4_XS", seed=5)
+    rng = np.random.default_rng(3)
+    motif = rng.integers(0, SHAPE["vocab"], 6)
+    prompt = np.concatenate([motif, rng.integers(0, SHAPE["vocab"], 4), motif, motif[:3]]).astype(np.int32)
+    with lw.Bundle(str(tmp_path / "m"), max_ctx=128, max_batch=8) as b:
+        plain = speculate.greedy(b, prompt, 24)
+        spec, passes, accepted = speculate.prompt_lookup(b, prompt, 24, n_draft=7, ngram=3)
+        assert spec == plain
+        assert passes <= 24 and accepted >= 0
+        assert speculate.lookup_draft([1, 2, 3, 9, 1, 2, 3], 3, 4) == [9, 1, 2, 3]
+        assert speculate.lookup_draft([1, 2, 3], 3, 4) == []
