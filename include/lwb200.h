@@ -105,6 +105,11 @@ int lw_matrix_id(void* handle, const char* name);
 int lw_matrix_info(void* handle, int id, int* N, int* K, int* fmt, long long* blob_bytes, long long* side_bytes,
                    long long* device_bytes);
 
+/* How the batch-1 kernel decodes matrix `id` (chosen from the data when the bundle is opened; no reference
+ * counterpart): symbols per refill group (0 = that kernel is not used), index bits of its replicated table (10 or 11)
+ * and the share of 64-row x quarter-tile work units that fall back to symbol-by-symbol decoding. */
+int lw_matrix_plan(void* handle, int id, int* group, int* index_bits, double* slow_fraction);
+
 /* y[m, N] (fp32, row stride N) = x[m, K] . W^T for 1 <= m <= 8; x is fp16 (x_is_half != 0) or fp32, row-major, on
  * the device.  Launches on `stream` (a cudaStream_t) and does not synchronise.  This is the device-pointer form of
  * the reference's internal matmul(), kernels/llmrt.cu:1794-1826. */

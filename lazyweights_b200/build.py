@@ -9,11 +9,12 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblwb200.so")
-SOURCES = ["lw_host.cpp", "lw_kernels.cu", "lw_capi.cu", "lw_runtime.cu"]
+SOURCES = ["lw_host.cpp", "lw_kernels.cu", "lw_gemv1.cu", "lw_capi.cu", "lw_runtime.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC,-O3,-Wall,-pthread", "-Xptxas", "-v"]
 
@@ -41,19 +42,23 @@ def build(force=False, verbose=False):
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
-    objs = []
-    for src in SOURCES:
+    def compile_one(src):
         obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
         cmd = [nvcc] + NVCC_FLAGS + ["-x", "cu", "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         with open(os.path.join(objdir, os.path.splitext(src)[0] + ".log"), "w") as f:
             f.write(r.stdout + r.stderr)
-        if r.returncode:
-            sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("nvcc failed on " + src)
-        if verbose:
-            sys.stderr.write(r.stderr)
-        objs.append(obj)
+        return src, obj, r
+
+    objs = []
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:   # one nvcc per source, side by side
+        for src, obj, r in pool.map(compile_one, SOURCES):
+            if r.returncode:
+                sys.stderr.write(r.stdout + r.stderr)
+                raise RuntimeError("nvcc failed on " + src)
+            if verbose:
+                sys.stderr.write(r.stderr)
+            objs.append(obj)
     r = subprocess.run([nvcc, "-shared", "-o", LIB] + objs + ["-lcudart", "-lpthread", "-ldl"], capture_output=True, text=True)
     if r.returncode:
         sys.stderr.write(r.stdout + r.stderr)

@@ -45,34 +45,89 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct HostImage {
   std::vector<uint16_t> lut;
   std::vector<uint32_t> fat, group_base, words;
-  int KT = 0, T = 0, split = 1, pad = 0, max_len = 0;
+  std::vector<uint8_t> unit_slow;
+  int KT = 0, T = 0, split = 1, pad = 0, max_len = 0, group = 0, index_bits = 0;
+  double slow_fraction = 0.0;
   uint32_t max_unit = 0, max_tile = 0;
 };
 
-static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, int threads, HostImage& im) {
+static int check_side(const Matrix& mx, const uint8_t* side, size_t side_nbytes) {
+  if (mx.fmt == kFmtNone) return kOk;
+  const size_t want = static_cast<size_t>(mx.N) * (mx.K / 256) * side_bytes(mx.fmt);
+  if (mx.K % 256 || side_nbytes != want || !side) {
+    set_error("%s: side tensor of %zu bytes, expected %zu", mx.name.c_str(), side_nbytes, want);
+    return kErrFormat;
+  }
+  return kOk;
+}
+
+static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, const uint8_t* side, size_t side_nbytes,
+                          int threads, HostImage& im) {
   BlobView v;
   int rc = make_view(blob, nbytes, mx.N, mx.Ks, v);
   if (rc) return rc;
+  if ((rc = check_side(mx, side, side_nbytes))) return rc;
   auto tab = std::make_unique<HuffTable>();
   if ((rc = table_from_lut(v.lut(), *tab))) return rc;
-  // Column segments per tile row: more segments = shorter chains = more of them in flight for the same staging memory.
-  int split = mx.fmt == kFmtQ5K ? 2 : 4;
+  int split = default_split(mx.fmt);
   if (const char* e = getenv("LW_SPLIT")) {
     const int s = atoi(e);
     if (s == 1 || s == 2 || (s == 4 && mx.fmt != kFmtQ5K)) split = s;
   }
   if (mx.fmt == kFmtNone) split = 1;
-  // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
-  // table (7: 1024 windows x 32 copies, codes <= 10 bits; 6: 2048 windows x 16 copies).  LW_PAD overrides.
-  int pad = tab->max_len <= 10 ? 7 : 6;
-  if (const char* e = getenv("LW_PAD")) pad = std::max(0, std::min(7, atoi(e)));
-  if (pad == 7 && tab->max_len > 10) pad = 6;
   std::vector<uint32_t> chain_start, lane_end;
   im.fat.resize(kLutSize);
   fat_table(*tab, mx.fmt, im.fat.data());
-  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr))) return rc;
-  if ((rc = relayout(v, split, pad, chain_start, lane_end, threads, im.group_base, im.words, &im.max_unit, &im.max_tile)))
+  GroupScan scan;
+  scan.quad_syms = 4 * sub_syms(mx.fmt);
+  const bool grouped = mx.fmt != kFmtNone && split == default_split(mx.fmt);
+  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr, grouped ? &scan : nullptr))) return rc;
+  // The batch-1 kernel's table: 1024 windows x 32 copies (codes up to 10 bits, no bank conflicts; units that hold a
+  // longer code take the kernel's slow path) or 2048 windows x 16 copies; and the largest group size that leaves few
+  // units on the slow path.  Estimated cost per symbol: 5.6 instructions + 9 per group (+ 8 % for the conflicts of the
+  // 16-copy table); a slow unit costs about 25.  LW_GEMV1_G / LW_GEMV1_IDX override.
+  int idx_bits = tab->max_len <= 10 ? 10 : 11, group = 0;
+  if (grouped) {
+    const int gmax = is_paired(mx.fmt) ? 4 : kScanMaxG;
+    const char* eg = getenv("LW_GEMV1_G");
+    const char* ei = getenv("LW_GEMV1_IDX");
+    double best = 1e30;
+    for (int ib = 10; ib <= 11; ++ib) {
+      if (ei && atoi(ei) != ib) continue;
+      for (int g = kScanMinG; g <= gmax; ++g) {
+        if (eg && atoi(eg) != g) continue;
+        const uint8_t bits = static_cast<uint8_t>((1u << (g - kScanMinG)) | (ib == 10 ? 0x80u : 0u));
+        size_t slow = 0;
+        for (uint8_t m : scan.mask) slow += (m & bits) != 0;
+        const double f = static_cast<double>(slow) / std::max<size_t>(1, scan.mask.size());
+        const double cost = (1.0 - f) * (5.6 + 9.0 / g) * (ib == 11 ? 1.08 : 1.0) + f * 30.0;
+        if (cost < best) {
+          best = cost;
+          group = g;
+          idx_bits = ib;
+          im.slow_fraction = f;
+        }
+      }
+    }
+    if (group) {
+      const uint8_t bits = static_cast<uint8_t>((1u << (group - kScanMinG)) | (idx_bits == 10 ? 0x80u : 0u));
+      im.unit_slow.resize(scan.mask.size());
+      for (size_t i = 0; i < scan.mask.size(); ++i) im.unit_slow[i] = (scan.mask[i] & bits) != 0;
+    }
+  }
+  // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
+  // table of 4-byte entries, 16 copies (64 bytes) per window.  LW_PAD overrides (and switches that kernel off).
+  int pad = 6;
+  if (const char* e = getenv("LW_PAD")) {
+    const int p = std::max(0, std::min(7, atoi(e)));
+    if (p != pad) group = 0;
+    pad = p;
+  }
+  if ((rc = relayout(v, split, pad, chain_start, lane_end, threads, im.group_base, im.words, &im.max_unit, &im.max_tile,
+                     mx.fmt, group ? side : nullptr)))
     return rc;
+  im.group = group;
+  im.index_bits = idx_bits;
   im.lut.assign(v.lut(), v.lut() + kLutSize);
   im.KT = v.KT;
   im.T = v.T;
@@ -83,18 +138,15 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
 }
 
 static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, size_t side_nbytes) {
-  if (mx.fmt != kFmtNone) {
-    const size_t want = static_cast<size_t>(mx.N) * (mx.K / 256) * side_bytes(mx.fmt);
-    if (mx.K % 256 || side_nbytes != want || !side) {
-      set_error("%s: side tensor of %zu bytes, expected %zu", mx.name.c_str(), side_nbytes, want);
-      return kErrFormat;
-    }
-  }
+  const int rc_side = check_side(mx, side, side_nbytes);
+  if (rc_side) return rc_side;
   const size_t off_fat = align_up(2 * kLutSize, 256);
   const size_t off_gb = align_up(off_fat + 4 * kLutSize, 256);
   const size_t off_words = align_up(off_gb + im.group_base.size() * 4, 256);
   const size_t off_side = align_up(off_words + im.words.size() * 4, 256);
-  const size_t total = off_side + align_up(side_nbytes, 256);
+  const size_t off_slow = off_side + align_up(side_nbytes, 256);
+  const size_t off_done = off_slow + align_up(im.unit_slow.size(), 256);
+  const size_t total = off_done + align_up(static_cast<size_t>(mx.N / kTileRows) * 4, 256);
   cudaError_t e = cudaMalloc(&mx.d_block, total);
   if (e != cudaSuccess) return cuda_fail("cudaMalloc (matrix)", e);
   uint8_t* d = static_cast<uint8_t*>(mx.d_block);
@@ -102,9 +154,14 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
       (e = cudaMemcpy(d + off_fat, im.fat.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_gb, im.group_base.data(), im.group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_words, im.words.data(), im.words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
-      (side_nbytes && (e = cudaMemcpy(d + off_side, side, side_nbytes, cudaMemcpyHostToDevice)) != cudaSuccess))
+      (side_nbytes && (e = cudaMemcpy(d + off_side, side, side_nbytes, cudaMemcpyHostToDevice)) != cudaSuccess) ||
+      (!im.unit_slow.empty() &&
+       (e = cudaMemcpy(d + off_slow, im.unit_slow.data(), im.unit_slow.size(), cudaMemcpyHostToDevice)) != cudaSuccess))
     return cuda_fail("cudaMemcpy (matrix)", e);
+  if ((e = cudaMemset(d + off_done, 0, total - off_done)) != cudaSuccess) return cuda_fail("cudaMemset (matrix)", e);
+  mx.dev.row_done = reinterpret_cast<unsigned int*>(d + off_done);
   mx.device_bytes = total;
+  mx.slow_fraction = im.slow_fraction;
   mx.dev.lut = reinterpret_cast<const uint16_t*>(d);
   mx.dev.tab32 = reinterpret_cast<const uint32_t*>(d + off_fat);
   mx.dev.pad = im.pad;
@@ -112,6 +169,9 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   mx.dev.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
   mx.dev.words = reinterpret_cast<const uint32_t*>(d + off_words);
   mx.dev.side = side_nbytes ? d + off_side : nullptr;
+  mx.dev.unit_slow = im.unit_slow.empty() ? nullptr : d + off_slow;
+  mx.dev.group = im.unit_slow.empty() ? 0 : im.group;
+  mx.dev.index_bits = im.index_bits;
   mx.dev.N = mx.N;
   mx.dev.K = mx.K;
   mx.dev.Ks = mx.Ks;
@@ -128,7 +188,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
 static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uint8_t* side, size_t side_nbytes,
                        int threads) {
   HostImage im;
-  const int rc = prepare_matrix(mx, blob, nbytes, threads, im);
+  const int rc = prepare_matrix(mx, blob, nbytes, side, side_nbytes, threads, im);
   return rc ? rc : upload_matrix(mx, im, side, side_nbytes);
 }
 
@@ -279,7 +339,7 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
   const auto t0 = std::chrono::steady_clock::now();
   const int threads = default_threads();
   std::vector<uint8_t> blob, side;
-  std::map<std::tuple<long long, long long, int>, HostImage> images;
+  std::map<std::tuple<long long, long long, int, long long>, HostImage> images;
   for (const TensorEntry& t : M->man.tensors) {
     if (t.enc != "huf8" && t.enc != "huf4p") continue;
     Matrix mx;
@@ -310,11 +370,13 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
       mx.side_bytes = s->nbytes;
     }
     // several tensors may share one blob in the file (synthetic models reuse a layer): prepare it once
-    const auto key = std::make_tuple(t.offset, t.nbytes, mx.fmt);
+    const auto key = std::make_tuple(t.offset, t.nbytes, mx.fmt, s ? s->offset : -1ll);
     auto hit = images.find(key);
     if (hit == images.end()) {
       HostImage im;
-      if (note_status(prepare_matrix(mx, blob.data(), static_cast<size_t>(t.nbytes), threads, im))) return nullptr;
+      if (note_status(prepare_matrix(mx, blob.data(), static_cast<size_t>(t.nbytes), s ? side.data() : nullptr, sbytes,
+                                     threads, im)))
+        return nullptr;
       if (images.size() >= 16) images.clear();
       hit = images.emplace(key, std::move(im)).first;
     }
@@ -380,6 +442,15 @@ int lw_matrix_info(void* handle, int id, int* N, int* K, int* fmt, long long* bl
   if (blob_bytes) *blob_bytes = mx->blob_bytes;
   if (side_bytes) *side_bytes = mx->side_bytes;
   if (device_bytes) *device_bytes = static_cast<long long>(mx->device_bytes);
+  return kOk;
+}
+
+int lw_matrix_plan(void* handle, int id, int* group, int* index_bits, double* slow_fraction) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (group) *group = mx->dev.group;
+  if (index_bits) *index_bits = mx->dev.group ? mx->dev.index_bits : 0;
+  if (slow_fraction) *slow_fraction = mx->slow_fraction;
   return kOk;
 }
 

@@ -33,6 +33,17 @@ enum Format : int { kFmtNone = 0, kFmtQ4K = 1, kFmtQ5K = 2, kFmtQ6K = 3, kFmtIQ4
 constexpr int side_bytes(int f) { return f == kFmtQ6K ? 18 : f == kFmtIQ4XS ? 8 : 16; }
 constexpr int sub_width(int f) { return f == kFmtQ6K ? 16 : 32; }
 constexpr bool is_paired(int f) { return f == kFmtQ4K || f == kFmtIQ4XS; }
+// Column segments per tile row of the device layout: more segments = shorter chains = more of them in flight for the
+// same staging memory; a segment must hold whole quads of sub-blocks (four 32-weight sub-blocks of Q5_K = 128 symbols).
+constexpr int default_split(int f) { return f == kFmtNone ? 1 : f == kFmtQ5K ? 2 : 4; }
+// Scales of one work unit of the batch-1 kernel (64 rows r = 0..63 x one quad of four sub-blocks), stored behind the
+// unit's chain words as arrays over the rows:
+//   Q6_K    word[r] = the four int8 scales;                      half[2 * 64 + r] = fp16 d
+//   IQ4_XS  word[r] = the four 6-bit scales (one per byte);      half[2 * 64 + r] = fp16 d
+//   Q4_K / Q5_K  word[r] = fp16 d | fp16 dmin << 16; word[64 + r] = the four 6-bit scales; word[128 + r] = the mins
+constexpr int unit_side_words(int f) { return f == kFmtNone ? 0 : (f == kFmtQ6K || f == kFmtIQ4XS) ? 96 : 192; }
+// Symbols per sub-block (one scale), and per quad of sub-blocks
+constexpr int sub_syms(int f) { return is_paired(f) ? sub_width(f) / 2 : sub_width(f); }
 
 // Status codes of the C ABI (0 = success; the reference's -1 / nullptr conventions are kept where it has them).
 enum Status : int {

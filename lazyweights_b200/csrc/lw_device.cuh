@@ -11,9 +11,6 @@
 
 namespace lw {
 
-// Error word set by kernels that give up on a wait instead of spinning for ever (bit 0: bulk-copy wait timed out).
-__device__ unsigned int g_kernel_error;
-
 // ------------------------------------------------------------------------------------------- shared memory + TMA
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
@@ -37,9 +34,9 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 }
 
 // Waits for phase `parity` of the barrier.  The wait is bounded: after kWaitLimit polls it records the failure in
-// g_kernel_error and returns false, so a copy that never lands cannot hang the device.
+// the device error word `err` (bit 0) and returns false, so a copy that never lands cannot hang the device.
 constexpr uint32_t kWaitLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* err) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     uint32_t done;
     asm volatile(
@@ -51,7 +48,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     if (done) return true;
   }
-  atomicOr(&g_kernel_error, 1u);
+  atomicOr(err, 1u);
   return false;
 }
 

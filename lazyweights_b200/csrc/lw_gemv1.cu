@@ -1,0 +1,138 @@
+// Instantiations and launcher of the batch-1 kernel: one persistent block per SM; see lw_gemv1.cuh.
+#include "lw_gemv1.h"
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "lw_gemv1.cuh"
+
+namespace lw {
+
+constexpr size_t kSmemLimit = 227 * 1024;
+constexpr int kMaxStagedColumns = 8;    // tile columns whose activations one block keeps in shared memory
+constexpr int kRingSlackWords = 96;     // read-ahead of the last chains of the last staging buffer lands here
+
+struct Gemv1Plan {
+  int warps, helpers, producers, producer_lanes, slots, nsets, cols_per_set, blocks, max_units;
+  uint32_t buf_words;
+  size_t smem;
+};
+
+static int env_int(const char* name, int fallback) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : fallback;
+}
+
+template <int FMT>
+static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
+  constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT);
+  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
+  p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
+  // a chain reader looks up to three words past its chain; for all buffers but the last that lands in the next buffer
+  // (harmless: those bits are never used), so only the end of the ring needs slack
+  p.buf_words = (M.max_unit_words + 31u) & ~31u;
+  const int units = (M.N / kTileRows) * M.KT * SPLIT;
+  p.blocks = std::max(p.nsets, std::min(sm_count(), units));
+  p.max_units = 0;   // the longest list any block gets: blocks b, b + nsets, ... serve the tile columns of set b % nsets
+  for (int set = 0; set < p.nsets; ++set) {
+    const int nb_set = (p.blocks - set + p.nsets - 1) / p.nsets, ncol = (M.KT - set + p.nsets - 1) / p.nsets;
+    const int set_units = (M.N / kTileRows) * ncol * SPLIT;
+    p.max_units = std::max(p.max_units, (set_units + nb_set - 1) / nb_set);
+  }
+  p.max_units = (p.max_units + 1) & ~1;
+  if (p.max_units > kGemv1MaxUnits) return false;
+  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
+                       static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
+                       2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
+  if (fixed + static_cast<size_t>(p.buf_words) * 4 > kSmemLimit) return false;
+  // as many staging buffers as fit; about three consumers per four buffers, so that copies run ahead of the decoding
+  p.slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));
+  // The decoding is bound by instruction issue from about 18 warps on: more warps only make each unit slower.  So
+  // take the largest number of warps that leaves the last round of the block's list nearly full.
+  // A block whose whole list fits its buffers needs no run-ahead: one warp per unit.
+  constexpr int kSaturating = 18;
+  const int wmax = std::max(1, std::min(kGemv1MaxWarps, p.max_units <= p.slots ? p.slots : p.slots * 3 / 4));
+  const int rounds = (p.max_units + wmax - 1) / wmax;
+  p.warps = wmax <= kSaturating ? wmax : std::max(kSaturating, std::min(wmax, (p.max_units + rounds - 1) / rounds));
+  p.warps = std::min(p.warps, p.max_units);
+  p.warps = std::max(1, std::min(std::min(kGemv1MaxWarps, p.slots), env_int("LW_GEMV1_WARPS", p.warps)));
+  p.producers = std::max(1, std::min(4, env_int("LW_GEMV1_PRODUCERS", 2)));
+  p.helpers = std::max(p.warps, std::min(kGemv1MaxWarps, env_int("LW_GEMV1_HELPERS", kGemv1MaxWarps)));
+  p.producer_lanes = std::max(1, std::min(32, env_int("LW_GEMV1_LANES", 4)));
+  p.smem = fixed + static_cast<size_t>(p.slots) * p.buf_words * 4;
+  return true;
+}
+
+template <int FMT, int G, int IDXBITS, int LOG_R>
+static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+  Gemv1Plan p;
+  if (!plan_gemv1<FMT>(M, p)) {
+    set_kernel_error_text("gemv1", "work unit does not fit shared memory");
+    return kErrTooLarge;
+  }
+  if (cudaFuncSetAttribute(k_gemv1<FMT, G, IDXBITS, LOG_R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(p.smem)) != cudaSuccess)
+    return note_launch("cudaFuncSetAttribute(k_gemv1)");
+  Gemv1Args a;
+  a.x = X;
+  a.partials = P;
+  a.y = Y;
+  a.err = err;
+  a.x_is_half = x_is_half;
+  a.warps = p.warps;
+  a.helpers = p.helpers;
+  a.slots = p.slots;
+  a.producers = p.producers;
+  a.producer_lanes = p.producer_lanes;
+  a.buf_words = p.buf_words;
+  a.nsets = p.nsets;
+  a.cols_per_set = p.cols_per_set;
+  a.max_units = p.max_units;
+  k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
+  return note_launch("k_gemv1");
+}
+
+template <int FMT, int G>
+static int launch_i(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+  if (M.index_bits == 10) return launch_t<FMT, G, 10, kGemv1LogCopies>(M, X, x_is_half, P, Y, err, st);
+  return launch_t<FMT, G, 11, kGemv1LogCopies>(M, X, x_is_half, P, Y, err, st);
+}
+
+template <int FMT>
+static int launch_g(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+  switch (M.group) {
+    case 3: return launch_i<FMT, 3>(M, X, x_is_half, P, Y, err, st);
+    case 4: return launch_i<FMT, 4>(M, X, x_is_half, P, Y, err, st);
+  }
+  if constexpr (!is_paired(FMT)) {
+    switch (M.group) {
+      case 5: return launch_i<FMT, 5>(M, X, x_is_half, P, Y, err, st);
+      case 6: return launch_i<FMT, 6>(M, X, x_is_half, P, Y, err, st);
+    }
+  }
+  set_kernel_error_text("gemv1", "no kernel for this group size");
+  return kErrArg;
+}
+
+bool gemv1_usable(const MatDev& M) {
+  const bool fmt_ok = M.fmt >= kFmtQ4K && M.fmt <= kFmtIQ4XS;
+  const int gmax = is_paired(M.fmt) ? 4 : 6;
+  return fmt_ok && (M.index_bits == 10 || M.index_bits == 11) && M.pad == kGemv1LogCopies + 2 && M.split == default_split(M.fmt) && M.unit_slow && M.row_done && M.group >= 3 &&
+         M.group <= gmax;
+}
+
+int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+  if (!err) {
+    set_kernel_error_text("gemv1", "no device error word");
+    return kErrCuda;
+  }
+  switch (M.fmt) {
+    case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, P, Y, err, st);
+    case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, P, Y, err, st);
+    case kFmtIQ4XS: return launch_g<kFmtIQ4XS>(M, X, x_is_half, P, Y, err, st);
+    default: return launch_g<kFmtQ6K>(M, X, x_is_half, P, Y, err, st);
+  }
+}
+
+}  // namespace lw

@@ -1,31 +1,35 @@
-// Fused decode + dequant + matrix-vector product for ONE activation row (batch 1).  Included by lw_kernels.cu.
+// Fused decode + dequant + matrix-vector product for ONE activation row (batch 1).  Included by lw_gemv1.cu.
 //
 // Design, each point backed by a measured counter of an earlier variant (Q6_K 14336 x 4096, ncu on B200):
 //  * 32-bit decode-table entries (lw::fat_table): the code length sits in the top four bits, so the bit position
 //    advances with one multiply-high-and-add (FMA pipe, not the half-rate integer pipe), and the grid values of the
 //    symbol are signed bytes that feed a dp2a instruction directly: no mask, no int-to-float conversion, and one
-//    instruction for the two weights of a paired symbol (or for two consecutive symbols of an unpaired format).
-//    The activations are re-quantised once per launch to 16-bit fixed point with one scale per sub-block (error at
-//    most 2^-16 of the sub-block's largest |x|; the reference's default kernel uses 8 bits per 32, kernels/llmrt.cu:
-//    1037-1055); products accumulate exactly in int32 inside a sub-block and in float32 across sub-blocks.
-//    Together with the points below this took the loop from 19 to about 9 instructions per symbol.
-//  * The table is replicated so that every lane reads its own bank: with one copy, 32 lanes looking up 32 pseudo-random
-//    windows collide about 3.4 ways and the shared-memory pipe (one 128-byte wavefront per clock per SM) is the bound
-//    (4.3 wavefronts per warp-symbol; 1.4 with the replicated table).
-//      longest code <= 10 bits: 1024 windows x 32 lanes x 4 bytes = 128 KB, entry = (window << 7) | lane << 2
-//      longest code == 11 bits: 2048 windows x 16 lanes x 4 bytes = 128 KB (lanes l and l + 16 share a bank pair)
-//    Every chain starts with M.pad = 7 (or 6) zero bits, which puts the window on exactly those address bits of the
-//    funnel-shifted word: the entry address is one AND.
+//    instruction per symbol (both weights of a paired symbol; an unpaired symbol meets an activation word whose upper
+//    half is zero).  The activations are re-quantised once per launch to 16-bit fixed point with one scale per
+//    sub-block (error at most 2^-16 of the sub-block's largest |x|; the reference's default kernel uses 8 bits per 32,
+//    kernels/llmrt.cu:1037-1055); products accumulate exactly in int32 inside a sub-block and in float32 across
+//    sub-blocks.
+//  * The table is replicated so that lanes read their own banks: with one copy, 32 lanes looking up 32 pseudo-random
+//    windows collide about 3.4 ways and the shared-memory pipe (one 128-byte wavefront per clock per SM) is the bound.
+//    R = 2^LOG_R copies of a table of 2^IDXBITS windows (10 bits if few work units hold an 11-bit code, else 11):
+//    entry address = (window << (LOG_R + 2)) | (lane % R) << 2.  With 32 copies no two lanes share a bank; with 16
+//    (8) copies two (four) lanes share a copy and collide when their windows agree modulo 32 / R (about 1.5 and 2.1
+//    wavefronts per lookup), in exchange for 64 KB more staging buffers, i.e. more warps in flight.
+//    Every chain starts with M.pad = LOG_R + 2 zero bits, which puts the window on exactly those address bits of the
+//    funnel-shifted word: the entry address is one three-input logic operation (mask, then OR the lane's offset).
 //  * Refills are checked once per group of G symbols: the 64-bit window is normalised to the chain's bit position when
 //    a group starts (two funnel shifts), the G symbols only add their lengths to a local offset, one predicated word
-//    shift follows.  G x longest code <= 32 keeps that to one word per group.
+//    shift follows.  That is exact only while every symbol of a group starts within 31 bits of the group and one word
+//    per group keeps up; the loader (lw::walk_blob) checks both for every chain of the matrix, picks the largest G that
+//    leaves few exceptions, and flags the work units that hold one.  A flagged unit (and, with the 10-bit table, a unit
+//    that holds an 11-bit code) is decoded symbol by symbol through a single-copy table (8 KB of shared memory).
 //  * The chain words are staged in shared memory by bulk copies (cp.async.bulk + mbarrier), one per work unit, issued
-//    by lane 0.  Reading them from global memory instead cannot be hidden: a register that is still being loaded
-//    cannot be shifted along the window without waiting for it, and per-lane cp.async rings cost 6 more instructions
-//    per symbol in divergent refill code.
-//  * A work unit is one column segment of a tile (M.split segments per tile row): lane l decodes rows l and l + 32
-//    over that segment as two independent chains that share their activations.  One persistent block per SM; units
-//    are dealt round-robin over all warps of the grid, so that every SM gets the same share.
+//    by a few lanes of dedicated producer warps.  Reading them from global memory instead cannot be hidden: a register
+//    that is still being loaded cannot be shifted along the window without waiting for it, and per-lane cp.async rings
+//    cost 6 more instructions per symbol in divergent refill code.
+//  * A work unit is one column segment of a tile (default_split segments per tile row): lane l decodes rows l and
+//    l + 32 over that segment as two independent chains that share their activations.  One persistent block per SM;
+//    units are dealt round-robin over all warps of the grid, so that every SM gets the same share.
 #pragma once
 #include "lw_device.cuh"
 
@@ -47,182 +51,200 @@ struct GroupChain {
     b = __funnelshift_r(w1, w2, bp);
     off = 0;
   }
-  // next table entry; tab_lane = table base + this lane's bank offset; MASK selects the window's address bits
+  // next table entry; tab = replicated table (start of shared memory), lane_off = this lane's byte offset inside the
+  // copies of one window, MASK selects the window's address bits
   template <uint32_t MASK>
-  __device__ __forceinline__ uint32_t sym(const uint8_t* tab_lane) {
+  __device__ __forceinline__ uint32_t sym(const uint8_t* tab, uint32_t lane_off) {
     const uint32_t t = __funnelshift_r(a, b, off);
-    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab_lane + (t & MASK));
+    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + ((t & MASK) | lane_off));
     off = __umulhi(e, 16u) + off;   // e >> 28 = code length
     return e;
   }
+  __device__ __forceinline__ void refill() {
+    bp -= 32;
+    w0 = w1;
+    w1 = w2;
+    w2 = *p;
+    p += 32;
+  }
   __device__ __forceinline__ void end() {
     bp += off;
-    if (bp >= 32) {
-      bp -= 32;
-      w0 = w1;
-      w1 = w2;
-      w2 = *p;
-      p += 32;
-    }
+    if (bp >= 32) refill();
+  }
+  // symbol by symbol, any data: tab32 = the single-copy table (shared memory)
+  __device__ __forceinline__ uint32_t slow_sym(const uint32_t* tab32, uint32_t pad) {
+    const uint32_t e = tab32[(__funnelshift_r(w0, w1, bp) >> pad) & (kLutSize - 1)];
+    bp += e >> 28;
+    if (bp >= 32) refill();
+    return e;
   }
 };
 
 // One sub-block (SPG symbols) of both chains: acc_a / acc_b += sum x16 * v (exact, int32).  xq points at the
-// sub-block's activations, packed as pairs of int16 (weight 2i in the low half of word i).
-template <int FMT, int G, int SPG, uint32_t MASK>
-__device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const uint8_t* tab_lane, const uint32_t* xq,
-                                          int& acc_a, int& acc_b) {
-  constexpr bool PAIR = is_paired(FMT);
+// sub-block's activation words (one per symbol: the int16 pair of a paired symbol's two weights, or one int16 in the
+// low half).  `first` = index of the sub-block's first symbol within its quad (fixes the phase of the groups); `last`:
+// the quad ends with this sub-block.
+template <int G, int SPG, uint32_t MASK>
+__device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const uint8_t* tab, uint32_t lane_off,
+                                          const uint32_t* xq, const int first, const bool last, int& acc_a,
+                                          int& acc_b) {
   uint4 x = make_uint4(0u, 0u, 0u, 0u);
-  uint32_t pa = 0, pb = 0;
 #pragma unroll
   for (int c = 0; c < SPG; ++c) {
-    if (c % G == 0) {
+    const int f = first + c;
+    if (f % G == 0) {
       ca.begin();
       cb.begin();
     }
-    const uint32_t ea = ca.template sym<MASK>(tab_lane), eb = cb.template sym<MASK>(tab_lane);
-    if (PAIR) {   // one symbol = weights 2c, 2c + 1 = word c of xq
-      if (c % 4 == 0) x = *reinterpret_cast<const uint4*>(xq + c);
-      const uint32_t xw = c % 4 == 0 ? x.x : c % 4 == 1 ? x.y : c % 4 == 2 ? x.z : x.w;
-      acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
-      acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
-    } else if (c % 2 == 0) {
-      pa = ea;
-      pb = eb;
-    } else {      // symbols c - 1, c = word (c - 1) / 2 of xq
-      if ((c / 2) % 4 == 0) x = *reinterpret_cast<const uint4*>(xq + c / 2);
-      const uint32_t xw = (c / 2) % 4 == 0 ? x.x : (c / 2) % 4 == 1 ? x.y : (c / 2) % 4 == 2 ? x.z : x.w;
-      acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(__byte_perm(pa, ea, 0x0040)), acc_a);
-      acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(__byte_perm(pb, eb, 0x0040)), acc_b);
-    }
-    if (c % G == G - 1 || c == SPG - 1) {
+    const uint32_t ea = ca.template sym<MASK>(tab, lane_off), eb = cb.template sym<MASK>(tab, lane_off);
+    if (c % 4 == 0) x = *reinterpret_cast<const uint4*>(xq + c);
+    const uint32_t xw = c % 4 == 0 ? x.x : c % 4 == 1 ? x.y : c % 4 == 2 ? x.z : x.w;
+    acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
+    acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
+    if (f % G == G - 1 || (last && c == SPG - 1)) {
       ca.end();
       cb.end();
     }
   }
 }
 
-__device__ __forceinline__ uint32_t ldg_u32_2byte_aligned(const uint8_t* p) {
-  const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
-  return __ldg(h) | (static_cast<uint32_t>(__ldg(h + 1)) << 16);
+template <int SPG>
+__device__ __forceinline__ void sub_block_slow(GroupChain& ca, GroupChain& cb, const uint32_t* tab32, uint32_t pad,
+                                               const uint32_t* xq, int& acc_a, int& acc_b) {
+#pragma unroll 2
+  for (int c = 0; c < SPG; ++c) {
+    const uint32_t ea = ca.slow_sym(tab32, pad), eb = cb.slow_sym(tab32, pad);
+    const uint32_t xw = xq[c];
+    acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
+    acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
+  }
 }
 
-// Side bytes of the NQ "quads" (four sub-blocks each) that one work unit of one row covers, loaded in one go when the
-// unit starts.  Quads are consumed in order; next() rotates the raw words so that no register is indexed at run time.
-// Q6_K: a quad = four int8 scales (one word); Q4_K / Q5_K: a super-block = two quads of 6-bit scales and mins
-// (llama.cpp's get_scale_min_k4 packing), kept as its 16 raw bytes.
-template <int FMT, int NQ>
+// Scales of the unit's two rows (row `lane` and row `lane + 32`), read from the block that follows the unit's chain
+// words in its staging buffer (layout: lw::unit_side_words).  sub(j) = (scale, offset) of sub-block j (a constant
+// after unrolling): weight = scale * f(code) - offset, every operation rounded separately in float32 (llama.cpp's
+// block formulas; reference: scripts/a2_kq_bundle.py:50-68, kernels/llmrt.cu:126-149).
+template <int FMT>
 struct UnitSide {
-  static constexpr int kBlocks = NQ >= 2 ? NQ / 2 : 1;
-  float d;
-  uint32_t sc[NQ];
-  uint4 w[kBlocks];   // IQ4_XS: x, y = the 8 side bytes of a super-block (fp16 d, scales_h; scales_l)
-  // sp: side bytes of the row's first super-block in this tile; quad0: first quad of the unit within the tile row
-  __device__ __forceinline__ void load(const uint8_t* sp, int quad0) {
+  uint32_t sc, mn, dd;
+  __device__ __forceinline__ void load(const uint32_t* sb, int row) {
+    if (FMT == kFmtQ4K || FMT == kFmtQ5K) {
+      dd = sb[row];
+      sc = sb[64 + row];
+      mn = sb[128 + row];
+    } else {
+      sc = sb[row];
+      dd = reinterpret_cast<const uint16_t*>(sb)[128 + row];
+      mn = 0;
+    }
+  }
+  __device__ __forceinline__ void sub(int j, float& s, float& o) const {
+    const uint32_t q = (sc >> (8 * j)) & 255u;
     if (FMT == kFmtQ6K) {
-      const uint8_t* blk = sp + (quad0 >> 2) * 18;
-      d = half_bits_to_float(__ldg(reinterpret_cast<const uint16_t*>(blk + 16)));
-#pragma unroll
-      for (int q = 0; q < NQ; ++q) sc[q] = ldg_u32_2byte_aligned(blk + 4 * ((quad0 & 3) + q));
+      s = __fmul_rn(half_bits_to_float(dd), static_cast<float>(static_cast<int8_t>(q)));
+      o = 0.f;
     } else if (FMT == kFmtIQ4XS) {
-#pragma unroll
-      for (int i = 0; i < kBlocks; ++i) {
-        const uint2 v = __ldg(reinterpret_cast<const uint2*>(sp) + (quad0 >> 1) + i);
-        w[i] = make_uint4(v.x, v.y, 0u, 0u);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < kBlocks; ++i) w[i] = __ldg(reinterpret_cast<const uint4*>(sp) + (quad0 >> 1) + i);
-    }
-  }
-  // (scale, offset) of sub-block j (0..3, a constant after unrolling) of the current quad; hi: second quad of its
-  // super-block (Q4_K / Q5_K)
-  __device__ __forceinline__ void sub(bool hi, int j, float& s, float& o) const {
-    if (FMT == kFmtQ6K) {
-      s = __fmul_rn(d, static_cast<float>(static_cast<int8_t>((sc[0] >> (8 * j)) & 255u)));
-      o = 0.f;
-    } else if (FMT == kFmtIQ4XS) {   // sub-block 4 hi + j of the super-block: 4-bit low part, 2-bit high part
-      const uint4 v = w[0];
-      const uint32_t lo = hi ? v.y >> 16 : v.y, h2 = hi ? v.x >> 24 : v.x >> 16;
-      const uint32_t ls = ((lo >> (4 * j)) & 15u) | (((h2 >> (2 * j)) & 3u) << 4);
-      s = __fmul_rn(half_bits_to_float(v.x), static_cast<float>(static_cast<int>(ls) - 32));
+      s = __fmul_rn(half_bits_to_float(dd), static_cast<float>(static_cast<int>(q) - 32));
       o = 0.f;
     } else {
-      const uint4 v = w[0];
-      const uint32_t sc_lo = (v.y >> (8 * j)) & 63u, mn_lo = (v.z >> (8 * j)) & 63u;
-      const uint32_t sc_hi = ((v.w >> (8 * j)) & 15u) | (((v.y >> (8 * j + 6)) & 3u) << 4);
-      const uint32_t mn_hi = ((v.w >> (8 * j + 4)) & 15u) | (((v.z >> (8 * j + 6)) & 3u) << 4);
-      s = __fmul_rn(half_bits_to_float(v.x), static_cast<float>(hi ? sc_hi : sc_lo));
-      o = __fmul_rn(half_bits_to_float(v.x >> 16), static_cast<float>(hi ? mn_hi : mn_lo));
-    }
-  }
-  __device__ __forceinline__ void next(bool hi) {
-    if (FMT == kFmtQ6K) {
-#pragma unroll
-      for (int q = 0; q + 1 < NQ; ++q) sc[q] = sc[q + 1];
-    } else if (hi) {
-#pragma unroll
-      for (int i = 0; i + 1 < kBlocks; ++i) w[i] = w[i + 1];
+      s = __fmul_rn(half_bits_to_float(dd), static_cast<float>(q));
+      o = __fmul_rn(half_bits_to_float(dd >> 16), static_cast<float>((mn >> (8 * j)) & 255u));
     }
   }
 };
 
-constexpr int kReplicatedTableBytes = 128 * 1024;
+constexpr int kGemv1LogCopies = 4;         // 16 copies of the table: 64 KB (1024 windows) or 128 KB (2048)
 constexpr int kGemv1MaxWarps = 28;         // consumer warps; up to four more warps produce
 constexpr int kGemv1MaxSlots = 64;         // staging buffers in the ring
-constexpr int kGemv1MaxUnits = 512;        // work units one block can be dealt
+constexpr int kGemv1MaxUnits = 1024;       // work units one block can be dealt
 
 struct Gemv1Args {
   const void* x;          // activations [K], fp16 or fp32
   float* partials;        // [KT * SPLIT][N]
+  float* y;               // [N] result
+  unsigned int* err;      // device error word (bit 0: a bounded wait gave up)
   int x_is_half;
   int warps;              // consumer warps per block
+  int helpers;            // warps that share the prologue (table, activations): the consumers and then some
   int producers;          // producer warps per block
-  int prefetch;           // units pulled into L2 ahead of their copy (0 = none)
+  int producer_lanes;     // lanes of a producer warp that issue copies
   int slots;              // staging buffers in the ring (>= warps)
   uint32_t buf_words;     // one staging buffer, in words
   int nsets;              // tile columns are dealt to `nsets` sets of blocks (bounds the staged activations)
   int cols_per_set;       // ceil(KT / nsets)
+  int max_units;          // capacity of the block's unit list (>= units of any block, multiple of 2)
 };
 
-struct UnitMeta {
+struct UnitMeta {          // 16 bytes: one shared-memory load per unit
   uint32_t src;           // word offset of the unit's first group
   uint16_t lines;         // size of both groups in 128-byte lines (a group is a whole number of lines)
-  uint16_t second;        // offset of the second group inside the unit, in lines
+  uint16_t second;        // offset of the second group inside the unit, in lines; bit 15: decode symbol by symbol
+  uint16_t tr;            // tile row
+  uint16_t round;         // use of its staging buffer: unit index / slots
+  uint8_t j, seg, slot;   // tile column within the block's set, column segment, staging buffer: unit index % slots
+  uint8_t unused;
 };
+static_assert(sizeof(UnitMeta) == 16, "UnitMeta is read as one 16-byte word");
 
-// Block = `warps` consumer warps + one producer warp.  The producer (one lane) walks the block's list of work units
-// and, for each, waits until a staging buffer of the ring is free and starts the bulk copy of the unit's words into
-// it; consumer warp c takes units c, c + warps, ... of the list, waits for the buffer to fill, decodes, and frees it.
-// With more buffers than consumers the copies run ahead of the decoding, so no warp waits for DRAM in steady state.
-// Every wait is bounded (mbar_wait): a warp that gives up sets the device error word and leaves.
-template <int FMT, int G, int IDXBITS, int SPLIT>
+// Block = `warps` consumer warps + `producers` producer warps.  Unit k of the block's list goes through staging
+// buffer k % slots ("round" k / slots of that buffer).  Producer lanes each own a subset of the buffers and, round
+// after round, wait until a buffer is free and start the bulk copy of its next unit; a consumer warp draws the next
+// unit of the list from a shared counter, waits for the buffer to fill, decodes, and frees it.  With more buffers
+// than consumers the copies run ahead of the decoding, so no warp waits for DRAM in steady state.
+// Everything a unit needs (coordinates, buffer, round) is worked out once, in parallel, when the block starts: the
+// per-unit path has no integer division.
+// The warp that finishes the last unit of a tile row (counted in M.row_done, which it resets) adds the row's partial
+// products in a fixed order and writes the result: no second kernel.
+// A parity wait on an mbarrier is only exact for a waiter that is at most one phase away, and here the waiters of
+// consecutive rounds of a buffer are different threads.  So every buffer also has a plain counter of the rounds that
+// were released: both sides first wait until it reaches their round (exact at any distance), after which the
+// barrier is known to be in the phase the parity wait assumes.
+// Every wait is bounded: a warp that gives up sets the device error word and leaves.
+__device__ __forceinline__ bool wait_released(const uint32_t* released, uint32_t round, unsigned int* err) {
+  const uint32_t addr = smem_addr(released);
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    if (v >= round) return true;
+  }
+  atomicOr(err, 1u);
+  return false;
+}
+
+template <int FMT, int G, int IDXBITS, int LOG_R>
 __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   constexpr bool PAIR = is_paired(FMT);
+  constexpr int SPLIT = default_split(FMT);
   constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;            // weights per tile row
-  constexpr int GW = sub_width(FMT), SPG = PAIR ? GW / 2 : GW, SB = side_bytes(FMT);
+  constexpr int GW = sub_width(FMT), SPG = sub_syms(FMT), SIDEW = unit_side_words(FMT);
   constexpr int NSU = TW / GW / SPLIT;                            // sub-blocks per unit
-  constexpr int NQ = NSU / 4;                                     // quads per unit
-  static_assert(NQ >= 1 && NSU % 4 == 0, "a unit must hold whole quads of sub-blocks");
+  constexpr int USYM = kTileSyms / SPLIT;                         // symbols (= activation words) per chain
+  static_assert(NSU == 4, "a unit is one quad of sub-blocks");
   constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K;
-  constexpr int LOG_R = IDXBITS == 10 ? 5 : 4;                    // copies of the table = 1 << LOG_R
-  constexpr uint32_t MASK = IDXBITS == 10 ? 0x1FF80u : 0x1FFC0u;
+  constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;              // windows, copies of the table
+  constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
+  constexpr int kReplicatedTableBytes = NIDX * R * 4;
   extern __shared__ __align__(128) uint8_t smem[];
   uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* xq = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);  // [cols_per_set][TW / 2] int16 pairs
-  float* xscale = reinterpret_cast<float*>(xq + static_cast<size_t>(A.cols_per_set) * (TW / 2));   // [cols][TW / GW]
+  uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);  // [2048] single copy
+  uint32_t* xq = tab1 + kLutSize;                                             // [cols_per_set][kTileSyms] words
+  float* xscale = reinterpret_cast<float*>(xq + static_cast<size_t>(A.cols_per_set) * kTileSyms);  // [cols][TW / GW]
   float* xg = xscale + static_cast<size_t>(A.cols_per_set) * (TW / GW);      // [cols][TW / GW] sums (offset formats)
   uint64_t* full = reinterpret_cast<uint64_t*>(xg + (HAS_OFFSET ? A.cols_per_set * (TW / GW) : 0));
   uint64_t* empty = full + kGemv1MaxSlots;
-  UnitMeta* meta = reinterpret_cast<UnitMeta*>(empty + kGemv1MaxSlots);      // [kGemv1MaxUnits]
-  uint32_t* bufs = reinterpret_cast<uint32_t*>(meta + kGemv1MaxUnits);
+  uint32_t* released = reinterpret_cast<uint32_t*>(empty + kGemv1MaxSlots);  // [slots] rounds released so far
+  int* next_unit = reinterpret_cast<int*>(released + kGemv1MaxSlots);        // the list's shared counter
+  int* list_count = next_unit + 1;                                           // [2] slow / other units placed so far
+  UnitMeta* meta = reinterpret_cast<UnitMeta*>(next_unit + 4);               // [max_units]
+  uint32_t* bufs = reinterpret_cast<uint32_t*>(meta + A.max_units);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int set = blockIdx.x % A.nsets, bi = blockIdx.x / A.nsets;
   const int nb_set = (gridDim.x - set + A.nsets - 1) / A.nsets;              // blocks of this set
   const int ncol = (M.KT - set + A.nsets - 1) / A.nsets;                     // tile columns of this set
   const int nunits = (M.N / kTileRows) * ncol * SPLIT;                       // units of this set
   const int nmine = bi < nunits ? (nunits - bi + nb_set - 1) / nb_set : 0;   // units of this block: bi + k nb_set
+  const bool consumer = warp < A.helpers;   // takes part in the prologue; warps >= A.warps leave after it
+  const int nthr = A.helpers * 32;
 
   // unit of the set -> (tile row, column index in the set, segment), segment fastest
   auto coords = [&](int u, int& tr, int& j, int& seg) {
@@ -232,88 +254,146 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     tr = v / ncol;
   };
 
-  // 1. every thread: where the block's units live (global loads in parallel), barriers
-  for (int k = threadIdx.x; k < nmine; k += blockDim.x) {
-    int tr, j, seg;
-    coords(bi + k * nb_set, tr, j, seg);
-    const int t = tr * M.KT + set + A.nsets * j;
-    const uint32_t* gb = M.group_base + static_cast<size_t>(t) * (2 * SPLIT) + 2 * seg;
-    const uint32_t g0 = __ldg(gb), g1 = __ldg(gb + 1), g2 = __ldg(gb + 2);
-    meta[k] = UnitMeta{g0, static_cast<uint16_t>((g2 - g0) >> 5), static_cast<uint16_t>((g1 - g0) >> 5)};
+  // 1. everything the prologue needs from global memory is requested at once: table entries and the first activations
+  // (consumers), then where the block's units live (all threads)
+  constexpr int TAB_PRE = 2, XB = 6;
+  uint32_t tab_pre[TAB_PRE];
+  float xv[XB];
+  auto load_x = [&](int base) {
+#pragma unroll
+    for (int u = 0; u < XB; ++u) {
+      const int i = base + u * nthr + threadIdx.x;
+      xv[u] = 0.f;
+      if (i < ncol * TW) {
+        const int j = i / TW, k = i - j * TW;
+        const size_t src = static_cast<size_t>(set + A.nsets * j) * TW + k;
+        xv[u] = A.x_is_half ? __half2float(static_cast<const __half*>(A.x)[src]) : static_cast<const float*>(A.x)[src];
+      }
+    }
+  };
+  if (consumer) {
+#pragma unroll
+    for (int i = 0; i < TAB_PRE; ++i) {
+      const int idx = (i * A.helpers + warp) * 32 + lane;
+      tab_pre[i] = idx < NIDX ? __ldg(M.tab32 + idx) : 0u;
+    }
+    load_x(0);
+  }
+  // The block's list: units bi, bi + nb_set, ... of the set, with the symbol-by-symbol units moved to the front (they
+  // take several times longer: started last, one of them would keep the whole block waiting).  The order within the
+  // two classes is whatever the counters hand out; results do not depend on it.
+  if (threadIdx.x == 0) {
+    list_count[0] = 0;
+    list_count[1] = 0;
+    *next_unit = 0;
+  }
+  __syncthreads();
+  for (int k0 = warp * 32; k0 < nmine; k0 += (blockDim.x >> 5) * 32) {
+    const int k = k0 + lane;
+    const bool valid = k < nmine;
+    int tr = 0, j = 0, seg = 0;
+    uint32_t g0 = 0, g1 = 0, g2 = 0, slow = 0;
+    if (valid) {
+      coords(bi + k * nb_set, tr, j, seg);
+      const int t = tr * M.KT + set + A.nsets * j;
+      const uint32_t* gb = M.group_base + static_cast<size_t>(t) * (2 * SPLIT) + 2 * seg;
+      g0 = __ldg(gb);
+      g1 = __ldg(gb + 1);
+      g2 = __ldg(gb + 2);
+      slow = __ldg(M.unit_slow + static_cast<size_t>(t) * SPLIT + seg);
+    }
+    const uint32_t bs = __ballot_sync(0xffffffffu, valid && slow), bf = __ballot_sync(0xffffffffu, valid && !slow);
+    int base_s = 0, base_f = 0;
+    if (lane == 0) {
+      base_s = atomicAdd(list_count, __popc(bs));
+      base_f = atomicAdd(list_count + 1, __popc(bf));
+    }
+    base_s = __shfl_sync(0xffffffffu, base_s, 0);
+    base_f = __shfl_sync(0xffffffffu, base_f, 0);
+    if (valid) {
+      const uint32_t below = (1u << lane) - 1u;
+      const int pos = slow ? base_s + __popc(bs & below) : nmine - 1 - (base_f + __popc(bf & below));
+      meta[pos] = UnitMeta{g0,
+                           static_cast<uint16_t>((g2 - g0) >> 5),
+                           static_cast<uint16_t>(((g1 - g0) >> 5) | (slow ? 0x8000u : 0u)),
+                           static_cast<uint16_t>(tr),
+                           static_cast<uint16_t>(pos / A.slots),
+                           static_cast<uint8_t>(j),
+                           static_cast<uint8_t>(seg),
+                           static_cast<uint8_t>(pos % A.slots),
+                           0};
+    }
   }
   if (threadIdx.x < A.slots) {
     mbar_init(smem_addr(full + threadIdx.x), 1);
     mbar_init(smem_addr(empty + threadIdx.x), 1);
+    released[threadIdx.x] = 0u;
   }
   __syncthreads();
 
-  if (warp >= A.warps) {
-    // 2a. producers: warp A.warps + i feeds units i, i + producers, ... of the block's list (one lane each: issuing a
-    // bulk copy costs a few hundred cycles, so several lanes in different warps keep more copies in flight)
-    if (lane == 0) {
-      const int pw = warp - A.warps;
-      // units further down the list are pulled into L2 ahead of time, so that their copy finds them there
-      auto prefetch = [&](int k) {
-        if (A.prefetch && k < nmine)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(M.words + meta[k].src),
-                       "r"(meta[k].lines * 128u)
-                       : "memory");
-      };
-      for (int k = pw; k < nmine; k += A.producers) {
-        const int slot = k % A.slots, round = k / A.slots;
-        prefetch(k + A.prefetch);
-        if (round > 0 && !mbar_wait(smem_addr(empty + slot), (round - 1) & 1)) return;
-        const UnitMeta um = meta[k];
-        bulk_load(smem_addr(bufs + static_cast<size_t>(slot) * A.buf_words), M.words + um.src, um.lines * 128u,
-                  smem_addr(full + slot));
-      }
+  if (!consumer) {
+    // 2a. producers: issuer s = (producer warp) * producer_lanes + lane owns buffers s, s + S, ... (S issuers) and
+    // feeds them round by round, i.e. in the order of the block's list.  Issuing a bulk copy takes a few hundred
+    // cycles, so several issuers keep more copies in flight.
+    if (lane < A.producer_lanes) {
+      const int issuers = A.producers * A.producer_lanes;
+      for (int round = 0; round * A.slots < nmine; ++round)
+        for (int slot = (warp - A.helpers) * A.producer_lanes + lane; slot < A.slots; slot += issuers) {
+          const int k = round * A.slots + slot;
+          if (k >= nmine) break;
+          if (round > 0) {
+            if (!wait_released(released + slot, round, A.err)) return;
+            if (!mbar_wait(smem_addr(empty + slot), (round - 1) & 1, A.err)) return;
+          }
+          const UnitMeta um = meta[k];
+          bulk_load(smem_addr(bufs + static_cast<size_t>(slot) * A.buf_words), M.words + um.src, um.lines * 128u,
+                    smem_addr(full + slot));
+        }
     }
     return;
   }
 
-  // 2b. consumers: table and activations first (the first copies are already on their way)
-  const int nthr = A.warps * 32;
+  // 2b. consumers: table and activations (the first copies are already on their way).
+  // Replicate the table: a warp holds 32 entries, broadcasts them one by one and every lane stores its own copy
+  // (bank = lane, no conflicts).  With 16 copies two entries go out per store.
   {
-    // replicate the table: a warp loads 32 entries with one coalesced read, then broadcasts them one by one and every
-    // lane stores its own copy (bank = lane, no conflicts).  With 16 copies two entries go out per store.
-    constexpr int NIDX = 1 << IDXBITS, PER = IDXBITS == 10 ? 1 : 2;
-    for (int i0 = warp * 32; i0 < NIDX; i0 += A.warps * 32) {
-      const uint32_t mine = __ldg(M.tab32 + i0 + lane);
+    constexpr int PER = 32 / R;   // entries per store: lane l writes copy l % R of entry i0 + j + l / R
+    auto spread = [&](int i0, uint32_t mine) {
 #pragma unroll 8
       for (int j = 0; j < 32; j += PER) {
-        const uint32_t v = __shfl_sync(0xffffffffu, mine, PER == 1 ? j : j + (lane >> 4));
-        tab[(i0 + j) * (32 / PER) + lane] = v;
+        const uint32_t v = __shfl_sync(0xffffffffu, mine, j + (lane >> LOG_R));
+        tab[(i0 + j) * R + lane] = v;
       }
-    }
-  }
-  // activations -> 16-bit fixed point with one scale per sub-block (GW consecutive weights sit in GW consecutive
-  // lanes).  Loads go out eight at a time so that their global-memory latencies overlap.
-  constexpr int XB = 8;
-  for (int base = 0; base < ncol * TW; base += XB * nthr) {
-    float v[XB];
+    };
 #pragma unroll
-    for (int u = 0; u < XB; ++u) {
-      const int i = base + u * nthr + threadIdx.x;
-      v[u] = 0.f;
-      if (i < ncol * TW) {
-        const int j = i / TW, k = i - j * TW;
-        const size_t src = static_cast<size_t>(set + A.nsets * j) * TW + k;
-        v[u] = A.x_is_half ? __half2float(static_cast<const __half*>(A.x)[src]) : static_cast<const float*>(A.x)[src];
-      }
+    for (int i = 0; i < TAB_PRE; ++i) {
+      const int i0 = (i * A.helpers + warp) * 32;
+      if (i0 < NIDX) spread(i0, tab_pre[i]);
     }
+    for (int i0 = (TAB_PRE * A.helpers + warp) * 32; i0 < NIDX; i0 += A.helpers * 32) spread(i0, __ldg(M.tab32 + i0 + lane));
+  }
+  for (int i = threadIdx.x; i < kLutSize; i += nthr) tab1[i] = __ldg(M.tab32 + i);
+  // activations -> 16-bit fixed point with one scale per sub-block (GW consecutive weights sit in GW consecutive
+  // lanes).  Loads go out XB at a time so that their global-memory latencies overlap.
+  for (int base = 0; base < ncol * TW; base += XB * nthr) {
+    if (base > 0) load_x(base);
 #pragma unroll
     for (int u = 0; u < XB; ++u) {
       const int i = base + u * nthr + threadIdx.x;
       if (i < ncol * TW) {   // whole warps take this branch together: sizes are multiples of 32
-        float amax = fabsf(v[u]), sum = v[u];
+        float amax = fabsf(xv[u]), sum = xv[u];
 #pragma unroll
         for (int o = 1; o < GW; o <<= 1) {
           amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
           if (HAS_OFFSET) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        const int q = __float2int_rn(v[u] * (amax > 0.f ? 32767.f / amax : 0.f));
-        const int qn = __shfl_down_sync(0xffffffffu, q, 1);
-        if ((lane & 1) == 0) xq[i >> 1] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
+        const int q = __float2int_rn(xv[u] * (amax > 0.f ? 32767.f / amax : 0.f));
+        if (PAIR) {
+          const int qn = __shfl_down_sync(0xffffffffu, q, 1);
+          if ((lane & 1) == 0) xq[i >> 1] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
+        } else {
+          xq[i] = static_cast<uint32_t>(q) & 0xFFFFu;
+        }
         if ((lane & (GW - 1)) == 0) {
           xscale[i / GW] = amax * (1.f / 32767.f);
           if (HAS_OFFSET) xg[i / GW] = sum;
@@ -322,81 +402,113 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
-  const uint8_t* tab_lane = smem + ((lane & ((1 << LOG_R) - 1)) << 2);
-  const size_t side_row = static_cast<size_t>(M.K / 256) * SB;
-  // side bytes of a unit's two rows: fetched one unit ahead (they come from DRAM in small strided pieces)
-  auto side_ptrs = [&](int k, const uint8_t*& pa, const uint8_t*& pb, int& seg) {
-    int tr, j;
-    coords(bi + k * nb_set, tr, j, seg);
-    const size_t col = static_cast<size_t>(set + A.nsets * j) * (TW / 256) * SB;
-    pa = M.side + static_cast<size_t>(tr * kTileRows + lane) * side_row + col;
-    pb = pa + 32 * side_row;
-  };
-  UnitSide<FMT, NQ> side_a, side_b, next_a, next_b;
-  if (warp < nmine) {
-    const uint8_t *pa, *pb;
-    int sg;
-    side_ptrs(warp, pa, pb, sg);
-    side_a.load(pa, sg * NQ);
-    side_b.load(pb, sg * NQ);
-  }
-#pragma unroll 1
-  for (int k = warp; k < nmine; k += A.warps) {
-    int tr, j, seg;
-    coords(bi + k * nb_set, tr, j, seg);
-    const int tc = set + A.nsets * j;
-    const int na = tr * kTileRows + lane, nb = na + 32;
-    if (k + A.warps < nmine) {
-      const uint8_t *pa, *pb;
-      int sg;
-      side_ptrs(k + A.warps, pa, pb, sg);
-      next_a.load(pa, sg * NQ);
-      next_b.load(pb, sg * NQ);
-    }
-    const uint32_t* xt = xq + static_cast<size_t>(j) * (TW / 2) + seg * (TW / SPLIT / 2);
-    const float* xst = xscale + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
-    const float* xgt = xg + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
-    const int slot = k % A.slots;
-    const uint32_t* buf = bufs + static_cast<size_t>(slot) * A.buf_words;
-    if (!mbar_wait(smem_addr(full + slot), (k / A.slots) & 1)) return;
-    GroupChain ca, cb;
-    ca.init(buf + lane);
-    cb.init(buf + meta[k].second * 32u + lane);
-    float tot_a = 0.f, tot_b = 0.f;
-#pragma unroll 1
-    for (int q = 0; q < NQ; ++q) {
-      const bool hi = (seg * NQ + q) & 1;
+  if (warp >= A.warps) return;
+  const uint32_t lane_off = (lane & (R - 1)) << 2;
+  const unsigned int terms = static_cast<unsigned int>(M.KT * SPLIT);
+  // The warp that finishes the last unit of a tile row adds the row's partial products.  Counting a unit needs its
+  // partial products to be visible first; so that the fence never waits for stores that were only just issued, a
+  // unit is counted one unit late (cnt_tr), and the count comes back from memory while the warp is decoding the unit
+  // after that: (pend_tr, pend_done) is looked at two units after the stores.
+  constexpr unsigned int kNone = 0xFFFFFFFFu;
+  unsigned int cnt_tr = kNone, pend_tr = 0, pend_done = kNone;
+  auto resolve = [&]() {
+    const unsigned int done = __shfl_sync(0xffffffffu, pend_done, 0);
+    if (done == terms - 1u) {
+      __syncwarp();   // orders the loads below after lane 0's acquire; they bypass L1 (ld.cg)
+      float ya = 0.f, yb = 0.f;
+      const float* pr = A.partials + pend_tr * kTileRows + lane;
+      // terms is a multiple of SPLIT; 2 x 16 loads in flight per lane, then the adds in the fixed order
+      for (unsigned int t0 = 0; t0 < terms; t0 += 16) {
+        float va[16], vb[16];
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int g = q * 4 + jj;
-        int acc_a = 0, acc_b = 0;
-        sub_block<FMT, G, SPG, MASK>(ca, cb, tab_lane, xt + g * (GW / 2), acc_a, acc_b);
-        float s_a, o_a, s_b, o_b;
-        side_a.sub(hi, jj, s_a, o_a);
-        side_b.sub(hi, jj, s_b, o_b);
-        const float xsc = xst[g];
-        const float fa = static_cast<float>(acc_a) * xsc, fb = static_cast<float>(acc_b) * xsc;
-        if (HAS_OFFSET) {
-          const float gx = xgt[g];
-          tot_a += s_a * fa - o_a * gx;
-          tot_b += s_b * fb - o_b * gx;
-        } else {
-          tot_a = fmaf(s_a, fa, tot_a);
-          tot_b = fmaf(s_b, fb, tot_b);
+        for (int i = 0; i < 16; ++i) {
+          const bool in = t0 + i < terms;
+          va[i] = in ? __ldcg(pr + static_cast<size_t>(t0 + i) * M.N) : 0.f;
+          vb[i] = in ? __ldcg(pr + static_cast<size_t>(t0 + i) * M.N + 32) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          ya += va[i];
+          yb += vb[i];
         }
       }
-      side_a.next(hi);
-      side_b.next(hi);
+      A.y[pend_tr * kTileRows + lane] = ya;
+      A.y[pend_tr * kTileRows + lane + 32] = yb;
+      if (lane == 0) M.row_done[pend_tr] = 0u;
+    }
+    pend_done = kNone;
+  };
+  // lane 0 releases (at GPU scope) the stores that the warp barrier ordered before it, and counts the unit
+  auto count = [&]() {
+    resolve();
+    if (cnt_tr != kNone) {
+      __syncwarp();
+      pend_tr = cnt_tr;
+      if (lane == 0)
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(pend_done) : "l"(M.row_done + cnt_tr) : "memory");
+      cnt_tr = kNone;
+    }
+  };
+#pragma unroll 1
+  for (;;) {
+    int k = 0;
+    if (lane == 0) k = atomicAdd(next_unit, 1);
+    k = __shfl_sync(0xffffffffu, k, 0);
+    if (k >= nmine) break;
+    const uint4 raw = *reinterpret_cast<const uint4*>(meta + k);
+    const uint32_t lines = raw.y & 0xFFFFu, second = raw.y >> 16, tr = raw.z & 0xFFFFu, round = raw.z >> 16;
+    const uint32_t j = raw.w & 255u, seg = (raw.w >> 8) & 255u, slot = (raw.w >> 16) & 255u;
+    const bool slow = (second & 0x8000u) != 0;
+    const int tc = set + A.nsets * static_cast<int>(j);
+    const int na = static_cast<int>(tr) * kTileRows + lane, nb = na + 32;
+    const uint32_t* xt = xq + static_cast<size_t>(j) * kTileSyms + seg * USYM;
+    const float* xst = xscale + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
+    const float* xgt = xg + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
+    const uint32_t* buf = bufs + static_cast<size_t>(slot) * A.buf_words;
+    if (round > 0 && !wait_released(released + slot, round, A.err)) return;
+    if (!mbar_wait(smem_addr(full + slot), round & 1, A.err)) return;
+    UnitSide<FMT> side_a, side_b;
+    side_a.load(buf + lines * 32u - SIDEW, lane);
+    side_b.load(buf + lines * 32u - SIDEW, lane + 32);
+    GroupChain ca, cb;
+    ca.init(buf + lane);
+    cb.init(buf + (second & 0x7FFFu) * 32u + lane);
+    float tot_a = 0.f, tot_b = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      int acc_a = 0, acc_b = 0;
+      if (slow)
+        sub_block_slow<SPG>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG, acc_a, acc_b);
+      else
+        sub_block<G, SPG, MASK>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+      float s_a, o_a, s_b, o_b;
+      side_a.sub(jj, s_a, o_a);
+      side_b.sub(jj, s_b, o_b);
+      const float xsc = xst[jj];
+      const float fa = static_cast<float>(acc_a) * xsc, fb = static_cast<float>(acc_b) * xsc;
+      if (HAS_OFFSET) {
+        const float gx = xgt[jj];
+        tot_a += s_a * fa - o_a * gx;
+        tot_b += s_b * fb - o_b * gx;
+      } else {
+        tot_a = fmaf(s_a, fa, tot_a);
+        tot_b = fmaf(s_b, fb, tot_b);
+      }
     }
     // every lane has read its last word: hand the buffer back to the producer
     __syncwarp();
-    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + slot)) : "memory");
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + slot)) : "memory");
+      asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(released + slot)), "r"(round + 1u) : "memory");
+    }
+    count();   // the previous unit, whose stores have long landed
     float* prow = A.partials + static_cast<size_t>(tc * SPLIT + seg) * M.N;
     prow[na] = tot_a;
     prow[nb] = tot_b;
-    side_a = next_a;
-    side_b = next_b;
+    cnt_tr = tr;
   }
+  count();
+  resolve();
 }
 
 }  // namespace lw

@@ -1,0 +1,17 @@
+// Launcher of the batch-1 kernel (lw_gemv1.cuh; instantiated in lw_gemv1.cu) and helpers it shares with lw_kernels.cu.
+#pragma once
+#include "lw_kernels.h"
+
+namespace lw {
+
+// True if the matrix was laid out for the batch-1 kernel (default column split, pad 6 or 7, unit flags present).
+bool gemv1_usable(const MatDev& M);
+// y[N] = W x for one activation row; partials[KT * split][N] is scratch for the per-segment partial products (added
+// in a fixed order by the same kernel); `err` = device error word.
+int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* partials, float* y, unsigned int* err,
+                 cudaStream_t st);
+
+int note_launch(const char* what);   // counts a launch and returns the status of cudaGetLastError
+int sm_count();
+
+}  // namespace lw

@@ -278,8 +278,30 @@ int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, i
   return kOk;
 }
 
+// Grouped decoding (lw_gemv1.cuh) normalises the bit window once per group of g symbols and refills at most one word
+// after it.  With bp < 32 the window offset at the start of a group, that is exact iff every symbol of the group
+// starts at most 31 bits into the group and bp plus the group's bits stays below 64.  rel[i] = bit offset of symbol i
+// inside its chain (rel[n] = chain length); the phase of the groups restarts every `quad` symbols.
+static uint8_t scan_chain(const uint16_t* rel, int n, int quad) {
+  uint8_t bad = 0;
+  for (int g = kScanMinG; g <= kScanMaxG; ++g) {
+    uint32_t bp = 0;
+    bool ok = true;
+    for (int q0 = 0; q0 < n && ok; q0 += quad)
+      for (int i = q0; i < q0 + quad && ok; i += g) {
+        const int last = std::min(i + g, q0 + quad) - 1;   // last symbol of the group
+        if (rel[last] - rel[i] > 31) ok = false;
+        bp += rel[last + 1] - rel[i];
+        if (bp >= 64) ok = false;
+        if (bp >= 32) bp -= 32;
+      }
+    if (!ok) bad |= static_cast<uint8_t>(1u << (g - kScanMinG));
+  }
+  return bad;
+}
+
 int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, std::vector<uint32_t>* chain_start,
-              std::vector<uint32_t>* lane_end, uint8_t* out) {
+              std::vector<uint32_t>* lane_end, uint8_t* out, GroupScan* scan) {
   if (split != 1 && split != 2 && split != 4) {
     set_error("split must be 1, 2 or 4");
     return kErrArg;
@@ -294,12 +316,16 @@ int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, s
   const uint8_t* pay = reinterpret_cast<const uint8_t*>(v.payload());
   const uint64_t pay_bits = static_cast<uint64_t>(v.payload_words() - 2) * 32;   // the two tail words are padding
   std::atomic<int> bad(0);
+  if (scan) scan->mask.assign(static_cast<size_t>(v.T) * split, 0);
   parallel_for(v.T, threads, [&](int t) {
     if (bad.load(std::memory_order_relaxed)) return;
     const int tr = t / v.KT, tc = t % v.KT;
+    uint16_t rel[kTileSyms + 1];
     for (int lane = 0; lane < kLanes; ++lane) {
       uint64_t bp = starts[static_cast<size_t>(t) * kLanes + lane];
       for (int half = 0; half < 2; ++half) {
+        uint64_t chain0 = bp;
+        uint8_t longcode = 0;
         uint8_t* row = out ? out + (static_cast<size_t>(tr) * kTileRows + half * 32 + lane) * v.Ks + tc * kTileSyms
                            : nullptr;
         for (int c = 0; c < kTileSyms; ++c) {
@@ -318,7 +344,19 @@ int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, s
             return;
           }
           if (row) row[c] = static_cast<uint8_t>(e);
+          if (scan) {
+            if (c % seg == 0) {
+              chain0 = bp;
+              longcode = 0;
+            }
+            rel[c % seg] = static_cast<uint16_t>(bp - chain0);
+            if ((e >> 8) > 10) longcode = 0x80;
+          }
           bp += e >> 8;
+          if (scan && c % seg == seg - 1) {
+            rel[seg] = static_cast<uint16_t>(bp - chain0);
+            scan->mask[static_cast<size_t>(t) * split + c / seg] |= scan_chain(rel, seg, scan->quad_syms) | longcode;
+          }
         }
       }
       ends[static_cast<size_t>(t) * kLanes + lane] = static_cast<uint32_t>(bp);
@@ -352,11 +390,58 @@ int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, s
   return kOk;
 }
 
+// Scales of tile row `row`, column segment `seg` of tile column tc: the four sub-blocks that a work unit covers.
+// sc / mn: one value per byte; dd: fp16 d (low half) and fp16 dmin (reference block formulas: kernels/llmrt.cu:126-149).
+static void unit_scales(int fmt, const uint8_t* side_row, int tc, int seg, int split, uint32_t* sc, uint32_t* mn,
+                        uint32_t* dd) {
+  const int sb = side_bytes(fmt);
+  const int subs_per_tile = (is_paired(fmt) ? 512 : 256) / sub_width(fmt);
+  const int sub0 = tc * subs_per_tile + seg * (subs_per_tile / split);   // first sub-block, counted along the row
+  const int per_block = 256 / sub_width(fmt);                            // sub-blocks per super-block
+  const uint8_t* blk = side_row + static_cast<size_t>(sub0 / per_block) * sb;
+  const int j0 = sub0 % per_block;
+  *sc = *mn = 0;
+  if (fmt == kFmtQ6K) {
+    for (int j = 0; j < 4; ++j) *sc |= static_cast<uint32_t>(blk[j0 + j]) << (8 * j);
+    *dd = blk[16] | (blk[17] << 8);
+  } else if (fmt == kFmtIQ4XS) {
+    const uint32_t sh = blk[2] | (blk[3] << 8);
+    for (int j = 0; j < 4; ++j) {
+      const int jj = j0 + j;
+      const uint32_t ls = ((blk[4 + jj / 2] >> (4 * (jj & 1))) & 15u) | (((sh >> (2 * jj)) & 3u) << 4);
+      *sc |= ls << (8 * j);
+    }
+    *dd = blk[0] | (blk[1] << 8);
+  } else {
+    const uint8_t* q = blk + 4;   // llama.cpp get_scale_min_k4
+    for (int j = 0; j < 4; ++j) {
+      const int jj = j0 + j;
+      uint32_t s6, m6;
+      if (jj < 4) {
+        s6 = q[jj] & 63u;
+        m6 = q[jj + 4] & 63u;
+      } else {
+        s6 = (q[jj + 4] & 15u) | ((q[jj - 4] >> 6) << 4);
+        m6 = (q[jj + 4] >> 4) | ((q[jj] >> 6) << 4);
+      }
+      *sc |= s6 << (8 * j);
+      *mn |= m6 << (8 * j);
+    }
+    *dd = blk[0] | (blk[1] << 8) | (blk[2] << 16) | (static_cast<uint32_t>(blk[3]) << 24);
+  }
+}
+
 int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>& chain_start,
              const std::vector<uint32_t>& lane_end, int threads, std::vector<uint32_t>& group_base,
-             std::vector<uint32_t>& words, uint32_t* max_group_words, uint32_t* max_tile_words) {
+             std::vector<uint32_t>& words, uint32_t* max_group_words, uint32_t* max_tile_words, int fmt,
+             const uint8_t* side) {
   const int G = 2 * split;
   const size_t ngroups = static_cast<size_t>(v.T) * G;
+  const uint32_t side_words = side ? unit_side_words(fmt) : 0;
+  if (side && (is_paired(fmt) ? 512 : 256) / sub_width(fmt) != 4 * split) {
+    set_error("relayout: a column segment must hold exactly four sub-blocks to carry its scales");
+    return kErrArg;
+  }
   group_base.assign(ngroups + 1, 0);
   // group gi of a tile = (column segment gi / 2, rows half gi % 2): the two halves of a segment are adjacent, so a
   // warp that decodes rows l and l + 32 over one segment stages one contiguous piece.  In stream order the lane's
@@ -381,16 +466,17 @@ int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>&
       gw[t * G + g] = w;
       tile_words += w * kLanes;
     }
+    tile_words += side_words * split;
     mt = std::max(mt, tile_words);
     for (int seg = 0; seg < split; ++seg)
-      mg = std::max(mg, (gw[t * G + 2 * seg] + gw[t * G + 2 * seg + 1]) * kLanes);
+      mg = std::max(mg, (gw[t * G + 2 * seg] + gw[t * G + 2 * seg + 1]) * kLanes + side_words);
     for (int g = 0; g < G; ++g) {
       if (total > 0xFFFFFFFFull) {
         set_error("matrix needs more than 2^32 device words");
         return kErrTooLarge;
       }
       group_base[t * G + g] = static_cast<uint32_t>(total);
-      total += static_cast<uint64_t>(gw[t * G + g]) * kLanes;
+      total += static_cast<uint64_t>(gw[t * G + g]) * kLanes + ((g & 1) ? side_words : 0);
     }
   }
   if (total > 0xFFFFFFFFull) {
@@ -400,6 +486,7 @@ int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>&
   group_base[ngroups] = static_cast<uint32_t>(total);
   words.assign(total + kTailWords, 0);
   const uint32_t* pay = v.payload();
+  const size_t side_row_bytes = side ? static_cast<size_t>(v.Ks) * (is_paired(fmt) ? 2 : 1) / 256 * side_bytes(fmt) : 0;
   parallel_for(v.T, threads, [&](int t) {
     for (int g = 0; g < G; ++g) {
       uint32_t* dst = words.data() + group_base[static_cast<size_t>(t) * G + g];
@@ -419,6 +506,22 @@ int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>&
           const uint32_t left = nbits - i * 32;
           if (left < 32) w &= (1u << left) - 1;
           dst[static_cast<size_t>(i) * kLanes + lane] = w;
+        }
+      }
+      if (side_words && (g & 1)) {   // the unit's scales follow its second group
+        uint32_t* sd = dst + static_cast<size_t>(gw[static_cast<size_t>(t) * G + g]) * kLanes;
+        uint16_t* sh = reinterpret_cast<uint16_t*>(sd);
+        const int tr = t / v.KT, tc = t % v.KT;
+        for (int r = 0; r < kTileRows; ++r) {
+          uint32_t sc, mn, dd;
+          unit_scales(fmt, side + (static_cast<size_t>(tr) * kTileRows + r) * side_row_bytes, tc, g >> 1, split, &sc, &mn, &dd);
+          sd[r] = (fmt == kFmtQ4K || fmt == kFmtQ5K) ? dd : sc;
+          if (fmt == kFmtQ4K || fmt == kFmtQ5K) {
+            sd[64 + r] = sc;
+            sd[128 + r] = mn;
+          } else {
+            sh[128 + r] = static_cast<uint16_t>(dd);
+          }
         }
       }
     }

@@ -33,14 +33,26 @@ int make_view(const uint8_t* blob, size_t nbytes, int N, int Ks, BlobView& v);
 // lane starts; lane_end[t * 32 + l] = bit offset after its 512th symbol.  Checks that every window resolves, that
 // each lane ends where the next begins and that the last one ends inside the payload.  If `out` is not null the
 // decoded symbols are written to it as [N, Ks].
+// If `scan` is not null it also receives, per work unit of the batch-1 kernel, which symbol-group sizes its grouped
+// decoder may use.
+struct GroupScan {
+  int quad_syms = 64;          // in: symbols of a chain after which the group phase restarts (four sub-blocks)
+  std::vector<uint8_t> mask;   // out: [T * split] per (tile, column segment): bit (g - kScanMinG) set = groups of g
+                               // symbols are unsafe there; bit 7 = the unit holds a code longer than 10 bits
+};
+constexpr int kScanMinG = 3, kScanMaxG = 6;
 int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, std::vector<uint32_t>* chain_start,
-              std::vector<uint32_t>* lane_end, uint8_t* out);
+              std::vector<uint32_t>* lane_end, uint8_t* out, GroupScan* scan = nullptr);
 
 // Re-layout into interleaved chain groups (the role of interleave_huf8, kernels/llmrt.cu:1208-1257).
 // Every chain starts with `pad` zero bits (the fused kernels fold the table's entry size into the shift).
+// If `side` is not null (block format `fmt`, [N, K / 256 * side_bytes]) every work unit - the two groups of one
+// column segment - is followed by unit_side_words(fmt) words with the scales of its 64 rows x 4 sub-blocks, so that
+// the unit's one bulk copy brings everything its decoding needs (layout: unit_side_words below).
 int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>& chain_start,
              const std::vector<uint32_t>& lane_end, int threads, std::vector<uint32_t>& group_base,
-             std::vector<uint32_t>& words, uint32_t* max_unit_words, uint32_t* max_tile_words);
+             std::vector<uint32_t>& words, uint32_t* max_unit_words, uint32_t* max_tile_words, int fmt = kFmtNone,
+             const uint8_t* side = nullptr);
 
 // ---- bundle directory (reference: lazyweights/bundle.py:114-148)
 struct TensorEntry {

@@ -17,8 +17,12 @@
 #include <mutex>
 
 #include "lw_device.cuh"
+#include "lw_gemv1.h"
 
 namespace lw {
+
+// Error word set by kernels that give up on a wait instead of spinning for ever (bit 0: bulk-copy wait timed out).
+__device__ unsigned int g_kernel_error;
 
 constexpr int kWarpsPerBlock = 8;
 constexpr int kSlackWords = 96;   // read-ahead of the last chains of a tile lands here
@@ -40,7 +44,7 @@ __device__ __forceinline__ bool stage_tile(const MatDev& M, int t, uint32_t* buf
     bulk_load(smem_addr(buf), M.words + b0, (b1 - b0) * 4u, bar_a);
   }
   __syncwarp();
-  return mbar_wait(bar_a, 0);
+  return mbar_wait(bar_a, 0, &g_kernel_error);
 }
 
 // ------------------------------------------------------------------------------------------------ decode to codes
@@ -214,7 +218,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   }
   if (!active) return;
   __syncwarp();
-  if (!mbar_wait(bar_a, 0)) return;
+  if (!mbar_wait(bar_a, 0, &g_kernel_error)) return;
 
   Chain ca, cb;
   const int G = 2 * M.split, sub_per_seg = NG / M.split;
@@ -291,7 +295,6 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 }
 
 }  // namespace lw
-#include "lw_gemv1.cuh"
 #include "lw_gemm_tc.cuh"
 namespace lw {
 
@@ -330,6 +333,32 @@ static int check_cuda(const char* what) {
 static int check_launch(const char* what) {
   g_launches.fetch_add(1);
   return check_cuda(what);
+}
+
+int note_launch(const char* what) { return check_launch(what); }
+
+int sm_count() {
+  static const int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 1;
+  }();
+  return n;
+}
+
+// Device address of the error word, for kernels of other translation units.
+static unsigned int* error_word() {
+  static std::mutex mu;
+  static unsigned int* per_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev] && cudaGetSymbolAddress(reinterpret_cast<void**>(&per_device[dev]), g_kernel_error) != cudaSuccess) {
+    cudaGetLastError();
+    per_device[dev] = nullptr;
+  }
+  return per_device[dev];
 }
 
 static size_t stage_bytes(const MatDev& M) { return static_cast<size_t>(tile_buf_words(M.max_tile_words)) * 4; }
@@ -428,110 +457,6 @@ static int launch_gemv_f(const MatDev& M, const XT* X, int m, float* P, cudaStre
   return kErrArg;
 }
 
-static int sm_count() {
-  static const int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 1;
-  }();
-  return n;
-}
-
-// ---- batch-1 kernel: one persistent block per SM; see lw_gemv1.cuh
-constexpr size_t kSmemLimit = 227 * 1024;
-constexpr int kMaxStagedColumns = 16;   // tile columns whose activations one block keeps in shared memory
-
-struct Gemv1Plan {
-  int warps, producers, prefetch, slots, nsets, cols_per_set, blocks;
-  uint32_t buf_words;
-  size_t smem;
-};
-
-template <int FMT, int SPLIT>
-static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
-  constexpr int TW = is_paired(FMT) ? 512 : 256;
-  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
-  p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
-  p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
-  // a chain reader looks up to three words past its chain; for all buffers but the last that lands in the next buffer
-  // (harmless: those bits are never used), so only the end of the ring needs slack
-  p.buf_words = (M.max_unit_words + 31u) & ~31u;
-  const size_t fixed0 = kReplicatedTableBytes +
-                        static_cast<size_t>(p.cols_per_set) * (TW / 2 + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
-                       2 * kGemv1MaxSlots * 8 + kGemv1MaxUnits * sizeof(UnitMeta);
-  const size_t fixed = fixed0 + kSlackWords * 4;
-  if (fixed + static_cast<size_t>(p.buf_words) * 4 > kSmemLimit) return false;
-  const int units = (M.N / kTileRows) * M.KT * SPLIT;
-  p.blocks = std::max(p.nsets, std::min(sm_count(), units));
-  if ((units + p.blocks - 1) / p.blocks + 1 > kGemv1MaxUnits) return false;
-  // as many staging buffers as fit; about three consumers per four buffers, so that copies run ahead of the decoding
-  p.slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));
-  p.warps = std::max(1, std::min(kGemv1MaxWarps, p.slots * 3 / 4));
-  if (const char* e = getenv("LW_GEMV1_WARPS")) p.warps = std::max(1, std::min(std::min(kGemv1MaxWarps, p.slots), atoi(e)));
-  p.producers = 3;
-  p.prefetch = 0;
-  if (const char* e = getenv("LW_GEMV1_PRODUCERS")) p.producers = std::max(1, std::min(4, atoi(e)));
-  if (const char* e = getenv("LW_GEMV1_PREFETCH")) p.prefetch = std::max(0, atoi(e));
-  p.smem = fixed + static_cast<size_t>(p.slots) * p.buf_words * 4;
-  return true;
-}
-
-template <int FMT, int G, int IDXBITS, int SPLIT>
-static int launch_gemv1_t(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
-  Gemv1Plan p;
-  if (!plan_gemv1<FMT, SPLIT>(M, p)) {
-    set_kernel_error_text("gemv1", "work unit does not fit shared memory");
-    return kErrTooLarge;
-  }
-  int rc;
-  if ((rc = prepare(k_gemv1<FMT, G, IDXBITS, SPLIT>, p.smem))) return rc;
-  Gemv1Args a;
-  a.x = X;
-  a.partials = P;
-  a.x_is_half = x_is_half;
-  a.warps = p.warps;
-  a.slots = p.slots;
-  a.producers = p.producers;
-  a.prefetch = p.prefetch;
-  a.buf_words = p.buf_words;
-  a.nsets = p.nsets;
-  a.cols_per_set = p.cols_per_set;
-  k_gemv1<FMT, G, IDXBITS, SPLIT><<<p.blocks, (p.warps + p.producers) * 32, p.smem, st>>>(M, a);
-  return check_launch("k_gemv1");
-}
-
-template <int FMT, int SPLIT>
-static int launch_gemv1_g(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
-  if (M.pad == 7) {
-    if (M.max_len <= 8) return launch_gemv1_t<FMT, 4, 10, SPLIT>(M, X, x_is_half, P, st);
-    return launch_gemv1_t<FMT, 3, 10, SPLIT>(M, X, x_is_half, P, st);
-  }
-  return launch_gemv1_t<FMT, 2, 11, SPLIT>(M, X, x_is_half, P, st);
-}
-
-template <int FMT>
-static int launch_gemv1_s(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
-  if (M.split == 4 && FMT != kFmtQ5K) return launch_gemv1_g<FMT, (FMT == kFmtQ5K ? 2 : 4)>(M, X, x_is_half, P, st);
-  if (M.split == 2) return launch_gemv1_g<FMT, 2>(M, X, x_is_half, P, st);
-  return launch_gemv1_g<FMT, 1>(M, X, x_is_half, P, st);
-}
-
-static int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P, cudaStream_t st) {
-  switch (M.fmt) {
-    case kFmtQ4K: return launch_gemv1_s<kFmtQ4K>(M, X, x_is_half, P, st);
-    case kFmtQ5K: return launch_gemv1_s<kFmtQ5K>(M, X, x_is_half, P, st);
-    case kFmtIQ4XS: return launch_gemv1_s<kFmtIQ4XS>(M, X, x_is_half, P, st);
-    default: return launch_gemv1_s<kFmtQ6K>(M, X, x_is_half, P, st);
-  }
-}
-
-static bool gemv1_usable(const MatDev& M) {
-  const bool pad_ok = (M.pad == 7 && M.max_len <= 10) || M.pad == 6;
-  const bool fmt_ok = M.fmt >= kFmtQ4K && M.fmt <= kFmtIQ4XS;
-  return pad_ok && fmt_ok && (M.split == 1 || M.split == 2 || (M.split == 4 && M.fmt != kFmtQ5K));
-}
-
 static int gemv1_variant() {
   static const int v = [] {
     const char* e = getenv("LW_GEMV1");
@@ -548,8 +473,7 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
   }
   int rc, terms = M.KT;
   if (m == 1 && gemv1_variant() != 0 && gemv1_usable(M)) {
-    rc = launch_gemv1(M, X, x_is_half, partials, st);
-    terms = M.KT * M.split;
+    return launch_gemv1(M, X, x_is_half, partials, Y, error_word(), st);   // adds its partial products itself
   } else {
     rc = x_is_half ? launch_gemv_f<__half>(M, static_cast<const __half*>(X), m, partials, st)
                    : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);

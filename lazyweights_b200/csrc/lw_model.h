@@ -20,6 +20,7 @@ struct Matrix {
   bool paired = false;
   long long blob_bytes = 0, side_bytes = 0, file_offset = -1;
   size_t device_bytes = 0;
+  double slow_fraction = 0.0;   // share of work units the batch-1 kernel decodes symbol by symbol
   void* d_block = nullptr;   // one allocation: table, group bases, words, side bytes
   MatDev dev{};
 };

@@ -64,6 +64,12 @@ class _Handle:
                                 side_bytes=sb.value, device_bytes=db.value, paired=fmt.value in (1, 4))
         return self._info[name]
 
+    def plan(self, name):
+        """How the batch-1 kernel decodes this matrix: {"group", "index_bits", "slow_fraction"}."""
+        g, ib, f = C.c_int(), C.c_int(), C.c_double()
+        nat.check(nat.lib().lw_matrix_plan(self._h, self.matrix_id(name), C.byref(g), C.byref(ib), C.byref(f)))
+        return dict(group=g.value, index_bits=ib.value, slow_fraction=f.value)
+
     # ---- device-pointer path
     def linear(self, name, x, out=None):
         """x: CUDA tensor [m, K] or [K], fp16 or fp32 -> fp32 [m, N] (or [N])."""

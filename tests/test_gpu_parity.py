@@ -130,6 +130,37 @@ def test_many_rows_tensor_core_path(lw):
         assert helpers.rel_err(y, orc.gemv_f64(w, x.astype(np.float32))) <= helpers.GEMV_TOL
 
 
+@pytest.mark.parametrize("ty,n,k", [("Q4_K", 256, 2048), ("Q5_K", 192, 1024), ("Q6_K", 320, 1024), ("IQ4_XS", 128, 2560)])
+@pytest.mark.parametrize("force", [None, ("3", "11"), ("max", "10"), ("max", "11")])
+def test_batch1_grouped_and_symbol_by_symbol_units(lw, monkeypatch, ty, n, k, force):
+    """The batch-1 kernel decodes groups of symbols per refill where the loader proved that exact and single symbols
+    elsewhere; both kinds of work unit, every group size and both table widths must give the oracle's product."""
+    import torch
+    q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=n * 7 + k)
+    # one work unit full of codes from the tails of the distribution (long codes, many bits per group)
+    tails = {"Q4_K": [0, 1, 2, 14, 15], "IQ4_XS": [0, 1, 2, 14, 15], "Q5_K": [0, 1, 2, 3, 4, 5, 27, 28, 29, 30, 31],
+             "Q6_K": list(range(0, 11)) + list(range(54, 64))}[ty]
+    q[64:128, 64:128] = rng.choice(tails, (64, 64))
+    sym, w = orc.symbols_of(ty, q), orc.dequant(ty, q, side)
+    if force:
+        gmax = "4" if ty in ("Q4_K", "IQ4_XS") else "6"
+        monkeypatch.setenv("LW_GEMV1_G", gmax if force[0] == "max" else force[0])
+        monkeypatch.setenv("LW_GEMV1_IDX", force[1])
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    with lw.CodedMatrix(blob, n, sym.shape[1], ty, side) as mat:
+        plan = mat.plan("m")
+        assert plan["group"] >= 3 and plan["index_bits"] in (10, 11)
+        if force:
+            assert str(plan["index_bits"]) == force[1]
+            if force[0] == "max":
+                assert 0.0 < plan["slow_fraction"] <= 1.0
+        x = rng.standard_normal(k).astype(np.float32)
+        y = mat.linear("m", torch.from_numpy(x).cuda()).cpu().numpy()
+        assert helpers.rel_err(y, orc.gemv_f64(w, x[None])[0]) <= helpers.GEMV_TOL
+        y16 = mat.linear("m", torch.from_numpy(x.astype(np.float16)).cuda()).cpu().numpy()
+        assert helpers.rel_err(y16, orc.gemv_f64(w, x.astype(np.float16).astype(np.float32)[None])[0]) <= helpers.GEMV_TOL
+
+
 def test_worst_case_code_lengths(lw):
     """Every symbol 11 bits long is the largest tile the format allows; the staging buffers must take it."""
     rng = np.random.default_rng(5)
