@@ -82,37 +82,42 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   scan.quad_syms = 4 * sub_syms(mx.fmt);
   const bool grouped = mx.fmt != kFmtNone && split == default_split(mx.fmt);
   if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr, grouped ? &scan : nullptr))) return rc;
-  // The batch-1 kernel's table: 1024 windows x 32 copies (codes up to 10 bits, no bank conflicts; units that hold a
-  // longer code take the kernel's slow path) or 2048 windows x 16 copies; and the largest group size that leaves few
-  // units on the slow path.  Estimated cost per symbol: 5.6 instructions + 9 per group (+ 8 % for the conflicts of the
-  // 16-copy table); a slow unit costs about 25.  LW_GEMV1_G / LW_GEMV1_IDX override.
+  // The batch-1 kernel's table: 1024 windows (codes up to 10 bits; units that hold a longer code are decoded symbol
+  // by symbol) or 2048, 16 copies each; and the group size: units where groups of g symbols are not exact fall back
+  // to groups of two.  Estimated cost per symbol: 8.3 instructions + 10 per group; the larger table leaves a third
+  // fewer staging buffers (+ 8 %); symbol by symbol costs about 30.  LW_GEMV1_G / LW_GEMV1_IDX override.
   int idx_bits = tab->max_len <= 10 ? 10 : 11, group = 0;
   if (grouped) {
     const int gmax = is_paired(mx.fmt) ? 4 : kScanMaxG;
     const char* eg = getenv("LW_GEMV1_G");
     const char* ei = getenv("LW_GEMV1_IDX");
     double best = 1e30;
+    const double n = static_cast<double>(std::max<size_t>(1, scan.mask.size()));
     for (int ib = 10; ib <= 11; ++ib) {
       if (ei && atoi(ei) != ib) continue;
       for (int g = kScanMinG; g <= gmax; ++g) {
         if (eg && atoi(eg) != g) continue;
-        const uint8_t bits = static_cast<uint8_t>((1u << (g - kScanMinG)) | (ib == 10 ? 0x80u : 0u));
-        size_t slow = 0;
-        for (uint8_t m : scan.mask) slow += (m & bits) != 0;
-        const double f = static_cast<double>(slow) / std::max<size_t>(1, scan.mask.size());
-        const double cost = (1.0 - f) * (5.6 + 9.0 / g) * (ib == 11 ? 1.08 : 1.0) + f * 30.0;
+        const uint8_t gbit = static_cast<uint8_t>(1u << (g - kScanMinG));
+        size_t two = 0, single = 0;
+        for (uint8_t m : scan.mask) {
+          if (ib == 10 && (m & 0x80u)) ++single;
+          else if (m & gbit) ++two;
+        }
+        const double f2 = two / n, f1 = single / n;
+        const double cost = ((1.0 - f2 - f1) * (8.3 + 10.0 / g) + f2 * 13.3) * (ib == 11 ? 1.08 : 1.0) + f1 * 30.0;
         if (cost < best) {
           best = cost;
           group = g;
           idx_bits = ib;
-          im.slow_fraction = f;
+          im.slow_fraction = f1 + f2;
         }
       }
     }
     if (group) {
-      const uint8_t bits = static_cast<uint8_t>((1u << (group - kScanMinG)) | (idx_bits == 10 ? 0x80u : 0u));
+      const uint8_t gbit = static_cast<uint8_t>(1u << (group - kScanMinG));
       im.unit_slow.resize(scan.mask.size());
-      for (size_t i = 0; i < scan.mask.size(); ++i) im.unit_slow[i] = (scan.mask[i] & bits) != 0;
+      for (size_t i = 0; i < scan.mask.size(); ++i)
+        im.unit_slow[i] = (idx_bits == 10 && (scan.mask[i] & 0x80u)) ? 2 : (scan.mask[i] & gbit) ? 1 : 0;
     }
   }
   // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's

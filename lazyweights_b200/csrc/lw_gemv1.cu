@@ -127,6 +127,10 @@ int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P, float
     set_kernel_error_text("gemv1", "no device error word");
     return kErrCuda;
   }
+  if ((reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(P)) & 15u) {
+    set_kernel_error_text("gemv1", "the result and the scratch must be 16-byte aligned");
+    return kErrArg;
+  }
   switch (M.fmt) {
     case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, P, Y, err, st);
     case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, P, Y, err, st);

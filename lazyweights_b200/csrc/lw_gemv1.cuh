@@ -21,8 +21,9 @@
 //    a group starts (two funnel shifts), the G symbols only add their lengths to a local offset, one predicated word
 //    shift follows.  That is exact only while every symbol of a group starts within 31 bits of the group and one word
 //    per group keeps up; the loader (lw::walk_blob) checks both for every chain of the matrix, picks the largest G that
-//    leaves few exceptions, and flags the work units that hold one.  A flagged unit (and, with the 10-bit table, a unit
-//    that holds an 11-bit code) is decoded symbol by symbol through a single-copy table (8 KB of shared memory).
+//    leaves few exceptions, and flags the work units that hold one: those run with groups of two symbols, which is
+//    exact for any data.  With the 10-bit table, a unit that holds an 11-bit code is decoded symbol by symbol through
+//    a single-copy table of all 2048 windows (8 KB of shared memory).
 //  * The chain words are staged in shared memory by bulk copies (cp.async.bulk + mbarrier), one per work unit, issued
 //    by a few lanes of dedicated producer warps.  Reading them from global memory instead cannot be hidden: a register
 //    that is still being loaded cannot be shifted along the window without waiting for it, and per-lane cp.async rings
@@ -160,7 +161,7 @@ constexpr int kGemv1MaxUnits = 1024;       // work units one block can be dealt
 
 struct Gemv1Args {
   const void* x;          // activations [K], fp16 or fp32
-  float* partials;        // [KT * SPLIT][N]
+  float* partials;        // [N / 64][KT * SPLIT][64]: per tile row, one 64-row partial product per work unit
   float* y;               // [N] result
   unsigned int* err;      // device error word (bit 0: a bounded wait gave up)
   int x_is_half;
@@ -178,7 +179,8 @@ struct Gemv1Args {
 struct UnitMeta {          // 16 bytes: one shared-memory load per unit
   uint32_t src;           // word offset of the unit's first group
   uint16_t lines;         // size of both groups in 128-byte lines (a group is a whole number of lines)
-  uint16_t second;        // offset of the second group inside the unit, in lines; bit 15: decode symbol by symbol
+  uint16_t second;        // offset of the second group inside the unit, in lines; bits 14-15: unit class (0 = groups
+                          // of G symbols, 1 = groups of two, 2 = symbol by symbol)
   uint16_t tr;            // tile row
   uint16_t round;         // use of its staging buffer: unit index / slots
   uint8_t j, seg, slot;   // tile column within the block's set, column segment, staging buffer: unit index % slots
@@ -209,6 +211,34 @@ __device__ __forceinline__ bool wait_released(const uint32_t* released, uint32_t
   }
   atomicOr(err, 1u);
   return false;
+}
+
+// y[64 rows of one tile row] = sum over `terms` partial products, p[term][64].  Lane l adds rows 4 (l % 16) .. + 3 of
+// the terms of its parity (l / 16) in ascending order, then the two parities are added: a fixed order.  Kept out of
+// line so that it gets registers of its own: inlined into the decoder (64 registers, all in use) the loads were issued
+// one at a time, 128 round trips to L2 per sum.
+__device__ __noinline__ void row_sum(const float* p, unsigned int terms, float* y, int lane) {
+  const float4* q = reinterpret_cast<const float4*>(p) + lane;   // float4 i of the block: term i / 16, rows 4 (i % 16)
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const unsigned int steps = terms / 2;                          // two terms per step of 32 float4
+  for (unsigned int s0 = 0; s0 < steps; s0 += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      v[i] = s0 + i < steps ? __ldcg(q + static_cast<size_t>(s0 + i) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      acc.x += v[i].x;
+      acc.y += v[i].y;
+      acc.z += v[i].z;
+      acc.w += v[i].w;
+    }
+  }
+  acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16);
+  acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
+  acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16);
+  acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
+  if (lane < 16) reinterpret_cast<float4*>(y)[lane] = acc;
 }
 
 template <int FMT, int G, int IDXBITS, int LOG_R>
@@ -292,7 +322,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     const int k = k0 + lane;
     const bool valid = k < nmine;
     int tr = 0, j = 0, seg = 0;
-    uint32_t g0 = 0, g1 = 0, g2 = 0, slow = 0;
+    uint32_t g0 = 0, g1 = 0, g2 = 0, cls = 0;
     if (valid) {
       coords(bi + k * nb_set, tr, j, seg);
       const int t = tr * M.KT + set + A.nsets * j;
@@ -300,8 +330,9 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       g0 = __ldg(gb);
       g1 = __ldg(gb + 1);
       g2 = __ldg(gb + 2);
-      slow = __ldg(M.unit_slow + static_cast<size_t>(t) * SPLIT + seg);
+      cls = __ldg(M.unit_slow + static_cast<size_t>(t) * SPLIT + seg);
     }
+    const bool slow = cls == 2;
     const uint32_t bs = __ballot_sync(0xffffffffu, valid && slow), bf = __ballot_sync(0xffffffffu, valid && !slow);
     int base_s = 0, base_f = 0;
     if (lane == 0) {
@@ -315,7 +346,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       const int pos = slow ? base_s + __popc(bs & below) : nmine - 1 - (base_f + __popc(bf & below));
       meta[pos] = UnitMeta{g0,
                            static_cast<uint16_t>((g2 - g0) >> 5),
-                           static_cast<uint16_t>(((g1 - g0) >> 5) | (slow ? 0x8000u : 0u)),
+                           static_cast<uint16_t>(((g1 - g0) >> 5) | (cls << 14)),
                            static_cast<uint16_t>(tr),
                            static_cast<uint16_t>(pos / A.slots),
                            static_cast<uint8_t>(j),
@@ -406,34 +437,16 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   const uint32_t lane_off = (lane & (R - 1)) << 2;
   const unsigned int terms = static_cast<unsigned int>(M.KT * SPLIT);
   // The warp that finishes the last unit of a tile row adds the row's partial products.  Counting a unit needs its
-  // partial products to be visible first; so that the fence never waits for stores that were only just issued, a
-  // unit is counted one unit late (cnt_tr), and the count comes back from memory while the warp is decoding the unit
-  // after that: (pend_tr, pend_done) is looked at two units after the stores.
+  // partial products to be visible first, and the count takes a round trip to L2 (about 2000 cycles each under load).
+  // Both hide inside the decoding of the warp's next unit: the unit is counted (cnt_tr) after that one's first
+  // sub-block, when its stores have long landed, and the answer (pend_tr, pend_done) is looked at after the third.
   constexpr unsigned int kNone = 0xFFFFFFFFu;
   unsigned int cnt_tr = kNone, pend_tr = 0, pend_done = kNone;
   auto resolve = [&]() {
     const unsigned int done = __shfl_sync(0xffffffffu, pend_done, 0);
     if (done == terms - 1u) {
       __syncwarp();   // orders the loads below after lane 0's acquire; they bypass L1 (ld.cg)
-      float ya = 0.f, yb = 0.f;
-      const float* pr = A.partials + pend_tr * kTileRows + lane;
-      // terms is a multiple of SPLIT; 2 x 16 loads in flight per lane, then the adds in the fixed order
-      for (unsigned int t0 = 0; t0 < terms; t0 += 16) {
-        float va[16], vb[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const bool in = t0 + i < terms;
-          va[i] = in ? __ldcg(pr + static_cast<size_t>(t0 + i) * M.N) : 0.f;
-          vb[i] = in ? __ldcg(pr + static_cast<size_t>(t0 + i) * M.N + 32) : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          ya += va[i];
-          yb += vb[i];
-        }
-      }
-      A.y[pend_tr * kTileRows + lane] = ya;
-      A.y[pend_tr * kTileRows + lane + 32] = yb;
+      row_sum(A.partials + static_cast<size_t>(pend_tr) * terms * kTileRows, terms, A.y + pend_tr * kTileRows, lane);
       if (lane == 0) M.row_done[pend_tr] = 0u;
     }
     pend_done = kNone;
@@ -458,9 +471,8 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     const uint4 raw = *reinterpret_cast<const uint4*>(meta + k);
     const uint32_t lines = raw.y & 0xFFFFu, second = raw.y >> 16, tr = raw.z & 0xFFFFu, round = raw.z >> 16;
     const uint32_t j = raw.w & 255u, seg = (raw.w >> 8) & 255u, slot = (raw.w >> 16) & 255u;
-    const bool slow = (second & 0x8000u) != 0;
+    const uint32_t cls = second >> 14;
     const int tc = set + A.nsets * static_cast<int>(j);
-    const int na = static_cast<int>(tr) * kTileRows + lane, nb = na + 32;
     const uint32_t* xt = xq + static_cast<size_t>(j) * kTileSyms + seg * USYM;
     const float* xst = xscale + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
     const float* xgt = xg + static_cast<size_t>(j) * (TW / GW) + seg * NSU;
@@ -472,18 +484,22 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     side_b.load(buf + lines * 32u - SIDEW, lane + 32);
     GroupChain ca, cb;
     ca.init(buf + lane);
-    cb.init(buf + (second & 0x7FFFu) * 32u + lane);
+    cb.init(buf + (second & 0x3FFFu) * 32u + lane);
     float tot_a = 0.f, tot_b = 0.f;
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       int acc_a = 0, acc_b = 0;
-      if (slow)
-        sub_block_slow<SPG>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG, acc_a, acc_b);
-      else
+      if (cls == 0)
         sub_block<G, SPG, MASK>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+      else if (cls == 1)
+        sub_block<2, SPG, MASK>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+      else
+        sub_block_slow<SPG>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG, acc_a, acc_b);
       float s_a, o_a, s_b, o_b;
       side_a.sub(jj, s_a, o_a);
       side_b.sub(jj, s_b, o_b);
+      if (jj == 0) count();
+      if (jj == 2) resolve();
       const float xsc = xst[jj];
       const float fa = static_cast<float>(acc_a) * xsc, fb = static_cast<float>(acc_b) * xsc;
       if (HAS_OFFSET) {
@@ -501,10 +517,9 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + slot)) : "memory");
       asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(released + slot)), "r"(round + 1u) : "memory");
     }
-    count();   // the previous unit, whose stores have long landed
-    float* prow = A.partials + static_cast<size_t>(tc * SPLIT + seg) * M.N;
-    prow[na] = tot_a;
-    prow[nb] = tot_b;
+    float* prow = A.partials + (static_cast<size_t>(tr) * terms + tc * SPLIT + seg) * kTileRows;
+    prow[lane] = tot_a;
+    prow[lane + 32] = tot_b;
     cnt_tr = tr;
   }
   count();

@@ -18,7 +18,8 @@ struct MatDev {
   const uint32_t* group_base;   // [T * groups + 1] word offset of every chain group
   const uint32_t* words;        // interleaved chain words (+ zero tail)
   const uint8_t* side;          // [N, K / 256 * side_bytes] or null (symbols only)
-  const uint8_t* unit_slow;     // [T * split] 1 = the batch-1 kernel decodes this unit symbol by symbol (or null)
+  const uint8_t* unit_slow;     // [T * split] how the batch-1 kernel decodes the unit: 0 = groups of `group` symbols,
+                                // 1 = groups of two, 2 = symbol by symbol (or null: kernel not usable)
   unsigned int* row_done;       // [N / 64] units of a tile row finished by the running batch-1 product (zero between launches)
   int index_bits;               // windows of the batch-1 kernel's table = 1 << index_bits; its copies = 1 << (pad - 2)
   int group;                    // symbols per group of the batch-1 kernel's grouped decoder (0 = kernel not usable)
