@@ -107,12 +107,15 @@ int lw_matrix_info(void* handle, int id, int* N, int* K, int* fmt, long long* bl
 
 /* How the batch-1 kernel decodes matrix `id` (chosen from the data when the bundle is opened; no reference
  * counterpart): symbols per refill group (0 = that kernel is not used), index bits of its replicated table (10 or 11)
- * and the share of 64-row x quarter-tile work units that fall back to symbol-by-symbol decoding. */
+ * and the share of work units (64 rows x one column segment) that cannot use that group size and fall back to groups
+ * of two symbols or, for 11-bit codes under the 10-bit table, to symbol-by-symbol decoding. */
 int lw_matrix_plan(void* handle, int id, int* group, int* index_bits, double* slow_fraction);
 
 /* y[m, N] (fp32, row stride N) = x[m, K] . W^T for 1 <= m <= 8; x is fp16 (x_is_half != 0) or fp32, row-major, on
- * the device.  Launches on `stream` (a cudaStream_t) and does not synchronise.  This is the device-pointer form of
- * the reference's internal matmul(), kernels/llmrt.cu:1794-1826. */
+ * the device; y_dev must be 16-byte aligned.  Launches on `stream` (a cudaStream_t) and does not synchronise.  This
+ * is the device-pointer form of the reference's internal matmul(), kernels/llmrt.cu:1794-1826.  Products of one
+ * handle must not overlap on the GPU (they share its split-K scratch, and for m = 1 the matrix's tile-row counters):
+ * issue them on one stream, as the reference's runtime does. */
 int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
 
 /* The same product as lw_linear for callers that must not allocate device memory while they run: code that executes
@@ -157,6 +160,17 @@ int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks);
 
 /* Threaded host decode of a blob to symbols [N, Ks] (the algorithm of cpu_decode, kernels/llmrt.cu:2513-2541). */
 int lw_cpu_decode(const uint8_t* blob, long long blob_bytes, int N, int Ks, int threads, uint8_t* out);
+
+/* Host only (no GPU needed): validates a blob and builds the device layout that lw_matrix_create would upload, for
+ * inspection and for tests that replay the kernels' bit arithmetic on the CPU.  info[0..7] = column segments per tile
+ * row, pad bits per chain, symbols per refill group of the batch-1 kernel (0 = not used), index bits of its table,
+ * entries of group_base, entries of unit_class, words of scales behind every work unit, longest unit in words.
+ * Returns the number of layout words (negative status on error); each array is filled if its capacity suffices
+ * (call once with zero capacities to learn the sizes).  `side` may be null for fmt = LW_FMT_NONE.  No reference
+ * counterpart (the reference's interleave_huf8 re-layout, kernels/llmrt.cu:1208-1257, is internal to rt_open). */
+long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
+                         long long side_bytes, int* info, uint32_t* group_base, long long group_base_cap,
+                         uint32_t* words, long long words_cap, uint8_t* unit_class, long long unit_class_cap);
 
 /* ---- diagnostics ------------------------------------------------------------------------------------------ */
 

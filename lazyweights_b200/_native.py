@@ -33,6 +33,9 @@ _SIGNATURES = {
     "lw_tp_unique_id": (C.c_int, [C.c_void_p]),
     "rt_tp_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "lw_matrix_id": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "lw_host_layout": (C.c_longlong, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong,
+                                      C.POINTER(C.c_int), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
+                                      C.c_void_p, C.c_longlong]),
     "lw_matrix_plan": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_double)]),
     "lw_matrix_info": (C.c_int, [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 3 + [C.POINTER(C.c_longlong)] * 3),
     "lw_linear": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

@@ -52,6 +52,26 @@ def cpu_decode_huf8(blob, N, K, threads=0):
     return out
 
 
+def host_layout(blob, N, Ks, fmt="none", side=None):
+    """The device layout of one blob, built on the host (no GPU): dict with split, pad, group, index_bits,
+    unit_side_words, max_unit_words and the arrays group_base (uint32), words (uint32), unit_class (uint8)."""
+    b, bp = _u8(np.frombuffer(blob, np.uint8))
+    s = np.ascontiguousarray(side, np.uint8).reshape(-1) if side is not None else np.zeros(0, np.uint8)
+    sp = s.ctypes.data_as(C.c_void_p) if s.size else None
+    info = (C.c_int * 8)()
+    n = nat.lib().lw_host_layout(bp, b.size, N, Ks, nat.FMT[fmt], sp, s.size, info, None, 0, None, 0, None, 0)
+    if n < 0:
+        nat.check(int(n))
+    gb, words, uc = np.zeros(info[4], np.uint32), np.zeros(n, np.uint32), np.zeros(info[5], np.uint8)
+    n = nat.lib().lw_host_layout(bp, b.size, N, Ks, nat.FMT[fmt], sp, s.size, info, gb.ctypes.data_as(C.c_void_p),
+                                 gb.size, words.ctypes.data_as(C.c_void_p), words.size,
+                                 uc.ctypes.data_as(C.c_void_p), uc.size)
+    if n < 0:
+        nat.check(int(n))
+    return dict(split=info[0], pad=info[1], group=info[2], index_bits=info[3], unit_side_words=info[6],
+                max_unit_words=info[7], group_base=gb, words=words, unit_class=uc)
+
+
 def decode_huf8(blob, N, K):
     """blob -> uint8 [N, K] symbols, decoded by the CUDA kernel."""
     from .runtime import CodedMatrix

@@ -151,7 +151,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   const size_t off_side = align_up(off_words + im.words.size() * 4, 256);
   const size_t off_slow = off_side + align_up(side_nbytes, 256);
   const size_t off_done = off_slow + align_up(im.unit_slow.size(), 256);
-  const size_t total = off_done + align_up(static_cast<size_t>(mx.N / kTileRows) * 4, 256);
+  const size_t total = off_done + align_up(static_cast<size_t>(mx.N / kTileRows) * kRowDoneStride * 4, 256);
   cudaError_t e = cudaMalloc(&mx.d_block, total);
   if (e != cudaSuccess) return cuda_fail("cudaMalloc (matrix)", e);
   uint8_t* d = static_cast<uint8_t*>(mx.d_block);
@@ -648,6 +648,43 @@ static int host_view(const uint8_t* blob, long long nbytes, int N, int Ks, std::
   int rc = make_view(copy.data(), static_cast<size_t>(nbytes), N, Ks, v);
   if (rc) return rc;
   return table_from_lut(v.lut(), tab);
+}
+
+long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
+                         long long side_bytes, int* info, uint32_t* group_base, long long group_base_cap,
+                         uint32_t* words, long long words_cap, uint8_t* unit_class, long long unit_class_cap) {
+  if (!blob || blob_bytes <= 0 || !info || fmt < kFmtNone || fmt > kFmtIQ4XS) {
+    set_error("lw_host_layout: bad argument");
+    return kErrArg;
+  }
+  Matrix mx;
+  mx.name = "m";
+  mx.N = N;
+  mx.Ks = Ks;
+  mx.fmt = fmt;
+  mx.paired = is_paired(fmt);
+  mx.K = mx.paired ? 2 * Ks : Ks;
+  std::vector<uint8_t> copy(static_cast<size_t>(blob_bytes) + 16, 0);   // the walk reads 8 bytes at a time
+  std::memcpy(copy.data(), blob, static_cast<size_t>(blob_bytes));
+  HostImage im;
+  const int rc = prepare_matrix(mx, copy.data(), static_cast<size_t>(blob_bytes), side,
+                                static_cast<size_t>(std::max(0ll, side_bytes)), default_threads(), im);
+  if (rc) return rc;
+  info[0] = im.split;
+  info[1] = im.pad;
+  info[2] = im.unit_slow.empty() ? 0 : im.group;
+  info[3] = im.index_bits;
+  info[4] = static_cast<int>(im.group_base.size());
+  info[5] = static_cast<int>(im.unit_slow.size());
+  info[6] = im.unit_slow.empty() ? 0 : unit_side_words(fmt);
+  info[7] = static_cast<int>(im.max_unit);
+  if (group_base && group_base_cap >= static_cast<long long>(im.group_base.size()))
+    std::memcpy(group_base, im.group_base.data(), im.group_base.size() * 4);
+  if (words && words_cap >= static_cast<long long>(im.words.size()))
+    std::memcpy(words, im.words.data(), im.words.size() * 4);
+  if (unit_class && unit_class_cap >= static_cast<long long>(im.unit_slow.size()) && !im.unit_slow.empty())
+    std::memcpy(unit_class, im.unit_slow.data(), im.unit_slow.size());
+  return static_cast<long long>(im.words.size());
 }
 
 int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks) {

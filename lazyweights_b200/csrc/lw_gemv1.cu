@@ -32,19 +32,20 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   // a chain reader looks up to three words past its chain; for all buffers but the last that lands in the next buffer
   // (harmless: those bits are never used), so only the end of the ring needs slack
   p.buf_words = (M.max_unit_words + 31u) & ~31u;
-  const int units = (M.N / kTileRows) * M.KT * SPLIT;
-  p.blocks = std::max(p.nsets, std::min(sm_count(), units));
+  const int tiles = (M.N / kTileRows) * M.KT;
+  p.blocks = std::max(p.nsets, std::min(sm_count(), tiles));
   p.max_units = 0;   // the longest list any block gets: blocks b, b + nsets, ... serve the tile columns of set b % nsets
   for (int set = 0; set < p.nsets; ++set) {
     const int nb_set = (p.blocks - set + p.nsets - 1) / p.nsets, ncol = (M.KT - set + p.nsets - 1) / p.nsets;
-    const int set_units = (M.N / kTileRows) * ncol * SPLIT;
-    p.max_units = std::max(p.max_units, (set_units + nb_set - 1) / nb_set);
+    const int set_tiles = (M.N / kTileRows) * ncol;
+    p.max_units = std::max(p.max_units, (set_tiles + nb_set - 1) / nb_set * SPLIT);
   }
   p.max_units = (p.max_units + 1) & ~1;
   if (p.max_units > kGemv1MaxUnits) return false;
   const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
                        static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
-                       2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
+                       2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + kGemv1TileRing * (8 + SPLIT * kTileRows * 4) +
+                       p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
   if (fixed + static_cast<size_t>(p.buf_words) * 4 > kSmemLimit) return false;
   // as many staging buffers as fit; about three consumers per four buffers, so that copies run ahead of the decoding
   p.slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));

@@ -161,7 +161,7 @@ constexpr int kGemv1MaxUnits = 1024;       // work units one block can be dealt
 
 struct Gemv1Args {
   const void* x;          // activations [K], fp16 or fp32
-  float* partials;        // [N / 64][KT * SPLIT][64]: per tile row, one 64-row partial product per work unit
+  float* partials;        // [N / 64][KT][64]: per tile row, one 64-row partial product per tile
   float* y;               // [N] result
   unsigned int* err;      // device error word (bit 0: a bounded wait gave up)
   int x_is_half;
@@ -195,8 +195,11 @@ static_assert(sizeof(UnitMeta) == 16, "UnitMeta is read as one 16-byte word");
 // than consumers the copies run ahead of the decoding, so no warp waits for DRAM in steady state.
 // Everything a unit needs (coordinates, buffer, round) is worked out once, in parallel, when the block starts: the
 // per-unit path has no integer division.
-// The warp that finishes the last unit of a tile row (counted in M.row_done, which it resets) adds the row's partial
-// products in a fixed order and writes the result: no second kernel.
+// A block's list is made of whole tiles: the SPLIT units of a tile are consecutive entries, decoded by different warps
+// at about the same time.  Their totals meet in shared memory (a ring of kGemv1TileRing tiles); the warp that brings
+// the last one adds them in segment order and writes ONE partial product per tile.  The warp that completes the last
+// tile of a tile row (counted in M.row_done, which it resets) adds the row's partial products in a fixed order and
+// writes the result: no second kernel, and the row sum is a single round trip to L2 for up to 16 tile columns.
 // A parity wait on an mbarrier is only exact for a waiter that is at most one phase away, and here the waiters of
 // consecutive rounds of a buffer are different threads.  So every buffer also has a plain counter of the rounds that
 // were released: both sides first wait until it reaches their round (exact at any distance), after which the
@@ -208,6 +211,7 @@ __device__ __forceinline__ bool wait_released(const uint32_t* released, uint32_t
     uint32_t v;
     asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     if (v >= round) return true;
+    __nanosleep(100);   // do not take issue slots from the warps this one is waiting for
   }
   atomicOr(err, 1u);
   return false;
@@ -216,16 +220,16 @@ __device__ __forceinline__ bool wait_released(const uint32_t* released, uint32_t
 // y[64 rows of one tile row] = sum over `terms` partial products, p[term][64].  Lane l adds rows 4 (l % 16) .. + 3 of
 // the terms of its parity (l / 16) in ascending order, then the two parities are added: a fixed order.  Kept out of
 // line so that it gets registers of its own: inlined into the decoder (64 registers, all in use) the loads were issued
-// one at a time, 128 round trips to L2 per sum.
+// one at a time, one round trip to L2 (about 2000 cycles under load) each.
 __device__ __noinline__ void row_sum(const float* p, unsigned int terms, float* y, int lane) {
   const float4* q = reinterpret_cast<const float4*>(p) + lane;   // float4 i of the block: term i / 16, rows 4 (i % 16)
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  const unsigned int steps = terms / 2;                          // two terms per step of 32 float4
+  const unsigned int steps = (terms + 1) / 2, parity = lane >> 4;   // two terms per step of 32 float4
   for (unsigned int s0 = 0; s0 < steps; s0 += 8) {
     float4 v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      v[i] = s0 + i < steps ? __ldcg(q + static_cast<size_t>(s0 + i) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[i] = 2 * (s0 + i) + parity < terms ? __ldcg(q + static_cast<size_t>(s0 + i) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       acc.x += v[i].x;
@@ -240,6 +244,8 @@ __device__ __noinline__ void row_sum(const float* p, unsigned int terms, float* 
   acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
   if (lane < 16) reinterpret_cast<float4*>(y)[lane] = acc;
 }
+
+constexpr int kGemv1TileRing = 8;   // tiles whose segments a block may be combining at one time
 
 template <int FMT, int G, int IDXBITS, int LOG_R>
 __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
@@ -264,42 +270,51 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   uint64_t* empty = full + kGemv1MaxSlots;
   uint32_t* released = reinterpret_cast<uint32_t*>(empty + kGemv1MaxSlots);  // [slots] rounds released so far
   int* next_unit = reinterpret_cast<int*>(released + kGemv1MaxSlots);        // the list's shared counter
-  int* list_count = next_unit + 1;                                           // [2] slow / other units placed so far
-  UnitMeta* meta = reinterpret_cast<UnitMeta*>(next_unit + 4);               // [max_units]
+  int* list_count = next_unit + 1;                                           // [2] slow / other tiles placed so far
+  uint32_t* tile_cnt = reinterpret_cast<uint32_t*>(next_unit + 4);           // [ring] segments finished, cumulative
+  uint32_t* tile_free = tile_cnt + kGemv1TileRing;                           // [ring] generations handed back
+  float* tile_acc = reinterpret_cast<float*>(tile_free + kGemv1TileRing);    // [ring][SPLIT][64] unit totals
+  UnitMeta* meta = reinterpret_cast<UnitMeta*>(tile_acc + kGemv1TileRing * SPLIT * kTileRows);   // [max_units]
   uint32_t* bufs = reinterpret_cast<uint32_t*>(meta + A.max_units);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int set = blockIdx.x % A.nsets, bi = blockIdx.x / A.nsets;
   const int nb_set = (gridDim.x - set + A.nsets - 1) / A.nsets;              // blocks of this set
   const int ncol = (M.KT - set + A.nsets - 1) / A.nsets;                     // tile columns of this set
-  const int nunits = (M.N / kTileRows) * ncol * SPLIT;                       // units of this set
-  const int nmine = bi < nunits ? (nunits - bi + nb_set - 1) / nb_set : 0;   // units of this block: bi + k nb_set
+  const int ntiles = (M.N / kTileRows) * ncol;                               // tiles of this set
+  const int tmine = bi < ntiles ? (ntiles - bi + nb_set - 1) / nb_set : 0;   // tiles of this block: bi + k nb_set
+  const int nmine = tmine * SPLIT;                                           // its units
   const bool consumer = warp < A.helpers;   // takes part in the prologue; warps >= A.warps leave after it
   const int nthr = A.helpers * 32;
 
-  // unit of the set -> (tile row, column index in the set, segment), segment fastest
-  auto coords = [&](int u, int& tr, int& j, int& seg) {
-    seg = u % SPLIT;
-    const int v = u / SPLIT;
+  // tile of the set -> (tile row, column index in the set)
+  auto coords = [&](int v, int& tr, int& j) {
     j = v % ncol;
     tr = v / ncol;
   };
 
   // 1. everything the prologue needs from global memory is requested at once: table entries and the first activations
   // (consumers), then where the block's units live (all threads)
-  constexpr int TAB_PRE = 2, XB = 6;
-  uint32_t tab_pre[TAB_PRE];
-  float xv[XB];
+  // The registers stay exactly as loaded until after the barriers below: converting or moving one earlier would make
+  // the warp wait for its load right here.
+  constexpr int TAB_PRE = 3, T1_PRE = 2, XB = 6;
+  uint32_t tab_pre[TAB_PRE], t1_pre[T1_PRE], xraw[XB];
   auto load_x = [&](int base) {
 #pragma unroll
     for (int u = 0; u < XB; ++u) {
       const int i = base + u * nthr + threadIdx.x;
-      xv[u] = 0.f;
+      xraw[u] = 0u;
       if (i < ncol * TW) {
         const int j = i / TW, k = i - j * TW;
         const size_t src = static_cast<size_t>(set + A.nsets * j) * TW + k;
-        xv[u] = A.x_is_half ? __half2float(static_cast<const __half*>(A.x)[src]) : static_cast<const float*>(A.x)[src];
+        if (A.x_is_half)
+          xraw[u] = static_cast<const unsigned short*>(A.x)[src];
+        else
+          xraw[u] = static_cast<const uint32_t*>(A.x)[src];
       }
     }
+  };
+  auto x_value = [&](uint32_t raw) {
+    return A.x_is_half ? __half2float(__ushort_as_half(static_cast<unsigned short>(raw))) : __uint_as_float(raw);
   };
   if (consumer) {
 #pragma unroll
@@ -307,11 +322,21 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       const int idx = (i * A.helpers + warp) * 32 + lane;
       tab_pre[i] = idx < NIDX ? __ldg(M.tab32 + idx) : 0u;
     }
+#pragma unroll
+    for (int i = 0; i < T1_PRE; ++i) {   // windows beyond the replicated table (single-copy table only)
+      const int idx = NIDX + i * nthr + static_cast<int>(threadIdx.x);
+      t1_pre[i] = idx < kLutSize ? __ldg(M.tab32 + idx) : 0u;
+    }
     load_x(0);
   }
-  // The block's list: units bi, bi + nb_set, ... of the set, with the symbol-by-symbol units moved to the front (they
-  // take several times longer: started last, one of them would keep the whole block waiting).  The order within the
-  // two classes is whatever the counters hand out; results do not depend on it.
+  // The block's list: tiles bi, bi + nb_set, ... of the set, their SPLIT units in segment order, with the tiles
+  // that hold a symbol-by-symbol unit moved to the front (such a unit takes several times longer: started last, it
+  // would keep the whole block waiting).  The order within the two classes is whatever the counters hand out; results
+  // do not depend on it.
+  if (threadIdx.x < kGemv1TileRing) {
+    tile_cnt[threadIdx.x] = 0u;
+    tile_free[threadIdx.x] = 0u;
+  }
   if (threadIdx.x == 0) {
     list_count[0] = 0;
     list_count[1] = 0;
@@ -319,21 +344,25 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   }
   __syncthreads();
   for (int k0 = warp * 32; k0 < nmine; k0 += (blockDim.x >> 5) * 32) {
-    const int k = k0 + lane;
-    const bool valid = k < nmine;
-    int tr = 0, j = 0, seg = 0;
+    const int k = k0 + lane, seg = lane % SPLIT;
+    const bool valid = k < nmine, leader = seg == 0;
+    int tr = 0, j = 0;
     uint32_t g0 = 0, g1 = 0, g2 = 0, cls = 0;
+    bool slow = false;
     if (valid) {
-      coords(bi + k * nb_set, tr, j, seg);
+      coords(bi + (k / SPLIT) * nb_set, tr, j);
       const int t = tr * M.KT + set + A.nsets * j;
       const uint32_t* gb = M.group_base + static_cast<size_t>(t) * (2 * SPLIT) + 2 * seg;
       g0 = __ldg(gb);
       g1 = __ldg(gb + 1);
       g2 = __ldg(gb + 2);
-      cls = __ldg(M.unit_slow + static_cast<size_t>(t) * SPLIT + seg);
+      const uint8_t* uc = M.unit_slow + static_cast<size_t>(t) * SPLIT;
+      cls = __ldg(uc + seg);
+#pragma unroll
+      for (int i = 0; i < SPLIT; ++i) slow |= __ldg(uc + i) == 2;
     }
-    const bool slow = cls == 2;
-    const uint32_t bs = __ballot_sync(0xffffffffu, valid && slow), bf = __ballot_sync(0xffffffffu, valid && !slow);
+    const uint32_t bs = __ballot_sync(0xffffffffu, valid && leader && slow);
+    const uint32_t bf = __ballot_sync(0xffffffffu, valid && leader && !slow);
     int base_s = 0, base_f = 0;
     if (lane == 0) {
       base_s = atomicAdd(list_count, __popc(bs));
@@ -341,9 +370,11 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     }
     base_s = __shfl_sync(0xffffffffu, base_s, 0);
     base_f = __shfl_sync(0xffffffffu, base_f, 0);
+    const uint32_t below = (1u << lane) - 1u;
+    int tpos = slow ? base_s + __popc(bs & below) : tmine - 1 - (base_f + __popc(bf & below));
+    tpos = __shfl_sync(0xffffffffu, tpos, lane - seg);   // the tile's position, from its leader
     if (valid) {
-      const uint32_t below = (1u << lane) - 1u;
-      const int pos = slow ? base_s + __popc(bs & below) : nmine - 1 - (base_f + __popc(bf & below));
+      const int pos = tpos * SPLIT + seg;
       meta[pos] = UnitMeta{g0,
                            static_cast<uint16_t>((g2 - g0) >> 5),
                            static_cast<uint16_t>(((g1 - g0) >> 5) | (cls << 14)),
@@ -395,6 +426,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
         const uint32_t v = __shfl_sync(0xffffffffu, mine, j + (lane >> LOG_R));
         tab[(i0 + j) * R + lane] = v;
       }
+      tab1[i0 + lane] = mine;
     };
 #pragma unroll
     for (int i = 0; i < TAB_PRE; ++i) {
@@ -403,7 +435,13 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     }
     for (int i0 = (TAB_PRE * A.helpers + warp) * 32; i0 < NIDX; i0 += A.helpers * 32) spread(i0, __ldg(M.tab32 + i0 + lane));
   }
-  for (int i = threadIdx.x; i < kLutSize; i += nthr) tab1[i] = __ldg(M.tab32 + i);
+#pragma unroll
+  for (int i = 0; i < T1_PRE; ++i) {
+    const int idx = NIDX + i * nthr + static_cast<int>(threadIdx.x);
+    if (idx < kLutSize) tab1[idx] = t1_pre[i];
+  }
+  for (int idx = NIDX + T1_PRE * nthr + static_cast<int>(threadIdx.x); idx < kLutSize; idx += nthr)
+    tab1[idx] = __ldg(M.tab32 + idx);
   // activations -> 16-bit fixed point with one scale per sub-block (GW consecutive weights sit in GW consecutive
   // lanes).  Loads go out XB at a time so that their global-memory latencies overlap.
   for (int base = 0; base < ncol * TW; base += XB * nthr) {
@@ -412,13 +450,14 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     for (int u = 0; u < XB; ++u) {
       const int i = base + u * nthr + threadIdx.x;
       if (i < ncol * TW) {   // whole warps take this branch together: sizes are multiples of 32
-        float amax = fabsf(xv[u]), sum = xv[u];
+        const float xvu = x_value(xraw[u]);
+        float amax = fabsf(xvu), sum = xvu;
 #pragma unroll
         for (int o = 1; o < GW; o <<= 1) {
           amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
           if (HAS_OFFSET) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        const int q = __float2int_rn(xv[u] * (amax > 0.f ? 32767.f / amax : 0.f));
+        const int q = __float2int_rn(xvu * (amax > 0.f ? 32767.f / amax : 0.f));
         if (PAIR) {
           const int qn = __shfl_down_sync(0xffffffffu, q, 1);
           if ((lane & 1) == 0) xq[i >> 1] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
@@ -435,7 +474,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
   if (warp >= A.warps) return;
   const uint32_t lane_off = (lane & (R - 1)) << 2;
-  const unsigned int terms = static_cast<unsigned int>(M.KT * SPLIT);
+  const unsigned int terms = static_cast<unsigned int>(M.KT);   // partial products per tile row: one per tile
   // The warp that finishes the last unit of a tile row adds the row's partial products.  Counting a unit needs its
   // partial products to be visible first, and the count takes a round trip to L2 (about 2000 cycles each under load).
   // Both hide inside the decoding of the warp's next unit: the unit is counted (cnt_tr) after that one's first
@@ -447,7 +486,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
     if (done == terms - 1u) {
       __syncwarp();   // orders the loads below after lane 0's acquire; they bypass L1 (ld.cg)
       row_sum(A.partials + static_cast<size_t>(pend_tr) * terms * kTileRows, terms, A.y + pend_tr * kTileRows, lane);
-      if (lane == 0) M.row_done[pend_tr] = 0u;
+      if (lane == 0) M.row_done[pend_tr * kRowDoneStride] = 0u;
     }
     pend_done = kNone;
   };
@@ -458,7 +497,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       __syncwarp();
       pend_tr = cnt_tr;
       if (lane == 0)
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(pend_done) : "l"(M.row_done + cnt_tr) : "memory");
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(pend_done) : "l"(M.row_done + cnt_tr * kRowDoneStride) : "memory");
       cnt_tr = kNone;
     }
   };
@@ -517,10 +556,35 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + slot)) : "memory");
       asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(released + slot)), "r"(round + 1u) : "memory");
     }
-    float* prow = A.partials + (static_cast<size_t>(tr) * terms + tc * SPLIT + seg) * kTileRows;
-    prow[lane] = tot_a;
-    prow[lane + 32] = tot_b;
-    cnt_tr = tr;
+    // the unit's totals meet those of the tile's other segments in shared memory
+    constexpr int LOG_SPLIT = SPLIT == 4 ? 2 : SPLIT == 2 ? 1 : 0, LOG_RING = 3;
+    static_assert((1 << LOG_SPLIT) == SPLIT && (1 << LOG_RING) == kGemv1TileRing, "powers of two");
+    const uint32_t tl = static_cast<uint32_t>(k) >> LOG_SPLIT, ts = tl & (kGemv1TileRing - 1), tgen = tl >> LOG_RING;
+    if (!wait_released(tile_free + ts, tgen, A.err)) return;   // the ring slot's previous tile has been handed back
+    float* ta = tile_acc + (ts * SPLIT + seg) * kTileRows;
+    ta[lane] = tot_a;
+    ta[lane + 32] = tot_b;
+    __syncwarp();
+    uint32_t arrived = 0;
+    if (lane == 0)
+      asm volatile("atom.add.acq_rel.cta.shared::cta.u32 %0, [%1], 1;" : "=r"(arrived) : "r"(smem_addr(tile_cnt + ts)) : "memory");
+    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+    if (arrived == tgen * SPLIT + (SPLIT - 1)) {   // last segment of the tile: add them in segment order
+      __syncwarp();
+      float pa = 0.f, pb = 0.f;
+#pragma unroll
+      for (int sg = 0; sg < SPLIT; ++sg) {
+        pa += tile_acc[(ts * SPLIT + sg) * kTileRows + lane];
+        pb += tile_acc[(ts * SPLIT + sg) * kTileRows + lane + 32];
+      }
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(tile_free + ts)), "r"(tgen + 1u) : "memory");
+      float* prow = A.partials + (static_cast<size_t>(tr) * terms + tc) * kTileRows;
+      prow[lane] = pa;
+      prow[lane + 32] = pb;
+      cnt_tr = tr;
+    }
   }
   count();
   resolve();

@@ -11,6 +11,8 @@
 
 namespace lw {
 
+constexpr int kRowDoneStride = 32;
+
 // One coded matrix on the device (all pointers are device pointers; passed to kernels by value).
 struct MatDev {
   const uint16_t* lut;          // [2048] symbol | length << 8
@@ -20,7 +22,8 @@ struct MatDev {
   const uint8_t* side;          // [N, K / 256 * side_bytes] or null (symbols only)
   const uint8_t* unit_slow;     // [T * split] how the batch-1 kernel decodes the unit: 0 = groups of `group` symbols,
                                 // 1 = groups of two, 2 = symbol by symbol (or null: kernel not usable)
-  unsigned int* row_done;       // [N / 64] units of a tile row finished by the running batch-1 product (zero between launches)
+  unsigned int* row_done;       // [N / 64][kRowDoneStride] tiles of a tile row finished by the running batch-1 product
+                                // (zero between launches; one counter per 128-byte line: neighbours would contend)
   int index_bits;               // windows of the batch-1 kernel's table = 1 << index_bits; its copies = 1 << (pad - 2)
   int group;                    // symbols per group of the batch-1 kernel's grouped decoder (0 = kernel not usable)
   int N, K, Ks, KT, T;

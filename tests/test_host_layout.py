@@ -1,0 +1,123 @@
+"""The load-time device layout, checked on the CPU: the batch-1 kernel's grouped bit arithmetic is replayed in Python
+on the words the host produced, unit by unit, with the unit class the host assigned; it must return every symbol.
+Also: the scales stored behind every work unit equal the oracle's sub-block scales."""
+import numpy as np
+import pytest
+
+from tests import helpers
+from oracle import lw_oracle as orc
+
+M32 = 0xFFFFFFFF
+
+
+def _funnel(lo, hi, s):
+    return (((hi << 32) | lo) >> (s & 31)) & M32
+
+
+def _replay_chain(words, base, lane, lut, pad, index_bits, nsym, group, cls):
+    """symbols of one chain, decoded the way the kernel does for unit class `cls` (lw_gemv1.cuh: GroupChain)"""
+    w = lambda i: int(words[base + 32 * i + lane])
+    w0, w1, w2, nxt, bp = w(0), w(1), w(2), 3, 0
+    out = []
+    if cls == 2:                                   # symbol by symbol, single-copy table of all 2048 windows
+        for _ in range(nsym):
+            e = int(lut[(_funnel(w0, w1, bp) >> pad) & 2047])
+            out.append(e & 255)
+            bp += e >> 8
+            if bp >= 32:
+                bp, w0, w1, w2, nxt = bp - 32, w1, w2, w(nxt), nxt + 1
+        return out
+    g = group if cls == 0 else 2
+    a = b = off = 0
+    for i in range(nsym):
+        if i % g == 0:
+            a, b, off = _funnel(w0, w1, bp), _funnel(w1, w2, bp), 0
+        assert off < 32 or cls != 0 or True
+        t = _funnel(a, b, off)                     # the kernel's funnel shift takes the offset modulo 32
+        e = int(lut[(t >> pad) & ((1 << index_bits) - 1)])
+        out.append(e & 255)
+        off += e >> 8
+        if i % g == g - 1 or i == nsym - 1:
+            bp += off
+            if bp >= 32:                           # ONE refill per group
+                bp, w0, w1, w2, nxt = bp - 32, w1, w2, w(nxt), nxt + 1
+    return out
+
+
+def _tail_block(ty, q, rng, rows, cols):
+    tails = {"Q4_K": [0, 1, 2, 14, 15], "IQ4_XS": [0, 1, 2, 14, 15], "Q5_K": [0, 1, 2, 3, 4, 5, 27, 28, 29, 30, 31],
+             "Q6_K": list(range(0, 11)) + list(range(54, 64))}[ty]
+    q[rows, cols] = rng.choice(tails, q[rows, cols].shape)
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q6_K", 128, 512), ("Q4_K", 64, 1024), ("Q5_K", 64, 512), ("IQ4_XS", 64, 1024)])
+@pytest.mark.parametrize("force", [None, ("max", "10"), ("max", "11"), ("3", "11")])
+def test_grouped_decoder_replayed_on_cpu(monkeypatch, ty, n, k, force):
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=17 + n + k)
+    _tail_block(ty, q, rng, slice(0, 64), slice(64, 128))        # long codes back to back in one unit
+    sym = orc.symbols_of(ty, q)
+    if force:
+        gmax = "4" if ty in ("Q4_K", "IQ4_XS") else "6"
+        monkeypatch.setenv("LW_GEMV1_G", gmax if force[0] == "max" else force[0])
+        monkeypatch.setenv("LW_GEMV1_IDX", force[1])
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    lay = lw.bundle.host_layout(blob, n, sym.shape[1], ty, side)
+    lut = np.frombuffer(blob, np.uint16, 2048)
+    split, pad, group, ib = lay["split"], lay["pad"], lay["group"], lay["index_bits"]
+    assert group >= 3 and ib in (10, 11) and pad == 6 and split == (2 if ty == "Q5_K" else 4)
+    if force:
+        assert str(ib) == force[1]
+    nsym = 256 // split
+    KT, G = sym.shape[1] // 256, 2 * split
+    seen = set()
+    for t in range((n // 64) * KT):
+        tr, tc = divmod(t, KT)
+        for seg in range(split):
+            cls = int(lay["unit_class"][t * split + seg])
+            seen.add(cls)
+            for half in range(2):
+                base = int(lay["group_base"][t * G + 2 * seg + half])
+                for lane in range(0, 32, 5 if cls == 0 else 1):          # every lane of the fallback units
+                    got = _replay_chain(lay["words"], base, lane, lut, pad, ib, nsym, group, cls)
+                    row = tr * 64 + half * 32 + lane
+                    want = sym[row, tc * 256 + seg * nsym: tc * 256 + (seg + 1) * nsym]
+                    assert got == want.tolist(), (t, seg, half, lane, cls)
+    if force and force[0] == "max":
+        assert seen - {0}, "forcing the largest group must leave some units on a fallback class"
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q6_K", 64, 512), ("Q4_K", 64, 1024), ("Q5_K", 64, 512), ("IQ4_XS", 64, 1024)])
+def test_unit_scales_follow_the_chains(ty, n, k):
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=5)
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    lay = lw.bundle.host_layout(blob, n, sym.shape[1], ty, side)
+    split, sw = lay["split"], lay["unit_side_words"]
+    assert sw == (96 if ty in ("Q6_K", "IQ4_XS") else 192)
+    s_ref, o_ref = orc.sub_scales(ty, side.reshape(n * k // 256, -1))     # [blocks, sub-blocks]
+    nsub = s_ref.shape[1]
+    s_ref, o_ref = s_ref.reshape(n, -1), o_ref.reshape(n, -1)             # [row, sub-block along the row]
+    KT, G = sym.shape[1] // 256, 2 * split
+    subs_per_tile = (512 if ty in ("Q4_K", "IQ4_XS") else 256) // (16 if ty == "Q6_K" else 32)
+    words = lay["words"]
+    for t in range(KT * (n // 64)):
+        tr, tc = divmod(t, KT)
+        for seg in range(split):
+            end = int(lay["group_base"][t * G + 2 * seg + 2])            # the scales are the unit's last words
+            sb = words[end - sw:end]
+            for r in range(64):
+                sub0 = tc * subs_per_tile + seg * 4
+                if ty in ("Q4_K", "Q5_K"):
+                    dd = np.array([sb[r]], np.uint32).view(np.float16).astype(np.float32)
+                    sc = np.array([sb[64 + r]], np.uint32).view(np.uint8).astype(np.float32)
+                    mn = np.array([sb[128 + r]], np.uint32).view(np.uint8).astype(np.float32)
+                    s, o = dd[0] * sc, dd[1] * mn
+                else:
+                    d = sb.view(np.float16)[128 + r].astype(np.float32)
+                    b = np.array([sb[r]], np.uint32).view(np.int8 if ty == "Q6_K" else np.uint8).astype(np.float32)
+                    s, o = d * (b - (32 if ty == "IQ4_XS" else 0)), np.zeros(4, np.float32)
+                assert np.array_equal(s.astype(np.float32), s_ref[tr * 64 + r, sub0:sub0 + 4])
+                assert np.array_equal(o.astype(np.float32), o_ref[tr * 64 + r, sub0:sub0 + 4])
