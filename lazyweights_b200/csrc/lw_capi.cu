@@ -84,8 +84,9 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr, grouped ? &scan : nullptr))) return rc;
   // The batch-1 kernel's table: 1024 windows (codes up to 10 bits; units that hold a longer code are decoded symbol
   // by symbol) or 2048, 16 copies each; and the group size: units where groups of g symbols are not exact fall back
-  // to groups of two.  Estimated cost per symbol: 8.3 instructions + 10 per group; the larger table leaves a third
-  // fewer staging buffers (+ 8 %); symbol by symbol costs about 30.  LW_GEMV1_G / LW_GEMV1_IDX override.
+  // to groups of two.  Estimated cost per symbol: 8.3 instructions + 10 per group; groups of two cost about 22
+  // (measured: more than their instruction count); the larger table leaves a third fewer staging buffers (+ 8 %);
+  // symbol by symbol costs about 30.  LW_GEMV1_G / LW_GEMV1_IDX override.
   int idx_bits = tab->max_len <= 10 ? 10 : 11, group = 0;
   if (grouped) {
     const int gmax = is_paired(mx.fmt) ? 4 : kScanMaxG;
@@ -104,7 +105,7 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
           else if (m & gbit) ++two;
         }
         const double f2 = two / n, f1 = single / n;
-        const double cost = ((1.0 - f2 - f1) * (8.3 + 10.0 / g) + f2 * 13.3) * (ib == 11 ? 1.08 : 1.0) + f1 * 30.0;
+        const double cost = ((1.0 - f2 - f1) * (8.3 + 10.0 / g) + f2 * 22.0) * (ib == 11 ? 1.08 : 1.0) + f1 * 30.0;
         if (cost < best) {
           best = cost;
           group = g;
