@@ -100,32 +100,69 @@ __global__ void k_embed8(const int* __restrict__ ids, const uint8_t* __restrict_
   }
 }
 
-// h += res (if res), out = h * rsqrt(mean(h^2) + eps) * g.  One block per token.
-__global__ void k_rmsnorm(float* __restrict__ h, const float* __restrict__ res, const float* __restrict__ g,
-                          float* __restrict__ out, int D, float eps) {
-  __shared__ float red[32];
+// h += res (if res), out = h * rsqrt(mean(h^2) + eps) * g.  One block of 1024 threads per token; every thread keeps up
+// to eight elements in registers (float4 loads), so the row is read once.  Longer rows fall back to a second read.
+constexpr int kNormThreads = 1024;
+__global__ void __launch_bounds__(kNormThreads)
+    k_rmsnorm(float* __restrict__ h, const float* __restrict__ res, const float* __restrict__ g,
+              float* __restrict__ out, int D, float eps) {
+  __shared__ float red[33];
   float* hr = h + static_cast<size_t>(blockIdx.x) * D;
   const float* rr = res ? res + static_cast<size_t>(blockIdx.x) * D : nullptr;
+  float* orow = out + static_cast<size_t>(blockIdx.x) * D;
+  const bool vec = (D & 3) == 0 && D <= 8 * kNormThreads;
+  float4 v[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
   float ss = 0.f;
-  for (int k = threadIdx.x; k < D; k += blockDim.x) {
-    float v = hr[k];
-    if (rr) {
-      v += rr[k];
-      hr[k] = v;
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = (i * kNormThreads + threadIdx.x) * 4;
+      if (k < D) {
+        v[i] = *reinterpret_cast<const float4*>(hr + k);
+        if (rr) {
+          const float4 r4 = *reinterpret_cast<const float4*>(rr + k);
+          v[i].x += r4.x;
+          v[i].y += r4.y;
+          v[i].z += r4.z;
+          v[i].w += r4.w;
+          *reinterpret_cast<float4*>(hr + k) = v[i];
+        }
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+      }
     }
-    ss += v * v;
+  } else {
+    for (int k = threadIdx.x; k < D; k += blockDim.x) {
+      float x = hr[k];
+      if (rr) {
+        x += rr[k];
+        hr[k] = x;
+      }
+      ss += x * x;
+    }
   }
   for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (threadIdx.x == 0) red[0] = rsqrtf(v / D + eps);
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) red[32] = rsqrtf(t / D + eps);
   }
   __syncthreads();
-  const float r = red[0];
-  for (int k = threadIdx.x; k < D; k += blockDim.x) out[static_cast<size_t>(blockIdx.x) * D + k] = hr[k] * r * g[k];
+  const float r = red[32];
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = (i * kNormThreads + threadIdx.x) * 4;
+      if (k < D) {
+        const float4 g4 = *reinterpret_cast<const float4*>(g + k);
+        *reinterpret_cast<float4*>(orow + k) = make_float4(v[i].x * r * g4.x, v[i].y * r * g4.y, v[i].z * r * g4.z,
+                                                           v[i].w * r * g4.w);
+      }
+    }
+  } else {
+    for (int k = threadIdx.x; k < D; k += blockDim.x) orow[k] = hr[k] * r * g[k];
+  }
 }
 
 // rotate-half RoPE on q (in place) and k (into the cache), v into the cache.  grid (heads + 2 kv heads, tokens).
@@ -159,62 +196,105 @@ __global__ void k_rope_cache(float* __restrict__ qkv, const float* __restrict__ 
 // maximum, its sum of exponentials and the unnormalised weighted sum of v; k_attn_combine merges the chunks of one
 // (head, token) with the usual running-maximum rescaling.  Per-query arithmetic does not depend on how many tokens the
 // pass carries.
-constexpr int kAttnChunk = 128;
+constexpr int kAttnChunk = 128, kAttnThreads = 256, kAttnMaxDh = 128;
+constexpr int kAttnStride = kAttnMaxDh / 2 + 1;   // words per staged row: odd, so 32 consecutive rows hit 32 banks
 
-__global__ void __launch_bounds__(128)
+// GH query heads that share one kv head (grouped-query attention) per block: the chunk's keys, then its values, are
+// staged once in shared memory (16-byte loads) and serve all of them.
+template <int GH>
+__global__ void __launch_bounds__(kAttnThreads)
     k_attn_part(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
                 float* __restrict__ part, const int* __restrict__ posp, int H, int Hk, int Dh, int Tmax, float scale,
                 int window, int max_chunks) {
-  __shared__ float sc[kAttnChunk];
-  __shared__ float red[8];
-  const int head = blockIdx.x, j = blockIdx.y, c = blockIdx.z, kh = head / (H / Hk), last = *posp + j;
+  __shared__ uint32_t kv[kAttnChunk * kAttnStride];
+  __shared__ float qs[GH][kAttnMaxDh];
+  __shared__ float sc[GH][kAttnChunk];
+  constexpr int HT = GH >= 2 ? GH / 2 : 1;   // heads per thread: the two halves of the block split the heads
+  const int head0 = blockIdx.x * GH, j = blockIdx.y, c = blockIdx.z, kh = head0 / (H / Hk), last = *posp + j;
   const int lo = window > 0 ? max(0, last - window + 1) : 0;
   const int p0 = lo + c * kAttnChunk, n = min(kAttnChunk, last + 1 - p0);
-  float* out = part + ((static_cast<size_t>(j) * H + head) * max_chunks + c) * (Dh + 2);
+  auto out_of = [&](int h) { return part + ((static_cast<size_t>(j) * H + head0 + h) * max_chunks + c) * (Dh + 2); };
   if (n <= 0) {   // chunk beyond this token's causal range
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < GH) {
+      float* out = out_of(threadIdx.x);
       out[0] = -INFINITY;
       out[1] = 0.f;
     }
     return;
   }
-  const float* q = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head) * Dh;
-  const __half* K = kc + (static_cast<size_t>(kh) * Tmax + p0) * Dh;
-  const __half* Vv = vc + (static_cast<size_t>(kh) * Tmax + p0) * Dh;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float mx = -INFINITY;
-  for (int t = warp; t < n; t += 4) {
-    const __half* kr = K + static_cast<size_t>(t) * Dh;
-    float a = 0.f;
-    for (int i = 2 * lane; i < Dh; i += 64) {
-      const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kr + i));
-      a += q[i] * kk.x + q[i + 1] * kk.y;
+  const float* q = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head0) * Dh;
+  for (int i = threadIdx.x; i < GH * Dh; i += kAttnThreads) qs[i / Dh][i % Dh] = q[i];
+  const int cpr = Dh / 8;   // 16-byte pieces per row
+  auto stage = [&](const __half* src) {
+    for (int idx = threadIdx.x; idx < kAttnChunk * cpr; idx += kAttnThreads) {
+      const int t = idx / cpr, ch = idx - t * cpr;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (t < n) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * Dh) + ch);
+      uint32_t* d = kv + t * kAttnStride + ch * 4;
+      d[0] = v.x;
+      d[1] = v.y;
+      d[2] = v.z;
+      d[3] = v.w;
     }
-    for (int o = 16; o; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-    a *= scale;
-    if (lane == 0) sc[t] = a;
-    mx = fmaxf(mx, a);
-  }
-  if (lane == 0) red[warp] = mx;
+  };
+  stage(kc + (static_cast<size_t>(kh) * Tmax + p0) * Dh);
   __syncthreads();
-  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  float sum = 0.f;
-  for (int t = threadIdx.x; t < n; t += blockDim.x) {
-    const float e = __expf(sc[t] - mx);
-    sc[t] = e;
-    sum += e;
+  const int t = threadIdx.x & (kAttnChunk - 1), hp = threadIdx.x / kAttnChunk, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (hp * HT < GH) {   // scores of position t against this thread's heads
+    float acc[HT];
+#pragma unroll
+    for (int h = 0; h < HT; ++h) acc[h] = 0.f;
+    const uint32_t* kr = kv + t * kAttnStride;
+    for (int w = 0; w < Dh / 2; ++w) {
+      const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kr + w));
+#pragma unroll
+      for (int h = 0; h < HT; ++h) {
+        const float2 qq = *reinterpret_cast<const float2*>(&qs[hp * HT + h][2 * w]);
+        acc[h] = fmaf(qq.x, kk.x, acc[h]);
+        acc[h] = fmaf(qq.y, kk.y, acc[h]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < HT; ++h) sc[hp * HT + h][t] = t < n ? acc[h] * scale : -INFINITY;
   }
-  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if (lane == 0) red[4 + warp] = sum;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    out[0] = mx;
-    out[1] = red[4] + red[5] + red[6] + red[7];
+  if (warp < GH) {   // one warp per head: maximum, exponentials, their sum
+    float s4[4], mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s4[i] = sc[warp][lane + 32 * i];
+      mx = fmaxf(mx, s4[i]);
+    }
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float e = __expf(s4[i] - mx);   // exp(-inf) = 0 for the positions past n
+      sc[warp][lane + 32 * i] = e;
+      sum += e;
+    }
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) {
+      float* out = out_of(warp);
+      out[0] = mx;
+      out[1] = sum;
+    }
   }
-  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
-    float a = 0.f;
-    for (int t = 0; t < n; ++t) a += sc[t] * __half2float(Vv[static_cast<size_t>(t) * Dh + d]);
-    out[2 + d] = a;
+  __syncthreads();   // scores final, keys no longer needed
+  stage(vc + (static_cast<size_t>(kh) * Tmax + p0) * Dh);
+  __syncthreads();
+  if (hp * HT < GH && t < Dh) {   // t is now the output dimension
+    float acc[HT];
+#pragma unroll
+    for (int h = 0; h < HT; ++h) acc[h] = 0.f;
+    const __half* vcol = reinterpret_cast<const __half*>(kv) + t;
+    for (int p = 0; p < n; ++p) {
+      const float v = __half2float(vcol[p * (2 * kAttnStride)]);
+#pragma unroll
+      for (int h = 0; h < HT; ++h) acc[h] = fmaf(sc[hp * HT + h][p], v, acc[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < HT; ++h) out_of(hp * HT + h)[2 + t] = acc[h];
   }
 }
 
@@ -320,8 +400,8 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
     while (std::getline(es, x, ',')) R->eos.push_back(atoi(x.c_str()));
   }
   if (R->L <= 0 || R->D <= 0 || R->H <= 0 || R->Hk <= 0 || R->Dh <= 0 || R->I <= 0 || R->V <= 0 || R->H % R->Hk ||
-      R->Dh % 2 || R->Dh > 256) {
-    set_error("bundle cfg: bad model shape");
+      R->Dh % 8 || R->Dh > kAttnMaxDh) {
+    set_error("bundle cfg: bad model shape (head_dim must be a multiple of 8, at most %d)", kAttnMaxDh);
     return kErrFormat;
   }
   int rc;
@@ -434,7 +514,7 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
   const float* pending = nullptr;   // output of the previous block, added to h by the next norm
   int rc;
   for (int l = 0; l < R->L; ++l) {
-    k_rmsnorm<<<m, 256, 0, st>>>(R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
+    k_rmsnorm<<<m, kNormThreads, 0, st>>>(R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
     if (R->m_qkv[l] >= 0) {
       if ((rc = linear_device(M, M->mats[R->m_qkv[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st))) return rc;
     } else {
@@ -448,14 +528,27 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     __half* vc = R->vc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
     k_rope_cache<<<dim3(R->H + 2 * R->Hk, m), 64, 0, st>>>(R->qkv, R->cosv, R->sinv, kc, vc, posp, R->H, R->Hk, R->Dh,
                                                           R->Tmax);
-    k_attn_part<<<dim3(R->H, m, nchunks), 128, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk, R->Dh, R->Tmax,
-                                                        R->attn_scale, R->window, R->max_chunks);
+    {
+      const int group = R->H / R->Hk;
+      if (group % 4 == 0)
+        k_attn_part<4><<<dim3(R->H / 4, m, nchunks), kAttnThreads, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
+                                                                           R->Dh, R->Tmax, R->attn_scale, R->window,
+                                                                           R->max_chunks);
+      else if (group % 2 == 0)
+        k_attn_part<2><<<dim3(R->H / 2, m, nchunks), kAttnThreads, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
+                                                                           R->Dh, R->Tmax, R->attn_scale, R->window,
+                                                                           R->max_chunks);
+      else
+        k_attn_part<1><<<dim3(R->H, m, nchunks), kAttnThreads, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
+                                                                       R->Dh, R->Tmax, R->attn_scale, R->window,
+                                                                       R->max_chunks);
+    }
     k_attn_combine<<<dim3(R->H, m), 128, 0, st>>>(R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
     if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
                                                      R->comm, st), "all-reduce (o)")))
       return rc;
-    k_rmsnorm<<<m, 256, 0, st>>>(R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
+    k_rmsnorm<<<m, kNormThreads, 0, st>>>(R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
     if ((rc = linear_device(M, M->mats[R->m_gate[l]], R->xn, false, m, R->g, R->I, st)) ||
         (rc = linear_device(M, M->mats[R->m_up[l]], R->xn, false, m, R->u, R->I, st)))
       return rc;
@@ -467,7 +560,7 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
       return rc;
     pending = R->o;
   }
-  k_rmsnorm<<<m, 256, 0, st>>>(R->h, pending, R->lnf, R->xn, R->D, R->eps);
+  k_rmsnorm<<<m, kNormThreads, 0, st>>>(R->h, pending, R->lnf, R->xn, R->D, R->eps);
   const int rows = all_logits ? m : 1;
   const float* xlast = all_logits ? R->xn : R->xn + static_cast<size_t>(m - 1) * R->D;
   if ((rc = linear_device(M, M->mats[R->m_head], xlast, false, rows, R->logits, R->V, st))) return rc;
