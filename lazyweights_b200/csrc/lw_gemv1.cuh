@@ -221,7 +221,7 @@ __device__ __forceinline__ bool wait_released(const uint32_t* released, uint32_t
 // the terms of its parity (l / 16) in ascending order, then the two parities are added: a fixed order.  Kept out of
 // line so that it gets registers of its own: inlined into the decoder (64 registers, all in use) the loads were issued
 // one at a time, one round trip to L2 (about 2000 cycles under load) each.
-__device__ __noinline__ void row_sum(const float* p, unsigned int terms, float* y, int lane) {
+static __device__ __noinline__ void row_sum(const float* p, unsigned int terms, float* y, int lane) {
   const float4* q = reinterpret_cast<const float4*>(p) + lane;   // float4 i of the block: term i / 16, rows 4 (i % 16)
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const unsigned int steps = (terms + 1) / 2, parity = lane >> 4;   // two terms per step of 32 float4

@@ -11,6 +11,12 @@ bool gemv1_usable(const MatDev& M);
 int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* partials, float* y, unsigned int* err,
                  cudaStream_t st);
 
+// 2 <= m <= 8 rows (lw_gemvm.cuh): partials[KT * split][m][N] = one partial product per work unit and row, to be added
+// by the caller over KT * split terms; gemvm_partial_floats = the floats that takes.
+size_t gemvm_partial_floats(const MatDev& M, int m);
+int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* partials, unsigned int* err,
+                 cudaStream_t st);
+
 int note_launch(const char* what);   // counts a launch and returns the status of cudaGetLastError
 int sm_count();
 

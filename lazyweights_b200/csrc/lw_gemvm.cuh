@@ -1,0 +1,329 @@
+// Fused decode + dequant + product for 2..8 activation rows: the batch-1 kernel's decoder (lw_gemv1.cuh: replicated
+// 32-bit table, grouped refills chosen from the data, unit scales staged with the chains, producer warps feeding a ring
+// of staging buffers, units drawn from a shared counter) with MR dot products per decoded symbol instead of one.
+// Included by lw_gemvm.cu.
+//
+// What differs from the batch-1 kernel:
+//  * activations: MR rows, quantised to 16-bit fixed point per sub-block as there, stored symbol-major
+//    (xq[column][symbol][row]) so that one 16-byte shared-memory load brings four rows' operands of one symbol;
+//  * registers: 2 x MR integer sums and 2 x MR float totals per lane, so the block is smaller (768 threads for four
+//    rows, 640 for eight) and holds fewer tile columns of activations;
+//  * output: one partial product per work unit and row, P[unit term][row][N], added by k_sum_partials (a second
+//    launch; the in-kernel sum of the batch-1 kernel would need MR times its shared-memory ring).
+#pragma once
+#include "lw_gemv1.cuh"
+
+namespace lw {
+
+// One sub-block of both chains against MR activation rows.  xs points at the sub-block's operands, [symbol][MR] words.
+template <int G, int SPG, uint32_t MASK, int MR>
+__device__ __forceinline__ void sub_block_m(GroupChain& ca, GroupChain& cb, const uint8_t* tab, uint32_t lane_off,
+                                            const uint32_t* xs, const int first, const bool last, int (&acc_a)[MR],
+                                            int (&acc_b)[MR]) {
+#pragma unroll
+  for (int c = 0; c < SPG; ++c) {
+    const int f = first + c;
+    if (f % G == 0) {
+      ca.begin();
+      cb.begin();
+    }
+    const uint32_t ea = ca.template sym<MASK>(tab, lane_off), eb = cb.template sym<MASK>(tab, lane_off);
+#pragma unroll
+    for (int r4 = 0; r4 < MR / 4; ++r4) {
+      const uint4 x = *reinterpret_cast<const uint4*>(xs + c * MR + 4 * r4);
+      acc_a[4 * r4 + 0] = __dp2a_lo(static_cast<int>(x.x), static_cast<int>(ea), acc_a[4 * r4 + 0]);
+      acc_a[4 * r4 + 1] = __dp2a_lo(static_cast<int>(x.y), static_cast<int>(ea), acc_a[4 * r4 + 1]);
+      acc_a[4 * r4 + 2] = __dp2a_lo(static_cast<int>(x.z), static_cast<int>(ea), acc_a[4 * r4 + 2]);
+      acc_a[4 * r4 + 3] = __dp2a_lo(static_cast<int>(x.w), static_cast<int>(ea), acc_a[4 * r4 + 3]);
+      acc_b[4 * r4 + 0] = __dp2a_lo(static_cast<int>(x.x), static_cast<int>(eb), acc_b[4 * r4 + 0]);
+      acc_b[4 * r4 + 1] = __dp2a_lo(static_cast<int>(x.y), static_cast<int>(eb), acc_b[4 * r4 + 1]);
+      acc_b[4 * r4 + 2] = __dp2a_lo(static_cast<int>(x.z), static_cast<int>(eb), acc_b[4 * r4 + 2]);
+      acc_b[4 * r4 + 3] = __dp2a_lo(static_cast<int>(x.w), static_cast<int>(eb), acc_b[4 * r4 + 3]);
+    }
+    if (f % G == G - 1 || (last && c == SPG - 1)) {
+      ca.end();
+      cb.end();
+    }
+  }
+}
+
+template <int SPG, int MR>
+__device__ __forceinline__ void sub_block_slow_m(GroupChain& ca, GroupChain& cb, const uint32_t* tab32, uint32_t pad,
+                                                 const uint32_t* xs, int (&acc_a)[MR], int (&acc_b)[MR]) {
+#pragma unroll 1
+  for (int c = 0; c < SPG; ++c) {
+    const uint32_t ea = ca.slow_sym(tab32, pad), eb = cb.slow_sym(tab32, pad);
+#pragma unroll
+    for (int r = 0; r < MR; ++r) {
+      const uint32_t xw = xs[c * MR + r];
+      acc_a[r] = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a[r]);
+      acc_b[r] = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b[r]);
+    }
+  }
+}
+
+constexpr int gemvm_threads(int mr) { return mr <= 4 ? 768 : 640; }
+
+struct GemvmArgs {
+  Gemv1Args g;   // x = activations [m][K]; partials = P[KT * SPLIT][m][N]; y unused
+  int m;         // rows in use (<= MR; the others are computed as zeros and not written)
+};
+
+template <int FMT, int G, int IDXBITS, int LOG_R, int MR>
+__global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmArgs GA) {
+  const Gemv1Args& A = GA.g;
+  constexpr bool PAIR = is_paired(FMT);
+  constexpr int SPLIT = default_split(FMT);
+  constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;
+  constexpr int GW = sub_width(FMT), SPG = sub_syms(FMT), SIDEW = unit_side_words(FMT);
+  constexpr int NSB = TW / GW;                                    // sub-blocks per tile row
+  constexpr int USYM = kTileSyms / SPLIT;
+  static_assert(NSB / SPLIT == 4, "a unit is one quad of sub-blocks");
+  static_assert(MR == 4 || MR == 8, "four or eight rows");
+  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
+  constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
+  constexpr int kReplicatedTableBytes = NIDX * R * 4;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
+  uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);
+  uint32_t* xq = tab1 + kLutSize;                                                   // [cols][kTileSyms][MR] words
+  float* xscale = reinterpret_cast<float*>(xq + static_cast<size_t>(A.cols_per_set) * kTileSyms * MR);   // [cols][NSB][MR]
+  float* xg = xscale + static_cast<size_t>(A.cols_per_set) * NSB * MR;              // [cols][NSB][MR] (offset formats)
+  uint64_t* full = reinterpret_cast<uint64_t*>(xg + (HAS_OFFSET ? A.cols_per_set * NSB * MR : 0));
+  uint64_t* empty = full + kGemv1MaxSlots;
+  uint32_t* released = reinterpret_cast<uint32_t*>(empty + kGemv1MaxSlots);
+  int* next_unit = reinterpret_cast<int*>(released + kGemv1MaxSlots);
+  int* list_count = next_unit + 1;
+  UnitMeta* meta = reinterpret_cast<UnitMeta*>(next_unit + 4);
+  uint32_t* bufs = reinterpret_cast<uint32_t*>(meta + A.max_units);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int set = blockIdx.x % A.nsets, bi = blockIdx.x / A.nsets;
+  const int nb_set = (gridDim.x - set + A.nsets - 1) / A.nsets;
+  const int ncol = (M.KT - set + A.nsets - 1) / A.nsets;
+  const int ntiles = (M.N / kTileRows) * ncol;
+  const int tmine = bi < ntiles ? (ntiles - bi + nb_set - 1) / nb_set : 0;
+  const int nmine = tmine * SPLIT;
+  const bool consumer = warp < A.warps;
+  const int nthr = A.warps * 32, m = GA.m;
+
+  // 1. the block's list (whole tiles, symbol-by-symbol tiles first), exactly as in the batch-1 kernel
+  if (threadIdx.x == 0) {
+    list_count[0] = 0;
+    list_count[1] = 0;
+    *next_unit = 0;
+  }
+  __syncthreads();
+  for (int k0 = warp * 32; k0 < nmine; k0 += (blockDim.x >> 5) * 32) {
+    const int k = k0 + lane, seg = lane % SPLIT;
+    const bool valid = k < nmine, leader = seg == 0;
+    int tr = 0, j = 0;
+    uint32_t g0 = 0, g1 = 0, g2 = 0, cls = 0;
+    bool slow = false;
+    if (valid) {
+      const int v = bi + (k / SPLIT) * nb_set;
+      j = v % ncol;
+      tr = v / ncol;
+      const int t = tr * M.KT + set + A.nsets * j;
+      const uint32_t* gb = M.group_base + static_cast<size_t>(t) * (2 * SPLIT) + 2 * seg;
+      g0 = __ldg(gb);
+      g1 = __ldg(gb + 1);
+      g2 = __ldg(gb + 2);
+      const uint8_t* uc = M.unit_slow + static_cast<size_t>(t) * SPLIT;
+      cls = __ldg(uc + seg);
+#pragma unroll
+      for (int i = 0; i < SPLIT; ++i) slow |= __ldg(uc + i) == 2;
+    }
+    const uint32_t bs = __ballot_sync(0xffffffffu, valid && leader && slow);
+    const uint32_t bf = __ballot_sync(0xffffffffu, valid && leader && !slow);
+    int base_s = 0, base_f = 0;
+    if (lane == 0) {
+      base_s = atomicAdd(list_count, __popc(bs));
+      base_f = atomicAdd(list_count + 1, __popc(bf));
+    }
+    base_s = __shfl_sync(0xffffffffu, base_s, 0);
+    base_f = __shfl_sync(0xffffffffu, base_f, 0);
+    const uint32_t below = (1u << lane) - 1u;
+    int tpos = slow ? base_s + __popc(bs & below) : tmine - 1 - (base_f + __popc(bf & below));
+    tpos = __shfl_sync(0xffffffffu, tpos, lane - seg);
+    if (valid) {
+      const int pos = tpos * SPLIT + seg;
+      meta[pos] = UnitMeta{g0,
+                           static_cast<uint16_t>((g2 - g0) >> 5),
+                           static_cast<uint16_t>(((g1 - g0) >> 5) | (cls << 14)),
+                           static_cast<uint16_t>(tr),
+                           static_cast<uint16_t>(pos / A.slots),
+                           static_cast<uint8_t>(j),
+                           static_cast<uint8_t>(seg),
+                           static_cast<uint8_t>(pos % A.slots),
+                           0};
+    }
+  }
+  if (threadIdx.x < A.slots) {
+    mbar_init(smem_addr(full + threadIdx.x), 1);
+    mbar_init(smem_addr(empty + threadIdx.x), 1);
+    released[threadIdx.x] = 0u;
+  }
+  __syncthreads();
+
+  if (!consumer) {
+    // 2a. producers: issuer s owns buffers s, s + S, ... and feeds them round by round
+    if (lane < A.producer_lanes) {
+      const int issuers = A.producers * A.producer_lanes;
+      for (int round = 0; round * A.slots < nmine; ++round)
+        for (int slot = (warp - A.warps) * A.producer_lanes + lane; slot < A.slots; slot += issuers) {
+          const int k = round * A.slots + slot;
+          if (k >= nmine) break;
+          if (round > 0) {
+            if (!wait_released(released + slot, round, A.err)) return;
+            if (!mbar_wait(smem_addr(empty + slot), (round - 1) & 1, A.err)) return;
+          }
+          const UnitMeta um = meta[k];
+          bulk_load(smem_addr(bufs + static_cast<size_t>(slot) * A.buf_words), M.words + um.src, um.lines * 128u,
+                    smem_addr(full + slot));
+        }
+    }
+    return;
+  }
+
+  // 2b. consumers: tables, then the activations of the block's tile columns for all rows
+  {
+    constexpr int PER = 32 / R;
+    for (int i0 = warp * 32; i0 < NIDX; i0 += A.warps * 32) {
+      const uint32_t mine = __ldg(M.tab32 + i0 + lane);
+#pragma unroll 8
+      for (int j = 0; j < 32; j += PER) {
+        const uint32_t v = __shfl_sync(0xffffffffu, mine, j + (lane >> LOG_R));
+        tab[(i0 + j) * R + lane] = v;
+      }
+      tab1[i0 + lane] = mine;
+    }
+    for (int idx = NIDX + static_cast<int>(threadIdx.x); idx < kLutSize; idx += nthr) tab1[idx] = __ldg(M.tab32 + idx);
+  }
+  constexpr int XB = 8;
+  const int per_row = ncol * TW, total = per_row * MR;   // rows >= m are stored as zeros
+  for (int base = 0; base < total; base += XB * nthr) {
+    float xv[XB];
+#pragma unroll
+    for (int u = 0; u < XB; ++u) {
+      const int i = base + u * nthr + threadIdx.x;
+      xv[u] = 0.f;
+      if (i < total) {
+        const int r = i / per_row, w = i - r * per_row, j = w / TW, k = w - j * TW;
+        if (r < m) {
+          const size_t src = static_cast<size_t>(r) * M.K + static_cast<size_t>(set + A.nsets * j) * TW + k;
+          xv[u] = A.x_is_half ? __half2float(static_cast<const __half*>(A.x)[src]) : static_cast<const float*>(A.x)[src];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < XB; ++u) {
+      const int i = base + u * nthr + threadIdx.x;
+      if (i < total) {   // whole warps take this branch together: sizes are multiples of 32
+        const int r = i / per_row, w = i - r * per_row;
+        float amax = fabsf(xv[u]), sum = xv[u];
+#pragma unroll
+        for (int o = 1; o < GW; o <<= 1) {
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          if (HAS_OFFSET) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        const int q = __float2int_rn(xv[u] * (amax > 0.f ? 32767.f / amax : 0.f));
+        if (PAIR) {
+          const int qn = __shfl_down_sync(0xffffffffu, q, 1);
+          if ((lane & 1) == 0) xq[static_cast<size_t>(w >> 1) * MR + r] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
+        } else {
+          xq[static_cast<size_t>(w) * MR + r] = static_cast<uint32_t>(q) & 0xFFFFu;
+        }
+        if ((lane & (GW - 1)) == 0) {
+          xscale[static_cast<size_t>(w / GW) * MR + r] = amax * (1.f / 32767.f);
+          if (HAS_OFFSET) xg[static_cast<size_t>(w / GW) * MR + r] = sum;
+        }
+      }
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
+  const uint32_t lane_off = (lane & (R - 1)) << 2;
+#pragma unroll 1
+  for (;;) {
+    int k = 0;
+    if (lane == 0) k = atomicAdd(next_unit, 1);
+    k = __shfl_sync(0xffffffffu, k, 0);
+    if (k >= nmine) break;
+    const uint4 raw = *reinterpret_cast<const uint4*>(meta + k);
+    const uint32_t lines = raw.y & 0xFFFFu, second = raw.y >> 16, tr = raw.z & 0xFFFFu, round = raw.z >> 16;
+    const uint32_t j = raw.w & 255u, seg = (raw.w >> 8) & 255u, slot = (raw.w >> 16) & 255u;
+    const uint32_t cls = second >> 14;
+    const int tc = set + A.nsets * static_cast<int>(j);
+    const int na = static_cast<int>(tr) * kTileRows + lane, nb = na + 32;
+    const uint32_t* xt = xq + (static_cast<size_t>(j) * kTileSyms + seg * USYM) * MR;
+    const float* xst = xscale + (static_cast<size_t>(j) * NSB + seg * 4) * MR;
+    const float* xgt = xg + (static_cast<size_t>(j) * NSB + seg * 4) * MR;
+    const uint32_t* buf = bufs + static_cast<size_t>(slot) * A.buf_words;
+    if (round > 0 && !wait_released(released + slot, round, A.err)) return;
+    if (!mbar_wait(smem_addr(full + slot), round & 1, A.err)) return;
+    UnitSide<FMT> side_a, side_b;
+    side_a.load(buf + lines * 32u - SIDEW, lane);
+    side_b.load(buf + lines * 32u - SIDEW, lane + 32);
+    GroupChain ca, cb;
+    ca.init(buf + lane);
+    cb.init(buf + (second & 0x3FFFu) * 32u + lane);
+    float tot_a[MR], tot_b[MR];
+#pragma unroll
+    for (int r = 0; r < MR; ++r) tot_a[r] = tot_b[r] = 0.f;
+    auto finish_sub = [&](const int jj, const int (&acc_a)[MR], const int (&acc_b)[MR]) {
+      float s_a, o_a, s_b, o_b;
+      side_a.sub(jj, s_a, o_a);
+      side_b.sub(jj, s_b, o_b);
+#pragma unroll
+      for (int r = 0; r < MR; ++r) {
+        const float xsc = xst[jj * MR + r];
+        const float fa = static_cast<float>(acc_a[r]) * xsc, fb = static_cast<float>(acc_b[r]) * xsc;
+        if (HAS_OFFSET) {
+          const float gx = xgt[jj * MR + r];
+          tot_a[r] += s_a * fa - o_a * gx;
+          tot_b[r] += s_b * fb - o_b * gx;
+        } else {
+          tot_a[r] = fmaf(s_a, fa, tot_a[r]);
+          tot_b[r] = fmaf(s_b, fb, tot_b[r]);
+        }
+      }
+    };
+    if (cls == 0) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        int acc_a[MR], acc_b[MR];
+#pragma unroll
+        for (int r = 0; r < MR; ++r) acc_a[r] = acc_b[r] = 0;
+        sub_block_m<G, SPG, MASK, MR>(ca, cb, smem, lane_off, xt + jj * SPG * MR, jj * SPG, jj == 3, acc_a, acc_b);
+        finish_sub(jj, acc_a, acc_b);
+      }
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        int acc_a[MR], acc_b[MR];
+#pragma unroll
+        for (int r = 0; r < MR; ++r) acc_a[r] = acc_b[r] = 0;
+        if (cls == 1)
+          sub_block_m<2, SPG, MASK, MR>(ca, cb, smem, lane_off, xt + jj * SPG * MR, jj * SPG, jj == 3, acc_a, acc_b);
+        else
+          sub_block_slow_m<SPG, MR>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG * MR, acc_a, acc_b);
+        finish_sub(jj, acc_a, acc_b);
+      }
+    }
+    // every lane has read its last word: hand the buffer back to the producer
+    __syncwarp();
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + slot)) : "memory");
+      asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(released + slot)), "r"(round + 1u) : "memory");
+    }
+    float* prow = A.partials + static_cast<size_t>(tc * SPLIT + static_cast<int>(seg)) * m * M.N;
+#pragma unroll
+    for (int r = 0; r < MR; ++r)
+      if (r < m) {
+        prow[static_cast<size_t>(r) * M.N + na] = tot_a[r];
+        prow[static_cast<size_t>(r) * M.N + nb] = tot_b[r];
+      }
+  }
+}
+
+}  // namespace lw

@@ -420,8 +420,14 @@ int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
   return launch_decode_weights_rows(M, out, 0, M.N / kTileRows, st);
 }
 
-size_t gemv_partial_floats(const MatDev& M, int m) {
+// Scratch every product can run with, and the larger scratch that lets 2..8 rows take the faster kernel (one partial
+// product per work unit and row instead of one per tile column and row).
+size_t gemv_partial_floats_min(const MatDev& M, int m) {
   return static_cast<size_t>(M.KT) * std::max(m, M.split) * M.N;
+}
+size_t gemv_partial_floats(const MatDev& M, int m) {
+  return m > 1 && gemv1_usable(M) ? std::max(gemv_partial_floats_min(M, m), gemvm_partial_floats(M, m))
+                                  : gemv_partial_floats_min(M, m);
 }
 
 template <int FMT, int MT, typename XT>
@@ -466,14 +472,21 @@ static int gemv1_variant() {
 }
 
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
-                cudaStream_t st) {
+                size_t partial_capacity, cudaStream_t st) {
   if (m < 1 || m > 8) {
     set_kernel_error_text("gemv", "m must be 1..8");
     return kErrArg;
   }
+  if (partial_capacity < gemv_partial_floats_min(M, m)) {
+    set_kernel_error_text("gemv", "scratch too small for this product");
+    return kErrTooLarge;
+  }
   int rc, terms = M.KT;
   if (m == 1 && gemv1_variant() != 0 && gemv1_usable(M)) {
     return launch_gemv1(M, X, x_is_half, partials, Y, error_word(), st);   // adds its partial products itself
+  } else if (m > 1 && gemv1_variant() != 0 && gemv1_usable(M) && partial_capacity >= gemvm_partial_floats(M, m)) {
+    rc = launch_gemvm(M, X, x_is_half, m, partials, error_word(), st);
+    terms = M.KT * M.split;
   } else {
     rc = x_is_half ? launch_gemv_f<__half>(M, static_cast<const __half*>(X), m, partials, st)
                    : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
@@ -532,7 +545,7 @@ extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_i
     set_kernel_error_text("lw_linear_static", "matrix has no block format");
     return kErrArg;
   }
-  if (gemv_partial_floats(*M, m) > kStaticPartialFloats) {
+  if (gemv_partial_floats_min(*M, m) > kStaticPartialFloats) {
     set_kernel_error_text("lw_linear_static",
                           "this product needs more partial sums than the built-in scratch holds "
                           "(tile columns x max(m, segments) x N must be <= 4194304); use lw_linear");
@@ -541,7 +554,8 @@ extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_i
   float* scratch = nullptr;
   const int rc = static_partials(&scratch);
   if (rc) return rc;
-  return launch_gemv(*M, x_dev, x_is_half != 0, m, y_dev, M->N, scratch, static_cast<cudaStream_t>(stream));
+  return launch_gemv(*M, x_dev, x_is_half != 0, m, y_dev, M->N, scratch, kStaticPartialFloats,
+                     static_cast<cudaStream_t>(stream));
 }
 
 namespace lw {

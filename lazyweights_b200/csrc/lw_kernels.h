@@ -44,9 +44,12 @@ int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, c
 int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st);
 int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, cudaStream_t st);
 // Y[j, n] (row stride ldy) = sum_k X[j, k] W[n, k] for m <= 8 rows of X (fp16 or fp32, row-major [m, K]).
-// `partials` must hold gemv_partial_floats(M, m) floats.
+// `partials` (partial_capacity floats) must hold gemv_partial_floats_min(M, m) floats; with gemv_partial_floats(M, m)
+// products of 2..8 rows take the faster kernel.
+size_t gemv_partial_floats_min(const MatDev& M, int m);
 size_t gemv_partial_floats(const MatDev& M, int m);
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
+                size_t partial_capacity,
                 cudaStream_t st);
 // Reads (and optionally clears) the device error word that kernels set when a bounded wait gives up.
 int read_kernel_error(unsigned int* value, bool clear);
