@@ -13,7 +13,7 @@ constexpr int kMaxStagedColumns = 8;    // tile columns whose activations one bl
 constexpr int kRingSlackWords = 96;     // read-ahead of the last chains of the last staging buffer lands here
 
 struct Gemv1Plan {
-  int warps, helpers, producers, producer_lanes, slots, nsets, cols_per_set, blocks, max_units;
+  int warps, helpers, producers, producer_lanes, tile_ring_log2, slots, nsets, cols_per_set, blocks, max_units;
   uint32_t buf_words;
   size_t smem;
 };
@@ -42,10 +42,17 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   }
   p.max_units = (p.max_units + 1) & ~1;
   if (p.max_units > kGemv1MaxUnits) return false;
-  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
-                       static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
-                       2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + kGemv1TileRing * (8 + SPLIT * kTileRows * 4) +
-                       p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
+  // The ring in which the segments of a tile meet: 8 tiles (28 warps have 7 tiles in flight); 16 with
+  // LW_GEMV1_RING=16 where 36 staging buffers still fit (measured: no difference on the bench matrix).
+  size_t fixed = 0;
+  for (p.tile_ring_log2 = env_int("LW_GEMV1_RING", 8) >= 16 ? 4 : 3; p.tile_ring_log2 >= 3; --p.tile_ring_log2) {
+    fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
+            static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
+            2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + (size_t(1) << p.tile_ring_log2) * (8 + SPLIT * kTileRows * 4) +
+            p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
+    if (fixed + static_cast<size_t>(p.buf_words) * 4 * 36 <= kSmemLimit) break;   // 36 buffers still fit
+  }
+  p.tile_ring_log2 = std::max(3, p.tile_ring_log2);
   if (fixed + static_cast<size_t>(p.buf_words) * 4 > kSmemLimit) return false;
   // as many staging buffers as fit; about three consumers per four buffers, so that copies run ahead of the decoding
   p.slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));
@@ -86,6 +93,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
   a.nsets = p.nsets;
   a.cols_per_set = p.cols_per_set;
   a.max_units = p.max_units;
+  a.tile_ring_log2 = p.tile_ring_log2;
   k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
   return note_launch("k_gemv1");
 }

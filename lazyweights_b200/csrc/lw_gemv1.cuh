@@ -174,6 +174,7 @@ struct Gemv1Args {
   int nsets;              // tile columns are dealt to `nsets` sets of blocks (bounds the staged activations)
   int cols_per_set;       // ceil(KT / nsets)
   int max_units;          // capacity of the block's unit list (>= units of any block, multiple of 2)
+  int tile_ring_log2;     // the ring in which the segments of a tile meet holds 1 << tile_ring_log2 tiles
 };
 
 struct UnitMeta {          // 16 bytes: one shared-memory load per unit
@@ -196,7 +197,7 @@ static_assert(sizeof(UnitMeta) == 16, "UnitMeta is read as one 16-byte word");
 // Everything a unit needs (coordinates, buffer, round) is worked out once, in parallel, when the block starts: the
 // per-unit path has no integer division.
 // A block's list is made of whole tiles: the SPLIT units of a tile are consecutive entries, decoded by different warps
-// at about the same time.  Their totals meet in shared memory (a ring of kGemv1TileRing tiles); the warp that brings
+// at about the same time.  Their totals meet in shared memory (a ring of 8 or 16 tiles); the warp that brings
 // the last one adds them in segment order and writes ONE partial product per tile.  The warp that completes the last
 // tile of a tile row (counted in M.row_done, which it resets) adds the row's partial products in a fixed order and
 // writes the result: no second kernel, and the row sum is a single round trip to L2 for up to 16 tile columns.
@@ -245,7 +246,7 @@ static __device__ __noinline__ void row_sum(const float* p, unsigned int terms, 
   if (lane < 16) reinterpret_cast<float4*>(y)[lane] = acc;
 }
 
-constexpr int kGemv1TileRing = 8;   // tiles whose segments a block may be combining at one time
+constexpr int kGemv1MaxTileRing = 16;   // tiles whose segments a block may be combining at one time (8 or 16)
 
 template <int FMT, int G, int IDXBITS, int LOG_R>
 __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
@@ -272,9 +273,10 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   int* next_unit = reinterpret_cast<int*>(released + kGemv1MaxSlots);        // the list's shared counter
   int* list_count = next_unit + 1;                                           // [2] slow / other tiles placed so far
   uint32_t* tile_cnt = reinterpret_cast<uint32_t*>(next_unit + 4);           // [ring] segments finished, cumulative
-  uint32_t* tile_free = tile_cnt + kGemv1TileRing;                           // [ring] generations handed back
-  float* tile_acc = reinterpret_cast<float*>(tile_free + kGemv1TileRing);    // [ring][SPLIT][64] unit totals
-  UnitMeta* meta = reinterpret_cast<UnitMeta*>(tile_acc + kGemv1TileRing * SPLIT * kTileRows);   // [max_units]
+  const int ring = 1 << A.tile_ring_log2;
+  uint32_t* tile_free = tile_cnt + ring;                                     // [ring] generations handed back
+  float* tile_acc = reinterpret_cast<float*>(tile_free + ring);              // [ring][SPLIT][64] unit totals
+  UnitMeta* meta = reinterpret_cast<UnitMeta*>(tile_acc + ring * SPLIT * kTileRows);   // [max_units]
   uint32_t* bufs = reinterpret_cast<uint32_t*>(meta + A.max_units);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int set = blockIdx.x % A.nsets, bi = blockIdx.x / A.nsets;
@@ -333,7 +335,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   // that hold a symbol-by-symbol unit moved to the front (such a unit takes several times longer: started last, it
   // would keep the whole block waiting).  The order within the two classes is whatever the counters hand out; results
   // do not depend on it.
-  if (threadIdx.x < kGemv1TileRing) {
+  if (threadIdx.x < ring) {
     tile_cnt[threadIdx.x] = 0u;
     tile_free[threadIdx.x] = 0u;
   }
@@ -571,9 +573,9 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(released + slot)), "r"(round + 1u) : "memory");
     }
     // the unit's totals meet those of the tile's other segments in shared memory
-    constexpr int LOG_SPLIT = SPLIT == 4 ? 2 : SPLIT == 2 ? 1 : 0, LOG_RING = 3;
-    static_assert((1 << LOG_SPLIT) == SPLIT && (1 << LOG_RING) == kGemv1TileRing, "powers of two");
-    const uint32_t tl = static_cast<uint32_t>(k) >> LOG_SPLIT, ts = tl & (kGemv1TileRing - 1), tgen = tl >> LOG_RING;
+    constexpr int LOG_SPLIT = SPLIT == 4 ? 2 : SPLIT == 2 ? 1 : 0;
+    static_assert((1 << LOG_SPLIT) == SPLIT, "power of two");
+    const uint32_t tl = static_cast<uint32_t>(k) >> LOG_SPLIT, ts = tl & (ring - 1), tgen = tl >> A.tile_ring_log2;
     if (!wait_released(tile_free + ts, tgen, A.err)) return;   // the ring slot's previous tile has been handed back
     float* ta = tile_acc + (ts * SPLIT + seg) * kTileRows;
     ta[lane] = tot_a;
