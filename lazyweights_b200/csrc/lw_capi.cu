@@ -510,11 +510,23 @@ int rt_test_matmul(void* handle, const char* name, const float* X, int m, float*
     if ((e = cudaMalloc(&M->d_y, ny * 4)) != cudaSuccess) return cuda_fail("rt_test_matmul buffers", e);
     M->y_floats = ny;
   }
-  if ((e = cudaMemcpy(M->d_x, X, nx * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+  // Host buffers go through one pinned staging area with asynchronous copies on the stream of the product and a
+  // single synchronisation: two blocking copies from pageable memory cost about 10 us more per call.
+  if (nx + ny > M->pin_floats) {
+    if (M->h_pin) cudaFreeHost(M->h_pin);
+    M->h_pin = nullptr;
+    M->pin_floats = 0;
+    if ((e = cudaMallocHost(&M->h_pin, (nx + ny) * 4)) != cudaSuccess) return cuda_fail("rt_test_matmul pinned buffer", e);
+    M->pin_floats = nx + ny;
+  }
+  std::memcpy(M->h_pin, X, nx * 4);
+  if ((e = cudaMemcpyAsync(M->d_x, M->h_pin, nx * 4, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess)
     return cuda_fail("rt_test_matmul copy in", e);
   int rc = linear_device(M, mx, M->d_x, false, m, M->d_y, mx.N, nullptr, path);
-  if (!rc && (e = cudaMemcpy(Y, M->d_y, ny * 4, cudaMemcpyDeviceToHost)) != cudaSuccess)
+  if (!rc && (e = cudaMemcpyAsync(M->h_pin + nx, M->d_y, ny * 4, cudaMemcpyDeviceToHost, nullptr)) != cudaSuccess)
     rc = cuda_fail("rt_test_matmul copy back", e);
+  if ((e = cudaStreamSynchronize(nullptr)) != cudaSuccess && !rc) rc = cuda_fail("rt_test_matmul", e);
+  if (!rc) std::memcpy(Y, M->h_pin + nx, ny * 4);
   return rc;
 }
 

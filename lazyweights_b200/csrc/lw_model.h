@@ -39,6 +39,8 @@ struct Model {
   size_t partial_floats = 0;
   float *d_x = nullptr, *d_y = nullptr;   // staging of rt_test_matmul's host buffers (grown on demand, kept)
   size_t x_floats = 0, y_floats = 0;
+  float* h_pin = nullptr;                 // pinned host staging for the same call (x, then y)
+  size_t pin_floats = 0;
   __half *d_w16 = nullptr, *d_x16 = nullptr;   // decode + GEMM path: decoded weights of a chunk of tile rows, fp16 x
   size_t w16_halfs = 0, x16_halfs = 0;
   size_t resident_bytes = 0;
@@ -50,6 +52,7 @@ struct Model {
     if (d_partials) cudaFree(d_partials);
     if (d_x) cudaFree(d_x);
     if (d_y) cudaFree(d_y);
+    if (h_pin) cudaFreeHost(h_pin);
     if (d_w16) cudaFree(d_w16);
     if (d_x16) cudaFree(d_x16);
     if (fd >= 0) close(fd);
