@@ -3,8 +3,8 @@
   oracle/liblw_oracle.so   the C restatement (lw_oracle_c.c), gcc -O2 -pthread
   oracle/_ref/huff_csim    the REFERENCE's own C++ decoder test bench (hw/huff/tb/csim_main.cpp with
                            hw/huff/huff_engine.h), compiled from the sources where they lie in a reference
-                           checkout; only built when such a checkout is present (default /root/reference or
-                           $LW_REFERENCE).  Nothing of the reference is copied into this repository.
+                           checkout; only built when such a checkout is present (its directory: $LW_REFERENCE,
+                           else the build machine's default location).  Nothing of the reference is copied into this repository.
 """
 import ctypes as C
 import os
