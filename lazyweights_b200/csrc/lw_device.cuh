@@ -52,6 +52,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
   return false;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
+// predecessor in the stream is still running (as soon as every block of the predecessor has called pdl_trigger or
+// left), and must call pdl_wait before it touches anything the predecessor writes: the wait returns when the
+// predecessor has completed and its writes are visible.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------ chain reader
 
 // Reads one chain (a re-based bit stream whose word i sits at base + 32 i + lane) out of shared memory.  Three words

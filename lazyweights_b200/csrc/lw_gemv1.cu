@@ -94,7 +94,22 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
   a.cols_per_set = p.cols_per_set;
   a.max_units = p.max_units;
   a.tile_ring_log2 = p.tile_ring_log2;
-  k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
+  a.pdl = env_int("LW_PDL", 1) != 0;
+  if (a.pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.blocks);
+    cfg.blockDim = dim3((p.helpers + p.producers) * 32);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R>, M, a);
+  } else {
+    k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
+  }
   return note_launch("k_gemv1");
 }
 

@@ -174,6 +174,7 @@ struct Gemv1Args {
   int nsets;              // tile columns are dealt to `nsets` sets of blocks (bounds the staged activations)
   int cols_per_set;       // ceil(KT / nsets)
   int max_units;          // capacity of the block's unit list (>= units of any block, multiple of 2)
+  int pdl;                // launched as a programmatic dependent: the activations may only be read after pdl_wait
   int tile_ring_log2;     // the ring in which the segments of a tile meet holds 1 << tile_ring_log2 tiles
 };
 
@@ -285,6 +286,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   const int ntiles = (M.N / kTileRows) * ncol;                               // tiles of this set
   const int tmine = bi < ntiles ? (ntiles - bi + nb_set - 1) / nb_set : 0;   // tiles of this block: bi + k nb_set
   const int nmine = tmine * SPLIT;                                           // its units
+  pdl_trigger();   // the next kernel of the stream may be set up while this one runs (it waits before it reads)
   const bool consumer = warp < A.helpers;   // takes part in the prologue; warps >= A.warps leave after it
   const int nthr = A.helpers * 32;
 
@@ -329,7 +331,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
       const int idx = NIDX + i * nthr + static_cast<int>(threadIdx.x);
       t1_pre[i] = idx < kLutSize ? __ldg(M.tab32 + idx) : 0u;
     }
-    load_x(0);
+    if (!A.pdl) load_x(0);
   }
   // The block's list: tiles bi, bi + nb_set, ... of the set, their SPLIT units in segment order, with the tiles
   // that hold a symbol-by-symbol unit moved to the front (such a unit takes several times longer: started last, it
@@ -444,10 +446,13 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   }
   for (int idx = NIDX + T1_PRE * nthr + static_cast<int>(threadIdx.x); idx < kLutSize; idx += nthr)
     tab1[idx] = __ldg(M.tab32 + idx);
+  // Everything up to here read only the matrix (tables, list, and the producers' copies of chain words): with a
+  // programmatic launch it overlaps the tail of the previous kernel in the stream, which may still be writing x.
+  if (A.pdl) pdl_wait();
   // activations -> 16-bit fixed point with one scale per sub-block (GW consecutive weights sit in GW consecutive
   // lanes).  Loads go out XB at a time so that their global-memory latencies overlap.
   for (int base = 0; base < ncol * TW; base += XB * nthr) {
-    if (base > 0) load_x(base);
+    if (base > 0 || A.pdl) load_x(base);
 #pragma unroll
     for (int u = 0; u < XB; ++u) {
       const int i = base + u * nthr + threadIdx.x;

@@ -73,6 +73,8 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float
   a.g.nsets = p.nsets;
   a.g.cols_per_set = p.cols_per_set;
   a.g.max_units = p.max_units;
+  a.g.pdl = 0;
+  a.g.tile_ring_log2 = 3;
   a.m = m;
   kernel<<<p.blocks, (p.warps + p.producers) * 32, p.smem, st>>>(M, a);
   return note_launch("k_gemvm");
