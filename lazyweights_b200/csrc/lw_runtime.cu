@@ -100,12 +100,34 @@ __global__ void k_embed8(const int* __restrict__ ids, const uint8_t* __restrict_
   }
 }
 
+// Programmatic dependent launch (see lw_device.cuh): every kernel of a pass lets its successor be set up at once and
+// waits for its predecessor before it reads or writes anything.
+__device__ __forceinline__ void dep_begin() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // h += res (if res), out = h * rsqrt(mean(h^2) + eps) * g.  One block of 1024 threads per token; every thread keeps up
 // to eight elements in registers (float4 loads), so the row is read once.  Longer rows fall back to a second read.
 constexpr int kNormThreads = 1024;
 __global__ void __launch_bounds__(kNormThreads)
     k_rmsnorm(float* __restrict__ h, const float* __restrict__ res, const float* __restrict__ g,
               float* __restrict__ out, int D, float eps) {
+  dep_begin();
   __shared__ float red[33];
   float* hr = h + static_cast<size_t>(blockIdx.x) * D;
   const float* rr = res ? res + static_cast<size_t>(blockIdx.x) * D : nullptr;
@@ -169,6 +191,7 @@ __global__ void __launch_bounds__(kNormThreads)
 __global__ void k_rope_cache(float* __restrict__ qkv, const float* __restrict__ cosv, const float* __restrict__ sinv,
                              __half* __restrict__ kc, __half* __restrict__ vc, const int* __restrict__ posp, int H, int Hk,
                              int Dh, int Tmax) {
+  dep_begin();
   const int head = blockIdx.x, j = blockIdx.y, p = *posp + j, half = Dh / 2;
   float* row = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head) * Dh;
   if (head < H + Hk) {
@@ -206,6 +229,7 @@ __global__ void __launch_bounds__(kAttnThreads)
     k_attn_part(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
                 float* __restrict__ part, const int* __restrict__ posp, int H, int Hk, int Dh, int Tmax, float scale,
                 int window, int max_chunks) {
+  dep_begin();
   __shared__ uint32_t kv[kAttnChunk * kAttnStride];
   __shared__ float qs[GH][kAttnMaxDh];
   __shared__ float sc[GH][kAttnChunk];
@@ -300,6 +324,7 @@ __global__ void __launch_bounds__(kAttnThreads)
 
 __global__ void k_attn_combine(const float* __restrict__ part, float* __restrict__ att, int H, int Dh, int nchunks,
                                int max_chunks) {
+  dep_begin();
   const int head = blockIdx.x, j = blockIdx.y;
   const float* p = part + (static_cast<size_t>(j) * H + head) * max_chunks * (Dh + 2);
   float mx = -INFINITY;
@@ -321,6 +346,7 @@ __global__ void k_attn_combine(const float* __restrict__ part, float* __restrict
 }
 
 __global__ void k_silu_mul(float* __restrict__ g, const float* __restrict__ u, size_t n) {
+  dep_begin();
   const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (i < n) {
     const float v = g[i];
@@ -514,7 +540,7 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
   const float* pending = nullptr;   // output of the previous block, added to h by the next norm
   int rc;
   for (int l = 0; l < R->L; ++l) {
-    k_rmsnorm<<<m, kNormThreads, 0, st>>>(R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
+    launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
     if (R->m_qkv[l] >= 0) {
       if ((rc = linear_device(M, M->mats[R->m_qkv[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st))) return rc;
     } else {
@@ -526,41 +552,41 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     }
     __half* kc = R->kc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
     __half* vc = R->vc + static_cast<size_t>(l) * R->Hk * R->Tmax * R->Dh;
-    k_rope_cache<<<dim3(R->H + 2 * R->Hk, m), 64, 0, st>>>(R->qkv, R->cosv, R->sinv, kc, vc, posp, R->H, R->Hk, R->Dh,
+    launch_dep(k_rope_cache, dim3(R->H + 2 * R->Hk, m), dim3(64), st, R->qkv, R->cosv, R->sinv, kc, vc, posp, R->H, R->Hk, R->Dh,
                                                           R->Tmax);
     {
       const int group = R->H / R->Hk;
       if (group % 4 == 0)
-        k_attn_part<4><<<dim3(R->H / 4, m, nchunks), kAttnThreads, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
+        launch_dep(k_attn_part<4>, dim3(R->H / 4, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
                                                                            R->Dh, R->Tmax, R->attn_scale, R->window,
                                                                            R->max_chunks);
       else if (group % 2 == 0)
-        k_attn_part<2><<<dim3(R->H / 2, m, nchunks), kAttnThreads, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
+        launch_dep(k_attn_part<2>, dim3(R->H / 2, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
                                                                            R->Dh, R->Tmax, R->attn_scale, R->window,
                                                                            R->max_chunks);
       else
-        k_attn_part<1><<<dim3(R->H, m, nchunks), kAttnThreads, 0, st>>>(R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
+        launch_dep(k_attn_part<1>, dim3(R->H, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
                                                                        R->Dh, R->Tmax, R->attn_scale, R->window,
                                                                        R->max_chunks);
     }
-    k_attn_combine<<<dim3(R->H, m), 128, 0, st>>>(R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
+    launch_dep(k_attn_combine, dim3(R->H, m), dim3(128), st, R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
     if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
                                                      R->comm, st), "all-reduce (o)")))
       return rc;
-    k_rmsnorm<<<m, kNormThreads, 0, st>>>(R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
+    launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
     if ((rc = linear_device(M, M->mats[R->m_gate[l]], R->xn, false, m, R->g, R->I, st)) ||
         (rc = linear_device(M, M->mats[R->m_up[l]], R->xn, false, m, R->u, R->I, st)))
       return rc;
     const size_t ng = static_cast<size_t>(m) * R->I;
-    k_silu_mul<<<static_cast<unsigned>((ng + 255) / 256), 256, 0, st>>>(R->g, R->u, ng);
+    launch_dep(k_silu_mul, dim3(static_cast<unsigned>((ng + 255) / 256)), dim3(256), st, R->g, R->u, ng);
     if ((rc = linear_device(M, M->mats[R->m_down[l]], R->g, false, m, R->o, R->D, st))) return rc;
     if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
                                                      R->comm, st), "all-reduce (down)")))
       return rc;
     pending = R->o;
   }
-  k_rmsnorm<<<m, kNormThreads, 0, st>>>(R->h, pending, R->lnf, R->xn, R->D, R->eps);
+  launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, pending, R->lnf, R->xn, R->D, R->eps);
   const int rows = all_logits ? m : 1;
   const float* xlast = all_logits ? R->xn : R->xn + static_cast<size_t>(m - 1) * R->D;
   if ((rc = linear_device(M, M->mats[R->m_head], xlast, false, rows, R->logits, R->V, st))) return rc;
