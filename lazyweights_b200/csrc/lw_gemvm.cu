@@ -73,10 +73,20 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float
   a.g.nsets = p.nsets;
   a.g.cols_per_set = p.cols_per_set;
   a.g.max_units = p.max_units;
-  a.g.pdl = 0;
+  a.g.pdl = 1;
   a.g.tile_ring_log2 = 3;
   a.m = m;
-  kernel<<<p.blocks, (p.warps + p.producers) * 32, p.smem, st>>>(M, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.blocks);
+  cfg.blockDim = dim3((p.warps + p.producers) * 32);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, M, a);
   return note_launch("k_gemvm");
 }
 

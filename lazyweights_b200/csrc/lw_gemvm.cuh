@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
   const int ntiles = (M.N / kTileRows) * ncol;
   const int tmine = bi < ntiles ? (ntiles - bi + nb_set - 1) / nb_set : 0;
   const int nmine = tmine * SPLIT;
+  pdl_trigger();   // see lw_gemv1.cuh: set-up overlaps the previous kernel's tail, pdl_wait before the activations
   const bool consumer = warp < A.warps;
   const int nthr = A.warps * 32, m = GA.m;
 
@@ -200,6 +201,7 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
     }
     for (int idx = NIDX + static_cast<int>(threadIdx.x); idx < kLutSize; idx += nthr) tab1[idx] = __ldg(M.tab32 + idx);
   }
+  if (A.pdl) pdl_wait();
   constexpr int XB = 8;
   const int per_row = ncol * TW, total = per_row * MR;   // rows >= m are stored as zeros
   for (int base = 0; base < total; base += XB * nthr) {
