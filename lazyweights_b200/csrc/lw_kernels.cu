@@ -298,22 +298,32 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 #include "lw_gemm_tc.cuh"
 namespace lw {
 
-// Y[j, n] = sum over the `terms` partial rows of P[term, j, n], in a fixed order (no atomics: results do not depend on
-// scheduling).  Four threads share one output: thread q adds terms q, q + 4, ... and the four sums are then combined
-// in lane order, so there are enough threads in flight to cover the loads' latency.
+// Y[j, n] = sum over the `terms` partial rows of P[term, j, n], added in term order (no atomics: results do not
+// depend on scheduling).  One thread per four consecutive outputs: 16-byte loads, eight terms in flight.
 __global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int terms) {
-  const int i = blockIdx.x * (blockDim.x / 4) + (threadIdx.x >> 2), q = threadIdx.x & 3;
-  float a = 0.f;
-  if (i < m * N) {
-    const int j = i / N, n = i - j * N;
-    for (int t = q; t < terms; t += 4) a += P[(static_cast<size_t>(t) * m + j) * N + n];
+  const int quads = N / 4, i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m * quads) return;
+  const int j = i / quads, n = (i - j * quads) * 4;
+  const float4* p = reinterpret_cast<const float4*>(P + static_cast<size_t>(j) * N + n);
+  const size_t stride = static_cast<size_t>(m) * quads;   // one term further, in float4
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int t0 = 0; t0 < terms; t0 += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = t0 + u < terms ? __ldg(p + (t0 + u) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      acc.x += v[u].x;
+      acc.y += v[u].y;
+      acc.z += v[u].z;
+      acc.w += v[u].w;
+    }
   }
-  a += __shfl_xor_sync(0xffffffffu, a, 1);
-  a += __shfl_xor_sync(0xffffffffu, a, 2);
-  if (q == 0 && i < m * N) {
-    const int j = i / N, n = i - j * N;
-    Y[static_cast<size_t>(j) * ldy + n] = a;
-  }
+  float* y = Y + static_cast<size_t>(j) * ldy + n;
+  y[0] = acc.x;
+  y[1] = acc.y;
+  y[2] = acc.z;
+  y[3] = acc.w;
 }
 
 // ------------------------------------------------------------------------------------------------------ launchers
@@ -492,7 +502,7 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
                    : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
   }
   if (rc) return rc;
-  k_sum_partials<<<(m * M.N + 63) / 64, 256, 0, st>>>(partials, Y, m, M.N, ldy, terms);
+  k_sum_partials<<<(m * (M.N / 4) + 127) / 128, 128, 0, st>>>(partials, Y, m, M.N, ldy, terms);
   return check_launch("k_sum_partials");
 }
 
