@@ -161,6 +161,29 @@ def test_batch1_grouped_and_symbol_by_symbol_units(lw, monkeypatch, ty, n, k, fo
         assert helpers.rel_err(y16, orc.gemv_f64(w, x.astype(np.float16).astype(np.float32)[None])[0]) <= helpers.GEMV_TOL
 
 
+@pytest.mark.parametrize("ty", helpers.FORMATS)
+def test_shapes_and_row_counts_sweep(lw, ty):
+    """Ragged shapes (1..28 tile columns, 1..32 tile rows), every row count 1..8 and 11 (chunks), fp16 and fp32
+    activations, with a flat patch of codes (long code words) in some matrices: products against the oracle."""
+    import torch
+    rng = np.random.default_rng(123)
+    tk = 512 if ty in ("Q4_K", "IQ4_XS") else 256
+    hi = 15 if tk == 512 else (31 if ty == "Q5_K" else 63)
+    for n, kt in ((64, 1), (128, 3), (192, 5), (448, 11), (64, 28), (2048, 9)):
+        k = kt * tk
+        q, side = orc.synth_codes(ty, n, k, rng), orc.synth_side(ty, n, k, rng)
+        if (n + kt) % 2:
+            q[:64, :min(k, 128)] = rng.integers(0, hi + 1, (64, min(k, 128)))
+        sym, w = orc.symbols_of(ty, q), orc.dequant(ty, q, side)
+        blob, _, _ = lw.bundle.encode_huf8(sym)
+        with lw.CodedMatrix(blob, n, sym.shape[1], ty, side) as mat:
+            for m in (1, 2, 3, 4, 5, 7, 8, 11):
+                x = rng.standard_normal((m, k)).astype(np.float16 if m % 2 else np.float32)
+                y = mat.linear("m", torch.from_numpy(x).cuda()).cpu().numpy()
+                assert helpers.rel_err(y, orc.gemv_f64(w, x.astype(np.float32))) <= helpers.GEMV_TOL, (ty, n, k, m)
+    assert lw.lib().lw_kernel_error() == 0
+
+
 def test_worst_case_code_lengths(lw):
     """Every symbol 11 bits long is the largest tile the format allows; the staging buffers must take it."""
     rng = np.random.default_rng(5)
