@@ -38,7 +38,7 @@ namespace lw {
 
 struct GroupChain {
   const uint32_t* p;
-  uint32_t w0, w1, w2, bp;   // three stream words; bp < 32 between groups
+  uint32_t w0, w1, w2, bp;   // three stream words; bp = bits consumed so far (its low five bits place the window)
   uint32_t a, b, off;        // window normalised to bp, offset inside the group
   __device__ __forceinline__ void init(const uint32_t* chain_words) {
     w0 = chain_words[0];
@@ -62,21 +62,24 @@ struct GroupChain {
     return e;
   }
   __device__ __forceinline__ void refill() {
-    bp -= 32;
     w0 = w1;
     w1 = w2;
     w2 = *p;
     p += 32;
   }
+  // bp is a running bit count: the funnel shifts only look at its low five bits, and a word was used up exactly when
+  // bit 5 changed (the loader guarantees at most one word per group)
   __device__ __forceinline__ void end() {
-    bp += off;
-    if (bp >= 32) refill();
+    const uint32_t nb = bp + off;
+    if ((nb ^ bp) & 32u) refill();
+    bp = nb;
   }
   // symbol by symbol, any data: tab32 = the single-copy table (shared memory)
   __device__ __forceinline__ uint32_t slow_sym(const uint32_t* tab32, uint32_t pad) {
     const uint32_t e = tab32[(__funnelshift_r(w0, w1, bp) >> pad) & (kLutSize - 1)];
-    bp += e >> 28;
-    if (bp >= 32) refill();
+    const uint32_t nb = bp + (e >> 28);
+    if ((nb ^ bp) & 32u) refill();
+    bp = nb;
     return e;
   }
 };
