@@ -75,9 +75,17 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
     set_kernel_error_text("gemv1", "work unit does not fit shared memory");
     return kErrTooLarge;
   }
-  if (cudaFuncSetAttribute(k_gemv1<FMT, G, IDXBITS, LOG_R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(p.smem)) != cudaSuccess)
-    return note_launch("cudaFuncSetAttribute(k_gemv1)");
+  // the attribute is raised once per kernel instantiation and device, not on every launch
+  static size_t configured_per_device[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  size_t& configured = configured_per_device[dev & 63];
+  if (p.smem > configured) {
+    if (cudaFuncSetAttribute(k_gemv1<FMT, G, IDXBITS, LOG_R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kSmemLimit)) != cudaSuccess)
+      return note_launch("cudaFuncSetAttribute(k_gemv1)");
+    configured = kSmemLimit;
+  }
   Gemv1Args a;
   a.x = X;
   a.partials = P;
