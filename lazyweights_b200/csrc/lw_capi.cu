@@ -286,9 +286,9 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
     set_error("%s has no side tensor: products need a block format", mx.name.c_str());
     return kErrArg;
   }
-  // measured on B200 (Q6_K 14336 x 4096): fused pass of eight rows 81 us, decode + GEMM 310-370 us for 16-32 rows,
-  // so up to 24 rows go through the fused kernel in chunks of eight
-  if (path == 2 || (path == 0 && m > 24)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);
+  // measured on B200 (Q6_K 14336 x 4096): fused pass of eight rows 78 us, decode + GEMM 377 us for 32 rows (Q4_K
+  // 4096 x 4096: 25 us and 149 us), so up to 32 rows go through the fused kernel in chunks of eight
+  if (path == 2 || (path == 0 && m > 32)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);
   const size_t xe = x_half ? 2 : 4;
   for (int r0 = 0; r0 < m; r0 += 8) {
     const int mm = std::min(8, m - r0);
