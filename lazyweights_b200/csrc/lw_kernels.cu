@@ -301,6 +301,8 @@ namespace lw {
 // Y[j, n] = sum over the `terms` partial rows of P[term, j, n], added in term order (no atomics: results do not
 // depend on scheduling).  One thread per four consecutive outputs: 16-byte loads, eight terms in flight.
 __global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int terms) {
+  pdl_trigger();   // launched as a programmatic dependent of the kernel that writes P (see lw_device.cuh)
+  pdl_wait();
   const int quads = N / 4, i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= m * quads) return;
   const int j = i / quads, n = (i - j * quads) * 4;
@@ -502,7 +504,20 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
                    : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
   }
   if (rc) return rc;
-  k_sum_partials<<<(m * (M.N / 4) + 127) / 128, 128, 0, st>>>(partials, Y, m, M.N, ldy, terms);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((m * (M.N / 4) + 127) / 128);
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // measured: waiting early pays for small products (Q4_K 4096 x 4096, 8 rows: 26 -> 20 us) and costs on large ones
+    // (Q6_K 14336 x 4096, 8 rows: 78 -> 88 us), so only up to 16 MB of partial products
+    cfg.numAttrs = static_cast<size_t>(terms) * m * M.N * 4 <= (size_t(16) << 20) ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, k_sum_partials, static_cast<const float*>(partials), Y, m, M.N, ldy, terms);
+  }
   return check_launch("k_sum_partials");
 }
 
