@@ -1,0 +1,81 @@
+// Instantiations and launcher of the decode-to-weights kernel; see lw_decw.cuh.
+#include "lw_gemv1.h"
+
+#include <algorithm>
+
+#include "lw_decw.cuh"
+
+namespace lw {
+
+constexpr size_t kSmemLimit = 227 * 1024;
+constexpr int kRingSlackWords = 96;
+
+template <int FMT, int G, int IDXBITS>
+static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  constexpr int SPLIT = default_split(FMT);
+  const uint32_t buf_words = (M.max_unit_words + 31u) & ~31u;
+  const int tiles = (tr1 - tr0) * M.KT;
+  const int blocks = std::max(1, std::min(sm_count(), tiles));
+  const int max_units = (((tiles + blocks - 1) / blocks) * SPLIT + 1) & ~1;
+  if (max_units > kGemv1MaxUnits) return kErrTooLarge;
+  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 + 2 * kGemv1MaxSlots * 8 +
+                       kGemv1MaxSlots * 4 + 16 + max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
+  if (fixed + static_cast<size_t>(buf_words) * 4 > kSmemLimit) return kErrTooLarge;
+  const int slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (buf_words * 4)));
+  const int warps = std::max(1, std::min(std::min(kGemv1MaxWarps, max_units), max_units <= slots ? slots : slots * 3 / 4));
+  const size_t smem = fixed + static_cast<size_t>(slots) * buf_words * 4;
+  auto kernel = k_decw<FMT, G, IDXBITS, kGemv1LogCopies>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return note_launch("cudaFuncSetAttribute(k_decw)");
+  DecwArgs a = {};
+  a.g.err = err;
+  a.g.warps = warps;
+  a.g.helpers = warps;
+  a.g.producers = 2;
+  a.g.producer_lanes = 4;
+  a.g.slots = slots;
+  a.g.buf_words = buf_words;
+  a.g.nsets = 1;
+  a.g.cols_per_set = M.KT;
+  a.g.max_units = max_units;
+  a.out = out;
+  a.tr0 = tr0;
+  a.tr1 = tr1;
+  kernel<<<blocks, (warps + 2) * 32, smem, st>>>(M, a);
+  return note_launch("k_decw");
+}
+
+template <int FMT, int G>
+static int launch_x(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  if (M.index_bits == 10) return launch_t<FMT, G, 10>(M, out, tr0, tr1, err, st);
+  return launch_t<FMT, G, 11>(M, out, tr0, tr1, err, st);
+}
+
+template <int FMT>
+static int launch_i(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  switch (M.group) {
+    case 3: return launch_x<FMT, 3>(M, out, tr0, tr1, err, st);
+    case 4: return launch_x<FMT, 4>(M, out, tr0, tr1, err, st);
+  }
+  if constexpr (!is_paired(FMT)) {
+    switch (M.group) {
+      case 5: return launch_x<FMT, 5>(M, out, tr0, tr1, err, st);
+      case 6: return launch_x<FMT, 6>(M, out, tr0, tr1, err, st);
+    }
+  }
+  return kErrTooLarge;
+}
+
+// Returns kErrTooLarge where this kernel cannot take the product (the caller then uses the warp-per-tile kernel).
+int launch_decw(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  if (!err || M.KT > 255 || tr1 <= tr0) return kErrTooLarge;
+  switch (M.fmt) {
+    case kFmtQ4K: return launch_i<kFmtQ4K>(M, out, tr0, tr1, err, st);
+    case kFmtQ5K: return launch_i<kFmtQ5K>(M, out, tr0, tr1, err, st);
+    case kFmtIQ4XS: return launch_i<kFmtIQ4XS>(M, out, tr0, tr1, err, st);
+    case kFmtQ6K: return launch_i<kFmtQ6K>(M, out, tr0, tr1, err, st);
+  }
+  return kErrTooLarge;
+}
+
+}  // namespace lw

@@ -17,6 +17,10 @@ size_t gemvm_partial_floats(const MatDev& M, int m);
 int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* partials, unsigned int* err,
                  cudaStream_t st);
 
+// fp16 weights of tile rows tr0 .. tr1 - 1 on the batch-1 kernel's decoder (lw_decw.cuh); kErrTooLarge (nothing
+// launched) where it cannot take the matrix.
+int launch_decw(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st);
+
 int note_launch(const char* what);   // counts a launch and returns the status of cudaGetLastError
 int sm_count();
 

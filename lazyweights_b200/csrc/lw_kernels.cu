@@ -401,7 +401,13 @@ int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaSt
   return check_launch("k_decode_codes");
 }
 
+static int gemv1_variant();
+
 int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st) {
+  if (gemv1_variant() != 0 && gemv1_usable(M)) {   // the decoder of the batch-1 kernel, where the layout allows
+    const int rc = launch_decw(M, out, tr0, tr1, error_word(), st);
+    if (rc != kErrTooLarge) return rc;
+  }
   const size_t smem = 2 * kLutSize + 128 + kWarpsPerBlock * stage_bytes(M);
   const int tiles = (tr1 - tr0) * M.KT;
   const int blocks = (tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
