@@ -274,7 +274,7 @@ static int linear_decode_gemm(Model* M, Matrix& mx, const void* x, bool x_half, 
     const int tr1 = std::min(NT, tr0 + chunk);
     if ((rc = launch_decode_weights_rows(mx.dev, M->d_w16, tr0, tr1, st))) return rc;
     if ((rc = launch_gemm_tc(x16, M->d_w16, y + static_cast<size_t>(tr0) * kTileRows, m, (tr1 - tr0) * kTileRows, mx.K,
-                             ldy, st)))
+                             ldy, M->d_partials, M->partial_floats, st)))
       return rc;
   }
   return kOk;
@@ -286,9 +286,10 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
     set_error("%s has no side tensor: products need a block format", mx.name.c_str());
     return kErrArg;
   }
-  // measured on B200 (Q6_K 14336 x 4096): fused pass of eight rows 78 us, decode + GEMM 377 us for 32 rows (Q4_K
-  // 4096 x 4096: 25 us and 149 us), so up to 32 rows go through the fused kernel in chunks of eight
-  if (path == 2 || (path == 0 && m > 32)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);
+  // measured on B200 (Q6_K 14336 x 4096): fused pass of eight rows 77 us, decode + split-K GEMM 165 us for 33 rows
+  // and 175 us for 64 (Q4_K 4096 x 4096: 21 us per pass, 70 us), so up to 16 rows go through the fused kernel in
+  // chunks of eight
+  if (path == 2 || (path == 0 && m > 16)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);
   const size_t xe = x_half ? 2 : 4;
   for (int r0 = 0; r0 < m; r0 += 8) {
     const int mm = std::min(8, m - r0);

@@ -20,7 +20,8 @@ __global__ void k_to_half(const float* __restrict__ src, __half* __restrict__ ds
 }
 
 __global__ void __launch_bounds__(128)
-    k_gemm_tc(const __half* __restrict__ X, const __half* __restrict__ W, float* __restrict__ Y, int m, int K, int ldy) {
+    k_gemm_tc(const __half* __restrict__ X, const __half* __restrict__ W, float* __restrict__ Y, int m, int K, int ldy,
+              int kspan, size_t zstride) {
   __shared__ __align__(16) __half ws[kGemmRows][kGemmK + kGemmPad];
   __shared__ __align__(16) __half xs[kGemmTokens][kGemmK + kGemmPad];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -31,7 +32,10 @@ __global__ void __launch_bounds__(128)
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-  for (int k0 = 0; k0 < K; k0 += kGemmK) {
+  // blockIdx.z takes the K range [z * kspan, (z + 1) * kspan) and writes its own output plane (split K: more blocks
+  // and more loads in flight than one block per 64 rows streaming all of K)
+  Y += blockIdx.z * zstride;
+  for (int k0 = blockIdx.z * kspan; k0 < (blockIdx.z + 1) * kspan; k0 += kGemmK) {
     // stage 64 x 64 weights and up to 32 x 64 activations (16-byte chunks)
     for (int c = threadIdx.x; c < kGemmRows * (kGemmK / 8); c += blockDim.x) {
       const int r = c / (kGemmK / 8), q = c % (kGemmK / 8);

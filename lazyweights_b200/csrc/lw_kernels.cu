@@ -597,14 +597,25 @@ int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st) {
 }
 
 // Y[m, rows] (row stride ldy, starting at column col0) = X[m, K] . W[rows, K]^T on the tensor cores
-int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, cudaStream_t st) {
+int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, float* partials,
+                   size_t partial_capacity, cudaStream_t st) {
   if (m < 1 || rows % kGemmRows || K % kGemmK) {
     set_kernel_error_text("gemm_tc", "shape must be a multiple of 64 rows x 64 columns");
     return kErrArg;
   }
-  dim3 grid(rows / kGemmRows, (m + kGemmTokens - 1) / kGemmTokens);
-  k_gemm_tc<<<grid, 128, 0, st>>>(X, W, Y, m, K, ldy);
-  return check_launch("k_gemm_tc");
+  // split K while the partial planes fit the scratch: one block per 64 rows streaming all of K leaves the SMs idle
+  int ks = 8;
+  while (ks > 1 && (K % (ks * kGemmK) || static_cast<size_t>(ks) * m * rows > partial_capacity || !partials)) ks /= 2;
+  dim3 grid(rows / kGemmRows, (m + kGemmTokens - 1) / kGemmTokens, ks);
+  if (ks == 1) {
+    k_gemm_tc<<<grid, 128, 0, st>>>(X, W, Y, m, K, ldy, K, 0);
+    return check_launch("k_gemm_tc");
+  }
+  k_gemm_tc<<<grid, 128, 0, st>>>(X, W, partials, m, K, rows, K / ks, static_cast<size_t>(m) * rows);
+  int rc = check_launch("k_gemm_tc");
+  if (rc) return rc;
+  k_sum_partials<<<(m * (rows / 4) + 127) / 128, 128, 0, st>>>(partials, Y, m, rows, ldy, ks);
+  return check_launch("k_sum_partials");
 }
 
 int read_kernel_error(unsigned int* value, bool clear) {

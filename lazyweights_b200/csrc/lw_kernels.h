@@ -42,7 +42,8 @@ int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st);
 int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st);
 // fp32 -> fp16 copy, and Y[m, rows] = X[m, K] . W[rows, K]^T (fp16 in, fp32 out, tensor cores) for the decode + GEMM path.
 int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st);
-int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, cudaStream_t st);
+int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, float* partials,
+                   size_t partial_capacity, cudaStream_t st);
 // Y[j, n] (row stride ldy) = sum_k X[j, k] W[n, k] for m <= 8 rows of X (fp16 or fp32, row-major [m, K]).
 // `partials` (partial_capacity floats) must hold gemv_partial_floats_min(M, m) floats; with gemv_partial_floats(M, m)
 // products of 2..8 rows take the faster kernel.

@@ -60,7 +60,7 @@ struct Model {
 };
 
 int cuda_fail(const char* what, cudaError_t e);
-// path 0: fused decode + product in chunks of eight rows up to 32 rows, decode + tensor-core GEMM above; 1: always
+// path 0: fused decode + product in chunks of eight rows up to 16 rows, decode + tensor-core GEMM above; 1: always
 // fused; 2: always decode + GEMM.
 int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
                   int path = 0);
