@@ -136,10 +136,11 @@ int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, flo
 int lw_linear_static(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
 
 /* Decoded and dequantised weights as fp16 [N, K] on the device: float32 block arithmetic (scale * f(q) - offset,
- * each operation rounded) rounded once to fp16. */
+ * each operation rounded) rounded once to fp16.  w_half_dev must be 32-byte aligned (32-byte stores). */
 int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream);
 
-/* Decoded codes on the device, one per byte [N, K] (expand != 0) or symbols [N, K / (8 / bits)] (expand == 0). */
+/* Decoded codes on the device, one per byte [N, K] (expand != 0) or symbols [N, K / (8 / bits)] (expand == 0).
+ * out_dev must be 32-byte aligned (32-byte stores). */
 int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* stream);
 
 /* ---- single matrices without a bundle directory (additions) ---------------------------------------------- */

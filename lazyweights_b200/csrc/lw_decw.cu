@@ -69,6 +69,10 @@ static int launch_i(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
 // Returns kErrTooLarge where this kernel cannot take the product (the caller then uses the warp-per-tile kernel).
 int launch_decw(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
   if (!err || M.KT > 255 || tr1 <= tr0) return kErrTooLarge;
+  if (reinterpret_cast<uintptr_t>(out) & 31u) {
+    set_kernel_error_text("decode_weights", "the output must be 32-byte aligned");
+    return kErrArg;
+  }
   switch (M.fmt) {
     case kFmtQ4K: return launch_i<kFmtQ4K>(M, out, tr0, tr1, err, st);
     case kFmtQ5K: return launch_i<kFmtQ5K>(M, out, tr0, tr1, err, st);

@@ -68,18 +68,19 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_codes(MatDev M, 
   const int row_bytes = EXPAND ? 2 * M.Ks : M.Ks;
   const int tile_bytes = EXPAND ? 2 * kTileSyms : kTileSyms;
 #pragma unroll 1
-  const int G = 2 * M.split, per_seg = tile_bytes / 16 / M.split;
+  // A lane owns a row, so every store instruction touches 32 different lines: 32-byte pieces (a whole sector each).
+  const int G = 2 * M.split, per_seg = tile_bytes / 32 / M.split;
   for (int half = 0; half < 2; ++half) {
     Chain ch;
-    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(tr * kTileRows + half * 32 + lane) * row_bytes +
-                                          static_cast<size_t>(tc) * tile_bytes);
+    uint8_t* dst = out + static_cast<size_t>(tr * kTileRows + half * 32 + lane) * row_bytes +
+                   static_cast<size_t>(tc) * tile_bytes;
 #pragma unroll 1
-    for (int c = 0; c < tile_bytes / 16; ++c) {
+    for (int c = 0; c < tile_bytes / 32; ++c) {
       if (c % per_seg == 0)   // next column segment: its own chain
         ch.init(buf + (__ldg(M.group_base + static_cast<size_t>(t) * G + 2 * (c / per_seg) + half) - base) + lane, M.pad);
-      uint32_t v[4];
+      uint32_t v[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         if (EXPAND) {
           const uint32_t e0 = ch.next(lut), e1 = ch.next(lut);
           v[j] = (e0 & 15u) | ((e0 & 0xF0u) << 4) | ((e1 & 15u) << 16) | ((e1 & 0xF0u) << 20);
@@ -90,7 +91,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) k_decode_codes(MatDev M, 
           v[j] |= (ch.next(lut) & 255u) << 24;
         }
       }
-      dst[c] = make_uint4(v[0], v[1], v[2], v[3]);
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 32 * c), "r"(v[0]), "r"(v[1]),
+                   "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                   : "memory");
     }
   }
 }
@@ -388,6 +391,10 @@ static int prepare(K kernel, size_t smem) {
 }
 
 int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaStream_t st) {
+  if (reinterpret_cast<uintptr_t>(out) & 31u) {
+    set_kernel_error_text("decode_codes", "the output must be 32-byte aligned");
+    return kErrArg;
+  }
   const size_t smem = 2 * kLutSize + 128 + kWarpsPerBlock * stage_bytes(M);
   const int blocks = (M.T + kWarpsPerBlock - 1) / kWarpsPerBlock;
   int rc;
