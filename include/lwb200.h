@@ -67,8 +67,11 @@ double rt_gpu_decode_all(void* handle, int reps);
  * rt_cpu_decode_all, kernels/llmrt.cu:2558. */
 double rt_cpu_decode_all(void* handle, int threads, long long* symbols);
 
-/* Counters by name ("resident_bytes", "coded_bytes", "side_bytes", "n_matrices", ...); -1 for an unknown key.
- * Replaces rt_stat, kernels/llmrt.cu:2276. */
+/* Counters by name ("resident_bytes", "coded_bytes", "side_bytes", "n_matrices", "graph_launches", "graph_captures");
+ * -1 for an unknown key.  Replaces rt_stat, kernels/llmrt.cu:2276.  Additions for tensor-parallel runs:
+ * "time_collectives" arms a measurement (returns 0): the next rt_forward pass is launched directly with CUDA events
+ * around every collective; afterwards "collective_us" is the time spent between those event pairs and
+ * "collective_calls" their number. */
 double rt_stat(void* handle, const char* key);
 
 /* ---- decoder runtime (bundles whose cfg describes a model: n_layers, hidden, n_heads, ...) ------------------- */
@@ -124,8 +127,9 @@ int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, flo
  * by someone else and must not grow).  lw_linear draws its split-K scratch from the handle, which rt_open /
  * lw_matrix_create allocated; this entry point uses a fixed 16 MiB scratch array that is part of the library image
  * instead, so nothing is allocated or freed here, by this library or by any library it calls.
- *   - Limit: (K / tile width) x max(m, column segments) x N <= 4,194,304 partial sums and m <= 8; larger products are
- *     refused with LW_ERR_TOO_LARGE and a message (use lw_linear for those).
+ *   - Limit: m <= 8 and at most 4,194,304 partial sums: (K / tile width) x N of them for one row, (K / tile width) x
+ *     column segments x m x N for more rows; larger products are refused with LW_ERR_TOO_LARGE and a message (use
+ *     lw_linear for those).
  *   - The first call on a device looks the array's device address up (once per device, with that device current); make
  *     that first call before any stream capture begins.
  *   - All calls share the one array and it keeps whatever the previous call left.  Nothing needs clearing (a call
@@ -159,6 +163,12 @@ long long lw_encode_huf8(const uint8_t* sym, int N, int Ks, uint8_t* out, long l
 /* Full host-side validation of a blob: canonical table, every lane decodes and ends where the next begins. */
 int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks);
 
+/* Host only: reads a bundle directory's manifest, checks that every tensor lies inside weights.bin and, if the cfg
+ * describes a model, that every tensor the decoder runtime indexes has the shape the cfg implies (coded matrices vs
+ * heads / hidden / inter / vocab, norm vectors, rotary tables, embedding and its scale tensors).  rt_open runs the
+ * same check before it uploads anything.  The reference exits on such bundles (kernels/llmrt.cu:2146-2171). */
+int lw_validate_bundle(const char* dir);
+
 /* Threaded host decode of a blob to symbols [N, Ks] (the algorithm of cpu_decode, kernels/llmrt.cu:2513-2541). */
 int lw_cpu_decode(const uint8_t* blob, long long blob_bytes, int N, int Ks, int threads, uint8_t* out);
 
@@ -181,11 +191,25 @@ const char* lw_last_error(void);
 /* Status code of the last rt_open / lw_matrix_create on the calling thread (they can only return NULL). */
 int lw_last_status(void);
 
-/* Reads and clears the device error word (bit 0: a bounded wait on a bulk copy gave up). */
+/* Reads and clears the device error word (bit 0: a bounded wait on a bulk copy gave up).  After a non-zero answer the
+ * results of products that were in flight are undefined; the next product of every matrix first zeroes the matrix's
+ * tile-row counters again, so later products are correct. */
 int lw_kernel_error(void);
 
 /* Number of kernels this library has launched since it was loaded. */
 long long lw_launch_count(void);
+
+/* Test switches (no reference counterpart).  Keys: "max_units" (2..1024: units a block is dealt per launch; smaller
+ * values make a product run as several launches over ranges of tile rows, the path very tall matrices take),
+ * "wait_limit" (polls after which a device-side wait gives up), "drop_unit" (block 0's producers never copy this unit
+ * of their list, so the waits for it run out; -1 = none), "reset" (all back to the production values). */
+int lw_debug_set(const char* key, long long value);
+
+/* Launches one warp that waits, `limit` polls each, on a copy barrier nothing completes and on a release counter
+ * nothing advances.  Returns 1 (barrier wait gave up) + 2 (counter wait gave up) = 3, or a negative status; the device
+ * error word is set as by any wait that gives up (lw_kernel_error then returns 1).  Shows, without a fault, that a
+ * lost copy ends a kernel instead of hanging it. */
+int lw_debug_wait_probe(long long limit);
 
 #ifdef __cplusplus
 }

@@ -46,6 +46,9 @@ _SIGNATURES = {
     "lw_encode_huf8": (C.c_longlong, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.POINTER(C.c_longlong)]),
     "lw_validate_blob": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_int]),
     "lw_cpu_decode": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "lw_validate_bundle": (C.c_int, [C.c_char_p]),
+    "lw_debug_set": (C.c_int, [C.c_char_p, C.c_longlong]),
+    "lw_debug_wait_probe": (C.c_int, [C.c_longlong]),
     "lw_last_error": (C.c_char_p, []),
     "lw_last_status": (C.c_int, []),
     "lw_kernel_error": (C.c_int, []),

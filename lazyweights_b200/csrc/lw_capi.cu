@@ -15,6 +15,7 @@
 
 #include "../../include/lwb200.h"
 #include "lw_host.h"
+#include "lw_gemv1.h"
 #include "lw_kernels.h"
 #include "lw_model.h"
 
@@ -69,12 +70,7 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   if ((rc = check_side(mx, side, side_nbytes))) return rc;
   auto tab = std::make_unique<HuffTable>();
   if ((rc = table_from_lut(v.lut(), *tab))) return rc;
-  int split = default_split(mx.fmt);
-  if (const char* e = getenv("LW_SPLIT")) {
-    const int s = atoi(e);
-    if (s == 1 || s == 2 || (s == 4 && mx.fmt != kFmtQ5K)) split = s;
-  }
-  if (mx.fmt == kFmtNone) split = 1;
+  const int split = default_split(mx.fmt);
   std::vector<uint32_t> chain_start, lane_end;
   im.fat.resize(kLutSize);
   fat_table(*tab, mx.fmt, im.fat.data());
@@ -122,13 +118,8 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
     }
   }
   // Leading zero bits of every chain: they place the decode window on the address bits of the batch-1 kernel's
-  // table of 4-byte entries, 16 copies (64 bytes) per window.  LW_PAD overrides (and switches that kernel off).
-  int pad = 6;
-  if (const char* e = getenv("LW_PAD")) {
-    const int p = std::max(0, std::min(7, atoi(e)));
-    if (p != pad) group = 0;
-    pad = p;
-  }
+  // table of 4-byte entries, 16 copies (64 bytes) per window.
+  const int pad = 6;
   if ((rc = relayout(v, split, pad, chain_start, lane_end, threads, im.group_base, im.words, &im.max_unit, &im.max_tile,
                      mx.fmt, group ? side : nullptr)))
     return rc;
@@ -201,7 +192,7 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
 static int finish_model(Model* M) {
   size_t need = 0;
   for (auto& m : M->mats) {
-    if (m.fmt != kFmtNone) need = std::max(need, gemv_partial_floats(m.dev, 8));
+    if (m.fmt != kFmtNone && m.dev.group) need = std::max(need, gemv_partial_floats(m.dev, 8));
     M->resident_bytes += m.device_bytes;
     M->coded_bytes += m.blob_bytes;
     M->side_bytes += m.side_bytes;
@@ -225,7 +216,23 @@ static Matrix* matrix_by_id(void* h, int id) {
 
 const MatDev* matrix_descriptor(void* handle, int id) {
   Matrix* mx = matrix_by_id(handle, id);
-  return mx ? &mx->dev : nullptr;
+  if (!mx || check_device(static_cast<Model*>(handle))) return nullptr;
+  return &mx->dev;
+}
+
+unsigned int* matrix_clean_epoch(void* handle, int id) {
+  Matrix* mx = matrix_by_id(handle, id);
+  return mx ? &mx->clean_epoch : nullptr;
+}
+
+int check_device(const Model* M) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return cuda_fail("cudaGetDevice", cudaGetLastError());
+  if (dev != M->device) {
+    set_error("the handle was opened on device %d but the current device is %d", M->device, dev);
+    return kErrArg;
+  }
+  return kOk;
 }
 
 static int matrix_id(Model* M, const char* name) {
@@ -282,6 +289,7 @@ static int linear_decode_gemm(Model* M, Matrix& mx, const void* x, bool x_half, 
 
 int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
                   int path) {
+  if (const int rc = check_device(M)) return rc;
   if (mx.fmt == kFmtNone) {
     set_error("%s has no side tensor: products need a block format", mx.name.c_str());
     return kErrArg;
@@ -294,7 +302,8 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   for (int r0 = 0; r0 < m; r0 += 8) {
     const int mm = std::min(8, m - r0);
     const int rc = launch_gemv(mx.dev, static_cast<const uint8_t*>(x) + static_cast<size_t>(r0) * mx.K * xe, x_half,
-                               mm, y + static_cast<size_t>(r0) * ldy, ldy, M->d_partials, M->partial_floats, st);
+                               mm, y + static_cast<size_t>(r0) * ldy, ldy, M->d_partials, M->partial_floats, st,
+                               &mx.clean_epoch);
     if (rc) return rc;
   }
   return kOk;
@@ -318,11 +327,32 @@ int lw_kernel_error(void) {
 
 long long lw_launch_count(void) { return launch_count(); }
 
-void rt_close(void* handle) {
-  Model* M = static_cast<Model*>(handle);
-  if (M) runtime_free(M);
-  delete M;
+int lw_debug_set(const char* key, long long value) {
+  if (!key) return kErrArg;
+  DebugKnobs& k = debug_knobs();
+  const std::string s(key);
+  if (s == "max_units" && value >= 2 && value <= 1024) k.max_units = static_cast<int>(value) & ~1;
+  else if (s == "wait_limit" && value >= 1 && value <= (1ll << 30)) k.wait_limit = static_cast<uint32_t>(value);
+  else if (s == "drop_unit" && value >= -1 && value < 1024) k.drop_unit = static_cast<int>(value);
+  else if (s == "reset") k = DebugKnobs();
+  else {
+    set_error("lw_debug_set: unknown key or value out of range (%s)", key);
+    return kErrArg;
+  }
+  return kOk;
 }
+
+int lw_debug_wait_probe(long long limit) {
+  if (limit < 1 || limit > (1ll << 22)) return kErrArg;
+  int dev = 0;
+  int rc = require_device(&dev);
+  if (rc) return rc;
+  int gave_up = 0;
+  if ((rc = launch_wait_probe(static_cast<unsigned int>(limit), &gave_up))) return rc;
+  return gave_up;
+}
+
+void rt_close(void* handle) { delete static_cast<Model*>(handle); }
 
 void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, int floor_mb, int verbose) {
   (void)max_ctx; (void)max_batch; (void)budget_mb; (void)floor_mb;
@@ -336,6 +366,7 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
   M->dir = dir;
   M->verbose = verbose != 0;
   if (note_status(read_manifest(M->dir, M->man))) return nullptr;
+  if (M->man.cfg.count("n_layers") && note_status(validate_model(M->man))) return nullptr;
   M->fd = open((M->dir + "/weights.bin").c_str(), O_RDONLY);
   if (M->fd < 0) {
     set_error("cannot open %s/weights.bin", dir);
@@ -476,6 +507,7 @@ int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream) {
   Matrix* mx = matrix_by_id(handle, id);
   if (!mx) return kErrGeneric;
   if (!w_half_dev) return kErrArg;
+  if (const int rc = check_device(static_cast<Model*>(handle))) return rc;
   return launch_decode_weights(mx->dev, static_cast<__half*>(w_half_dev), static_cast<cudaStream_t>(stream));
 }
 
@@ -483,6 +515,7 @@ int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* st
   Matrix* mx = matrix_by_id(handle, id);
   if (!mx) return kErrGeneric;
   if (!out_dev) return kErrArg;
+  if (const int rc = check_device(static_cast<Model*>(handle))) return rc;
   return launch_decode_codes(mx->dev, out_dev, expand != 0 && mx->paired, static_cast<cudaStream_t>(stream));
 }
 
@@ -537,6 +570,7 @@ int rt_test_decode(void* handle, const char* name, uint8_t* out) {
   if (id < 0) return -1;
   Matrix& mx = M->mats[id];
   if (!out) return kErrArg;
+  if (const int rc = check_device(M)) return rc;
   const size_t n = static_cast<size_t>(mx.N) * mx.K;
   uint8_t* d = nullptr;
   cudaError_t e = cudaMalloc(&d, n);
@@ -593,7 +627,7 @@ double rt_cpu_decode_all(void* handle, int threads, long long* symbols) {
 
 double rt_gpu_decode_all(void* handle, int reps) {
   Model* M = static_cast<Model*>(handle);
-  if (!M || reps < 1) return -1;
+  if (!M || reps < 1 || check_device(M)) return -1;
   size_t cap = 0;
   for (auto& mx : M->mats) cap = std::max(cap, static_cast<size_t>(mx.N) * mx.K);
   uint8_t* scratch = nullptr;
@@ -632,7 +666,9 @@ double rt_stat(void* handle, const char* key) {
   if (k == "coded_bytes") return static_cast<double>(M->coded_bytes);
   if (k == "side_bytes") return static_cast<double>(M->side_bytes);
   if (k == "n_matrices") return static_cast<double>(M->mats.size());
-  if (k == "graph_launches" || k == "graph_captures") return runtime_stat(M, k.c_str());
+  if (k == "graph_launches" || k == "graph_captures" || k == "collective_us" || k == "collective_calls" ||
+      k == "time_collectives")
+    return runtime_stat(M, k.c_str());
   if (k == "streamed_bytes" || k == "n_streamed" || k == "stream_wait_s" || k == "stream_bytes_moved") return 0;
   return -1;
 }
@@ -699,6 +735,26 @@ long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int K
   if (unit_class && unit_class_cap >= static_cast<long long>(im.unit_slow.size()) && !im.unit_slow.empty())
     std::memcpy(unit_class, im.unit_slow.data(), im.unit_slow.size());
   return static_cast<long long>(im.words.size());
+}
+
+int lw_validate_bundle(const char* dir) {
+  if (!dir) return kErrArg;
+  Manifest man;
+  int rc = read_manifest(dir, man);
+  if (rc) return rc;
+  const int fd = open((std::string(dir) + "/weights.bin").c_str(), O_RDONLY);
+  if (fd < 0) {
+    set_error("cannot open %s/weights.bin", dir);
+    return kErrGeneric;
+  }
+  const off_t size = lseek(fd, 0, SEEK_END);
+  close(fd);
+  for (const TensorEntry& t : man.tensors)
+    if (t.offset + t.nbytes > size) {
+      set_error("tensor %s reaches past the end of weights.bin", t.name.c_str());
+      return kErrFormat;
+    }
+  return man.cfg.count("n_layers") ? validate_model(man) : kOk;
 }
 
 int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks) {

@@ -17,7 +17,12 @@ static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
   const int tiles = (tr1 - tr0) * M.KT;
   const int blocks = std::max(1, std::min(sm_count(), tiles));
   const int max_units = (((tiles + blocks - 1) / blocks) * SPLIT + 1) & ~1;
-  if (max_units > kGemv1MaxUnits) return kErrTooLarge;
+  if (max_units > kGemv1MaxUnits) {   // more tile rows than one block's list holds: two halves
+    const int mid = tr0 + (tr1 - tr0) / 2;
+    if (mid == tr0) return kErrTooLarge;
+    const int rc = launch_t<FMT, G, IDXBITS>(M, out, tr0, mid, err, st);
+    return rc ? rc : launch_t<FMT, G, IDXBITS>(M, out + static_cast<size_t>(mid - tr0) * kTileRows * M.K, mid, tr1, err, st);
+  }
   const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 + 2 * kGemv1MaxSlots * 8 +
                        kGemv1MaxSlots * 4 + 16 + max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
   if (fixed + static_cast<size_t>(buf_words) * 4 > kSmemLimit) return kErrTooLarge;
@@ -28,19 +33,20 @@ static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return note_launch("cudaFuncSetAttribute(k_decw)");
   DecwArgs a = {};
-  a.g.err = err;
-  a.g.warps = warps;
-  a.g.helpers = warps;
-  a.g.producers = 2;
-  a.g.producer_lanes = 4;
-  a.g.slots = slots;
-  a.g.buf_words = buf_words;
-  a.g.nsets = 1;
-  a.g.cols_per_set = M.KT;
-  a.g.max_units = max_units;
+  a.r.err = err;
+  a.r.wait_limit = debug_knobs().wait_limit;
+  a.r.drop_unit = -1;
+  a.r.warps = warps;
+  a.r.producers = 2;
+  a.r.producer_lanes = 4;
+  a.r.slots = slots;
+  a.r.buf_words = buf_words;
+  a.r.nsets = 1;
+  a.r.cols_per_set = M.KT;
+  a.r.max_units = max_units;
+  a.r.tr0 = tr0;
+  a.r.ntr = tr1 - tr0;
   a.out = out;
-  a.tr0 = tr0;
-  a.tr1 = tr1;
   kernel<<<blocks, (warps + 2) * 32, smem, st>>>(M, a);
   return note_launch("k_decw");
 }

@@ -10,9 +10,8 @@
 namespace lw {
 
 struct DecwArgs {
-  Gemv1Args g;      // x, y, partials unused
-  __half* out;      // [(tr1 - tr0) * 64][K]
-  int tr0, tr1;     // tile rows to decode
+  RingArgs r;       // r.tr0, r.ntr: tile rows to decode
+  __half* out;      // [ntr * 64][K]
 };
 
 // Collects sixteen weights of one chain and stores them as one 32-byte piece (a whole sector: a lane writes to its
@@ -35,8 +34,8 @@ __device__ __forceinline__ float grid_of_entry(uint32_t e, int which) {
 }
 
 template <int FMT, int G, int IDXBITS, int LOG_R>
-__global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs DA) {
-  const Gemv1Args& A = DA.g;
+__global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
+  const RingArgs& RA = A.r;
   constexpr bool PAIR = is_paired(FMT);
   constexpr int SPLIT = default_split(FMT);
   constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;
@@ -47,136 +46,45 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs DA) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
   uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);
-  uint64_t* full = reinterpret_cast<uint64_t*>(tab1 + kLutSize);
-  uint64_t* empty = full + kGemv1MaxSlots;
-  uint32_t* released = reinterpret_cast<uint32_t*>(empty + kGemv1MaxSlots);
-  int* next_unit = reinterpret_cast<int*>(released + kGemv1MaxSlots);
-  int* list_count = next_unit + 1;
-  UnitMeta* meta = reinterpret_cast<UnitMeta*>(next_unit + 4);
-  uint32_t* bufs = reinterpret_cast<uint32_t*>(meta + A.max_units);
+  RingMem RM;
+  RM.carve(tab1 + kLutSize, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int set = 0, bi = blockIdx.x, nb_set = gridDim.x, ncol = M.KT;   // one column set: no activations to stage
-  const int ntiles = (DA.tr1 - DA.tr0) * ncol;
-  const int tmine = bi < ntiles ? (ntiles - bi + nb_set - 1) / nb_set : 0;
-  const int nmine = tmine * SPLIT;
-  const bool consumer = warp < A.warps;
-  const int nthr = A.warps * 32;
+  BlockShare S;
+  S.init(M, RA, SPLIT);   // one column set (nsets = 1): there are no activations to stage
+  const int nmine = S.nmine;
+  const bool consumer = warp < RA.warps;
+  const int nthr = RA.warps * 32;
 
-  // 1. the block's list (whole tiles, symbol-by-symbol tiles first), exactly as in the batch-1 kernel
-  if (threadIdx.x == 0) {
-    list_count[0] = 0;
-    list_count[1] = 0;
-    *next_unit = 0;
-  }
+  // 1. the block's list (whole tiles, symbol-by-symbol tiles first) and the ring's barriers
+  ring_reset(RM);
   __syncthreads();
-  for (int k0 = warp * 32; k0 < nmine; k0 += (blockDim.x >> 5) * 32) {
-    const int k = k0 + lane, seg = lane % SPLIT;
-    const bool valid = k < nmine, leader = seg == 0;
-    int tr = 0, j = 0;
-    uint32_t g0 = 0, g1 = 0, g2 = 0, cls = 0;
-    bool slow = false;
-    if (valid) {
-      const int v = bi + (k / SPLIT) * nb_set;
-      j = v % ncol;
-      tr = DA.tr0 + v / ncol;
-      const int t = tr * M.KT + set + A.nsets * j;
-      const uint32_t* gb = M.group_base + static_cast<size_t>(t) * (2 * SPLIT) + 2 * seg;
-      g0 = __ldg(gb);
-      g1 = __ldg(gb + 1);
-      g2 = __ldg(gb + 2);
-      const uint8_t* uc = M.unit_slow + static_cast<size_t>(t) * SPLIT;
-      cls = __ldg(uc + seg);
-#pragma unroll
-      for (int i = 0; i < SPLIT; ++i) slow |= __ldg(uc + i) == 2;
-    }
-    const uint32_t bs = __ballot_sync(0xffffffffu, valid && leader && slow);
-    const uint32_t bf = __ballot_sync(0xffffffffu, valid && leader && !slow);
-    int base_s = 0, base_f = 0;
-    if (lane == 0) {
-      base_s = atomicAdd(list_count, __popc(bs));
-      base_f = atomicAdd(list_count + 1, __popc(bf));
-    }
-    base_s = __shfl_sync(0xffffffffu, base_s, 0);
-    base_f = __shfl_sync(0xffffffffu, base_f, 0);
-    const uint32_t below = (1u << lane) - 1u;
-    int tpos = slow ? base_s + __popc(bs & below) : tmine - 1 - (base_f + __popc(bf & below));
-    tpos = __shfl_sync(0xffffffffu, tpos, lane - seg);
-    if (valid) {
-      const int pos = tpos * SPLIT + seg;
-      meta[pos] = UnitMeta{g0,
-                           static_cast<uint16_t>((g2 - g0) >> 5),
-                           static_cast<uint16_t>(((g1 - g0) >> 5) | (cls << 14)),
-                           static_cast<uint16_t>(tr),
-                           static_cast<uint16_t>(pos / A.slots),
-                           static_cast<uint8_t>(j),
-                           static_cast<uint8_t>(seg),
-                           static_cast<uint8_t>(pos % A.slots),
-                           0};
-    }
-  }
-  if (threadIdx.x < A.slots) {
-    mbar_init(smem_addr(full + threadIdx.x), 1);
-    mbar_init(smem_addr(empty + threadIdx.x), 1);
-    released[threadIdx.x] = 0u;
-  }
+  ring_build_list<SPLIT>(M, RA, S, RM);
   __syncthreads();
 
   if (!consumer) {
-    // 2a. producers: issuer s owns buffers s, s + S, ... and feeds them round by round
-    if (lane < A.producer_lanes) {
-      const int issuers = A.producers * A.producer_lanes;
-      for (int round = 0; round * A.slots < nmine; ++round)
-        for (int slot = (warp - A.warps) * A.producer_lanes + lane; slot < A.slots; slot += issuers) {
-          const int k = round * A.slots + slot;
-          if (k >= nmine) break;
-          if (round > 0) {
-            if (!wait_released(released + slot, round, A.err)) return;
-            if (!mbar_wait(smem_addr(empty + slot), (round - 1) & 1, A.err)) return;
-          }
-          const UnitMeta um = meta[k];
-          bulk_load(smem_addr(bufs + static_cast<size_t>(slot) * A.buf_words), M.words + um.src, um.lines * 128u,
-                    smem_addr(full + slot));
-        }
-    }
+    ring_produce(M, RA, RM, nmine, warp - RA.warps, lane);   // 2a. producers
     return;
   }
 
-  // 2b. consumers: tables, then the activations of the block's tile columns for all rows
-  {
-    constexpr int PER = 32 / R;
-    for (int i0 = warp * 32; i0 < NIDX; i0 += A.warps * 32) {
-      const uint32_t mine = __ldg(M.tab32 + i0 + lane);
-#pragma unroll 8
-      for (int j = 0; j < 32; j += PER) {
-        const uint32_t v = __shfl_sync(0xffffffffu, mine, j + (lane >> LOG_R));
-        tab[(i0 + j) * R + lane] = v;
-      }
-      tab1[i0 + lane] = mine;
-    }
-    for (int idx = NIDX + static_cast<int>(threadIdx.x); idx < kLutSize; idx += nthr) tab1[idx] = __ldg(M.tab32 + idx);
-  }
+  // 2b. consumers: the tables
+  table_fill<IDXBITS, LOG_R>(M, tab, tab1, warp, lane, RA.warps);
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
   const uint32_t lane_off = (lane & (R - 1)) << 2;
 #pragma unroll 1
   for (;;) {
-    int k = 0;
-    if (lane == 0) k = atomicAdd(next_unit, 1);
-    k = __shfl_sync(0xffffffffu, k, 0);
-    if (k >= nmine) break;
-    const uint4 raw = *reinterpret_cast<const uint4*>(meta + k);
-    const uint32_t lines = raw.y & 0xFFFFu, second = raw.y >> 16, tr = raw.z & 0xFFFFu, round = raw.z >> 16;
-    const uint32_t tc = raw.w & 255u, seg = (raw.w >> 8) & 255u, slot = (raw.w >> 16) & 255u;
-    const uint32_t cls = second >> 14;
-    const uint32_t* buf = bufs + static_cast<size_t>(slot) * A.buf_words;
-    if (round > 0 && !wait_released(released + slot, round, A.err)) return;
-    if (!mbar_wait(smem_addr(full + slot), round & 1, A.err)) return;
+    Unit u;
+    const int got = ring_draw(RA, RM, nmine, lane, u);
+    if (got == 0) break;
+    if (got < 0) return;
+    const uint32_t tc = u.j, seg = u.seg, tr = u.tr, cls = u.cls, lines = u.lines, second = u.second;
+    const uint32_t* buf = u.buf;
     UnitSide<FMT> side_a, side_b;
     side_a.load(buf + lines * 32u - SIDEW, lane);
     side_b.load(buf + lines * 32u - SIDEW, lane + 32);
     GroupChain ca, cb;
     ca.init(buf + lane);
-    cb.init(buf + (second & 0x3FFFu) * 32u + lane);
-    __half* oa = DA.out + (static_cast<size_t>(tr - DA.tr0) * kTileRows + lane) * M.K + static_cast<size_t>(tc) * TW +
+    cb.init(buf + second * 32u + lane);
+    __half* oa = A.out + (static_cast<size_t>(tr - RA.tr0) * kTileRows + lane) * M.K + static_cast<size_t>(tc) * TW +
                  seg * (TW / SPLIT);
     __half* ob = oa + static_cast<size_t>(32) * M.K;
     // symbols per 32-byte store: eight paired symbols (two weights each) or sixteen single ones
@@ -259,11 +167,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs DA) {
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) {
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(empty + slot)) : "memory");
-      asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(released + slot)), "r"(round + 1u) : "memory");
-    }
+    ring_release(RM, u, lane);
   }
 }
 

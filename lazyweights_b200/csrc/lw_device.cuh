@@ -35,9 +35,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 // Waits for phase `parity` of the barrier.  The wait is bounded: after kWaitLimit polls it records the failure in
 // the device error word `err` (bit 0) and returns false, so a copy that never lands cannot hang the device.
+// `limit` is an argument so that a test can make a wait run out quickly.
 constexpr uint32_t kWaitLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* err) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* err,
+                                          uint32_t limit = kWaitLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

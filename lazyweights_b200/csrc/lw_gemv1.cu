@@ -23,8 +23,20 @@ static int env_int(const char* name, int fallback) {
   return e ? atoi(e) : fallback;
 }
 
+// Tuning switches from the environment, read once (a getenv per launch is host overhead on the direct-launch path).
+struct Gemv1Env {
+  int ring = env_int("LW_GEMV1_RING", 8), warps = env_int("LW_GEMV1_WARPS", 0), producers = env_int("LW_GEMV1_PRODUCERS", 2),
+      helpers = env_int("LW_GEMV1_HELPERS", kGemv1MaxWarps), lanes = env_int("LW_GEMV1_LANES", 4), pdl = env_int("LW_PDL", 1);
+};
+static const Gemv1Env& gemv1_env() {
+  static const Gemv1Env e;
+  return e;
+}
+
+// Plan for a launch over `ntr` tile rows.  False if a unit does not fit shared memory or a block would be dealt more
+// units than its list holds (the caller then covers the rows in several launches).
 template <int FMT>
-static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
+static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p) {
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT);
   constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
   p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
@@ -32,20 +44,20 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   // a chain reader looks up to three words past its chain; for all buffers but the last that lands in the next buffer
   // (harmless: those bits are never used), so only the end of the ring needs slack
   p.buf_words = (M.max_unit_words + 31u) & ~31u;
-  const int tiles = (M.N / kTileRows) * M.KT;
+  const int tiles = ntr * M.KT;
   p.blocks = std::max(p.nsets, std::min(sm_count(), tiles));
   p.max_units = 0;   // the longest list any block gets: blocks b, b + nsets, ... serve the tile columns of set b % nsets
   for (int set = 0; set < p.nsets; ++set) {
     const int nb_set = (p.blocks - set + p.nsets - 1) / p.nsets, ncol = (M.KT - set + p.nsets - 1) / p.nsets;
-    const int set_tiles = (M.N / kTileRows) * ncol;
+    const int set_tiles = ntr * ncol;
     p.max_units = std::max(p.max_units, (set_tiles + nb_set - 1) / nb_set * SPLIT);
   }
   p.max_units = (p.max_units + 1) & ~1;
-  if (p.max_units > kGemv1MaxUnits) return false;
+  if (p.max_units > debug_knobs().max_units) return false;
   // The ring in which the segments of a tile meet: 8 tiles (28 warps have 7 tiles in flight); 16 with
   // LW_GEMV1_RING=16 where 36 staging buffers still fit (measured: no difference on the bench matrix).
   size_t fixed = 0;
-  for (p.tile_ring_log2 = env_int("LW_GEMV1_RING", 8) >= 16 ? 4 : 3; p.tile_ring_log2 >= 3; --p.tile_ring_log2) {
+  for (p.tile_ring_log2 = gemv1_env().ring >= 16 ? 4 : 3; p.tile_ring_log2 >= 3; --p.tile_ring_log2) {
     fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
             static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
             2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + (size_t(1) << p.tile_ring_log2) * (8 + SPLIT * kTileRows * 4) +
@@ -60,20 +72,28 @@ static bool plan_gemv1(const MatDev& M, Gemv1Plan& p) {
   // consumers per four buffers (measured on the bench matrix: 28 warps 35.6 us, 25 warps 37.9 us, 20 warps 39.0 us).
   p.warps = std::max(1, std::min(kGemv1MaxWarps, p.max_units <= p.slots ? p.slots : p.slots * 3 / 4));
   p.warps = std::min(p.warps, p.max_units);
-  p.warps = std::max(1, std::min(std::min(kGemv1MaxWarps, p.slots), env_int("LW_GEMV1_WARPS", p.warps)));
-  p.producers = std::max(1, std::min(4, env_int("LW_GEMV1_PRODUCERS", 2)));
-  p.helpers = std::max(p.warps, std::min(kGemv1MaxWarps, env_int("LW_GEMV1_HELPERS", kGemv1MaxWarps)));
-  p.producer_lanes = std::max(1, std::min(32, env_int("LW_GEMV1_LANES", 4)));
+  p.warps = std::max(1, std::min(std::min(kGemv1MaxWarps, p.slots), gemv1_env().warps > 0 ? gemv1_env().warps : p.warps));
+  p.producers = std::max(1, std::min(4, gemv1_env().producers));
+  p.helpers = std::max(p.warps, std::min(kGemv1MaxWarps, gemv1_env().helpers));
+  p.producer_lanes = std::max(1, std::min(32, gemv1_env().lanes));
   p.smem = fixed + static_cast<size_t>(p.slots) * p.buf_words * 4;
   return true;
 }
 
 template <int FMT, int G, int IDXBITS, int LOG_R>
-static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err,
+                    cudaStream_t st) {
+  // A block's list holds at most kRingMaxUnits units; a matrix with more tile rows than that allows (a vocabulary
+  // projection of 128k rows x 8192 columns, say) is covered by several launches over ranges of tile rows.
+  const int NT = M.N / kTileRows;
   Gemv1Plan p;
-  if (!plan_gemv1<FMT>(M, p)) {
-    set_kernel_error_text("gemv1", "work unit does not fit shared memory");
-    return kErrTooLarge;
+  int chunks = 1;
+  while (!plan_gemv1<FMT>(M, (NT + chunks - 1) / chunks, p)) {
+    if (p.max_units <= debug_knobs().max_units || chunks >= NT) {
+      set_kernel_error_text("gemv1", "work unit does not fit shared memory");
+      return kErrTooLarge;
+    }
+    chunks = std::min(NT, std::max(chunks + 1, chunks * p.max_units / debug_knobs().max_units));
   }
   // the attribute is raised once per kernel instantiation and device, not on every launch
   static size_t configured_per_device[64] = {0};
@@ -86,39 +106,53 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
       return note_launch("cudaFuncSetAttribute(k_gemv1)");
     configured = kSmemLimit;
   }
-  Gemv1Args a;
-  a.x = X;
-  a.partials = P;
-  a.y = Y;
-  a.err = err;
-  a.x_is_half = x_is_half;
-  a.warps = p.warps;
-  a.helpers = p.helpers;
-  a.slots = p.slots;
-  a.producers = p.producers;
-  a.producer_lanes = p.producer_lanes;
-  a.buf_words = p.buf_words;
-  a.nsets = p.nsets;
-  a.cols_per_set = p.cols_per_set;
-  a.max_units = p.max_units;
-  a.tile_ring_log2 = p.tile_ring_log2;
-  a.pdl = env_int("LW_PDL", 1) != 0;
-  if (a.pdl) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.blocks);
-    cfg.blockDim = dim3((p.helpers + p.producers) * 32);
-    cfg.dynamicSmemBytes = p.smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R>, M, a);
-  } else {
-    k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
+  const int per = (NT + chunks - 1) / chunks;
+  for (int tr0 = 0; tr0 < NT; tr0 += per) {
+    const int ntr = std::min(per, NT - tr0);
+    if (ntr != per && !plan_gemv1<FMT>(M, ntr, p)) {
+      set_kernel_error_text("gemv1", "work unit does not fit shared memory");
+      return kErrTooLarge;
+    }
+    Gemv1Args a;
+    a.x = X;
+    a.partials = P;
+    a.y = Y;
+    a.x_is_half = x_is_half;
+    a.helpers = p.helpers;
+    a.tile_ring_log2 = p.tile_ring_log2;
+    a.pdl = gemv1_env().pdl != 0;
+    a.r.err = err;
+    a.r.wait_limit = debug_knobs().wait_limit;
+    a.r.drop_unit = debug_knobs().drop_unit;
+    a.r.warps = p.warps;
+    a.r.slots = p.slots;
+    a.r.producers = p.producers;
+    a.r.producer_lanes = p.producer_lanes;
+    a.r.buf_words = p.buf_words;
+    a.r.nsets = p.nsets;
+    a.r.cols_per_set = p.cols_per_set;
+    a.r.max_units = p.max_units;
+    a.r.tr0 = tr0;
+    a.r.ntr = ntr;
+    if (a.pdl) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(p.blocks);
+      cfg.blockDim = dim3((p.helpers + p.producers) * 32);
+      cfg.dynamicSmemBytes = p.smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R>, M, a);
+    } else {
+      k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
+    }
+    const int rc = note_launch("k_gemv1");
+    if (rc) return rc;
   }
-  return note_launch("k_gemv1");
+  return kOk;
 }
 
 template <int FMT, int G>

@@ -21,6 +21,14 @@ int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* p
 // launched) where it cannot take the matrix.
 int launch_decw(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st);
 
+// Test switches (set through lw_debug_set; defaults are the production values).
+struct DebugKnobs {
+  int max_units = 1024;            // cap on the units a block is dealt per launch (smaller: more launches per product)
+  uint32_t wait_limit = 1u << 22;  // polls after which a device-side wait gives up
+  int drop_unit = -1;              // the producers of block 0 skip the copy of this unit (its consumer's wait runs out)
+};
+DebugKnobs& debug_knobs();
+
 int note_launch(const char* what);   // counts a launch and returns the status of cudaGetLastError
 int sm_count();
 

@@ -18,23 +18,23 @@ struct GemvmPlan {
 };
 
 template <int FMT, int MR>
-static bool plan_gemvm(const MatDev& M, GemvmPlan& p) {
+static bool plan_gemvm(const MatDev& M, int ntr, GemvmPlan& p) {
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT), NSB = TW / sub_width(FMT);
   constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
   const int staged = std::max(1, 8 / MR);   // tile columns whose activations (all rows) one block keeps in shared memory
   p.nsets = (M.KT + staged - 1) / staged;
   p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
   p.buf_words = (M.max_unit_words + 31u) & ~31u;
-  const int tiles = (M.N / kTileRows) * M.KT;
+  const int tiles = ntr * M.KT;
   p.blocks = std::max(p.nsets, std::min(sm_count(), tiles));
   p.max_units = 0;
   for (int set = 0; set < p.nsets; ++set) {
     const int nb_set = (p.blocks - set + p.nsets - 1) / p.nsets, ncol = (M.KT - set + p.nsets - 1) / p.nsets;
-    const int set_tiles = (M.N / kTileRows) * ncol;
+    const int set_tiles = ntr * ncol;
     p.max_units = std::max(p.max_units, (set_tiles + nb_set - 1) / nb_set * SPLIT);
   }
   p.max_units = (p.max_units + 1) & ~1;
-  if (p.max_units > kGemv1MaxUnits) return false;
+  if (p.max_units > debug_knobs().max_units) return false;
   const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
                        static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * NSB) * MR * 4 +
                        2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + p.max_units * sizeof(UnitMeta) +
@@ -50,44 +50,68 @@ static bool plan_gemvm(const MatDev& M, GemvmPlan& p) {
 
 template <int FMT, int G, int IDXBITS, int MR>
 static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float* P, unsigned int* err, cudaStream_t st) {
+  // as in the batch-1 launcher: more tile rows than one block's list can hold are covered by several launches
+  const int NT = M.N / kTileRows;
   GemvmPlan p;
-  if (!plan_gemvm<FMT, MR>(M, p)) {
-    set_kernel_error_text("gemvm", "work unit does not fit shared memory");
-    return kErrTooLarge;
+  int chunks = 1;
+  while (!plan_gemvm<FMT, MR>(M, (NT + chunks - 1) / chunks, p)) {
+    if (p.max_units <= debug_knobs().max_units || chunks >= NT) {
+      set_kernel_error_text("gemvm", "work unit does not fit shared memory");
+      return kErrTooLarge;
+    }
+    chunks = std::min(NT, std::max(chunks + 1, chunks * p.max_units / debug_knobs().max_units));
   }
   auto kernel = k_gemvm<FMT, G, IDXBITS, kGemv1LogCopies, MR>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem)) != cudaSuccess)
-    return note_launch("cudaFuncSetAttribute(k_gemvm)");
-  GemvmArgs a;
-  a.g.x = X;
-  a.g.partials = P;
-  a.g.y = nullptr;
-  a.g.err = err;
-  a.g.x_is_half = x_is_half;
-  a.g.warps = p.warps;
-  a.g.helpers = p.warps;
-  a.g.slots = p.slots;
-  a.g.producers = p.producers;
-  a.g.producer_lanes = 4;
-  a.g.buf_words = p.buf_words;
-  a.g.nsets = p.nsets;
-  a.g.cols_per_set = p.cols_per_set;
-  a.g.max_units = p.max_units;
-  a.g.pdl = 1;
-  a.g.tile_ring_log2 = 3;
-  a.m = m;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.blocks);
-  cfg.blockDim = dim3((p.warps + p.producers) * 32);
-  cfg.dynamicSmemBytes = p.smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaLaunchKernelEx(&cfg, kernel, M, a);
-  return note_launch("k_gemvm");
+  static size_t configured_per_device[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  size_t& configured = configured_per_device[dev & 63];
+  if (p.smem > configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemLimit)) != cudaSuccess)
+      return note_launch("cudaFuncSetAttribute(k_gemvm)");
+    configured = kSmemLimit;
+  }
+  const int per = (NT + chunks - 1) / chunks;
+  for (int tr0 = 0; tr0 < NT; tr0 += per) {
+    const int ntr = std::min(per, NT - tr0);
+    if (ntr != per && !plan_gemvm<FMT, MR>(M, ntr, p)) {
+      set_kernel_error_text("gemvm", "work unit does not fit shared memory");
+      return kErrTooLarge;
+    }
+    GemvmArgs a;
+    a.x = X;
+    a.partials = P;
+    a.x_is_half = x_is_half;
+    a.pdl = 1;
+    a.m = m;
+    a.r.err = err;
+    a.r.wait_limit = debug_knobs().wait_limit;
+    a.r.drop_unit = -1;
+    a.r.warps = p.warps;
+    a.r.slots = p.slots;
+    a.r.producers = p.producers;
+    a.r.producer_lanes = 4;
+    a.r.buf_words = p.buf_words;
+    a.r.nsets = p.nsets;
+    a.r.cols_per_set = p.cols_per_set;
+    a.r.max_units = p.max_units;
+    a.r.tr0 = tr0;
+    a.r.ntr = ntr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.blocks);
+    cfg.blockDim = dim3((p.warps + p.producers) * 32);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, M, a);
+    const int rc = note_launch("k_gemvm");
+    if (rc) return rc;
+  }
+  return kOk;
 }
 
 template <int FMT, int G, int IDXBITS>

@@ -579,6 +579,88 @@ int read_blob(int fd, const TensorEntry& t, std::vector<uint8_t>& out) {
   return kOk;
 }
 
+// Everything rt_forward will index with the cfg's sizes is compared with the tensors' shapes here, on the host, so
+// that an inconsistent manifest is refused before anything is uploaded or launched.
+int validate_model(const Manifest& m) {
+  auto geti = [&](const char* k, int def) {
+    auto it = m.cfg.find(k);
+    return it == m.cfg.end() ? def : atoi(it->second.c_str());
+  };
+  const int L = geti("n_layers", 0), D = geti("hidden", 0), H = geti("n_heads", 0), Hk = geti("n_kv_heads", H);
+  const int Dh = geti("head_dim", H ? D / H : 0), I = geti("inter", 0), V = geti("vocab", 0);
+  const int rope_rows = geti("rope_rows", 4096);
+  if (L <= 0 || D <= 0 || H <= 0 || Hk <= 0 || Dh <= 0 || I <= 0 || V <= 0 || H % Hk || Dh % 8 || Dh > 128 || rope_rows <= 0) {
+    set_error("bundle cfg: bad model shape (head_dim must be a multiple of 8, at most 128)");
+    return kErrFormat;
+  }
+  auto want = [&](const std::string& name, const char* enc, long long n, long long k, bool any_rows) -> int {
+    const TensorEntry* t = m.find(name);
+    if (!t) {
+      set_error("bundle has no tensor %s", name.c_str());
+      return kErrFormat;
+    }
+    if (enc && t->enc != enc) {
+      set_error("tensor %s is %s, expected %s", name.c_str(), t->enc.c_str(), enc);
+      return kErrFormat;
+    }
+    if ((!any_rows && t->N != n) || t->K != k) {
+      set_error("tensor %s is %d x %d, the cfg wants %lld x %lld", name.c_str(), t->N, t->K, n, k);
+      return kErrFormat;
+    }
+    return kOk;
+  };
+  auto coded = [&](const std::string& name, long long n, long long k) -> int {
+    const TensorEntry* t = m.find(name);
+    if (!t || (t->enc != "huf8" && t->enc != "huf4p")) {
+      set_error("bundle has no coded matrix %s", name.c_str());
+      return kErrFormat;
+    }
+    if (t->N != n || t->K != k) {
+      set_error("matrix %s is %d x %d, the cfg wants %lld x %lld", name.c_str(), t->N, t->K, n, k);
+      return kErrFormat;
+    }
+    if (!m.find(name + ".kqs")) {
+      set_error("matrix %s has no side tensor", name.c_str());
+      return kErrFormat;
+    }
+    return kOk;
+  };
+  int rc;
+  const TensorEntry* emb = m.find("embed");
+  if (!emb || emb->K != D || emb->N <= 0 || (emb->enc != "f16" && emb->enc != "raw8")) {
+    set_error("embed must be an f16 or raw8 tensor with %d columns", D);
+    return kErrFormat;
+  }
+  if (emb->enc == "raw8") {
+    const TensorEntry* rs = m.find("embed.rs");
+    const TensorEntry* rsub = m.find("embed.rsub");
+    if (!rs || !rsub || rs->enc != "f32" || rsub->enc != "f32" || rs->N != emb->N || rsub->N != emb->N || rs->K <= 0 ||
+        rs->K > D || D % rs->K || rsub->K != rs->K) {
+      set_error("embed.rs / embed.rsub must be f32 [%d, G] with G dividing %d", emb->N, D);
+      return kErrFormat;
+    }
+  }
+  if ((rc = want("cos", "f32", rope_rows, Dh / 2, false)) || (rc = want("sin", "f32", rope_rows, Dh / 2, false)) ||
+      (rc = want("lnf", "f32", 1, D, false)))
+    return rc;
+  const long long QKV = static_cast<long long>(H + 2 * Hk) * Dh;
+  for (int l = 0; l < L; ++l) {
+    const std::string pre = "l" + std::to_string(l) + ".";
+    if ((rc = want(pre + "ln1", "f32", 1, D, false)) || (rc = want(pre + "ln2", "f32", 1, D, false))) return rc;
+    if (m.find(pre + "qkv")) {
+      if ((rc = coded(pre + "qkv", QKV, D))) return rc;
+    } else if ((rc = coded(pre + "q", static_cast<long long>(H) * Dh, D)) ||
+               (rc = coded(pre + "k", static_cast<long long>(Hk) * Dh, D)) ||
+               (rc = coded(pre + "v", static_cast<long long>(Hk) * Dh, D))) {
+      return rc;
+    }
+    if ((rc = coded(pre + "o", D, static_cast<long long>(H) * Dh)) || (rc = coded(pre + "gate", I, D)) ||
+        (rc = coded(pre + "up", I, D)) || (rc = coded(pre + "down", D, I)))
+      return rc;
+  }
+  return coded("lm_head", V, D);
+}
+
 int format_of_side_enc(const std::string& enc) {
   if (enc == "kq_Q4_K") return kFmtQ4K;
   if (enc == "kq_Q5_K") return kFmtQ5K;

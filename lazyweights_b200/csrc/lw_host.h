@@ -75,6 +75,8 @@ struct Manifest {
 
 int read_manifest(const std::string& dir, Manifest& m);
 int read_blob(int fd, const TensorEntry& t, std::vector<uint8_t>& out);
+// A bundle with a model configuration: every tensor the decoder runtime reads has the shape the cfg implies.
+int validate_model(const Manifest& m);
 int format_of_side_enc(const std::string& enc);   // "kq_Q4_K" -> kFmtQ4K, ... ; 0 if unknown
 int default_threads();
 

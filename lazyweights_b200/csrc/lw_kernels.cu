@@ -2,10 +2,12 @@
 //
 //   k_decode_codes    chain groups -> uint8 codes [N, K]           (role of k_decode_hufi, kernels/llmrt.cu:767-806)
 //   k_decode_weights  chain groups + side bytes -> fp16 [N, K]     (decode fused with the block dequantisation)
-//   k_gemv_fused      decode + dequant + product for m <= 8 rows   (role of k_gemvm_kq, kernels/llmrt.cu:896-1033)
 //   k_sum_partials    ordered sum over tile columns                (role of k_sum_kt, kernels/llmrt.cu:1173-1180)
 //
-// Common shape: one warp owns one 64 x 256-symbol tile.  Lane l decodes tile rows l and l + 32 as two independent
+// The fused decode + product kernels live in lw_gemv1.cu (one row) and lw_gemvm.cu (2..8 rows); this file dispatches
+// to them (launch_gemv, the role of matmul(), kernels/llmrt.cu:1794-1826).
+//
+// Common shape of the two decode kernels here: one warp owns one 64 x 256-symbol tile.  Lane l decodes tile rows l and l + 32 as two independent
 // chains.  The tile's interleaved words are staged into shared memory by one bulk copy (cp.async.bulk, completion
 // on an mbarrier) issued by lane 0; the lanes then read their next words from shared memory, bank = lane.
 #include "lw_kernels.h"
@@ -16,7 +18,7 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "lw_device.cuh"
+#include "lw_ring.cuh"
 #include "lw_gemv1.h"
 
 namespace lw {
@@ -164,139 +166,6 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   }
 }
 
-// ------------------------------------------------------------------------------------------- fused decode + GEMV
-
-__device__ __forceinline__ float to_f32(float v) { return v; }
-__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
-
-// P[tc, j, n] = sum over the tile column's sub-blocks g of  s_ng * sum_(k in g) X[j, k] f(q[n, k]) - o_ng * sum_(k in g) X[j, k]
-// A block's warps share one tile column (x staged once); warp w handles tile row blockIdx.y * 8 + w.
-template <int FMT, int MT, typename XT>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-    k_gemv_fused(MatDev M, const XT* __restrict__ X, float* __restrict__ P, int m) {
-  constexpr bool PAIR = is_paired(FMT);
-  constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;
-  constexpr int GW = sub_width(FMT), NG = TW / GW, SPG = PAIR ? GW / 2 : GW, SB = side_bytes(FMT);
-  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K;
-  extern __shared__ __align__(128) uint8_t smem[];
-  uint16_t* lut = reinterpret_cast<uint16_t*>(smem);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kLutSize);
-  float* iq4 = reinterpret_cast<float*>(smem + 2 * kLutSize + 64);
-  float* xs = reinterpret_cast<float*>(smem + 2 * kLutSize + 128);   // [TW][MT]
-  float* xg = xs + TW * MT;                                          // [NG][MT]
-  uint32_t* bufs = reinterpret_cast<uint32_t*>(xg + NG * MT);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tc = blockIdx.x, tr = blockIdx.y * kWarpsPerBlock + warp;
-  const int NT = M.N / kTileRows;
-  const bool active = tr < NT;
-  const int t = tr * M.KT + tc;
-  uint32_t* buf = bufs + static_cast<size_t>(warp) * tile_buf_words(M.max_tile_words);
-  uint32_t base = 0;
-  const uint32_t bar_a = smem_addr(bars + warp);
-  if (active) {   // start the tile's copy first: it overlaps the table and activation staging below
-    const uint32_t b0 = __ldg(M.group_base + static_cast<size_t>(t) * 2 * M.split);
-    const uint32_t b1 = __ldg(M.group_base + static_cast<size_t>(t + 1) * 2 * M.split);
-    base = b0;
-    if (lane == 0) {
-      mbar_init(bar_a, 1);
-      bulk_load(smem_addr(buf), M.words + b0, (b1 - b0) * 4u, bar_a);
-    }
-  }
-  for (int i = threadIdx.x; i < kLutSize / 2; i += blockDim.x)
-    reinterpret_cast<uint32_t*>(lut)[i] = __ldg(reinterpret_cast<const uint32_t*>(M.lut) + i);
-  if (threadIdx.x < 16) iq4[threadIdx.x] = c_iq4_grid[threadIdx.x];
-  for (int i = threadIdx.x; i < TW * MT; i += blockDim.x) {
-    const int j = i / TW, k = i - j * TW;
-    xs[k * MT + j] = j < m ? to_f32(X[static_cast<size_t>(j) * M.K + static_cast<size_t>(tc) * TW + k]) : 0.f;
-  }
-  __syncthreads();
-  if (HAS_OFFSET) {
-    for (int i = threadIdx.x; i < NG * MT; i += blockDim.x) {
-      const int g = i / MT, j = i - g * MT;
-      float a = 0.f;
-      for (int k = g * GW; k < (g + 1) * GW; ++k) a += xs[k * MT + j];
-      xg[i] = a;
-    }
-    __syncthreads();
-  }
-  if (!active) return;
-  __syncwarp();
-  if (!mbar_wait(bar_a, 0, &g_kernel_error)) return;
-
-  Chain ca, cb;
-  const int G = 2 * M.split, sub_per_seg = NG / M.split;
-  const int na = tr * kTileRows + lane, nb = na + 32;
-  const size_t side_row = static_cast<size_t>(M.K / 256) * SB;
-  const uint8_t* sa = M.side + na * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
-  const uint8_t* sbp = M.side + nb * side_row + static_cast<size_t>(tc) * (TW / 256) * SB;
-  float tot_a[MT], tot_b[MT];
-#pragma unroll
-  for (int j = 0; j < MT; ++j) tot_a[j] = tot_b[j] = 0.f;
-#pragma unroll 1
-  for (int sb = 0; sb < TW / 256; ++sb) {
-    SideRegs<FMT> ra, rb;
-    ra.load(sa + sb * SB);
-    rb.load(sbp + sb * SB);
-#pragma unroll
-    for (int jj = 0; jj < 256 / GW; ++jj) {
-      const int g = sb * (256 / GW) + jj;
-      if (g % sub_per_seg == 0) {   // next column segment: its own pair of chains
-        const uint32_t* gb = M.group_base + static_cast<size_t>(t) * G + 2 * (g / sub_per_seg);
-        ca.init(buf + (__ldg(gb) - base) + lane, M.pad);
-        cb.init(buf + (__ldg(gb + 1) - base) + lane, M.pad);
-      }
-      float s_a, o_a, s_b, o_b;
-      ra.sub(jj, s_a, o_a);
-      rb.sub(jj, s_b, o_b);
-      float acc_a[MT], acc_b[MT];
-#pragma unroll
-      for (int j = 0; j < MT; ++j) acc_a[j] = acc_b[j] = 0.f;
-      const float* xp = xs + static_cast<size_t>(g) * GW * MT;
-#pragma unroll 4
-      for (int c = 0; c < SPG; ++c) {
-        const uint32_t ea = ca.next(lut), eb = cb.next(lut);
-        if (PAIR) {
-          const float fa0 = grid_value<FMT>(ea & 15u, iq4), fa1 = grid_value<FMT>((ea >> 4) & 15u, iq4);
-          const float fb0 = grid_value<FMT>(eb & 15u, iq4), fb1 = grid_value<FMT>((eb >> 4) & 15u, iq4);
-#pragma unroll
-          for (int j = 0; j < MT; ++j) {
-            const float x0 = xp[(2 * c) * MT + j], x1 = xp[(2 * c + 1) * MT + j];
-            acc_a[j] = fmaf(x0, fa0, acc_a[j]);
-            acc_b[j] = fmaf(x0, fb0, acc_b[j]);
-            acc_a[j] = fmaf(x1, fa1, acc_a[j]);
-            acc_b[j] = fmaf(x1, fb1, acc_b[j]);
-          }
-        } else {
-          const float fa = grid_value<FMT>(ea & 255u, iq4), fb = grid_value<FMT>(eb & 255u, iq4);
-#pragma unroll
-          for (int j = 0; j < MT; ++j) {
-            const float x0 = xp[c * MT + j];
-            acc_a[j] = fmaf(x0, fa, acc_a[j]);
-            acc_b[j] = fmaf(x0, fb, acc_b[j]);
-          }
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < MT; ++j) {
-        if (HAS_OFFSET) {
-          const float gx = xg[g * MT + j];
-          tot_a[j] += s_a * acc_a[j] - o_a * gx;
-          tot_b[j] += s_b * acc_b[j] - o_b * gx;
-        } else {
-          tot_a[j] = fmaf(s_a, acc_a[j], tot_a[j]);
-          tot_b[j] = fmaf(s_b, acc_b[j], tot_b[j]);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < MT; ++j)
-    if (j < m) {
-      P[(static_cast<size_t>(tc) * m + j) * M.N + na] = tot_a[j];
-      P[(static_cast<size_t>(tc) * m + j) * M.N + nb] = tot_b[j];
-    }
-}
-
 }  // namespace lw
 #include "lw_gemm_tc.cuh"
 namespace lw {
@@ -333,6 +202,9 @@ __global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ 
 
 // ------------------------------------------------------------------------------------------------------ launchers
 
+static DebugKnobs g_debug_knobs;
+DebugKnobs& debug_knobs() { return g_debug_knobs; }
+
 static std::atomic<long long> g_launches{0};
 long long launch_count() { return g_launches.load(); }
 
@@ -352,14 +224,18 @@ static int check_launch(const char* what) {
 
 int note_launch(const char* what) { return check_launch(what); }
 
+// SMs of the current device (cached per device: a process may hold handles on several).
 int sm_count() {
-  static const int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 1;
-  }();
-  return n;
+  static std::atomic<int> per_device[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  int v = per_device[dev].load();
+  if (v > 0) return v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+  v = v > 0 ? v : 1;
+  per_device[dev].store(v);
+  return v;
 }
 
 // Device address of the error word, for kernels of other translation units.
@@ -408,10 +284,8 @@ int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaSt
   return check_launch("k_decode_codes");
 }
 
-static int gemv1_variant();
-
 int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st) {
-  if (gemv1_variant() != 0 && gemv1_usable(M)) {   // the decoder of the batch-1 kernel, where the layout allows
+  if (gemv1_usable(M)) {   // the decoder of the batch-1 kernel, where the layout allows
     const int rc = launch_decw(M, out, tr0, tr1, error_word(), st);
     if (rc != kErrTooLarge) return rc;
   }
@@ -445,78 +319,43 @@ int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st) {
   return launch_decode_weights_rows(M, out, 0, M.N / kTileRows, st);
 }
 
-// Scratch every product can run with, and the larger scratch that lets 2..8 rows take the faster kernel (one partial
-// product per work unit and row instead of one per tile column and row).
-size_t gemv_partial_floats_min(const MatDev& M, int m) {
-  return static_cast<size_t>(M.KT) * std::max(m, M.split) * M.N;
-}
+// Scratch of one product: one 64-row partial product per tile for one row (added by the same kernel), one per work
+// unit and row for 2..8 rows (added by k_sum_partials).
 size_t gemv_partial_floats(const MatDev& M, int m) {
-  return m > 1 && gemv1_usable(M) ? std::max(gemv_partial_floats_min(M, m), gemvm_partial_floats(M, m))
-                                  : gemv_partial_floats_min(M, m);
+  return m <= 1 ? static_cast<size_t>(M.KT) * M.N : gemvm_partial_floats(M, m);
 }
 
-template <int FMT, int MT, typename XT>
-static int launch_gemv_t(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
-  constexpr int TW = is_paired(FMT) ? 512 : 256;
-  constexpr int NG = TW / sub_width(FMT);
-  const size_t smem = 2 * kLutSize + 128 + (TW + NG) * MT * sizeof(float) + kWarpsPerBlock * stage_bytes(M);
-  int rc;
-  if ((rc = prepare(k_gemv_fused<FMT, MT, XT>, smem))) return rc;
-  const int NT = M.N / kTileRows;
-  dim3 grid(M.KT, (NT + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  k_gemv_fused<FMT, MT, XT><<<grid, kWarpsPerBlock * 32, smem, st>>>(M, X, P, m);
-  return check_launch("k_gemv_fused");
-}
-
-template <int FMT, typename XT>
-static int launch_gemv_m(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
-  if (m == 1) return launch_gemv_t<FMT, 1, XT>(M, X, m, P, st);
-  if (m == 2) return launch_gemv_t<FMT, 2, XT>(M, X, m, P, st);
-  if (m <= 4) return launch_gemv_t<FMT, 4, XT>(M, X, m, P, st);
-  return launch_gemv_t<FMT, 8, XT>(M, X, m, P, st);
-}
-
-template <typename XT>
-static int launch_gemv_f(const MatDev& M, const XT* X, int m, float* P, cudaStream_t st) {
-  switch (M.fmt) {
-    case kFmtQ4K: return launch_gemv_m<kFmtQ4K, XT>(M, X, m, P, st);
-    case kFmtQ5K: return launch_gemv_m<kFmtQ5K, XT>(M, X, m, P, st);
-    case kFmtQ6K: return launch_gemv_m<kFmtQ6K, XT>(M, X, m, P, st);
-    case kFmtIQ4XS: return launch_gemv_m<kFmtIQ4XS, XT>(M, X, m, P, st);
-  }
-  set_kernel_error_text("gemv", "matrix has no block format");
-  return kErrArg;
-}
-
-static int gemv1_variant() {
-  static const int v = [] {
-    const char* e = getenv("LW_GEMV1");
-    return e ? atoi(e) : 1;
-  }();
-  return v;
-}
+// Set by read_kernel_error when a kernel reported that a wait gave up: such a kernel may have left tile-row counters
+// of the batch-1 product non-zero, so every matrix zeroes its counters again before its next product.
+static std::atomic<unsigned int> g_error_epoch{1};
 
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
-                size_t partial_capacity, cudaStream_t st) {
+                size_t partial_capacity, cudaStream_t st, unsigned int* clean_epoch) {
   if (m < 1 || m > 8) {
     set_kernel_error_text("gemv", "m must be 1..8");
     return kErrArg;
   }
-  if (partial_capacity < gemv_partial_floats_min(M, m)) {
+  if (!gemv1_usable(M)) {
+    set_kernel_error_text("gemv", "matrix has no block format or was not laid out for the fused kernels");
+    return kErrArg;
+  }
+  if (partial_capacity < gemv_partial_floats(M, m)) {
     set_kernel_error_text("gemv", "scratch too small for this product");
     return kErrTooLarge;
   }
-  int rc, terms = M.KT;
-  if (m == 1 && gemv1_variant() != 0 && gemv1_usable(M)) {
+  if (m == 1) {
+    const unsigned int epoch = g_error_epoch.load();
+    if (clean_epoch && *clean_epoch != epoch) {
+      if (cudaMemsetAsync(M.row_done, 0, static_cast<size_t>(M.N / kTileRows) * kRowDoneStride * sizeof(unsigned int), st) !=
+          cudaSuccess)
+        return check_cuda("cudaMemsetAsync(row counters)");
+      *clean_epoch = epoch;
+    }
     return launch_gemv1(M, X, x_is_half, partials, Y, error_word(), st);   // adds its partial products itself
-  } else if (m > 1 && gemv1_variant() != 0 && gemv1_usable(M) && partial_capacity >= gemvm_partial_floats(M, m)) {
-    rc = launch_gemvm(M, X, x_is_half, m, partials, error_word(), st);
-    terms = M.KT * M.split;
-  } else {
-    rc = x_is_half ? launch_gemv_f<__half>(M, static_cast<const __half*>(X), m, partials, st)
-                   : launch_gemv_f<float>(M, static_cast<const float*>(X), m, partials, st);
   }
+  const int rc = launch_gemvm(M, X, x_is_half, m, partials, error_word(), st);
   if (rc) return rc;
+  const int terms = M.KT * M.split;
   {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((m * (M.N / 4) + 127) / 128);
@@ -583,17 +422,17 @@ extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_i
     set_kernel_error_text("lw_linear_static", "matrix has no block format");
     return kErrArg;
   }
-  if (gemv_partial_floats_min(*M, m) > kStaticPartialFloats) {
+  if (gemv_partial_floats(*M, m) > kStaticPartialFloats) {
     set_kernel_error_text("lw_linear_static",
-                          "this product needs more partial sums than the built-in scratch holds "
-                          "(tile columns x max(m, segments) x N must be <= 4194304); use lw_linear");
+                          "this product needs more partial sums than the built-in scratch holds (tile columns x N for "
+                          "one row, tile columns x column segments x m x N for more, must be <= 4194304); use lw_linear");
     return kErrTooLarge;
   }
   float* scratch = nullptr;
   const int rc = static_partials(&scratch);
   if (rc) return rc;
   return launch_gemv(*M, x_dev, x_is_half != 0, m, y_dev, M->N, scratch, kStaticPartialFloats,
-                     static_cast<cudaStream_t>(stream));
+                     static_cast<cudaStream_t>(stream), matrix_clean_epoch(handle, id));
 }
 
 namespace lw {
@@ -625,9 +464,37 @@ int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, 
   return check_launch("k_sum_partials");
 }
 
+// A wait that nothing ends: one warp waits on a barrier no copy will complete and on a release counter nothing
+// advances, each for `limit` polls; both must give up, set the error word and return.  Used by lw_debug_wait_probe
+// to show that a lost copy cannot hang a kernel.
+__global__ void k_wait_probe(unsigned int* err, uint32_t limit, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t released;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_addr(&bar), 1);
+    released = 0u;
+  }
+  __syncthreads();
+  const bool a = mbar_wait(smem_addr(&bar), 0, err, limit);
+  const bool b = wait_released(&released, 1u, err, limit);
+  if (threadIdx.x == 0) *gave_up = (a ? 0 : 1) + (b ? 0 : 2);
+}
+
+int launch_wait_probe(unsigned int limit, int* gave_up_host) {
+  int* d = nullptr;
+  if (cudaMalloc(&d, sizeof(int)) != cudaSuccess) return check_cuda("cudaMalloc(wait probe)");
+  cudaMemset(d, 0, sizeof(int));
+  k_wait_probe<<<1, 32>>>(error_word(), limit, d);
+  int rc = check_launch("k_wait_probe");
+  if (!rc && cudaMemcpy(gave_up_host, d, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) rc = check_cuda("wait probe");
+  cudaFree(d);
+  return rc;
+}
+
 int read_kernel_error(unsigned int* value, bool clear) {
   unsigned int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_kernel_error, sizeof v) != cudaSuccess) return check_cuda("read error word");
+  if (v) g_error_epoch.fetch_add(1);   // a kernel gave up: tile-row counters may be stale (see launch_gemv)
   if (clear && v) {
     const unsigned int z = 0;
     cudaMemcpyToSymbol(g_kernel_error, &z, sizeof z);

@@ -45,19 +45,23 @@ int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st);
 int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, float* partials,
                    size_t partial_capacity, cudaStream_t st);
 // Y[j, n] (row stride ldy) = sum_k X[j, k] W[n, k] for m <= 8 rows of X (fp16 or fp32, row-major [m, K]).
-// `partials` (partial_capacity floats) must hold gemv_partial_floats_min(M, m) floats; with gemv_partial_floats(M, m)
-// products of 2..8 rows take the faster kernel.
-size_t gemv_partial_floats_min(const MatDev& M, int m);
+// `partials` (partial_capacity floats) must hold gemv_partial_floats(M, m) floats.  `clean_epoch` (may be null) is the
+// caller's per-matrix note of when the matrix's tile-row counters were last known to be zero: after a kernel reported
+// a wait that gave up, the next one-row product of every matrix zeroes them again.
 size_t gemv_partial_floats(const MatDev& M, int m);
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
-                size_t partial_capacity,
-                cudaStream_t st);
+                size_t partial_capacity, cudaStream_t st, unsigned int* clean_epoch = nullptr);
 // Reads (and optionally clears) the device error word that kernels set when a bounded wait gives up.
 int read_kernel_error(unsigned int* value, bool clear);
 
+// Test entry: a kernel whose waits nothing ends, with `limit` polls each; *gave_up = 1 (barrier) + 2 (counter).
+int launch_wait_probe(unsigned int limit, int* gave_up);
+
 void set_kernel_error_text(const char* what, const char* detail);
-// Device descriptor of matrix `id` of a handle (implemented next to the handle type), or null.
+// Device descriptor of matrix `id` of a handle (implemented next to the handle type), or null; and that matrix's
+// clean-epoch note (see launch_gemv).
 const MatDev* matrix_descriptor(void* handle, int id);
+unsigned int* matrix_clean_epoch(void* handle, int id);
 // Kernels launched by this library since it was loaded.
 long long launch_count();
 

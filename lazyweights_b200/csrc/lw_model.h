@@ -23,9 +23,12 @@ struct Matrix {
   double slow_fraction = 0.0;   // share of work units the batch-1 kernel decodes symbol by symbol
   void* d_block = nullptr;   // one allocation: table, group bases, words, side bytes
   MatDev dev{};
+  unsigned int clean_epoch = 0;   // when the tile-row counters were last known to be zero (see launch_gemv)
 };
 
 struct Runtime;   // decoder state, defined in lw_runtime.cu
+struct Model;
+void runtime_free(Model* M);
 
 struct Model {
   std::string dir;
@@ -47,6 +50,7 @@ struct Model {
   long long coded_bytes = 0, side_bytes = 0;
   Runtime* rt = nullptr;
   ~Model() {
+    runtime_free(this);   // the decoder state, if any (also after a failed rt_open)
     for (auto& m : mats)
       if (m.d_block) cudaFree(m.d_block);
     if (d_partials) cudaFree(d_partials);
@@ -65,7 +69,8 @@ int cuda_fail(const char* what, cudaError_t e);
 int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
                   int path = 0);
 int runtime_init(Model* M, int max_ctx, int max_batch);
-void runtime_free(Model* M);
+// True if the calling thread's current device is the one the handle was opened on (kernels and scratch belong to it).
+int check_device(const Model* M);
 double runtime_stat(const Model* M, const char* key);
 
 }  // namespace lw

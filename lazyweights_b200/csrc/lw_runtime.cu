@@ -57,6 +57,12 @@ struct Runtime {
   int L = 0, D = 0, H = 0, Hk = 0, Dh = 0, I = 0, V = 0;   // heads, FFN width and vocabulary are the LOCAL sizes
   int Tmax = 0, max_batch = 0, pos = 0, window = 0;
   int tp_rank = 0, tp_world = 1;
+  int Vfull = 0, Vmax = 0;           // whole vocabulary; largest shard (ranks may hold 63 or 62 tile rows, say)
+  std::vector<int> voff, vcnt;       // first row and rows of every rank's vocabulary shard
+  bool time_collectives = false;     // next pass: direct launches with CUDA events around every collective
+  std::vector<cudaEvent_t> coll_events;
+  double collective_us = 0.0;        // time inside collectives during the last such pass
+  int collective_calls = 0;
   float eps = 1e-5f, attn_scale = 1.f;
   void* comm = nullptr;
   float *h = nullptr, *xn = nullptr, *att = nullptr, *o = nullptr, *qkv = nullptr, *g = nullptr, *u = nullptr;
@@ -74,7 +80,7 @@ struct Runtime {
   __half *kc = nullptr, *vc = nullptr, *embed16 = nullptr;
   uint8_t* embed8 = nullptr;
   float *embed_rs = nullptr, *embed_rsub = nullptr;
-  int embed_groups = 0;
+  int embed_groups = 0, embed_rows = 0;
   std::vector<float*> ln1, ln2;
   std::vector<int> m_qkv, m_q, m_k, m_v, m_o, m_gate, m_up, m_down;
   int m_head = -1;
@@ -402,6 +408,7 @@ static int find_matrix(Model* M, const std::string& n) {
 }
 
 int runtime_init(Model* M, int max_ctx, int max_batch) {
+  if (const int rc = validate_model(M->man)) return rc;   // shapes of everything the passes index
   auto R = new Runtime();
   M->rt = R;
   R->L = cfg_int(M, "n_layers", 0);
@@ -417,8 +424,24 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
   R->Tmax = std::max(1, std::min(max_ctx > 0 ? max_ctx : rope_rows, rope_rows));
   R->max_batch = std::max(1, max_batch);
   R->max_chunks = (R->Tmax + kAttnChunk - 1) / kAttnChunk;
-  R->tp_world = cfg_int(M, "tp_world", 1);
+  R->tp_world = std::max(1, cfg_int(M, "tp_world", 1));
   R->tp_rank = cfg_int(M, "tp_rank", 0);
+  // Vocabulary shards: tile rows (64 vocabulary rows) dealt as evenly as possible, the first (tile rows % world)
+  // ranks hold one more (32000 rows on 8 ranks: 63 tile rows on ranks 0..3, 62 on ranks 4..7).
+  R->Vfull = cfg_int(M, "vocab_full", R->V * R->tp_world);
+  {
+    const int units = R->Vfull / kTileRows, base = units / R->tp_world, rem = units % R->tp_world;
+    for (int r = 0; r < R->tp_world; ++r) {
+      R->voff.push_back((r * base + std::min(r, rem)) * kTileRows);
+      R->vcnt.push_back((base + (r < rem ? 1 : 0)) * kTileRows);
+      R->Vmax = std::max(R->Vmax, R->vcnt.back());
+    }
+    if (R->Vfull % kTileRows || R->tp_rank < 0 || R->tp_rank >= R->tp_world || R->vcnt[R->tp_rank] != R->V) {
+      set_error("bundle cfg: vocab %d is not rank %d's share of vocab_full %d over %d ranks", R->V, R->tp_rank, R->Vfull,
+                R->tp_world);
+      return kErrFormat;
+    }
+  }
   {
     auto it = M->man.cfg.find("eos");
     std::stringstream es(it == M->man.cfg.end() ? "" : it->second);
@@ -435,7 +458,7 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
   if ((rc = dalloc(R, &R->h, B * R->D)) || (rc = dalloc(R, &R->xn, B * R->D)) ||
       (rc = dalloc(R, &R->att, B * R->H * R->Dh)) || (rc = dalloc(R, &R->o, B * R->D)) ||
       (rc = dalloc(R, &R->qkv, B * QKV)) || (rc = dalloc(R, &R->g, B * R->I)) || (rc = dalloc(R, &R->u, B * R->I)) ||
-      (rc = dalloc(R, &R->logits, B * R->V)) || (rc = dalloc(R, &R->logits_all, B * R->V * R->tp_world)) ||
+      (rc = dalloc(R, &R->logits, B * R->Vmax)) || (rc = dalloc(R, &R->logits_all, B * R->Vmax * R->tp_world)) ||
       (rc = dalloc(R, &R->ids, B + 1)) ||
       (rc = dalloc(R, &R->attn_part, B * R->H * ((R->Tmax + kAttnChunk - 1) / kAttnChunk) * (R->Dh + 2))) ||
       (rc = dalloc(R, &R->kc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)) ||
@@ -465,6 +488,7 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
     set_error("embed has %d columns, hidden is %d", te->K, R->D);
     return kErrFormat;
   }
+  R->embed_rows = te->N;
   if ((rc = upload(M, R, "cos", "f32", 4, &p, &te))) return rc;
   R->cosv = static_cast<float*>(p);
   if (te->K != R->Dh / 2 || te->N < R->Tmax) {
@@ -518,9 +542,31 @@ void runtime_free(Model* M) {
 
 double runtime_stat(const Model* M, const char* key) {
   if (!M->rt) return 0;
-  return std::strcmp(key, "graph_launches") == 0 ? static_cast<double>(M->rt->graph_launches)
-                                                  : static_cast<double>(M->rt->graph_captures);
+  if (std::strcmp(key, "graph_launches") == 0) return static_cast<double>(M->rt->graph_launches);
+  if (std::strcmp(key, "graph_captures") == 0) return static_cast<double>(M->rt->graph_captures);
+  if (std::strcmp(key, "collective_us") == 0) return M->rt->collective_us;
+  if (std::strcmp(key, "collective_calls") == 0) return static_cast<double>(M->rt->collective_calls);
+  if (std::strcmp(key, "time_collectives") == 0) {   // arms the measurement for the next pass
+    M->rt->time_collectives = true;
+    return 0;
+  }
+  return -1;
 }
+
+// Brackets a collective with events when the pass is being timed (see rt_stat "collective_us").
+struct CollTimer {
+  Runtime* R;
+  cudaStream_t st;
+  CollTimer(Runtime* r, cudaStream_t s) : R(r), st(s) { mark(); }
+  ~CollTimer() { mark(); }
+  void mark() {
+    if (!R->time_collectives) return;
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    cudaEventRecord(e, st);
+    R->coll_events.push_back(e);
+  }
+};
 
 static int nccl_check(int r, const char* what) {
   if (r == 0) return kOk;
@@ -571,9 +617,12 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     }
     launch_dep(k_attn_combine, dim3(R->H, m), dim3(128), st, R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
-    if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
-                                                     R->comm, st), "all-reduce (o)")))
-      return rc;
+    if (R->comm) {
+      CollTimer t(R, st);
+      if ((rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum, R->comm, st),
+                           "all-reduce (o)")))
+        return rc;
+    }
     launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
     if ((rc = linear_device(M, M->mats[R->m_gate[l]], R->xn, false, m, R->g, R->I, st)) ||
         (rc = linear_device(M, M->mats[R->m_up[l]], R->xn, false, m, R->u, R->I, st)))
@@ -581,9 +630,12 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     const size_t ng = static_cast<size_t>(m) * R->I;
     launch_dep(k_silu_mul, dim3(static_cast<unsigned>((ng + 255) / 256)), dim3(256), st, R->g, R->u, ng);
     if ((rc = linear_device(M, M->mats[R->m_down[l]], R->g, false, m, R->o, R->D, st))) return rc;
-    if (R->comm && (rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
-                                                     R->comm, st), "all-reduce (down)")))
-      return rc;
+    if (R->comm) {
+      CollTimer t(R, st);
+      if ((rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum, R->comm, st),
+                           "all-reduce (down)")))
+        return rc;
+    }
     pending = R->o;
   }
   launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, pending, R->lnf, R->xn, R->D, R->eps);
@@ -591,8 +643,10 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
   const float* xlast = all_logits ? R->xn : R->xn + static_cast<size_t>(m - 1) * R->D;
   if ((rc = linear_device(M, M->mats[R->m_head], xlast, false, rows, R->logits, R->V, st))) return rc;
   if (R->comm) {
-    // ranks hold consecutive slices of the vocabulary: gathered rank-major [world][rows][V], reordered by the caller
-    if ((rc = nccl_check(g_nccl.AllGather(R->logits, R->logits_all, static_cast<size_t>(rows) * R->V, kNcclFloat,
+    // ranks hold consecutive slices of the vocabulary (of 63 or 62 tile rows, say): every rank contributes
+    // rows x Vmax floats of which its first rows x V count; gathered rank-major, reordered by the caller
+    CollTimer t(R, st);
+    if ((rc = nccl_check(g_nccl.AllGather(R->logits, R->logits_all, static_cast<size_t>(rows) * R->Vmax, kNcclFloat,
                                           R->comm, st), "all-gather (logits)")))
       return rc;
   }
@@ -614,7 +668,20 @@ static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool 
   const long long key = (static_cast<long long>(nchunks) << 8) | (m << 1) | (all_logits ? 1 : 0);
   int rc = kOk;
   auto it = R->graph_exec.find(key);
-  if (it != R->graph_exec.end()) {
+  if (R->time_collectives) {
+    // one pass launched directly, with events around every collective; the time between each pair is added up
+    rc = enqueue_pass(M, R, m, all_logits, nchunks, st);
+    cudaStreamSynchronize(st);
+    R->collective_us = 0.0;
+    R->collective_calls = static_cast<int>(R->coll_events.size() / 2);
+    for (size_t i = 0; i + 1 < R->coll_events.size(); i += 2) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, R->coll_events[i], R->coll_events[i + 1]) == cudaSuccess) R->collective_us += ms * 1e3;
+    }
+    for (cudaEvent_t e : R->coll_events) cudaEventDestroy(e);
+    R->coll_events.clear();
+    R->time_collectives = false;
+  } else if (it != R->graph_exec.end()) {
     const cudaError_t e = cudaGraphLaunch(it->second, st);
     if (e != cudaSuccess) return cuda_fail("cudaGraphLaunch", e);
     ++R->graph_launches;
@@ -659,8 +726,14 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
     return kErrArg;
   }
   Runtime* R = M->rt;
+  if (const int rc = check_device(M)) return rc;
+  for (int i = 0; i < n; ++i)
+    if (ids[i] < 0 || ids[i] >= R->embed_rows) {   // the embedding gather indexes device memory with it
+      set_error("rt_forward: token id %d at position %d is outside the embedding's %d rows", ids[i], i, R->embed_rows);
+      return kErrArg;
+    }
   if (R->pos + n > R->Tmax) return -1;   // context overflow (the reference's -1, kernels/llmrt.cu:2293)
-  const int W = R->tp_world, Vfull = R->V * W;
+  const int W = R->tp_world, Vfull = R->Vfull;
   std::vector<float> stage;
   for (int i0 = 0; i0 < n; i0 += R->max_batch) {
     const int m = std::min(R->max_batch, n - i0);
@@ -675,13 +748,14 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
       e = cudaMemcpyAsync(dst, R->logits, static_cast<size_t>(rows) * R->V * 4, cudaMemcpyDeviceToHost, R->stream);
       if (e == cudaSuccess) e = cudaStreamSynchronize(R->stream);
     } else {
-      stage.resize(static_cast<size_t>(W) * rows * R->V);
+      stage.resize(static_cast<size_t>(W) * rows * R->Vmax);
       e = cudaMemcpyAsync(stage.data(), R->logits_all, stage.size() * 4, cudaMemcpyDeviceToHost, R->stream);
       if (e == cudaSuccess) e = cudaStreamSynchronize(R->stream);
       for (int r = 0; r < W && e == cudaSuccess; ++r)
         for (int j = 0; j < rows; ++j)
-          std::memcpy(dst + static_cast<size_t>(j) * Vfull + static_cast<size_t>(r) * R->V,
-                      stage.data() + (static_cast<size_t>(r) * rows + j) * R->V, static_cast<size_t>(R->V) * 4);
+          std::memcpy(dst + static_cast<size_t>(j) * Vfull + R->voff[r],
+                      stage.data() + static_cast<size_t>(r) * rows * R->Vmax + static_cast<size_t>(j) * R->vcnt[r],
+                      static_cast<size_t>(R->vcnt[r]) * 4);
     }
     if (e != cudaSuccess) return cuda_fail("logits copy", e);
   }
@@ -714,7 +788,7 @@ int rt_pos(void* handle) {
 }
 int rt_vocab(void* handle) {
   Model* M = static_cast<Model*>(handle);
-  return M && M->rt ? M->rt->V * M->rt->tp_world : -1;
+  return M && M->rt ? M->rt->Vfull : -1;
 }
 
 int lw_tp_unique_id(uint8_t* out128) {

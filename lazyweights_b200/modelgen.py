@@ -11,7 +11,10 @@ The embedding is stored as fp16 (`enc f16`, an extension of the format for rando
 the loader still gives each layer its own device copy, so HBM traffic is that of a full model while the file stays small.
 Tensor parallel shards: `tp=(rank, world)` slices heads, FFN width and vocabulary Megatron-style (column-parallel qkv,
 gate, up, lm_head; row-parallel o, down) from the same seeded full model, so that shards of different world sizes
-describe one model.
+describe one model.  FFN width and vocabulary are dealt in whole tiles, as evenly as they go (`tile_split`): a paired
+4-bit FFN of width 14336 has 28 tile columns of 512 weights, so 8 ranks hold 4, 4, 4, 4, 3, 3, 3, 3 of them (the same
+split for the rows of gate / up and the columns of down), and 32000 vocabulary rows are 500 tile rows: 63 on the first
+four ranks, 62 on the others.
 """
 import os
 
@@ -57,6 +60,15 @@ def synth_side(ty, n, k, rng):
     return side.reshape(n, -1)
 
 
+def tile_split(total, unit, world, rank):
+    """[lo, hi) of rank's share of `total` (a multiple of `unit`): units dealt as evenly as they go, the first
+    `units % world` ranks get one more.  The runtime applies the same rule to the vocabulary (unit 64 rows)."""
+    units = total // unit
+    base, rem = divmod(units, world)
+    start = rank * base + min(rank, rem)
+    return start * unit, (start + base + (1 if rank < rem else 0)) * unit
+
+
 def _shard_rows(a, lo, hi):
     return np.ascontiguousarray(a[lo:hi])
 
@@ -74,14 +86,18 @@ def write_model(path, shape, fmt_attn="Q4_K", fmt_ffn=None, seed=0, tp=(0, 1), r
     L, D, H, Hk, Dh = shape["n_layers"], shape["hidden"], shape["n_heads"], shape["n_kv_heads"], shape["head_dim"]
     I, V = shape["inter"], shape["vocab"]
     tile_k = lambda f: 512 if f in PAIRED else 256
-    assert H % world == 0 and Hk % world == 0 and I % world == 0 and V % world == 0
-    Hl, Hkl, Il, Vl = H // world, Hk // world, I // world, V // world
-    assert (Hl * Dh) % tile_k(fmt_attn) == 0 and Il % tile_k(fmt_ffn) == 0 and Vl % 64 == 0 and D % 512 == 0
-    assert (Hl * Dh) % 64 == 0 and (Hkl * Dh) % 64 == 0 and Il % 64 == 0
+    assert H % world == 0 and Hk % world == 0 and I % tile_k(fmt_ffn) == 0 and V % 64 == 0
+    Hl, Hkl = H // world, Hk // world
+    i_lo, i_hi = tile_split(I, tile_k(fmt_ffn), world, rank)      # rows of gate / up, columns of down
+    v_lo, v_hi = tile_split(V, 64, world, rank)                   # rows of lm_head
+    Il, Vl = i_hi - i_lo, v_hi - v_lo
+    assert Il > 0 and Vl > 0, "more ranks than tiles"
+    assert (Hl * Dh) % tile_k(fmt_attn) == 0 and D % 512 == 0
+    assert (Hl * Dh) % 64 == 0 and (Hkl * Dh) % 64 == 0
     w = Writer(path)
     cfg = dict(n_layers=L, hidden=D, n_heads=Hl, n_kv_heads=Hkl, head_dim=Dh, inter=Il, vocab=Vl, eps=shape["eps"],
                rope_rows=ROPE_ROWS, rope_half=Dh // 2, attn_scale=Dh ** -0.5, enc="kq_huf", tied=0, eos="2",
-               tp_world=world, tp_rank=rank)
+               tp_world=world, tp_rank=rank, vocab_full=V)
     for k, v in cfg.items():
         w.cfg(k, v)
     rng = np.random.default_rng(seed)
@@ -153,10 +169,10 @@ def write_model(path, shape, fmt_attn="Q4_K", fmt_ffn=None, seed=0, tp=(0, 1), r
             if return_weights:
                 kept[name] = (fmt_attn, q, side)
         matrix("l%d.o" % i, fmt_attn, D, H * Dh, base + 2, cols=(rank * Hl * Dh, (rank + 1) * Hl * Dh), alias=al("o"))
-        matrix("l%d.gate" % i, fmt_ffn, I, D, base + 3, rows=(rank * Il, (rank + 1) * Il), alias=al("gate"))
-        matrix("l%d.up" % i, fmt_ffn, I, D, base + 4, rows=(rank * Il, (rank + 1) * Il), alias=al("up"))
-        matrix("l%d.down" % i, fmt_ffn, D, I, base + 5, cols=(rank * Il, (rank + 1) * Il), alias=al("down"))
-    matrix("lm_head", fmt_attn, V, D, seed * 100003 + 7777, rows=(rank * Vl, (rank + 1) * Vl))
+        matrix("l%d.gate" % i, fmt_ffn, I, D, base + 3, rows=(i_lo, i_hi), alias=al("gate"))
+        matrix("l%d.up" % i, fmt_ffn, I, D, base + 4, rows=(i_lo, i_hi), alias=al("up"))
+        matrix("l%d.down" % i, fmt_ffn, D, I, base + 5, cols=(i_lo, i_hi), alias=al("down"))
+    matrix("lm_head", fmt_attn, V, D, seed * 100003 + 7777, rows=(v_lo, v_hi))
     w.close()
     if return_weights:
         kept["__embed__"] = emb

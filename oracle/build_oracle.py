@@ -3,8 +3,8 @@
   oracle/liblw_oracle.so   the C restatement (lw_oracle_c.c), gcc -O2 -pthread
   oracle/_ref/huff_csim    the REFERENCE's own C++ decoder test bench (hw/huff/tb/csim_main.cpp with
                            hw/huff/huff_engine.h), compiled from the sources where they lie in a reference
-                           checkout; only built when such a checkout is present (its directory: $LW_REFERENCE,
-                           else the build machine's default location).  Nothing of the reference is copied into this repository.
+                           checkout; only built when $LW_REFERENCE names such a checkout.  Nothing of the
+                           reference is copied into this repository.
 """
 import ctypes as C
 import os
@@ -28,9 +28,9 @@ def build():
         # -ffp-contract=off: the dequantisation must round the product before the subtraction
         subprocess.run(["gcc", "-O2", "-std=c11", "-ffp-contract=off", "-fPIC", "-shared", "-pthread", src, "-o", LIB],
                        check=True)
-    ref = os.environ.get("LW_REFERENCE", "/root/reference")
+    ref = os.environ.get("LW_REFERENCE", "")
     tb = os.path.join(ref, "hw", "huff", "tb", "csim_main.cpp")
-    if os.path.exists(tb) and shutil.which("g++") and _newer(tb, REF_BIN):
+    if ref and os.path.exists(tb) and shutil.which("g++") and _newer(tb, REF_BIN):
         os.makedirs(REF_DIR, exist_ok=True)
         subprocess.run(["g++", "-O2", "-std=c++17", "-pthread", "-I", os.path.join(ref, "hw", "huff"), tb, "-o",
                         REF_BIN], check=True)
@@ -42,6 +42,8 @@ def lib():
     L = C.CDLL(LIB)
     L.orc_decode.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     L.orc_dequant.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    L.orc_pack.restype = C.c_longlong
+    L.orc_pack.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.orc_matvec.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
                              C.c_int]
     return L

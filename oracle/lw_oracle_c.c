@@ -8,6 +8,9 @@
  *                     (scripts/a2_kq_bundle.py:50-82)
  *   orc_matvec        decode -> dequant -> y = W x with float32 accumulation per row (the NumPy path of the
  *                     reference's bundle check followed by a float32 product)
+ *   orc_pack          the encoder's bit packing for given code lengths and reversed codes: lanes back to back in
+ *                     (tile, lane) order, each lane tile row l then l + 32, LSB-first into 32-bit words
+ *                     (lazyweights/bundle.py:57-85); the tables come from the NumPy oracle
  * Parity pin: tests/test_oracle_c.py checks these against the reference-made golden vectors in tests/golden.
  */
 #include <pthread.h>
@@ -91,6 +94,37 @@ int orc_decode(const uint8_t* blob, int N, int Ks, int threads, uint8_t* out) {
   free(th);
   free(jobs);
   return 0;
+}
+
+/* symbols [N, Ks] + per-symbol code length and bit-reversed code -> lane_start[T * 32] and payload words (zeroed by
+ * the caller, (total_bits + 31) / 32 + 2 of them).  Returns the payload bits. */
+long long orc_pack(const uint8_t* sym, int N, int Ks, const uint8_t* len, const uint32_t* rcode, uint32_t* starts,
+                   uint32_t* words) {
+  const int KT = Ks / TILE_SYMS, NT = N / TILE_ROWS;
+  uint64_t acc = 0, pos = 0;
+  size_t wi = 0;
+  int fill = 0;
+  for (int tr = 0; tr < NT; ++tr)
+    for (int tc = 0; tc < KT; ++tc)
+      for (int lane = 0; lane < LANES; ++lane) {
+        starts[((size_t)tr * KT + tc) * LANES + lane] = (uint32_t)pos;
+        for (int half = 0; half < 2; ++half) {
+          const uint8_t* row = sym + (size_t)(tr * TILE_ROWS + half * 32 + lane) * Ks + tc * TILE_SYMS;
+          for (int c = 0; c < TILE_SYMS; ++c) {
+            const int s = row[c], l = len[s];
+            acc |= (uint64_t)rcode[s] << fill;
+            fill += l;
+            pos += l;
+            if (fill >= 32) {
+              words[wi++] = (uint32_t)acc;
+              acc >>= 32;
+              fill -= 32;
+            }
+          }
+        }
+      }
+  if (fill) words[wi++] = (uint32_t)acc;
+  return (long long)pos;
 }
 
 /* (scale, offset) of the sub-blocks of one super-block */

@@ -20,7 +20,10 @@ import numpy as np
 
 
 def main():
-    ref = os.path.abspath(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LW_REFERENCE", "")
+    if not ref:
+        sys.exit("usage: make_golden.py <reference checkout>   (or set LW_REFERENCE)")
+    ref = os.path.abspath(ref)
     out = os.path.dirname(os.path.abspath(__file__))
     sys.path.insert(0, ref)
     sys.path.insert(0, os.path.join(ref, "scripts"))

@@ -36,6 +36,20 @@ def test_c_oracle_matches_golden(golden_dir, ty):
     assert helpers.rel_err(y, g["y"]) <= 1e-5
 
 
+@pytest.mark.parametrize("ty", helpers.FORMATS)
+def test_c_packer_reproduces_reference_blobs(golden_dir, ty):
+    g = helpers.golden(golden_dir, ty)
+    blob, bits, _ = orc.encode_huf8_native(g["sym"])
+    assert blob == g["blob"].tobytes()
+    assert blob == orc.encode_huf8(g["sym"])[0]
+
+
+@pytest.mark.parametrize("name", ["single", "uniform256", "two", "skewed"])
+def test_c_packer_edge_blobs(golden_dir, name):
+    g = np.load(os.path.join(golden_dir, "edge_%s.npz" % name))
+    assert orc.encode_huf8_native(g["sym"])[0] == g["blob"].tobytes()
+
+
 def test_reference_cpp_decoder_agrees(tmp_path):
     """The reference's C++ ref_decode (hw/huff/tb/csim_main.cpp:45-62), run as a binary, on an oracle-written
     bundle.  Skipped where no reference checkout was available to build it from."""

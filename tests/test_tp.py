@@ -76,3 +76,29 @@ def test_two_rank_forward_matches_one_gpu(tmp_path):
     for r in range(2):
         assert helpers.rel_err(np.load(tmp_path / ("logits%d.npy" % r)), ref) <= 1e-3
         assert helpers.rel_err(np.load(tmp_path / ("step%d.npy" % r)), ref_step) <= 1e-3
+
+
+def test_uneven_split_over_eight_ranks(tmp_path):
+    """A paired 4-bit FFN of 7 tile columns and a vocabulary of 13 tile rows over 4 ranks: 2, 2, 2, 1 tile columns and
+    4, 3, 3, 3 tile rows; the shards must tile the full model and every shard must validate (host only)."""
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    from lazyweights_b200 import modelgen
+    assert [modelgen.tile_split(14336, 512, 8, r) for r in (0, 3, 4, 7)] == [(0, 2048), (6144, 8192), (8192, 9728), (12800, 14336)]
+    assert [modelgen.tile_split(32000, 64, 8, r)[1] - modelgen.tile_split(32000, 64, 8, r)[0] for r in range(8)] == [4032] * 4 + [3968] * 4
+    shape = dict(SHAPE, inter=7 * 512, vocab=13 * 64, n_heads=16, n_kv_heads=4, n_layers=1)
+    full = modelgen.write_model(str(tmp_path / "full"), shape, "Q4_K", "Q4_K", seed=2, return_weights=True)
+    parts = []
+    for r in range(4):
+        path = str(tmp_path / ("s%d" % r))
+        parts.append(modelgen.write_model(path, shape, "Q4_K", "Q4_K", seed=2, tp=(r, 4), return_weights=True))
+        assert lw.lib().lw_validate_bundle(path.encode()) == 0, lw._native.last_error()
+        cfg, _ = lw.bundle.read_manifest(path)
+        assert int(cfg["vocab_full"]) == shape["vocab"] and int(cfg["inter"]) == parts[-1]["l0.gate"][1].shape[0]
+    assert [p["l0.gate"][1].shape[0] // 512 for p in parts] == [2, 2, 2, 1]
+    assert [p["lm_head"][1].shape[0] // 64 for p in parts] == [4, 3, 3, 3]
+    for name, axis in (("gate", 0), ("up", 0), ("down", 1)):
+        key = "l0." + name
+        assert np.array_equal(np.concatenate([p[key][1] for p in parts], axis), full[key][1])
+        assert np.array_equal(np.concatenate([p[key][2] for p in parts], axis), full[key][2])   # side bytes too
+    assert np.array_equal(np.concatenate([p["lm_head"][1] for p in parts]), full["lm_head"][1])
