@@ -160,6 +160,22 @@ void* lw_matrix_create(const uint8_t* blob, long long blob_bytes, int N, int Ks,
  * size is returned.  nbits receives the payload bits. */
 long long lw_encode_huf8(const uint8_t* sym, int N, int Ks, uint8_t* out, long long cap, long long* nbits);
 
+/* llama.cpp blocks of format fmt (Q4_K 144, Q5_K 176, Q6_K 210, IQ4_XS 136 bytes per 256 weights) <-> codes in weight
+ * order [nblk, 256] and the blocks' side bytes [nblk, 16 / 16 / 18 / 8].  join is the exact inverse of split (it
+ * refuses codes that do not fit the format).  Replace split / join, scripts/kq_code.py:37-81. */
+int lw_block_bytes(int fmt);
+int lw_split_blocks(int fmt, const uint8_t* blocks, long long nblk, uint8_t* q, uint8_t* side);
+int lw_join_blocks(int fmt, const uint8_t* q, const uint8_t* side, long long nblk, uint8_t* blocks);
+
+/* The n-gram draft cache of speculative decoding (the reference CLI's `--drafter ngramcache`,
+ * kernels/llmrt.cu:2604-2661): push every prompt and accepted token, one by one; draft proposes up to kmax tokens,
+ * each from the longest n-gram (n = 4..1) of the sequence so far whose most frequent continuation has enough samples
+ * and share (lax thresholds: 2 / 2 / 1 / 1 samples, 66 / 50 / 50 / 50 per cent).  Returns the number of drafted tokens. */
+void* lw_ngram_create(void);
+void lw_ngram_destroy(void* cache);
+int lw_ngram_push(void* cache, const int* tokens, int n);
+int lw_ngram_draft(void* cache, int* out, int kmax);
+
 /* Full host-side validation of a blob: canonical table, every lane decodes and ends where the next begins. */
 int lw_validate_blob(const uint8_t* blob, long long blob_bytes, int N, int Ks);
 

@@ -47,6 +47,13 @@ _SIGNATURES = {
     "lw_validate_blob": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_int]),
     "lw_cpu_decode": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "lw_validate_bundle": (C.c_int, [C.c_char_p]),
+    "lw_block_bytes": (C.c_int, [C.c_int]),
+    "lw_split_blocks": (C.c_int, [C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p]),
+    "lw_join_blocks": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
+    "lw_ngram_create": (C.c_void_p, []),
+    "lw_ngram_destroy": (None, [C.c_void_p]),
+    "lw_ngram_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "lw_ngram_draft": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "lw_debug_set": (C.c_int, [C.c_char_p, C.c_longlong]),
     "lw_debug_wait_probe": (C.c_int, [C.c_longlong]),
     "lw_last_error": (C.c_char_p, []),

@@ -77,6 +77,12 @@ int read_manifest(const std::string& dir, Manifest& m);
 int read_blob(int fd, const TensorEntry& t, std::vector<uint8_t>& out);
 // A bundle with a model configuration: every tensor the decoder runtime reads has the shape the cfg implies.
 int validate_model(const Manifest& m);
+// ---- llama.cpp blocks (reference: scripts/kq_code.py:37-81): [nblk][block_bytes] <-> codes [nblk][256] in weight order
+// + side bytes [nblk][side_bytes]
+int block_bytes(int fmt);
+int split_blocks(int fmt, const uint8_t* blocks, long long nblk, uint8_t* q, uint8_t* side);
+int join_blocks(int fmt, const uint8_t* q, const uint8_t* side, long long nblk, uint8_t* blocks);
+
 int format_of_side_enc(const std::string& enc);   // "kq_Q4_K" -> kFmtQ4K, ... ; 0 if unknown
 int default_threads();
 

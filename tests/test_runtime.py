@@ -16,7 +16,9 @@ def ref_forward(W, ids, shape, hk_round=True):
     """All-positions logits [n, V] in float64; k and v rounded to fp16 as the cache stores them."""
     L, D, H, Hk, Dh, I = (shape[k] for k in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "inter"))
     emb, norms, (cos, sin) = W["__embed__"], W["__norms__"], W["__rope__"]
-    deq = lambda name: orc.dequant(W[name][0], W[name][1], W[name][2]).astype(np.float64)
+    # a matrix is (format, codes, side bytes), or float weights that some other path has already dequantised
+    deq = lambda name: (W[name] if isinstance(W[name], np.ndarray)
+                        else orc.dequant(W[name][0], W[name][1], W[name][2])).astype(np.float64)
     h = emb[ids].astype(np.float64)
     n = len(ids)
 
@@ -94,5 +96,50 @@ def test_prompt_lookup_equals_greedy(tmp_path):
         spec, passes, accepted = speculate.prompt_lookup(b, prompt, 24, n_draft=7, ngram=3)
         assert spec == plain
         assert passes <= 24 and accepted >= 0
-        assert speculate.lookup_draft([1, 2, 3, 9, 1, 2, 3], 3, 4) == [9, 1, 2, 3]
-        assert speculate.lookup_draft([1, 2, 3], 3, 4) == []
+        cached, passes_c, accepted_c = speculate.prompt_lookup(b, prompt, 24, n_draft=7, drafter="ngramcache")
+        assert cached == plain and passes_c <= 24 and accepted_c >= 0
+
+
+def test_bundle_built_from_a_gguf_runs(tmp_path):
+    """A synthetic llama-architecture GGUF (permuted q / k rows, separate q / k / v of one type, Q6_K embedding) goes
+    through the bundle builder and the runtime; logits against the NumPy model on gguf-py's own dequantised tensors."""
+    import os
+    import sys
+    helpers.build_library()
+    import gguf
+    import lazyweights_b200 as lw
+    from lazyweights_b200 import gguf_bundle
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import synth_gguf as sg
+    path = str(tmp_path / "m.gguf")
+    made = sg.write(path, **sg.CASES["llama_fused"])
+    gguf_bundle.build_bundle(path, str(tmp_path / "b"), check=True)
+    shape = dict(n_layers=sg.LAYERS, hidden=sg.HIDDEN, n_heads=sg.HEADS, n_kv_heads=sg.KV_HEADS, head_dim=sg.HEAD_DIM,
+                 inter=sg.INTER, vocab=sg.VOCAB, eps=1e-5, theta=1e6)
+
+    def dq(name, heads=None):
+        ty, rows, cols, b = made[name]
+        w = gguf.quants.dequantize(b, getattr(gguf.GGMLQuantizationType, ty)).reshape(rows, cols)
+        if heads:                                                     # GGUF row order -> rotate-half order
+            w = w.reshape(heads, rows // heads // 2, 2, cols).swapaxes(1, 2).reshape(rows, cols)
+        return w
+
+    W = {"__embed__": dq("token_embd.weight").astype(np.float16), "__norms__": {"lnf": made["output_norm.weight"][3]}}
+    for i in range(sg.LAYERS):
+        p = "blk.%d." % i
+        W["l%d.qkv" % i] = np.concatenate([dq(p + "attn_q.weight", sg.HEADS), dq(p + "attn_k.weight", sg.KV_HEADS),
+                                           dq(p + "attn_v.weight")])
+        for ours, theirs in (("o", "attn_output"), ("gate", "ffn_gate"), ("up", "ffn_up"), ("down", "ffn_down")):
+            W["l%d.%s" % (i, ours)] = dq(p + theirs + ".weight")
+        W["__norms__"]["l%d.ln1" % i] = made[p + "attn_norm.weight"][3]
+        W["__norms__"]["l%d.ln2" % i] = made[p + "ffn_norm.weight"][3]
+    W["lm_head"] = dq("output.weight")
+    inv = 1.0 / (1e6 ** (np.arange(0, sg.HEAD_DIM, 2, dtype=np.float64) / sg.HEAD_DIM))
+    ang = np.arange(64, dtype=np.float64)[:, None] * inv[None]
+    W["__rope__"] = (np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32))
+    ids = np.random.default_rng(6).integers(0, sg.VOCAB, 9).astype(np.int32)
+    ref = ref_forward(W, ids, shape)
+    with lw.Bundle(str(tmp_path / "b"), max_ctx=64, max_batch=8) as b:
+        got = b.forward(ids, all_logits=True)
+        assert helpers.rel_err(got, ref) <= 5e-3
+        assert b.kernel_error() == 0
