@@ -139,6 +139,19 @@ int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, flo
  * No counterpart in the reference (its runtime always allocates through cudaMalloc in rt_open / rt_test_matmul). */
 int lw_linear_static(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
 
+/* Fixed-width twin of matrix `id` (the role of the reference's packed `_pk` bundles and their readers LaneR / LaneQ,
+ * kernels/llmrt.cu:543-630, :1733-1777): the matrix's codes at a fixed width (8 bits per pair of 4-bit codes, 5 or 6 bits
+ * otherwise) in the same device layout, read by the same kernel without any Huffman decoding.  It is the decode-free
+ * upper bound of the fused product: the difference between lw_linear (m = 1) and lw_linear_twin is what the entropy
+ * decoding costs.  make_twin allocates a second device image of the matrix (larger than the coded one); drop_twin frees
+ * it.  lw_linear_twin computes y[N] = W x for one activation row with bit-identical results to lw_linear (same
+ * integer sums, same order of float operations), as the reference demands of its twins (kernels/llmrt.cu:895).
+ * lw_matrix_twin_bytes: device bytes one twin product reads (-1 without a twin). */
+int lw_matrix_make_twin(void* handle, int id);
+int lw_matrix_drop_twin(void* handle, int id);
+long long lw_matrix_twin_bytes(void* handle, int id);
+int lw_linear_twin(void* handle, int id, const void* x_dev, int x_is_half, float* y_dev, void* stream);
+
 /* Decoded and dequantised weights as fp16 [N, K] on the device: float32 block arithmetic (scale * f(q) - offset,
  * each operation rounded) rounded once to fp16.  w_half_dev must be 32-byte aligned (32-byte stores). */
 int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream);

@@ -40,6 +40,10 @@ _SIGNATURES = {
     "lw_matrix_info": (C.c_int, [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 3 + [C.POINTER(C.c_longlong)] * 3),
     "lw_linear": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "lw_linear_static": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "lw_matrix_make_twin": (C.c_int, [C.c_void_p, C.c_int]),
+    "lw_matrix_drop_twin": (C.c_int, [C.c_void_p, C.c_int]),
+    "lw_matrix_twin_bytes": (C.c_longlong, [C.c_void_p, C.c_int]),
+    "lw_linear_twin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "lw_decode_weights": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "lw_decode_codes": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "lw_matrix_create": (C.c_void_p, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong]),

@@ -45,7 +45,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Host-side result of validating, indexing and re-laying out one blob: everything that goes to the device.
 struct HostImage {
   std::vector<uint16_t> lut;
-  std::vector<uint32_t> fat, group_base, words;
+  std::vector<uint32_t> fat, cmp, group_base, words;
   std::vector<uint8_t> unit_slow;
   int KT = 0, T = 0, split = 1, pad = 0, max_len = 0, group = 0, index_bits = 0;
   double slow_fraction = 0.0;
@@ -74,6 +74,8 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   std::vector<uint32_t> chain_start, lane_end;
   im.fat.resize(kLutSize);
   fat_table(*tab, mx.fmt, im.fat.data());
+  im.cmp.resize(kCmpTabWords);
+  comparator_table(*tab, mx.fmt, im.cmp.data());
   GroupScan scan;
   scan.quad_syms = 4 * sub_syms(mx.fmt);
   const bool grouped = mx.fmt != kFmtNone && split == default_split(mx.fmt);
@@ -138,7 +140,8 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   const int rc_side = check_side(mx, side, side_nbytes);
   if (rc_side) return rc_side;
   const size_t off_fat = align_up(2 * kLutSize, 256);
-  const size_t off_gb = align_up(off_fat + 4 * kLutSize, 256);
+  const size_t off_cmp = align_up(off_fat + 4 * kLutSize, 256);
+  const size_t off_gb = align_up(off_cmp + 4 * kCmpTabWords, 256);
   const size_t off_words = align_up(off_gb + im.group_base.size() * 4, 256);
   const size_t off_side = align_up(off_words + im.words.size() * 4, 256);
   const size_t off_slow = off_side + align_up(side_nbytes, 256);
@@ -149,6 +152,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   uint8_t* d = static_cast<uint8_t*>(mx.d_block);
   if ((e = cudaMemcpy(d, im.lut.data(), 2 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_fat, im.fat.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_cmp, im.cmp.data(), 4 * kCmpTabWords, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_gb, im.group_base.data(), im.group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_words, im.words.data(), im.words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (side_nbytes && (e = cudaMemcpy(d + off_side, side, side_nbytes, cudaMemcpyHostToDevice)) != cudaSuccess) ||
@@ -161,6 +165,8 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   mx.slow_fraction = im.slow_fraction;
   mx.dev.lut = reinterpret_cast<const uint16_t*>(d);
   mx.dev.tab32 = reinterpret_cast<const uint32_t*>(d + off_fat);
+  mx.dev.cmp_tab = reinterpret_cast<const uint32_t*>(d + off_cmp);
+  mx.dev.reader = 0;
   mx.dev.pad = im.pad;
   mx.dev.max_len = im.max_len;
   mx.dev.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
@@ -501,6 +507,93 @@ int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, flo
   }
   return linear_device(static_cast<Model*>(handle), *mx, x_dev, x_is_half != 0, m, y_dev, mx->N,
                        static_cast<cudaStream_t>(stream));
+}
+
+int lw_matrix_make_twin(void* handle, int id) {
+  Model* M = static_cast<Model*>(handle);
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (mx->d_twin) return kOk;
+  int rc = check_device(M);
+  if (rc) return rc;
+  if (mx->fmt == kFmtNone || !gemv1_usable(mx->dev)) {
+    set_error("%s: no block format, no twin", mx->name.c_str());
+    return kErrArg;
+  }
+  // the symbols come from the GPU decoder (bit-exact against the host decoder by the parity tests)
+  const size_t nsym = static_cast<size_t>(mx->N) * mx->Ks;
+  uint8_t* d_sym = nullptr;
+  cudaError_t e = cudaMalloc(&d_sym, nsym);
+  if (e != cudaSuccess) return cuda_fail("cudaMalloc (twin symbols)", e);
+  std::vector<uint8_t> sym(nsym), side(static_cast<size_t>(mx->side_bytes));
+  rc = launch_decode_codes(mx->dev, d_sym, false, nullptr);
+  if (!rc && ((e = cudaMemcpy(sym.data(), d_sym, nsym, cudaMemcpyDeviceToHost)) != cudaSuccess ||
+              (e = cudaMemcpy(side.data(), mx->dev.side, side.size(), cudaMemcpyDeviceToHost)) != cudaSuccess))
+    rc = cuda_fail("cudaMemcpy (twin symbols)", e);
+  cudaFree(d_sym);
+  if (rc) return rc;
+  std::vector<uint32_t> gb, words, vals(256);
+  uint32_t unit_words = 0;
+  if ((rc = build_twin(sym.data(), mx->N, mx->Ks, mx->fmt, side.data(), default_threads(), gb, words, &unit_words))) return rc;
+  symbol_values(mx->fmt, vals.data());
+  const size_t n_units = gb.size() / 2;
+  const size_t off_gb = align_up(256 * 4, 256), off_words = align_up(off_gb + gb.size() * 4, 256);
+  const size_t off_cls = align_up(off_words + words.size() * 4, 256), off_done = off_cls + align_up(n_units, 256);
+  const size_t total = off_done + align_up(static_cast<size_t>(mx->N / kTileRows) * kRowDoneStride * 4, 256);
+  if ((e = cudaMalloc(&mx->d_twin, total)) != cudaSuccess) return cuda_fail("cudaMalloc (twin)", e);
+  uint8_t* d = static_cast<uint8_t*>(mx->d_twin);
+  if ((e = cudaMemset(d, 0, total)) != cudaSuccess || (e = cudaMemcpy(d, vals.data(), 1024, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_gb, gb.data(), gb.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_words, words.data(), words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
+    cudaFree(mx->d_twin);
+    mx->d_twin = nullptr;
+    return cuda_fail("cudaMemcpy (twin)", e);
+  }
+  mx->twin = mx->dev;
+  mx->twin.reader = 1;
+  mx->twin.tab32 = reinterpret_cast<const uint32_t*>(d);
+  mx->twin.cmp_tab = nullptr;
+  mx->twin.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
+  mx->twin.words = reinterpret_cast<const uint32_t*>(d + off_words);
+  mx->twin.unit_slow = d + off_cls;
+  mx->twin.row_done = reinterpret_cast<unsigned int*>(d + off_done);
+  mx->twin.index_bits = 10;
+  mx->twin.group = 3;
+  mx->twin.max_unit_words = unit_words;
+  mx->twin.max_tile_words = unit_words * mx->dev.split;
+  mx->twin_bytes = (words.size() - kTailWords) * 4;
+  mx->twin_epoch = 0;
+  return kOk;
+}
+
+long long lw_matrix_twin_bytes(void* handle, int id) {
+  Matrix* mx = matrix_by_id(handle, id);
+  return mx && mx->d_twin ? static_cast<long long>(mx->twin_bytes) : -1;
+}
+
+int lw_matrix_drop_twin(void* handle, int id) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (mx->d_twin) {
+    cudaDeviceSynchronize();
+    cudaFree(mx->d_twin);
+    mx->d_twin = nullptr;
+    mx->twin_bytes = 0;
+  }
+  return kOk;
+}
+
+int lw_linear_twin(void* handle, int id, const void* x_dev, int x_is_half, float* y_dev, void* stream) {
+  Model* M = static_cast<Model*>(handle);
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return kErrGeneric;
+  if (!mx->d_twin || !x_dev || !y_dev) {
+    set_error("lw_linear_twin: no twin (call lw_matrix_make_twin) or bad argument");
+    return kErrArg;
+  }
+  if (const int rc = check_device(M)) return rc;
+  return launch_gemv(mx->twin, x_dev, x_is_half != 0, 1, y_dev, mx->N, M->d_partials, M->partial_floats,
+                     static_cast<cudaStream_t>(stream), &mx->twin_epoch);
 }
 
 int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream) {

@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <string>
 
 #include "lw_gemv1.cuh"
 
@@ -36,7 +37,7 @@ static const Gemv1Env& gemv1_env() {
 // Plan for a launch over `ntr` tile rows.  False if a unit does not fit shared memory or a block would be dealt more
 // units than its list holds (the caller then covers the rows in several launches).
 template <int FMT>
-static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p) {
+static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits) {
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT);
   constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
   p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
@@ -58,7 +59,7 @@ static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p) {
   // LW_GEMV1_RING=16 where 36 staging buffers still fit (measured: no difference on the bench matrix).
   size_t fixed = 0;
   for (p.tile_ring_log2 = gemv1_env().ring >= 16 ? 4 : 3; p.tile_ring_log2 >= 3; --p.tile_ring_log2) {
-    fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
+    fixed = (size_t(1) << (index_bits + M.pad)) + kLutSize * 4 +
             static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
             2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + (size_t(1) << p.tile_ring_log2) * (8 + SPLIT * kTileRows * 4) +
             p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
@@ -80,7 +81,7 @@ static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p) {
   return true;
 }
 
-template <int FMT, int G, int IDXBITS, int LOG_R>
+template <int FMT, int G, int IDXBITS, int LOG_R, int READER = kReaderTable>
 static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err,
                     cudaStream_t st) {
   // A block's list holds at most kRingMaxUnits units; a matrix with more tile rows than that allows (a vocabulary
@@ -88,7 +89,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
   const int NT = M.N / kTileRows;
   Gemv1Plan p;
   int chunks = 1;
-  while (!plan_gemv1<FMT>(M, (NT + chunks - 1) / chunks, p)) {
+  while (!plan_gemv1<FMT>(M, (NT + chunks - 1) / chunks, p, IDXBITS)) {
     if (p.max_units <= debug_knobs().max_units || chunks >= NT) {
       set_kernel_error_text("gemv1", "work unit does not fit shared memory");
       return kErrTooLarge;
@@ -101,7 +102,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
   cudaGetDevice(&dev);
   size_t& configured = configured_per_device[dev & 63];
   if (p.smem > configured) {
-    if (cudaFuncSetAttribute(k_gemv1<FMT, G, IDXBITS, LOG_R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(k_gemv1<FMT, G, IDXBITS, LOG_R, READER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kSmemLimit)) != cudaSuccess)
       return note_launch("cudaFuncSetAttribute(k_gemv1)");
     configured = kSmemLimit;
@@ -109,7 +110,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
   const int per = (NT + chunks - 1) / chunks;
   for (int tr0 = 0; tr0 < NT; tr0 += per) {
     const int ntr = std::min(per, NT - tr0);
-    if (ntr != per && !plan_gemv1<FMT>(M, ntr, p)) {
+    if (ntr != per && !plan_gemv1<FMT>(M, ntr, p, IDXBITS)) {
       set_kernel_error_text("gemv1", "work unit does not fit shared memory");
       return kErrTooLarge;
     }
@@ -145,9 +146,9 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
       attr[0].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R>, M, a);
+      cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R, READER>, M, a);
     } else {
-      k_gemv1<FMT, G, IDXBITS, LOG_R><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
+      k_gemv1<FMT, G, IDXBITS, LOG_R, READER><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
     }
     const int rc = note_launch("k_gemv1");
     if (rc) return rc;
@@ -157,12 +158,19 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
 
 template <int FMT, int G>
 static int launch_i(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+  // LW_GEMV1_LOOKUP=limit: the comparator decoder instead of the table (a measurement switch, read once)
+  static const bool use_limit = [] {
+    const char* e = getenv("LW_GEMV1_LOOKUP");
+    return e && std::string(e) == "limit";
+  }();
+  if (use_limit && M.cmp_tab) return launch_t<FMT, G, 10, kGemv1LogCopies, kReaderLimit>(M, X, x_is_half, P, Y, err, st);
   if (M.index_bits == 10) return launch_t<FMT, G, 10, kGemv1LogCopies>(M, X, x_is_half, P, Y, err, st);
   return launch_t<FMT, G, 11, kGemv1LogCopies>(M, X, x_is_half, P, Y, err, st);
 }
 
 template <int FMT>
 static int launch_g(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
+  if (M.reader == 1) return launch_t<FMT, 3, 10, kGemv1LogCopies, kReaderFixed>(M, X, x_is_half, P, Y, err, st);
   switch (M.group) {
     case 3: return launch_i<FMT, 3>(M, X, x_is_half, P, Y, err, st);
     case 4: return launch_i<FMT, 4>(M, X, x_is_half, P, Y, err, st);

@@ -180,6 +180,8 @@ static float grid_of(int fmt, int q) {
 // 32-bit decode table of the batch-1 kernel: bits 28-31 = code length (recovered by one multiply-high); byte 0 =
 // the grid value of the symbol (of its low nibble for paired formats) as a signed 8-bit integer, byte 1 = the grid
 // value of the high nibble (0 for unpaired formats).  The two bytes are the multiplier operand of a dp2a instruction.
+static uint32_t value_bytes(int fmt, uint32_t sym);
+
 void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]) {
   for (int i = 0; i < kLutSize; ++i) {
     const uint32_t sym = t.lut[i] & 255u, len = t.lut[i] >> 8;
@@ -194,6 +196,29 @@ void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]) {
     }
     out[i] = e;
   }
+}
+
+static uint32_t value_bytes(int fmt, uint32_t sym) {
+  if (is_paired(fmt)) {
+    const int v0 = static_cast<int>(grid_of(fmt, sym & 15)), v1 = static_cast<int>(grid_of(fmt, sym >> 4));
+    return (static_cast<uint32_t>(v0) & 255u) | ((static_cast<uint32_t>(v1) & 255u) << 8);
+  }
+  if (fmt == kFmtQ5K || fmt == kFmtQ6K)
+    return static_cast<uint32_t>(static_cast<int>(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)))) & 255u;
+  return sym;
+}
+
+void comparator_table(const HuffTable& t, int fmt, uint32_t out[kCmpTabWords]) {
+  std::memset(out, 0, sizeof(uint32_t) * kCmpTabWords);
+  for (int l = 1; l <= kMaxLen; ++l) {
+    out[l] = t.limit[l];   // = (first[l] + count[l]) << (11 - l): codes of length <= l lie below it
+    out[12 + l] = t.base[l] - t.first[l];
+  }
+  for (int i = 0; i < t.nsym; ++i) out[24 + i] = value_bytes(fmt, t.sorted[i]);
+}
+
+void symbol_values(int fmt, uint32_t out[256]) {
+  for (uint32_t s = 0; s < 256; ++s) out[s] = value_bytes(fmt, s);
 }
 
 // ------------------------------------------------------------------------------------------------ blob
@@ -528,6 +553,72 @@ int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>&
   });
   if (max_group_words) *max_group_words = mg;
   if (max_tile_words) *max_tile_words = mt;
+  return kOk;
+}
+
+int twin_bits(int fmt) { return fmt == kFmtQ5K ? 5 : fmt == kFmtQ6K ? 6 : 8; }
+
+int build_twin(const uint8_t* sym, int N, int Ks, int fmt, const uint8_t* side, int threads,
+               std::vector<uint32_t>& group_base, std::vector<uint32_t>& words, uint32_t* unit_words) {
+  if (fmt < kFmtQ4K || fmt > kFmtIQ4XS || !sym || !side || N % kTileRows || Ks % kTileSyms) {
+    set_error("build_twin: bad argument");
+    return kErrArg;
+  }
+  const int split = default_split(fmt), G = 2 * split, B = twin_bits(fmt), seg_syms = kTileSyms / split;
+  const int KT = Ks / kTileSyms, T = (N / kTileRows) * KT;
+  const uint32_t cw = static_cast<uint32_t>(seg_syms * B / 32);            // words per chain (whole words by construction)
+  const uint32_t side_words = unit_side_words(fmt), uw = 2 * cw * kLanes + side_words;
+  const uint64_t total = static_cast<uint64_t>(T) * split * uw;
+  if (total > 0xFFFFFFFFull) {
+    set_error("twin needs more than 2^32 device words");
+    return kErrTooLarge;
+  }
+  group_base.assign(static_cast<size_t>(T) * G + 1, 0);
+  words.assign(total + kTailWords, 0);
+  const size_t side_row_bytes = static_cast<size_t>(Ks) * (is_paired(fmt) ? 2 : 1) / 256 * side_bytes(fmt);
+  const uint32_t mask = (1u << B) - 1u;
+  parallel_for(T, threads, [&](int t) {
+    const int tr = t / KT, tc = t % KT;
+    for (int g = 0; g < G; ++g) {
+      const int seg = g >> 1, half = g & 1;
+      const uint32_t base = (static_cast<uint32_t>(t) * split + seg) * uw + half * cw * kLanes;
+      group_base[static_cast<size_t>(t) * G + g] = base;
+      for (int lane = 0; lane < kLanes; ++lane) {
+        const uint8_t* row = sym + (static_cast<size_t>(tr) * kTileRows + half * 32 + lane) * Ks + tc * kTileSyms + seg * seg_syms;
+        uint64_t acc = 0;
+        int fill = 0;
+        uint32_t wi = 0;
+        for (int c = 0; c < seg_syms; ++c) {
+          uint32_t v = row[c];
+          if (fmt == kFmtQ6K) v = (v - 32u) & mask;   // stored centred, so that a sign extension gives the grid value
+          acc |= static_cast<uint64_t>(v & mask) << fill;
+          fill += B;
+          if (fill >= 32) {
+            words[base + static_cast<size_t>(wi++) * kLanes + lane] = static_cast<uint32_t>(acc);
+            acc >>= 32;
+            fill -= 32;
+          }
+        }
+      }
+      if (half) {
+        uint32_t* sd = words.data() + base + static_cast<size_t>(cw) * kLanes;
+        uint16_t* sh = reinterpret_cast<uint16_t*>(sd);
+        for (int r = 0; r < kTileRows; ++r) {
+          uint32_t sc, mn, dd;
+          unit_scales(fmt, side + (static_cast<size_t>(tr) * kTileRows + r) * side_row_bytes, tc, seg, split, &sc, &mn, &dd);
+          sd[r] = (fmt == kFmtQ4K || fmt == kFmtQ5K) ? dd : sc;
+          if (fmt == kFmtQ4K || fmt == kFmtQ5K) {
+            sd[64 + r] = sc;
+            sd[128 + r] = mn;
+          } else {
+            sh[128 + r] = static_cast<uint16_t>(dd);
+          }
+        }
+      }
+    }
+  });
+  group_base[static_cast<size_t>(T) * G] = static_cast<uint32_t>(total);
+  if (unit_words) *unit_words = uw;
   return kOk;
 }
 

@@ -24,6 +24,23 @@ void table_from_lengths(const uint8_t len[256], HuffTable& t);
 // Recovers lengths from a stored table and checks that the table is exactly the canonical one for those lengths.
 int table_from_lut(const uint16_t* lut, HuffTable& t);
 void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]);
+// Comparator form for the limit-register decoder (reference: hw/huff/huff_engine.h:39-77, hw/huff/rtl/huff_lane.sv:86-93):
+// with v = the 11 window bits reversed (MSB first), len = 1 + #{l in 1..10 : v >= limit[l]} and the symbol is
+// sorted[(v >> (11 - len)) + off[len]].  out[0..11] = limit[l] (2048 where no longer code exists), out[12..23] = off[l]
+// = base[l] - first[l] (two's complement), out[24..279] = grid value bytes of sorted[i] as in fat_table (no length).
+constexpr int kCmpTabWords = 24 + 256;
+void comparator_table(const HuffTable& t, int fmt, uint32_t out[kCmpTabWords]);
+// Grid value bytes of every 8-bit symbol (the table of a fixed-width twin of a paired format), as in fat_table.
+void symbol_values(int fmt, uint32_t out[256]);
+
+// Fixed-width twin of a coded matrix (the role of interleave_packed / interleave_packed_q, kernels/llmrt.cu:1733-1777):
+// the decoded symbols packed at a fixed width (8 bits per paired symbol, 5 for Q5_K, 6 for Q6_K stored minus 32 in
+// two's complement) into the same unit structure as relayout() builds - chains of 256 / split symbols, 32 chains
+// interleaved word by word per group, the unit's scales behind its second group - so that the same kernel body can read
+// it without any Huffman decoding.  sym = decoded symbols [N, Ks].
+int twin_bits(int fmt);
+int build_twin(const uint8_t* sym, int N, int Ks, int fmt, const uint8_t* side, int threads,
+               std::vector<uint32_t>& group_base, std::vector<uint32_t>& words, uint32_t* unit_words);
 
 // ---- blob (reference: lazyweights/bundle.py:57-106, kernels/llmrt.cu:2513-2541)
 int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits);

@@ -16,7 +16,10 @@ constexpr int kRowDoneStride = 32;
 // One coded matrix on the device (all pointers are device pointers; passed to kernels by value).
 struct MatDev {
   const uint16_t* lut;          // [2048] symbol | length << 8
-  const uint32_t* tab32;        // [2048] length << 28 | grid value(s) as int8 (see lw::fat_table)
+  const uint32_t* tab32;        // [2048] length << 28 | grid value(s) as int8 (see lw::fat_table); for a fixed-width
+                                // twin: [256] grid values of a paired symbol (unused for unpaired formats)
+  const uint32_t* cmp_tab;      // comparator form of the code (lw::comparator_table): [0..11] limit per length,
+                                // [12..23] index offset per length, [24..279] grid values in canonical order; or null
   const uint32_t* group_base;   // [T * groups + 1] word offset of every chain group
   const uint32_t* words;        // interleaved chain words (+ zero tail)
   const uint8_t* side;          // [N, K / 256 * side_bytes] or null (symbols only)
@@ -28,6 +31,7 @@ struct MatDev {
   int group;                    // symbols per group of the batch-1 kernel's grouped decoder (0 = kernel not usable)
   int N, K, Ks, KT, T;
   int fmt, split;
+  int reader;                   // 0: Huffman-coded chains; 1: fixed-width twin (lw::build_twin)
   int pad;                      // zero bits at the start of every chain
   int max_len;                  // longest code of the table
   uint32_t max_tile_words;      // largest tile, in words

@@ -24,6 +24,11 @@ struct Matrix {
   void* d_block = nullptr;   // one allocation: table, group bases, words, side bytes
   MatDev dev{};
   unsigned int clean_epoch = 0;   // when the tile-row counters were last known to be zero (see launch_gemv)
+  // fixed-width twin (lw_matrix_make_twin): a second device image of the same matrix, read by the same kernel
+  void* d_twin = nullptr;
+  MatDev twin{};
+  size_t twin_bytes = 0;          // chain words + unit scales: what one product of the twin reads
+  unsigned int twin_epoch = 0;
 };
 
 struct Runtime;   // decoder state, defined in lw_runtime.cu
@@ -51,8 +56,10 @@ struct Model {
   Runtime* rt = nullptr;
   ~Model() {
     runtime_free(this);   // the decoder state, if any (also after a failed rt_open)
-    for (auto& m : mats)
+    for (auto& m : mats) {
       if (m.d_block) cudaFree(m.d_block);
+      if (m.d_twin) cudaFree(m.d_twin);
+    }
     if (d_partials) cudaFree(d_partials);
     if (d_x) cudaFree(d_x);
     if (d_y) cudaFree(d_y);

@@ -103,6 +103,30 @@ class _Handle:
                                              C.c_void_p(st)))
         return out
 
+    # ---- fixed-width twin (the same kernel without Huffman decoding)
+    def make_twin(self, name):
+        nat.check(nat.lib().lw_matrix_make_twin(self._h, self.matrix_id(name)))
+        return True
+
+    def drop_twin(self, name):
+        nat.check(nat.lib().lw_matrix_drop_twin(self._h, self.matrix_id(name)))
+
+    def twin_bytes(self, name):
+        return int(nat.lib().lw_matrix_twin_bytes(self._h, self.matrix_id(name)))
+
+    def linear_twin(self, name, x, out=None):
+        """y[N] = W x for one activation row, read from the twin (make_twin first)."""
+        torch = _torch()
+        inf = self.info(name)
+        x2 = x.reshape(1, -1).contiguous()
+        if not x2.is_cuda or x2.dtype not in (torch.float16, torch.float32) or x2.shape[1] != inf["K"]:
+            raise ValueError("linear_twin wants one CUDA fp16/fp32 row with %d columns" % inf["K"])
+        y = out if out is not None else torch.empty((1, inf["N"]), dtype=torch.float32, device=x2.device)
+        st = torch.cuda.current_stream(x2.device).cuda_stream
+        nat.check(nat.lib().lw_linear_twin(self._h, self.matrix_id(name), C.c_void_p(x2.data_ptr()),
+                                           int(x2.dtype == torch.float16), C.c_void_p(y.data_ptr()), C.c_void_p(st)))
+        return y
+
     def decode_weights(self, name):
         """fp16 CUDA tensor [N, K] of the dequantised weights."""
         torch = _torch()
