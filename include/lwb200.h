@@ -121,6 +121,17 @@ int lw_matrix_plan(void* handle, int id, int* group, int* index_bits, double* sl
  * issue them on one stream, as the reference's runtime does. */
 int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev, void* stream);
 
+/* n one-row products in as few launches as possible: y_j[N_j] = W_j x_j[K_j] for j < n, matrix j = matrix ids[j] of
+ * handles[j] (handles may repeat), every x_j fp16 (x_is_half != 0) or every x_j fp32.  Up to eight products whose
+ * matrices share block format and decode plan (lw_matrix_plan) run as ONE kernel launch in which every thread block
+ * works on a single matrix: the launch's set-up and tail are paid once and its blocks keep much longer work lists,
+ * which is worth about a fifth of the time of products launched one by one (the projections of a decoder layer that read
+ * the same activations - gate and up, or q, k and v - are the natural use).  Other combinations are launched one by
+ * one; results never depend on the grouping.  The reference runs every product as its own launch
+ * (kernels/llmrt.cu:1808-1826); this entry point has no counterpart there. */
+int lw_linear_batch(int n, void* const* handles, const int* ids, const void* const* xs_dev, int x_is_half,
+                    float* const* ys_dev, void* stream);
+
 /* The same product as lw_linear for callers that must not allocate device memory while they run: code that executes
  * inside a region where the allocator is off limits (a latency-critical serving loop that has already handed all of
  * its memory budget out, a plug-in running under a host framework that owns the device heap, a handle that was opened

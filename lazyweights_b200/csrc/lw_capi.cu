@@ -315,6 +315,30 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   return kOk;
 }
 
+int linear_batch_device(Model* M, int n, const int* mat_index, const float* const* xs, float* const* ys, cudaStream_t st) {
+  if (n < 1 || n > 8) return kErrArg;
+  const MatDev* mats[8];
+  const void* xv[8];
+  float* partials[8];
+  unsigned int* epochs[8];
+  size_t off = 0;
+  for (int j = 0; j < n; ++j) {
+    Matrix& mx = M->mats[mat_index[j]];
+    if (mx.fmt == kFmtNone || !gemv1_usable(mx.dev)) {
+      set_error("%s has no side tensor: products need a block format", mx.name.c_str());
+      return kErrArg;
+    }
+    const size_t need = (gemv_partial_floats(mx.dev, 1) + 63) & ~size_t(63);
+    if (off + need > M->partial_floats) return kErrTooLarge;
+    mats[j] = &mx.dev;
+    xv[j] = xs[j];
+    partials[j] = M->d_partials + off;
+    epochs[j] = &mx.clean_epoch;
+    off += need;
+  }
+  return launch_gemv_batch(n, mats, xv, false, ys, partials, st, epochs);
+}
+
 }  // namespace lw
 
 using namespace lw;
@@ -507,6 +531,46 @@ int lw_linear(void* handle, int id, const void* x_dev, int x_is_half, int m, flo
   }
   return linear_device(static_cast<Model*>(handle), *mx, x_dev, x_is_half != 0, m, y_dev, mx->N,
                        static_cast<cudaStream_t>(stream));
+}
+
+int lw_linear_batch(int n, void* const* handles, const int* ids, const void* const* xs_dev, int x_is_half,
+                    float* const* ys_dev, void* stream) {
+  if (n < 1 || !handles || !ids || !xs_dev || !ys_dev) {
+    set_error("lw_linear_batch: bad argument");
+    return kErrArg;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  constexpr int kChunk = 8;
+  for (int i0 = 0; i0 < n; i0 += kChunk) {
+    const int c = std::min(kChunk, n - i0);
+    const MatDev* mats[kChunk];
+    float* partials[kChunk];
+    unsigned int* epochs[kChunk];
+    std::map<Model*, size_t> used;   // scratch already handed out per handle within this chunk
+    for (int j = 0; j < c; ++j) {
+      Model* M = static_cast<Model*>(handles[i0 + j]);
+      Matrix* mx = matrix_by_id(M, ids[i0 + j]);
+      if (!mx) return kErrGeneric;
+      if (const int rc = check_device(M)) return rc;
+      if (!xs_dev[i0 + j] || !ys_dev[i0 + j] || mx->fmt == kFmtNone || !gemv1_usable(mx->dev)) {
+        set_error("lw_linear_batch: entry %d: null pointer or a matrix without block format", i0 + j);
+        return kErrArg;
+      }
+      size_t& off = used[M];
+      const size_t need = (gemv_partial_floats(mx->dev, 1) + 63) & ~size_t(63);
+      if (off + need > M->partial_floats) {
+        set_error("lw_linear_batch: the products of one handle need more scratch than the handle holds");
+        return kErrTooLarge;
+      }
+      mats[j] = &mx->dev;
+      partials[j] = M->d_partials + off;
+      epochs[j] = &mx->clean_epoch;
+      off += need;
+    }
+    const int rc = launch_gemv_batch(c, mats, xs_dev + i0, x_is_half != 0, ys_dev + i0, partials, st, epochs);
+    if (rc) return rc;
+  }
+  return kOk;
 }
 
 int lw_matrix_make_twin(void* handle, int id) {

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   RM.carve(tab1 + kLutSize, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   BlockShare S;
-  S.init(M, RA, SPLIT);   // one column set (nsets = 1): there are no activations to stage
+  S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);   // one column set (nsets = 1): there are no activations to stage
   const int nmine = S.nmine;
   const bool consumer = warp < RA.warps;
   const int nthr = RA.warps * 32;

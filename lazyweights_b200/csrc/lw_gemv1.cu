@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <memory>
 #include <string>
 
 #include "lw_gemv1.cuh"
@@ -37,7 +38,7 @@ static const Gemv1Env& gemv1_env() {
 // Plan for a launch over `ntr` tile rows.  False if a unit does not fit shared memory or a block would be dealt more
 // units than its list holds (the caller then covers the rows in several launches).
 template <int FMT>
-static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits) {
+static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits, int avail_blocks = 0) {
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT);
   constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
   p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
@@ -46,7 +47,7 @@ static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits) {
   // (harmless: those bits are never used), so only the end of the ring needs slack
   p.buf_words = (M.max_unit_words + 31u) & ~31u;
   const int tiles = ntr * M.KT;
-  p.blocks = std::max(p.nsets, std::min(sm_count(), tiles));
+  p.blocks = std::max(p.nsets, std::min(avail_blocks > 0 ? avail_blocks : sm_count(), tiles));
   p.max_units = 0;   // the longest list any block gets: blocks b, b + nsets, ... serve the tile columns of set b % nsets
   for (int set = 0; set < p.nsets; ++set) {
     const int nb_set = (p.blocks - set + p.nsets - 1) / p.nsets, ncol = (M.KT - set + p.nsets - 1) / p.nsets;
@@ -79,6 +80,139 @@ static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits) {
   p.producer_lanes = std::max(1, std::min(32, gemv1_env().lanes));
   p.smem = fixed + static_cast<size_t>(p.slots) * p.buf_words * 4;
   return true;
+}
+
+static Gemv1Args make_args(const Gemv1Plan& p, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, int tr0,
+                           int ntr) {
+  Gemv1Args a;
+  a.x = X;
+  a.partials = P;
+  a.y = Y;
+  a.x_is_half = x_is_half;
+  a.helpers = p.helpers;
+  a.tile_ring_log2 = p.tile_ring_log2;
+  a.pdl = gemv1_env().pdl != 0;
+  a.r.err = err;
+  a.r.wait_limit = debug_knobs().wait_limit;
+  a.r.drop_unit = debug_knobs().drop_unit;
+  a.r.warps = p.warps;
+  a.r.slots = p.slots;
+  a.r.producers = p.producers;
+  a.r.producer_lanes = p.producer_lanes;
+  a.r.buf_words = p.buf_words;
+  a.r.nsets = p.nsets;
+  a.r.cols_per_set = p.cols_per_set;
+  a.r.max_units = p.max_units;
+  a.r.tr0 = tr0;
+  a.r.ntr = ntr;
+  return a;
+}
+
+static void launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int blocks, int threads, size_t smem,
+                          cudaStream_t st, bool pdl) {
+  cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+}
+
+// Several one-row products in one launch (k_gemv1_batch): the grid's blocks are dealt to the matrices in proportion
+// to their tiles.  kErrTooLarge (nothing launched) where a matrix's share of the grid cannot hold its unit list; the
+// caller then launches the products one by one.
+template <int FMT, int G, int IDXBITS>
+static int launch_batch_t(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
+                          float* const* ys, unsigned int* err, cudaStream_t st) {
+  auto B = std::make_unique<Gemv1Batch>();
+  const int grid = sm_count();
+  long long total_tiles = 0;
+  for (int j = 0; j < n; ++j) total_tiles += static_cast<long long>(mats[j]->T);
+  int given = 0;
+  int share[kGemv1MaxBatch];
+  for (int j = 0; j < n; ++j) {
+    const int nsets = (mats[j]->KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
+    share[j] = std::max(nsets, static_cast<int>(static_cast<long long>(grid) * mats[j]->T / total_tiles));
+    given += share[j];
+  }
+  for (int j = 0; given < grid; j = (j + 1) % n, ++given) ++share[j];   // the remainder, one block each
+  if (given > grid) return kErrTooLarge;
+  size_t smem = 0;
+  int threads = 0;
+  B->count = n;
+  B->first[0] = 0;
+  for (int j = 0; j < n; ++j) {
+    Gemv1Plan p;
+    if (!plan_gemv1<FMT>(*mats[j], mats[j]->N / kTileRows, p, IDXBITS, share[j])) return kErrTooLarge;
+    B->mat[j] = *mats[j];
+    B->arg[j] = make_args(p, xs[j], x_is_half, partials[j], ys[j], err, 0, mats[j]->N / kTileRows);
+    B->first[j + 1] = B->first[j] + p.blocks;
+    smem = std::max(smem, p.smem);
+    threads = (p.helpers + p.producers) * 32;
+  }
+  static size_t configured_per_device[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  size_t& configured = configured_per_device[dev & 63];
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(k_gemv1_batch<FMT, G, IDXBITS, kGemv1LogCopies>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kSmemLimit)) != cudaSuccess)
+      return note_launch("cudaFuncSetAttribute(k_gemv1_batch)");
+    configured = kSmemLimit;
+  }
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  launch_config(cfg, attr, B->first[n], threads, smem, st, gemv1_env().pdl != 0);
+  cudaLaunchKernelEx(&cfg, k_gemv1_batch<FMT, G, IDXBITS, kGemv1LogCopies>, *B);
+  return note_launch("k_gemv1_batch");
+}
+
+template <int FMT, int G>
+static int launch_batch_i(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
+                          float* const* ys, unsigned int* err, cudaStream_t st) {
+  if (mats[0]->index_bits == 10) return launch_batch_t<FMT, G, 10>(n, mats, xs, x_is_half, partials, ys, err, st);
+  return launch_batch_t<FMT, G, 11>(n, mats, xs, x_is_half, partials, ys, err, st);
+}
+
+template <int FMT>
+static int launch_batch_g(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
+                          float* const* ys, unsigned int* err, cudaStream_t st) {
+  switch (mats[0]->group) {
+    case 3: return launch_batch_i<FMT, 3>(n, mats, xs, x_is_half, partials, ys, err, st);
+    case 4: return launch_batch_i<FMT, 4>(n, mats, xs, x_is_half, partials, ys, err, st);
+  }
+  if constexpr (!is_paired(FMT)) {
+    switch (mats[0]->group) {
+      case 5: return launch_batch_i<FMT, 5>(n, mats, xs, x_is_half, partials, ys, err, st);
+      case 6: return launch_batch_i<FMT, 6>(n, mats, xs, x_is_half, partials, ys, err, st);
+    }
+  }
+  return kErrTooLarge;
+}
+
+int launch_gemv1_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
+                       float* const* ys, unsigned int* err, cudaStream_t st) {
+  if (n < 1 || n > kGemv1MaxBatch || !err) return kErrTooLarge;
+  for (int j = 0; j < n; ++j) {
+    const MatDev& M = *mats[j];
+    if (!gemv1_usable(M) || M.reader != 0 || M.fmt != mats[0]->fmt || M.group != mats[0]->group ||
+        M.index_bits != mats[0]->index_bits)
+      return kErrTooLarge;   // not one kernel instantiation: the caller launches them one by one
+    if ((reinterpret_cast<uintptr_t>(ys[j]) | reinterpret_cast<uintptr_t>(partials[j])) & 15u) {
+      set_kernel_error_text("gemv1", "the result and the scratch must be 16-byte aligned");
+      return kErrArg;
+    }
+  }
+  if (debug_knobs().drop_unit >= 0 || debug_knobs().max_units < kGemv1MaxUnits) return kErrTooLarge;   // test switches: plain launches
+  switch (mats[0]->fmt) {
+    case kFmtQ4K: return launch_batch_g<kFmtQ4K>(n, mats, xs, x_is_half, partials, ys, err, st);
+    case kFmtQ5K: return launch_batch_g<kFmtQ5K>(n, mats, xs, x_is_half, partials, ys, err, st);
+    case kFmtIQ4XS: return launch_batch_g<kFmtIQ4XS>(n, mats, xs, x_is_half, partials, ys, err, st);
+    default: return launch_batch_g<kFmtQ6K>(n, mats, xs, x_is_half, partials, ys, err, st);
+  }
 }
 
 template <int FMT, int G, int IDXBITS, int LOG_R, int READER = kReaderTable>
@@ -114,42 +248,11 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, float* P, fl
       set_kernel_error_text("gemv1", "work unit does not fit shared memory");
       return kErrTooLarge;
     }
-    Gemv1Args a;
-    a.x = X;
-    a.partials = P;
-    a.y = Y;
-    a.x_is_half = x_is_half;
-    a.helpers = p.helpers;
-    a.tile_ring_log2 = p.tile_ring_log2;
-    a.pdl = gemv1_env().pdl != 0;
-    a.r.err = err;
-    a.r.wait_limit = debug_knobs().wait_limit;
-    a.r.drop_unit = debug_knobs().drop_unit;
-    a.r.warps = p.warps;
-    a.r.slots = p.slots;
-    a.r.producers = p.producers;
-    a.r.producer_lanes = p.producer_lanes;
-    a.r.buf_words = p.buf_words;
-    a.r.nsets = p.nsets;
-    a.r.cols_per_set = p.cols_per_set;
-    a.r.max_units = p.max_units;
-    a.r.tr0 = tr0;
-    a.r.ntr = ntr;
-    if (a.pdl) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(p.blocks);
-      cfg.blockDim = dim3((p.helpers + p.producers) * 32);
-      cfg.dynamicSmemBytes = p.smem;
-      cfg.stream = st;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[0].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R, READER>, M, a);
-    } else {
-      k_gemv1<FMT, G, IDXBITS, LOG_R, READER><<<p.blocks, (p.helpers + p.producers) * 32, p.smem, st>>>(M, a);
-    }
+    const Gemv1Args a = make_args(p, X, x_is_half, P, Y, err, tr0, ntr);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    launch_config(cfg, attr, p.blocks, (p.helpers + p.producers) * 32, p.smem, st, a.pdl != 0);
+    cudaLaunchKernelEx(&cfg, k_gemv1<FMT, G, IDXBITS, LOG_R, READER>, M, a);
     const int rc = note_launch("k_gemv1");
     if (rc) return rc;
   }

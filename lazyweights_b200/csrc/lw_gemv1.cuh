@@ -211,8 +211,9 @@ static __device__ __noinline__ void row_sum(const float* p, unsigned int terms, 
 
 constexpr int kGemv1MaxTileRing = 16;   // tiles whose segments a block may be combining at one time (8 or 16)
 
-template <int FMT, int G, int IDXBITS, int LOG_R, int READER = kReaderTable>
-__global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
+// The work of one block: block `bidx` of the `nblocks` blocks that share matrix M.
+template <int FMT, int G, int IDXBITS, int LOG_R, int READER>
+__device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A, const int bidx, const int nblocks) {
   constexpr bool PAIR = is_paired(FMT);
   constexpr int SPLIT = default_split(FMT);
   constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;            // weights per tile row
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   RM.carve(tile_acc + ring * SPLIT * kTileRows, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   BlockShare S;
-  S.init(M, RA, SPLIT);
+  S.init(M, RA, SPLIT, bidx, nblocks);
   const int set = S.set, ncol = S.ncol, nmine = S.nmine;
   pdl_trigger();   // the next kernel of the stream may be set up while this one runs (it waits before it reads)
   const bool consumer = warp < A.helpers;   // takes part in the prologue; warps >= RA.warps leave after it
@@ -502,6 +503,33 @@ __global__ void __launch_bounds__(1024, 1) k_gemv1(MatDev M, Gemv1Args A) {
   }
   count();
   resolve();
+}
+
+template <int FMT, int G, int IDXBITS, int LOG_R, int READER = kReaderTable>
+__global__ void __launch_bounds__(1024, 1) k_gemv1(const __grid_constant__ MatDev M, const __grid_constant__ Gemv1Args A) {
+  gemv1_block<FMT, G, IDXBITS, LOG_R, READER>(M, A, blockIdx.x, gridDim.x);
+}
+
+// Several products in ONE launch: matrix j (its own activations, scratch and result) is worked on by blocks
+// first[j] .. first[j + 1] - 1 of the grid.  Every block still serves a single matrix - one decode table, one unit list -
+// but a block's list is several times longer than when the whole grid shares one matrix: the set-up and the tail of a
+// launch are paid once for all the products, and warps that run out of units are a smaller share of the launch
+// (one matrix on 148 blocks of 28 warps gives a warp 3.5 units; eight matrices in one launch give it 28).
+// All matrices of a launch share the kernel's template parameters (format, group size, table width).
+constexpr int kGemv1MaxBatch = 8;
+struct Gemv1Batch {
+  MatDev mat[kGemv1MaxBatch];
+  Gemv1Args arg[kGemv1MaxBatch];
+  int first[kGemv1MaxBatch + 1];
+  int count;
+};
+
+template <int FMT, int G, int IDXBITS, int LOG_R>
+__global__ void __launch_bounds__(1024, 1) k_gemv1_batch(const __grid_constant__ Gemv1Batch B) {
+  int j = 0;
+#pragma unroll 1
+  while (j + 1 < B.count && static_cast<int>(blockIdx.x) >= B.first[j + 1]) ++j;
+  gemv1_block<FMT, G, IDXBITS, LOG_R, kReaderTable>(B.mat[j], B.arg[j], blockIdx.x - B.first[j], B.first[j + 1] - B.first[j]);
 }
 
 }  // namespace lw

@@ -11,6 +11,11 @@ bool gemv1_usable(const MatDev& M);
 int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* partials, float* y, unsigned int* err,
                  cudaStream_t st);
 
+// n <= 8 one-row products y_j = W_j x_j in ONE launch (matrices of one format and decode plan); kErrTooLarge, with
+// nothing launched, where the products cannot share a launch.
+int launch_gemv1_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
+                       float* const* ys, unsigned int* err, cudaStream_t st);
+
 // 2 <= m <= 8 rows (lw_gemvm.cuh): partials[KT * split][m][N] = one partial product per work unit and row, to be added
 // by the caller over KT * split terms; gemvm_partial_floats = the floats that takes.
 size_t gemvm_partial_floats(const MatDev& M, int m);

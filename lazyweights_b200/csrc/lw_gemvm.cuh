@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
   RM.carve(xg + (HAS_OFFSET ? RA.cols_per_set * NSB * MR : 0), RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   BlockShare S;
-  S.init(M, RA, SPLIT);
+  S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);
   const int set = S.set, ncol = S.ncol, nmine = S.nmine;
   pdl_trigger();   // see lw_gemv1.cuh: set-up overlaps the previous kernel's tail, pdl_wait before the activations
   const bool consumer = warp < RA.warps;

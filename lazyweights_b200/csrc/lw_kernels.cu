@@ -373,6 +373,25 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
   return check_launch("k_sum_partials");
 }
 
+int launch_gemv_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* ys,
+                      float* const* partials, cudaStream_t st, unsigned int* const* clean_epochs) {
+  const unsigned int epoch = g_error_epoch.load();
+  for (int j = 0; j < n; ++j) {
+    if (clean_epochs && clean_epochs[j] && *clean_epochs[j] != epoch) {
+      const MatDev& M = *mats[j];
+      if (cudaMemsetAsync(M.row_done, 0, static_cast<size_t>(M.N / kTileRows) * kRowDoneStride * sizeof(unsigned int), st) !=
+          cudaSuccess)
+        return check_cuda("cudaMemsetAsync(row counters)");
+      *clean_epochs[j] = epoch;
+    }
+  }
+  int rc = n > 1 ? launch_gemv1_batch(n, mats, xs, x_is_half, partials, ys, error_word(), st) : kErrTooLarge;
+  if (rc != kErrTooLarge) return rc;
+  for (int j = 0; j < n; ++j)   // not one launch: one by one
+    if ((rc = launch_gemv1(*mats[j], xs[j], x_is_half, partials[j], ys[j], error_word(), st))) return rc;
+  return kOk;
+}
+
 // ---------------------------------------------------------------------------------- product without any allocation
 //
 // Scratch for the split-K partial sums of lw_linear_static, built into the library image: every GPU that loads the

@@ -55,6 +55,11 @@ int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, 
 size_t gemv_partial_floats(const MatDev& M, int m);
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
                 size_t partial_capacity, cudaStream_t st, unsigned int* clean_epoch = nullptr);
+// n one-row products y_j = W_j x_j (each with its own scratch of gemv_partial_floats(M_j, 1) floats); in one launch
+// where the matrices share a format and decode plan, one by one otherwise.
+int launch_gemv_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* ys,
+                      float* const* partials, cudaStream_t st, unsigned int* const* clean_epochs);
+
 // Reads (and optionally clears) the device error word that kernels set when a bounded wait gives up.
 int read_kernel_error(unsigned int* value, bool clear);
 

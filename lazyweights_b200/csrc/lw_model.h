@@ -75,6 +75,9 @@ int cuda_fail(const char* what, cudaError_t e);
 // fused; 2: always decode + GEMM.
 int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float* y, int ldy, cudaStream_t st,
                   int path = 0);
+// n one-row products of matrices of this handle (indices into M->mats) against fp32 activations, in one launch where
+// they share format and decode plan (see launch_gemv_batch).
+int linear_batch_device(Model* M, int n, const int* mat_index, const float* const* xs, float* const* ys, cudaStream_t st);
 int runtime_init(Model* M, int max_ctx, int max_batch);
 // True if the calling thread's current device is the one the handle was opened on (kernels and scratch belong to it).
 int check_device(const Model* M);

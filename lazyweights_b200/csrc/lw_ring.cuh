@@ -80,10 +80,12 @@ __host__ __device__ constexpr size_t ring_fixed_bytes(int max_units) {
 // The share of one block: blocks b, b + nsets, ... serve the tile columns set, set + nsets, ... of the launch's rows.
 struct BlockShare {
   int set, bi, nb_set, ncol, ntiles, tmine, nmine;
-  __device__ __forceinline__ void init(const MatDev& M, const RingArgs& A, int split) {
-    set = blockIdx.x % A.nsets;
-    bi = blockIdx.x / A.nsets;
-    nb_set = (gridDim.x - set + A.nsets - 1) / A.nsets;               // blocks of this set
+  // bidx of nblocks: this block among the blocks that work on the matrix (the whole grid, or a part of it when one
+  // launch covers several matrices)
+  __device__ __forceinline__ void init(const MatDev& M, const RingArgs& A, int split, int bidx, int nblocks) {
+    set = bidx % A.nsets;
+    bi = bidx / A.nsets;
+    nb_set = (nblocks - set + A.nsets - 1) / A.nsets;                 // blocks of this set
     ncol = (M.KT - set + A.nsets - 1) / A.nsets;                      // tile columns of this set
     ntiles = A.ntr * ncol;                                            // tiles of this set
     tmine = bi < ntiles ? (ntiles - bi + nb_set - 1) / nb_set : 0;    // tiles of this block: bi + k nb_set

@@ -589,6 +589,11 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
     if (R->m_qkv[l] >= 0) {
       if ((rc = linear_device(M, M->mats[R->m_qkv[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st))) return rc;
+    } else if (m == 1) {   // one token: q, k and v read the same activations - one launch where their plans agree
+      const int idx[3] = {R->m_q[l], R->m_k[l], R->m_v[l]};
+      const float* xs[3] = {R->xn, R->xn, R->xn};
+      float* ys[3] = {R->qkv, R->qkv + R->H * R->Dh, R->qkv + (R->H + R->Hk) * R->Dh};
+      if ((rc = linear_batch_device(M, 3, idx, xs, ys, st))) return rc;
     } else {
       if ((rc = linear_device(M, M->mats[R->m_q[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st)) ||
           (rc = linear_device(M, M->mats[R->m_k[l]], R->xn, false, m, R->qkv + R->H * R->Dh, static_cast<int>(QKV), st)) ||
@@ -624,9 +629,15 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
         return rc;
     }
     launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
-    if ((rc = linear_device(M, M->mats[R->m_gate[l]], R->xn, false, m, R->g, R->I, st)) ||
-        (rc = linear_device(M, M->mats[R->m_up[l]], R->xn, false, m, R->u, R->I, st)))
+    if (m == 1) {          // one token: gate and up in one launch
+      const int idx[2] = {R->m_gate[l], R->m_up[l]};
+      const float* xs[2] = {R->xn, R->xn};
+      float* ys[2] = {R->g, R->u};
+      if ((rc = linear_batch_device(M, 2, idx, xs, ys, st))) return rc;
+    } else if ((rc = linear_device(M, M->mats[R->m_gate[l]], R->xn, false, m, R->g, R->I, st)) ||
+               (rc = linear_device(M, M->mats[R->m_up[l]], R->xn, false, m, R->u, R->I, st))) {
       return rc;
+    }
     const size_t ng = static_cast<size_t>(m) * R->I;
     launch_dep(k_silu_mul, dim3(static_cast<unsigned>((ng + 255) / 256)), dim3(256), st, R->g, R->u, ng);
     if ((rc = linear_device(M, M->mats[R->m_down[l]], R->g, false, m, R->o, R->D, st))) return rc;

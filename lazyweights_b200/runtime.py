@@ -170,6 +170,37 @@ class _Handle:
         return nat.lib().lw_kernel_error()
 
 
+class ProductBatch:
+    """A fixed list of one-row products y_j = W_j x_j prepared once and launched together (lw_linear_batch): up to
+    eight products per kernel launch where the matrices share format and decode plan.  entries: (handle, matrix
+    name, x CUDA tensor [K], y CUDA fp32 tensor [N]); all x of one dtype (fp16 or fp32).  The tensors are kept alive."""
+
+    def __init__(self, entries):
+        torch = _torch()
+        self._keep = list(entries)
+        n = len(self._keep)
+        if n == 0:
+            raise ValueError("empty batch")
+        half = self._keep[0][2].dtype == torch.float16
+        self._n, self._half = n, int(half)
+        self._handles = (C.c_void_p * n)()
+        self._ids = (C.c_int * n)()
+        self._xs = (C.c_void_p * n)()
+        self._ys = (C.c_void_p * n)()
+        for j, (h, name, x, y) in enumerate(self._keep):
+            inf = h.info(name)
+            if not (x.is_cuda and y.is_cuda and x.is_contiguous() and y.is_contiguous() and y.dtype == torch.float32 and
+                    x.numel() == inf["K"] and y.numel() == inf["N"] and (x.dtype == torch.float16) == half and
+                    x.dtype in (torch.float16, torch.float32)):
+                raise ValueError("entry %d: wrong shape, dtype or device" % j)
+            self._handles[j], self._ids[j] = h._h.value, h.matrix_id(name)
+            self._xs[j], self._ys[j] = x.data_ptr(), y.data_ptr()
+
+    def launch(self):
+        st = _torch().cuda.current_stream().cuda_stream
+        nat.check(nat.lib().lw_linear_batch(self._n, self._handles, self._ids, self._xs, self._half, self._ys, C.c_void_p(st)))
+
+
 class Bundle(_Handle):
     """A bundle directory opened on the current CUDA device."""
 

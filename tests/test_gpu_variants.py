@@ -97,3 +97,52 @@ def test_limit_register_decoder_equals_table_decoder(lw, tmp_path):
         w = orc.dequant(ty, q, side)
         x = rng.standard_normal(int(k)).astype(np.float32)
         assert helpers.rel_err(outs["limit"][key], orc.gemv_f64(w, x[None])[0]) <= helpers.GEMV_TOL
+
+
+def test_batched_launch_equals_single_products(lw, tmp_path):
+    """lw_linear_batch: several products in one launch (same format and plan), mixed formats (launched one by one),
+    several matrices of one handle; results equal the single-product entry point's bit for bit."""
+    import torch
+    rng = np.random.default_rng(8)
+    mats, entries, want = [], [], []
+    for j, (ty, n, k) in enumerate([("Q6_K", 1024, 1024), ("Q6_K", 512, 1024), ("Q6_K", 2048, 512), ("Q6_K", 64, 256),
+                                    ("Q4_K", 512, 2048), ("Q4_K", 256, 1024)]):
+        q, side = orc.synth_codes(ty, n, k, rng), orc.synth_side(ty, n, k, rng)
+        sym = orc.symbols_of(ty, q)
+        blob, _, _ = lw.bundle.encode_huf8(sym)
+        m = lw.CodedMatrix(blob, n, sym.shape[1], ty, side)
+        x = torch.from_numpy(rng.standard_normal(k).astype(np.float16)).cuda()
+        y = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+        mats.append(m)
+        entries.append((m, "m", x, y))
+        want.append(m.linear("m", x).cpu().numpy())
+        assert helpers.rel_err(want[-1], orc.gemv_f64(orc.dequant(ty, q, side), x.cpu().numpy().astype(np.float32)[None])[0]) <= helpers.GEMV_TOL
+    before = lw.lib().lw_launch_count()
+    batch = lw.ProductBatch(entries)
+    batch.launch()
+    launches = lw.lib().lw_launch_count() - before
+    assert launches < len(entries)                                      # the like matrices went out together
+    for (m, _, _, y), w in zip(entries, want):
+        assert np.array_equal(y.cpu().numpy(), w)
+    for _, _, _, y in entries:
+        y.fill_(float("nan"))
+    batch.launch()                                                      # again: counters and scratch are left clean
+    for (m, _, _, y), w in zip(entries, want):
+        assert np.array_equal(y.cpu().numpy(), w)
+    for m in mats:
+        m.close()
+    # several matrices of ONE handle share its scratch
+    wr = lw.bundle.Writer(str(tmp_path / "b"))
+    cases = {}
+    for i in range(3):
+        q, side = orc.synth_codes("Q5_K", 256, 1024, rng), orc.synth_side("Q5_K", 256, 1024, rng)
+        wr.add_kquant("l%d.up" % i, "Q5_K", q, side)
+        cases["l%d.up" % i] = (q, side)
+    wr.close()
+    with lw.Bundle(str(tmp_path / "b")) as b:
+        x = torch.from_numpy(rng.standard_normal(1024).astype(np.float32)).cuda()
+        ys = [torch.empty(256, dtype=torch.float32, device="cuda") for _ in cases]
+        lw.ProductBatch([(b, name, x, y) for name, y in zip(cases, ys)]).launch()
+        for (name, (q, side)), y in zip(cases.items(), ys):
+            assert np.array_equal(y.cpu().numpy(), b.linear(name, x).cpu().numpy())
+            assert helpers.rel_err(y.cpu().numpy(), orc.gemv_f64(orc.dequant("Q5_K", q, side), x.cpu().numpy()[None])[0]) <= helpers.GEMV_TOL
