@@ -47,7 +47,8 @@ void* rt_open(const char* dir, int max_ctx, int max_batch, long long budget_mb, 
 void rt_close(void* handle);
 
 /* Y[m, N] = X[m, K] . dequant(W)^T with host fp32 buffers; path 0 auto, 1 fused decode+product per chunk of up to
- * eight rows, 2 decode to fp16 weights then GEMM.  Returns -1 if the matrix is unknown.
+ * eight rows, 2 decode to fp16 weights then GEMM (the reference's paths), 3 (addition) the decode + tcgen05 GEMM for
+ * up to 64 rows.  Returns -1 if the matrix is unknown.
  * Replaces rt_test_matmul, kernels/llmrt.cu:2441. */
 int rt_test_matmul(void* handle, const char* name, const float* X, int m, float* Y, int path);
 

@@ -198,7 +198,10 @@ static int load_matrix(Matrix& mx, const uint8_t* blob, size_t nbytes, const uin
 static int finish_model(Model* M) {
   size_t need = 0;
   for (auto& m : M->mats) {
-    if (m.fmt != kFmtNone && m.dev.group) need = std::max(need, gemv_partial_floats(m.dev, 8));
+    if (m.fmt != kFmtNone && m.dev.group) {
+      need = std::max(need, gemv_partial_floats(m.dev, 8));
+      if (m.K % 512 == 0) need = std::max(need, gemm_t5_plane_floats(m.dev, 64));   // planes of the tcgen05 path
+    }
     M->resident_bytes += m.device_bytes;
     M->coded_bytes += m.blob_bytes;
     M->side_bytes += m.side_bytes;
@@ -300,9 +303,13 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
     set_error("%s has no side tensor: products need a block format", mx.name.c_str());
     return kErrArg;
   }
-  // measured on B200 (Q6_K 14336 x 4096): fused pass of eight rows 77 us, decode + split-K GEMM 165 us for 33 rows
-  // and 175 us for 64 (Q4_K 4096 x 4096: 21 us per pass, 70 us), so up to 16 rows go through the fused kernel in
-  // chunks of eight
+  // path 0: up to eight rows the fused decode + product kernels; 9 .. 64 rows the decode + tcgen05 GEMM (decoded weights
+  // go to tensor memory, never to DRAM); more rows, or shapes that kernel does not take, decode to fp16 weights in DRAM
+  // and a tensor-core GEMM over them (the decode is paid once however many rows follow).  path 3 forces the tcgen05 kernel.
+  if (path == 3 || (path == 0 && m > 8 && m <= 64)) {
+    const int rc = launch_gemm_coded(mx.dev, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, st);
+    if (rc != kErrTooLarge || path == 3) return rc;
+  }
   if (path == 2 || (path == 0 && m > 16)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);
   const size_t xe = x_half ? 2 : 4;
   for (int r0 = 0; r0 < m; r0 += 8) {
@@ -681,7 +688,7 @@ int rt_test_matmul(void* handle, const char* name, const float* X, int m, float*
   const int id = matrix_id(M, name);
   if (id < 0) return -1;
   Matrix& mx = M->mats[id];
-  if (!X || !Y || m < 1 || path < 0 || path > 2) {
+  if (!X || !Y || m < 1 || path < 0 || path > 3) {
     set_error("rt_test_matmul: bad argument");
     return kErrArg;
   }

@@ -21,11 +21,26 @@
 
 namespace lw {
 
+// Multiply-accumulate of one decoded table entry with its activation word.  Paired formats: dp2a (two int16
+// activations x the entry's two signed bytes).  Unpaired formats: one 32-bit multiply-add (the FMA pipe, which this
+// kernel leaves mostly idle, instead of the half-rate integer pipe that bounds it): the entry carries its grid value
+// sign-extended over bits 0-27 and the code length above, the activation is a sign-extended int16, so the low 28 bits of
+// the running sum are exact (|sum| < 2^26 over a sub-block) whatever the length bits add on top; mac_result drops them.
+template <bool PAIR>
+__device__ __forceinline__ int mac(uint32_t xw, uint32_t e, int acc) {
+  if (PAIR) return __dp2a_lo(static_cast<int>(xw), static_cast<int>(e), acc);
+  return static_cast<int>(xw) * static_cast<int>(e) + acc;
+}
+template <bool PAIR>
+__device__ __forceinline__ int mac_result(int acc) {
+  return PAIR ? acc : static_cast<int>(static_cast<uint32_t>(acc) << 4) >> 4;
+}
+
 // One sub-block (SPG symbols) of both chains: acc_a / acc_b += sum x16 * v (exact, int32).  xq points at the
 // sub-block's activation words (one per symbol: the int16 pair of a paired symbol's two weights, or one int16 in the
 // low half).  `first` = index of the sub-block's first symbol within its quad (fixes the phase of the groups); `last`:
 // the quad ends with this sub-block.
-template <int G, int SPG, uint32_t MASK>
+template <int G, int SPG, uint32_t MASK, bool PAIR>
 __device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const uint8_t* tab, uint32_t lane_off,
                                           const uint32_t* xq, const int first, const bool last, int& acc_a,
                                           int& acc_b) {
@@ -40,8 +55,8 @@ __device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const 
     const uint32_t ea = ca.template sym<MASK>(tab, lane_off), eb = cb.template sym<MASK>(tab, lane_off);
     if (c % 4 == 0) x = *reinterpret_cast<const uint4*>(xq + c);
     const uint32_t xw = c % 4 == 0 ? x.x : c % 4 == 1 ? x.y : c % 4 == 2 ? x.z : x.w;
-    acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
-    acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
+    acc_a = mac<PAIR>(xw, ea, acc_a);
+    acc_b = mac<PAIR>(xw, eb, acc_b);
     if (f % G == G - 1 || (last && c == SPG - 1)) {
       ca.end();
       cb.end();
@@ -49,15 +64,15 @@ __device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const 
   }
 }
 
-template <int SPG>
+template <int SPG, bool PAIR>
 __device__ __forceinline__ void sub_block_slow(GroupChain& ca, GroupChain& cb, const uint32_t* tab32, uint32_t pad,
                                                const uint32_t* xq, int& acc_a, int& acc_b) {
 #pragma unroll 2
   for (int c = 0; c < SPG; ++c) {
     const uint32_t ea = ca.slow_sym(tab32, pad), eb = cb.slow_sym(tab32, pad);
     const uint32_t xw = xq[c];
-    acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
-    acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
+    acc_a = mac<PAIR>(xw, ea, acc_a);
+    acc_b = mac<PAIR>(xw, eb, acc_b);
   }
 }
 
@@ -95,7 +110,7 @@ __device__ __forceinline__ uint32_t sym_limit(GroupChain& ch, const uint8_t* cta
   return *reinterpret_cast<const uint32_t*>(ctab + (((idx & 255u) << 7) | lane4));
 }
 
-template <int G, int SPG, int PAD>
+template <int G, int SPG, int PAD, bool PAIR>
 __device__ __forceinline__ void sub_block_limit(GroupChain& ca, GroupChain& cb, const uint8_t* ctab, uint32_t lane4,
                                                 const uint32_t (&lim)[10], const uint32_t* xq, const int first,
                                                 const bool last, int& acc_a, int& acc_b) {
@@ -110,8 +125,8 @@ __device__ __forceinline__ void sub_block_limit(GroupChain& ca, GroupChain& cb, 
     const uint32_t ea = sym_limit<PAD>(ca, ctab, lane4, lim), eb = sym_limit<PAD>(cb, ctab, lane4, lim);
     if (c % 4 == 0) x = *reinterpret_cast<const uint4*>(xq + c);
     const uint32_t xw = c % 4 == 0 ? x.x : c % 4 == 1 ? x.y : c % 4 == 2 ? x.z : x.w;
-    acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
-    acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
+    acc_a = mac<PAIR>(xw, ea, acc_a);
+    acc_b = mac<PAIR>(xw, eb, acc_b);
     if (f % G == G - 1 || (last && c == SPG - 1)) {
       ca.end();
       cb.end();
@@ -138,6 +153,7 @@ __device__ __forceinline__ void sub_block_fixed(const uint32_t* wa, const uint32
 #pragma unroll
   for (int c = 0; c < SPG; ++c) {
     constexpr uint32_t mask = (1u << B) - 1u;
+    constexpr bool PAIR = is_paired(FMT);
     const int i = c * B / 32, s = c * B % 32;
     uint32_t va = s + B <= 32 ? a[i] >> s : __funnelshift_r(a[i], a[i + 1], s);
     uint32_t vb = s + B <= 32 ? b[i] >> s : __funnelshift_r(b[i], b[i + 1], s);
@@ -146,16 +162,16 @@ __device__ __forceinline__ void sub_block_fixed(const uint32_t* wa, const uint32
       ea = *reinterpret_cast<const uint32_t*>(vtab + (((va & mask) << 7) | lane4));
       eb = *reinterpret_cast<const uint32_t*>(vtab + (((vb & mask) << 7) | lane4));
     } else if (FMT == kFmtQ6K) {
-      ea = static_cast<uint32_t>(static_cast<int>(va << (32 - B)) >> (32 - B)) & 255u;
-      eb = static_cast<uint32_t>(static_cast<int>(vb << (32 - B)) >> (32 - B)) & 255u;
+      ea = static_cast<uint32_t>(static_cast<int>(va << (32 - B)) >> (32 - B));
+      eb = static_cast<uint32_t>(static_cast<int>(vb << (32 - B)) >> (32 - B));
     } else {
       ea = va & mask;
       eb = vb & mask;
     }
     if (c % 4 == 0) x = *reinterpret_cast<const uint4*>(xq + c);
     const uint32_t xw = c % 4 == 0 ? x.x : c % 4 == 1 ? x.y : c % 4 == 2 ? x.z : x.w;
-    acc_a = __dp2a_lo(static_cast<int>(xw), static_cast<int>(ea), acc_a);
-    acc_b = __dp2a_lo(static_cast<int>(xw), static_cast<int>(eb), acc_b);
+    acc_a = mac<PAIR>(xw, ea, acc_a);
+    acc_b = mac<PAIR>(xw, eb, acc_b);
   }
 }
 
@@ -352,7 +368,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
           const int qn = __shfl_down_sync(0xffffffffu, q, 1);
           if ((lane & 1) == 0) xq[i >> 1] = (static_cast<uint32_t>(q) & 0xFFFFu) | (static_cast<uint32_t>(qn) << 16);
         } else {
-          xq[i] = static_cast<uint32_t>(q) & 0xFFFFu;
+          xq[i] = static_cast<uint32_t>(q);   // sign-extended: the operand of a 32-bit multiply-add
         }
         if ((lane & (GW - 1)) == 0) {
           xscale[i / GW] = amax * (1.f / 32767.f);
@@ -418,7 +434,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
       if (jj == 0) count();
       if (jj == 2) resolve();
       const float xsc = xst[jj];
-      const float fa = static_cast<float>(acc_a) * xsc, fb = static_cast<float>(acc_b) * xsc;
+      const float fa = static_cast<float>(mac_result<PAIR>(acc_a)) * xsc, fb = static_cast<float>(mac_result<PAIR>(acc_b)) * xsc;
       if (HAS_OFFSET) {
         const float gx = xgt[jj];
         tot_a += s_a * fa - o_a * gx;
@@ -445,10 +461,10 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
       for (int jj = 0; jj < 4; ++jj) {
         int acc_a = 0, acc_b = 0;
         if (cls == 0)
-          sub_block_limit<G, SPG, LOG_R + 2>(ca, cb, smem, static_cast<uint32_t>(lane) << 2, lim, xt + jj * SPG,
+          sub_block_limit<G, SPG, LOG_R + 2, PAIR>(ca, cb, smem, static_cast<uint32_t>(lane) << 2, lim, xt + jj * SPG,
                                              jj * SPG, jj == 3, acc_a, acc_b);
         else   // units where groups of G symbols are not exact: groups of two, exact for any data
-          sub_block_limit<2, SPG, LOG_R + 2>(ca, cb, smem, static_cast<uint32_t>(lane) << 2, lim, xt + jj * SPG,
+          sub_block_limit<2, SPG, LOG_R + 2, PAIR>(ca, cb, smem, static_cast<uint32_t>(lane) << 2, lim, xt + jj * SPG,
                                              jj * SPG, jj == 3, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
@@ -456,7 +472,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         int acc_a = 0, acc_b = 0;
-        sub_block<G, SPG, MASK>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+        sub_block<G, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
     } else {
@@ -464,9 +480,9 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
       for (int jj = 0; jj < 4; ++jj) {
         int acc_a = 0, acc_b = 0;
         if (cls == 1)
-          sub_block<2, SPG, MASK>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+          sub_block<2, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
         else
-          sub_block_slow<SPG>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG, acc_a, acc_b);
+          sub_block_slow<SPG, PAIR>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
     }

@@ -22,6 +22,12 @@ size_t gemvm_partial_floats(const MatDev& M, int m);
 int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* partials, unsigned int* err,
                  cudaStream_t st);
 
+// Decode + tcgen05 GEMM for up to 64 rows (lw_gemm_t5.cuh): planes[K / 512][m][N] of partial products, *terms = K / 512,
+// to be added by the caller; kErrTooLarge (nothing launched) where this kernel cannot take the product.
+size_t gemm_t5_plane_floats(const MatDev& M, int m);
+int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
+                   int* terms);
+
 // fp16 weights of tile rows tr0 .. tr1 - 1 on the batch-1 kernel's decoder (lw_decw.cuh); kErrTooLarge (nothing
 // launched) where it cannot take the matrix.
 int launch_decw(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st);

@@ -177,35 +177,23 @@ static float grid_of(int fmt, int q) {
   return static_cast<float>(q) - (fmt == kFmtQ6K ? 32.f : 0.f);
 }
 
-// 32-bit decode table of the batch-1 kernel: bits 28-31 = code length (recovered by one multiply-high); byte 0 =
-// the grid value of the symbol (of its low nibble for paired formats) as a signed 8-bit integer, byte 1 = the grid
-// value of the high nibble (0 for unpaired formats).  The two bytes are the multiplier operand of a dp2a instruction.
-static uint32_t value_bytes(int fmt, uint32_t sym);
-
-void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]) {
-  for (int i = 0; i < kLutSize; ++i) {
-    const uint32_t sym = t.lut[i] & 255u, len = t.lut[i] >> 8;
-    uint32_t e = len << 28;
-    if (is_paired(fmt)) {
-      const int v0 = static_cast<int>(grid_of(fmt, sym & 15)), v1 = static_cast<int>(grid_of(fmt, sym >> 4));
-      e |= (static_cast<uint32_t>(v0) & 255u) | ((static_cast<uint32_t>(v1) & 255u) << 8);
-    } else if (fmt == kFmtQ5K || fmt == kFmtQ6K) {
-      e |= static_cast<uint32_t>(static_cast<int>(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)))) & 255u;
-    } else {
-      e |= sym;
-    }
-    out[i] = e;
-  }
-}
-
+// 32-bit decode table of the fused kernels: bits 28-31 = code length (recovered by one multiply-high).  Paired
+// formats: byte 0 = the grid value of the low nibble as a signed 8-bit integer, byte 1 = that of the high nibble - the
+// multiplier operand of a dp2a instruction.  Unpaired formats: the grid value sign-extended over bits 0-27, so that a
+// plain 32-bit multiply-add with the activation accumulates the exact sum in its low 28 bits (the length field only
+// disturbs bits 28-31) and byte 0 is still the signed 8-bit value.
 static uint32_t value_bytes(int fmt, uint32_t sym) {
   if (is_paired(fmt)) {
     const int v0 = static_cast<int>(grid_of(fmt, sym & 15)), v1 = static_cast<int>(grid_of(fmt, sym >> 4));
     return (static_cast<uint32_t>(v0) & 255u) | ((static_cast<uint32_t>(v1) & 255u) << 8);
   }
-  if (fmt == kFmtQ5K || fmt == kFmtQ6K)
-    return static_cast<uint32_t>(static_cast<int>(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)))) & 255u;
+  if (fmt == kFmtQ5K || fmt == kFmtQ6K)   // one grid value, sign-extended over the 28 bits below the length field
+    return static_cast<uint32_t>(static_cast<int>(grid_of(fmt, sym & (fmt == kFmtQ6K ? 63 : 31)))) & 0x0FFFFFFFu;
   return sym;
+}
+
+void fat_table(const HuffTable& t, int fmt, uint32_t out[kLutSize]) {
+  for (int i = 0; i < kLutSize; ++i) out[i] = (static_cast<uint32_t>(t.lut[i] >> 8) << 28) | value_bytes(fmt, t.lut[i] & 255u);
 }
 
 void comparator_table(const HuffTable& t, int fmt, uint32_t out[kCmpTabWords]) {

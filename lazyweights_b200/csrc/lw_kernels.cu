@@ -373,6 +373,17 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
   return check_launch("k_sum_partials");
 }
 
+// Y[m, N] = X . W^T for up to 64 rows on the tcgen05 path: planes of partial products, then their ordered sum.
+int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
+                      size_t scratch_floats, cudaStream_t st) {
+  if (!gemv1_usable(M) || M.K % 512 || scratch_floats < gemm_t5_plane_floats(M, m)) return kErrTooLarge;
+  int terms = 0;
+  const int rc = launch_gemm_t5(M, X, x_is_half, m, scratch, error_word(), st, &terms);
+  if (rc) return rc;
+  k_sum_partials<<<(m * (M.N / 4) + 127) / 128, 128, 0, st>>>(scratch, Y, m, M.N, ldy, terms);
+  return check_launch("k_sum_partials");
+}
+
 int launch_gemv_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* ys,
                       float* const* partials, cudaStream_t st, unsigned int* const* clean_epochs) {
   const unsigned int epoch = g_error_epoch.load();

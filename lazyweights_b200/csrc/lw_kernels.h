@@ -55,6 +55,12 @@ int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, 
 size_t gemv_partial_floats(const MatDev& M, int m);
 int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* partials,
                 size_t partial_capacity, cudaStream_t st, unsigned int* clean_epoch = nullptr);
+// Y[m, N] = X[m, K] . W^T for 1 <= m <= 64 with the decode + tcgen05 kernel (lw_gemm_t5.cuh): the decoded weights go
+// from registers to tensor memory, never to DRAM.  `scratch` holds the K / 512 planes of partial products.  Returns
+// kErrTooLarge, with nothing launched, where that kernel cannot take the product.
+int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
+                      size_t scratch_floats, cudaStream_t st);
+
 // n one-row products y_j = W_j x_j (each with its own scratch of gemv_partial_floats(M_j, 1) floats); in one launch
 // where the matrices share a format and decode plan, one by one otherwise.
 int launch_gemv_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* ys,

@@ -146,3 +146,30 @@ def test_batched_launch_equals_single_products(lw, tmp_path):
         for (name, (q, side)), y in zip(cases.items(), ys):
             assert np.array_equal(y.cpu().numpy(), b.linear(name, x).cpu().numpy())
             assert helpers.rel_err(y.cpu().numpy(), orc.gemv_f64(orc.dequant("Q5_K", q, side), x.cpu().numpy()[None])[0]) <= helpers.GEMV_TOL
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q6_K", 512, 1024), ("Q4_K", 256, 2048), ("Q5_K", 256, 1024), ("IQ4_XS", 512, 1536),
+                                     ("Q6_K", 1792, 512)])
+def test_tensor_memory_gemm_path(lw, tmp_path, ty, n, k):
+    """The decode + tcgen05 GEMM (decoded weights go from registers to tensor memory): every row count class from one
+    row to 64, through the host-buffer entry point with path 3 and, for 9..64 rows, as the default path."""
+    rng = np.random.default_rng(n + k)
+    q, side = orc.synth_codes(ty, n, k, rng), orc.synth_side(ty, n, k, rng)
+    hi = 15 if ty in ("Q4_K", "IQ4_XS") else (31 if ty == "Q5_K" else 63)
+    q[:64, :128] = rng.integers(0, hi + 1, (64, 128))                   # a unit of rare codes: the fallback classes
+    w = orc.dequant(ty, q, side)
+    wr = lw.bundle.Writer(str(tmp_path / "b"))
+    wr.add_kquant("l0.up", ty, q, side)
+    wr.close()
+    with lw.Bundle(str(tmp_path / "b")) as b:
+        for m in (1, 9, 16, 17, 33, 48, 64):
+            X = rng.standard_normal((m, k)).astype(np.float32)
+            ref = orc.gemv_f64(w, X)
+            got = b.matmul("l0.up", X, 3)
+            assert helpers.rel_err(got, ref) <= helpers.GEMV_TOL, (ty, m)
+            if m > 8:
+                before = lw.lib().lw_launch_count()
+                auto = b.matmul("l0.up", X, 0)
+                assert np.array_equal(auto, got)                        # the default path for 9 .. 64 rows is this kernel
+                assert lw.lib().lw_launch_count() - before == 2         # the GEMM and the sum of its planes
+        assert b.kernel_error() == 0
