@@ -45,7 +45,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Host-side result of validating, indexing and re-laying out one blob: everything that goes to the device.
 struct HostImage {
   std::vector<uint16_t> lut;
-  std::vector<uint32_t> fat, cmp, group_base, words;
+  std::vector<uint32_t> fat, symtab, cmp, group_base, words;
   std::vector<uint8_t> unit_slow;
   int KT = 0, T = 0, split = 1, pad = 0, max_len = 0, group = 0, index_bits = 0;
   double slow_fraction = 0.0;
@@ -74,6 +74,8 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   std::vector<uint32_t> chain_start, lane_end;
   im.fat.resize(kLutSize);
   fat_table(*tab, mx.fmt, im.fat.data());
+  im.symtab.resize(kLutSize);
+  fat_table(*tab, kFmtNone, im.symtab.data());   // length << 28 | symbol
   im.cmp.resize(kCmpTabWords);
   comparator_table(*tab, mx.fmt, im.cmp.data());
   GroupScan scan;
@@ -140,7 +142,8 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   const int rc_side = check_side(mx, side, side_nbytes);
   if (rc_side) return rc_side;
   const size_t off_fat = align_up(2 * kLutSize, 256);
-  const size_t off_cmp = align_up(off_fat + 4 * kLutSize, 256);
+  const size_t off_sym = align_up(off_fat + 4 * kLutSize, 256);
+  const size_t off_cmp = align_up(off_sym + 4 * kLutSize, 256);
   const size_t off_gb = align_up(off_cmp + 4 * kCmpTabWords, 256);
   const size_t off_words = align_up(off_gb + im.group_base.size() * 4, 256);
   const size_t off_side = align_up(off_words + im.words.size() * 4, 256);
@@ -152,6 +155,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   uint8_t* d = static_cast<uint8_t*>(mx.d_block);
   if ((e = cudaMemcpy(d, im.lut.data(), 2 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_fat, im.fat.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_sym, im.symtab.data(), 4 * kLutSize, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_cmp, im.cmp.data(), 4 * kCmpTabWords, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_gb, im.group_base.data(), im.group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
       (e = cudaMemcpy(d + off_words, im.words.data(), im.words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
@@ -165,6 +169,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   mx.slow_fraction = im.slow_fraction;
   mx.dev.lut = reinterpret_cast<const uint16_t*>(d);
   mx.dev.tab32 = reinterpret_cast<const uint32_t*>(d + off_fat);
+  mx.dev.symtab32 = reinterpret_cast<const uint32_t*>(d + off_sym);
   mx.dev.cmp_tab = reinterpret_cast<const uint32_t*>(d + off_cmp);
   mx.dev.reader = 0;
   mx.dev.pad = im.pad;
@@ -306,7 +311,7 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   // path 0: up to eight rows the fused decode + product kernels; 9 .. 64 rows the decode + tcgen05 GEMM (decoded weights
   // go to tensor memory, never to DRAM); more rows, or shapes that kernel does not take, decode to fp16 weights in DRAM
   // and a tensor-core GEMM over them (the decode is paid once however many rows follow).  path 3 forces the tcgen05 kernel.
-  if (path == 3 || (path == 0 && m > 8 && m <= 64)) {
+  if (path == 3 || (path == 0 && m >= debug_knobs().t5_min_rows && m <= 64)) {
     const int rc = launch_gemm_coded(mx.dev, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, st);
     if (rc != kErrTooLarge || path == 3) return rc;
   }
@@ -371,6 +376,7 @@ int lw_debug_set(const char* key, long long value) {
   if (s == "max_units" && value >= 2 && value <= 1024) k.max_units = static_cast<int>(value) & ~1;
   else if (s == "wait_limit" && value >= 1 && value <= (1ll << 30)) k.wait_limit = static_cast<uint32_t>(value);
   else if (s == "drop_unit" && value >= -1 && value < 1024) k.drop_unit = static_cast<int>(value);
+  else if (s == "t5_min_rows" && value >= 1 && value <= 65) k.t5_min_rows = static_cast<int>(value);
   else if (s == "reset") k = DebugKnobs();
   else {
     set_error("lw_debug_set: unknown key or value out of range (%s)", key);
@@ -624,6 +630,7 @@ int lw_matrix_make_twin(void* handle, int id) {
   mx->twin.reader = 1;
   mx->twin.tab32 = reinterpret_cast<const uint32_t*>(d);
   mx->twin.cmp_tab = nullptr;
+  mx->twin.symtab32 = nullptr;
   mx->twin.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
   mx->twin.words = reinterpret_cast<const uint32_t*>(d + off_words);
   mx->twin.unit_slow = d + off_cls;

@@ -1,0 +1,137 @@
+// Decode to codes with the batch-1 kernel's decoder (lw_ring.cuh: replicated 32-bit table, grouped refills chosen from
+// the data, producer warps feeding a ring of staging buffers): the role of k_decode_hufi, kernels/llmrt.cu:767-806.
+// The table here maps a window to the SYMBOL itself (length << 28 | symbol; lw::MatDev::symtab32), not to grid values.
+// A lane writes the symbols of its two rows 32 bytes at a time: 32 symbols, or 16 paired symbols expanded to one 4-bit
+// code per byte (low nibble first, kernels/llmrt.cu:798-800).  Included by lw_decc.cu.
+#pragma once
+#include "lw_ring.cuh"
+
+namespace lw {
+
+struct DeccArgs {
+  RingArgs r;
+  uint8_t* out;      // [N][row_bytes]
+  int row_bytes;     // Ks, or 2 Ks when paired symbols are expanded
+};
+
+struct BytePack {
+  uint32_t w[8];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = 0u;
+  }
+  __device__ __forceinline__ void flush(uint8_t* dst) const {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+  }
+};
+
+template <int FMT, int G, int IDXBITS, int LOG_R, bool EXPAND>
+__global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_constant__ MatDev M, const __grid_constant__ DeccArgs A) {
+  const RingArgs& RA = A.r;
+  constexpr int SPLIT = default_split(FMT);
+  constexpr int USYM = kTileSyms / SPLIT;                          // symbols per chain
+  constexpr int PER = EXPAND ? 16 : 32;                            // symbols per 32-byte store
+  constexpr int OUT_PER_SYM = EXPAND ? 2 : 1;
+  static_assert(!EXPAND || is_paired(FMT), "only paired symbols expand");
+  constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
+  constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
+  constexpr int kReplicatedTableBytes = NIDX * R * 4;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
+  uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);
+  RingMem RM;
+  RM.carve(tab1 + kLutSize, RA);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  BlockShare S;
+  S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);
+  const int nmine = S.nmine;
+  ring_reset(RM);
+  __syncthreads();
+  ring_build_list<SPLIT>(M, RA, S, RM);
+  __syncthreads();
+  if (warp >= RA.warps) {
+    ring_produce(M, RA, RM, nmine, warp - RA.warps, lane);
+    return;
+  }
+  // the symbol table, replicated like the value table of the other kernels
+  for (int i0 = warp * 32; i0 < NIDX; i0 += RA.warps * 32) table_spread<LOG_R>(tab, tab1, i0, __ldg(M.symtab32 + i0 + lane), lane);
+  for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += RA.warps * 32) tab1[idx] = __ldg(M.symtab32 + idx);
+  asm volatile("bar.sync 1, %0;" ::"r"(RA.warps * 32) : "memory");
+  const uint32_t lane_off = (lane & (R - 1)) << 2;
+  auto put = [&](BytePack& p, int c, uint32_t e) {   // symbol c of the current 32 bytes
+    const uint32_t sym = e & 255u;
+    if (EXPAND)
+      p.w[c / 2] |= ((sym & 15u) | ((sym >> 4) << 8)) << (16 * (c % 2));
+    else
+      p.w[c / 4] |= sym << (8 * (c % 4));
+  };
+#pragma unroll 1
+  for (;;) {
+    Unit u;
+    const int got = ring_draw(RA, RM, nmine, lane, u);
+    if (got == 0) break;
+    if (got < 0) return;
+    GroupChain ca, cb;
+    ca.init(u.buf + lane);
+    cb.init(u.buf + u.second * 32u + lane);
+    uint8_t* oa = A.out + (static_cast<size_t>(u.tr) * kTileRows + lane) * A.row_bytes +
+                  (static_cast<size_t>(u.j) * kTileSyms + u.seg * USYM) * OUT_PER_SYM;
+    uint8_t* ob = oa + static_cast<size_t>(32) * A.row_bytes;
+    if (u.cls == 0) {
+#pragma unroll
+      for (int c0 = 0; c0 < USYM; c0 += PER) {
+        BytePack pa, pb;
+        pa.clear();
+        pb.clear();
+#pragma unroll
+        for (int c = 0; c < PER; ++c) {
+          const int f = c0 + c;
+          if (f % G == 0) {
+            ca.begin();
+            cb.begin();
+          }
+          const uint32_t ea = ca.template sym<MASK>(smem, lane_off), eb = cb.template sym<MASK>(smem, lane_off);
+          if (f % G == G - 1 || f == USYM - 1) {
+            ca.end();
+            cb.end();
+          }
+          put(pa, c, ea);
+          put(pb, c, eb);
+        }
+        pa.flush(oa + c0 * OUT_PER_SYM);
+        pb.flush(ob + c0 * OUT_PER_SYM);
+      }
+    } else {
+#pragma unroll 1
+      for (int c0 = 0; c0 < USYM; c0 += PER) {
+        BytePack pa, pb;
+        pa.clear();
+        pb.clear();
+#pragma unroll
+        for (int c = 0; c < PER; ++c) {
+          uint32_t ea, eb;
+          if (u.cls == 2) {
+            ea = ca.slow_sym(tab1, static_cast<uint32_t>(M.pad));
+            eb = cb.slow_sym(tab1, static_cast<uint32_t>(M.pad));
+          } else {
+            ca.begin();
+            cb.begin();
+            ea = ca.template sym<MASK>(smem, lane_off);
+            eb = cb.template sym<MASK>(smem, lane_off);
+            ca.end();
+            cb.end();
+          }
+          put(pa, c, ea);
+          put(pb, c, eb);
+        }
+        pa.flush(oa + c0 * OUT_PER_SYM);
+        pb.flush(ob + c0 * OUT_PER_SYM);
+      }
+    }
+    ring_release(RM, u, lane);
+  }
+}
+
+}  // namespace lw

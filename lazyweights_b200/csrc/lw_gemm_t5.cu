@@ -9,7 +9,8 @@ namespace lw {
 
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kRingSlackWords = 96;
-constexpr int kT5MinSlots = 20;   // sixteen consumer warps hold a unit each; the rest is run-ahead of the copies
+constexpr int kT5LogCopies = 3;   // 8 copies of the decode table: 32 KB (1024 windows) or 64 KB (2048)
+constexpr int kT5MinSlots = 17;   // sixteen consumer warps hold a unit each; the rest is run-ahead of the copies
 
 struct T5Plan {
   int nsets, blocks, max_units, slots, ntok;
@@ -21,18 +22,28 @@ template <int FMT>
 static bool plan_t5(const MatDev& M, int m, T5Plan& p) {
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT), TU = kT5SetK / TW * SPLIT;
   const int NT = M.N / kTileRows;
-  if (m < 1 || m > kT5MaxTokens || NT % 4 || M.K % kT5SetK || !gemv1_usable(M) || M.reader != 0) return false;
+  if (m < 1 || m > kT5MaxTokens || NT % 4 || M.K % kT5SetK || !gemv1_usable(M) || M.reader != 0) {
+    set_kernel_error_text("gemm (tcgen05)", "needs 1..64 rows, tile rows in fours and K in 512s");
+    return false;
+  }
   p.ntok = (m + 15) / 16 * 16;
   p.nsets = M.K / kT5SetK;
   const int NRG = NT / 4;
   p.blocks = std::max(p.nsets, std::min(sm_count(), p.nsets * NRG));
   const int nb_min = p.blocks / p.nsets;                           // the smallest number of blocks a column set gets
   p.max_units = ((NRG + nb_min - 1) / nb_min) * TU * 4;
-  if (p.max_units > kRingMaxUnits) return false;
+  if (p.max_units > kRingMaxUnits) {
+    set_kernel_error_text("gemm (tcgen05)", "too many units per block");
+    return false;
+  }
   p.buf_words = (M.max_unit_words + 31u) & ~31u;
-  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 + static_cast<size_t>(p.ntok) * kT5SetK * 2 +
+  const size_t fixed = (size_t(1) << (M.index_bits + kT5LogCopies + 2)) + (M.index_bits < kMaxLen ? kLutSize * 4 : 0) +
+                       static_cast<size_t>(p.ntok) * kT5SetK * 2 +
                        (2 * kT5Teams * kT5ASlots + 4) * 8 + 16 + ring_fixed_bytes(p.max_units) + kRingSlackWords * 4;
-  if (fixed + static_cast<size_t>(p.buf_words) * 4 * kT5MinSlots > kSmemLimit) return false;
+  if (fixed + static_cast<size_t>(p.buf_words) * 4 * kT5MinSlots > kSmemLimit) {
+    set_kernel_error_text("gemm (tcgen05)", "not enough shared memory for the staging ring");
+    return false;
+  }
   p.slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed) / (p.buf_words * 4)));
   p.smem = fixed + static_cast<size_t>(p.slots) * p.buf_words * 4;
   return true;
@@ -43,7 +54,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float
                     int* terms) {
   T5Plan p;
   if (!plan_t5<FMT>(M, m, p)) return kErrTooLarge;
-  auto kernel = k_gemm_t5<FMT, G, IDXBITS, kRingLogCopies>;
+  auto kernel = k_gemm_t5<FMT, G, IDXBITS, kT5LogCopies>;
   static size_t configured_per_device[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -97,6 +108,7 @@ static int launch_g(const MatDev& M, const void* X, bool x_is_half, int m, float
       case 6: return launch_i<FMT, 6>(M, X, x_is_half, m, planes, err, st, terms);
     }
   }
+  set_kernel_error_text("gemm (tcgen05)", "no kernel for this group size");
   return kErrTooLarge;
 }
 
@@ -107,7 +119,10 @@ size_t gemm_t5_plane_floats(const MatDev& M, int m) { return static_cast<size_t>
 // too little shared memory left for the staging ring (the 2048-window table with many rows).
 int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
                    int* terms) {
-  if (!err || !planes || !terms) return kErrTooLarge;
+  if (!err || !planes || !terms) {
+    set_kernel_error_text("gemm (tcgen05)", "null argument");
+    return kErrTooLarge;
+  }
   switch (M.fmt) {
     case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, m, planes, err, st, terms);
     case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, m, planes, err, st, terms);

@@ -142,6 +142,8 @@ __device__ __forceinline__ bool t5_wait_warp(uint64_t* bar, uint32_t parity, con
   return __all_sync(0xffffffffu, t5_wait(bar, parity, A, abort_flag));
 }
 
+// LOG_R: copies of the decode table in THIS kernel (8: half of what the chains' leading zero bits allow, because the
+// activations need the shared memory; lw::kRingLogCopies - LOG_R = the extra shift of every lookup).
 template <int FMT, int G, int IDXBITS, int LOG_R>
 __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant__ MatDev M, const __grid_constant__ GemmT5Args A) {
   const RingArgs& RA = A.r;
@@ -157,11 +159,15 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
   static_assert(TU % kT5Teams == 0 && KU % 16 == 0 && GW % 16 == 0, "team-units are dealt evenly; steps stay inside a sub-block");
   constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
+  constexpr int RSHIFT = kRingLogCopies - LOG_R;
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
   extern __shared__ __align__(128) uint8_t smem[];
   uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);       // [2048] single copy
-  uint8_t* xs = reinterpret_cast<uint8_t*>(tab1 + kLutSize);                       // B operand: [ntok][512] fp16, canonical
+  // the single-copy table serves the units that hold an 11-bit code under a 1024-window table; with 2048 windows
+  // replicated there are no such units and no such table
+  constexpr bool SINGLE = IDXBITS < kMaxLen;
+  uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);       // [2048] single copy (if SINGLE)
+  uint8_t* xs = reinterpret_cast<uint8_t*>(tab1 + (SINGLE ? kLutSize : 0));        // B operand: [ntok][512] fp16, canonical
   const int ntok = A.ntok;
   uint64_t* a_full = reinterpret_cast<uint64_t*>(xs + static_cast<size_t>(ntok) * kT5SetK * 2);   // [teams][slots]
   uint64_t* a_empty = a_full + kT5Teams * kT5ASlots;
@@ -248,7 +254,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads xs through the async proxy
   }
-  if (warp < kT5Consumers) table_fill<IDXBITS, LOG_R>(M, tab, tab1, warp, lane, kT5Consumers);
+  if (warp < kT5Consumers) table_fill<IDXBITS, LOG_R, SINGLE>(M, tab, tab1, warp, lane, kT5Consumers);
   if (warp < kT5Consumers || warp == kT5Consumers + kT5Producers)
     asm volatile("bar.sync 1, %0;" ::"r"((kT5Consumers + 1) * 32) : "memory");
 
@@ -359,8 +365,8 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
                   ca.begin();
                   cb.begin();
                 }
-                ea = ca.template sym<MASK>(smem, lane_off);
-                eb = cb.template sym<MASK>(smem, lane_off);
+                ea = ca.template sym<MASK, RSHIFT>(smem, lane_off);
+                eb = cb.template sym<MASK, RSHIFT>(smem, lane_off);
                 if (f % G == G - 1 || f == STEPS * SYM16 - 1) {
                   ca.end();
                   cb.end();
@@ -368,8 +374,8 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
               } else if constexpr (CLS == 1) {
                 ca.begin();
                 cb.begin();
-                ea = ca.template sym<MASK>(smem, lane_off);
-                eb = cb.template sym<MASK>(smem, lane_off);
+                ea = ca.template sym<MASK, RSHIFT>(smem, lane_off);
+                eb = cb.template sym<MASK, RSHIFT>(smem, lane_off);
                 ca.end();
                 cb.end();
               } else {
@@ -404,8 +410,9 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
           }
           return true;
         };
-        ok = cls == 0 ? run_unit(std::integral_constant<int, 0>{})
-                      : cls == 1 ? run_unit(std::integral_constant<int, 1>{}) : run_unit(std::integral_constant<int, 2>{});
+        if (cls == 0) ok = run_unit(std::integral_constant<int, 0>{});
+        else if (cls == 1 || !SINGLE) ok = run_unit(std::integral_constant<int, 1>{});
+        else ok = run_unit(std::integral_constant<int, 2>{});
         if (!ok) break;
         // every lane has read its last word: hand the staging buffer back
         __syncwarp();

@@ -22,6 +22,10 @@ size_t gemvm_partial_floats(const MatDev& M, int m);
 int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* partials, unsigned int* err,
                  cudaStream_t st);
 
+// Symbols [N, Ks] (or, for paired formats with `expand`, codes [N, K]) on the batch-1 kernel's decoder (lw_decc.cuh);
+// kErrTooLarge (nothing launched) where it cannot take the matrix.
+int launch_decode_codes_ring(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st);
+
 // Decode + tcgen05 GEMM for up to 64 rows (lw_gemm_t5.cuh): planes[K / 512][m][N] of partial products, *terms = K / 512,
 // to be added by the caller; kErrTooLarge (nothing launched) where this kernel cannot take the product.
 size_t gemm_t5_plane_floats(const MatDev& M, int m);
@@ -37,6 +41,7 @@ struct DebugKnobs {
   int max_units = 1024;            // cap on the units a block is dealt per launch (smaller: more launches per product)
   uint32_t wait_limit = 1u << 22;  // polls after which a device-side wait gives up
   int drop_unit = -1;              // the producers of block 0 skip the copy of this unit (its consumer's wait runs out)
+  int t5_min_rows = 9;             // products of at least this many rows (and at most 64) take the tcgen05 kernel
 };
 DebugKnobs& debug_knobs();
 

@@ -271,6 +271,10 @@ int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaSt
     set_kernel_error_text("decode_codes", "the output must be 32-byte aligned");
     return kErrArg;
   }
+  if (gemv1_usable(M) && M.symtab32) {   // the shared decoder, where the layout allows
+    const int rc = launch_decode_codes_ring(M, out, expand_pairs, error_word(), st);
+    if (rc != kErrTooLarge) return rc;
+  }
   const size_t smem = 2 * kLutSize + 128 + kWarpsPerBlock * stage_bytes(M);
   const int blocks = (M.T + kWarpsPerBlock - 1) / kWarpsPerBlock;
   int rc;
@@ -376,7 +380,10 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
 // Y[m, N] = X . W^T for up to 64 rows on the tcgen05 path: planes of partial products, then their ordered sum.
 int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
                       size_t scratch_floats, cudaStream_t st) {
-  if (!gemv1_usable(M) || M.K % 512 || scratch_floats < gemm_t5_plane_floats(M, m)) return kErrTooLarge;
+  if (!gemv1_usable(M) || M.K % 512 || scratch_floats < gemm_t5_plane_floats(M, m)) {
+    set_kernel_error_text("gemm (tcgen05)", "matrix not laid out for it, K not a multiple of 512, or scratch too small");
+    return kErrTooLarge;
+  }
   int terms = 0;
   const int rc = launch_gemm_t5(M, X, x_is_half, m, scratch, error_word(), st, &terms);
   if (rc) return rc;
@@ -396,10 +403,32 @@ int launch_gemv_batch(int n, const MatDev* const* mats, const void* const* xs, b
       *clean_epochs[j] = epoch;
     }
   }
-  int rc = n > 1 ? launch_gemv1_batch(n, mats, xs, x_is_half, partials, ys, error_word(), st) : kErrTooLarge;
-  if (rc != kErrTooLarge) return rc;
-  for (int j = 0; j < n; ++j)   // not one launch: one by one
-    if ((rc = launch_gemv1(*mats[j], xs[j], x_is_half, partials[j], ys[j], error_word(), st))) return rc;
+  // products whose matrices share format and decode plan go out together, the others one by one
+  bool done[8] = {false, false, false, false, false, false, false, false};
+  for (int j = 0; j < n; ++j) {
+    if (done[j]) continue;
+    int idx[8], c = 0;
+    for (int i = j; i < n; ++i)
+      if (!done[i] && mats[i]->fmt == mats[j]->fmt && mats[i]->group == mats[j]->group &&
+          mats[i]->index_bits == mats[j]->index_bits && mats[i]->reader == mats[j]->reader)
+        idx[c++] = i;
+    const MatDev* gm[8];
+    const void* gx[8];
+    float* gp[8];
+    float* gy[8];
+    for (int i = 0; i < c; ++i) {
+      gm[i] = mats[idx[i]];
+      gx[i] = xs[idx[i]];
+      gp[i] = partials[idx[i]];
+      gy[i] = ys[idx[i]];
+      done[idx[i]] = true;
+    }
+    int rc = c > 1 ? launch_gemv1_batch(c, gm, gx, x_is_half, gp, gy, error_word(), st) : kErrTooLarge;
+    if (rc == kErrTooLarge)
+      for (int i = 0; i < c && (rc == kErrTooLarge || rc == kOk); ++i)
+        rc = launch_gemv1(*gm[i], gx[i], x_is_half, gp[i], gy[i], error_word(), st);
+    if (rc) return rc;
+  }
   return kOk;
 }
 

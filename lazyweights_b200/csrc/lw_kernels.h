@@ -18,6 +18,7 @@ struct MatDev {
   const uint16_t* lut;          // [2048] symbol | length << 8
   const uint32_t* tab32;        // [2048] length << 28 | grid value(s) as int8 (see lw::fat_table); for a fixed-width
                                 // twin: [256] grid values of a paired symbol (unused for unpaired formats)
+  const uint32_t* symtab32;     // [2048] length << 28 | symbol: the decode-to-codes kernel's table (or null)
   const uint32_t* cmp_tab;      // comparator form of the code (lw::comparator_table): [0..11] limit per length,
                                 // [12..23] index offset per length, [24..279] grid values in canonical order; or null
   const uint32_t* group_base;   // [T * groups + 1] word offset of every chain group

@@ -250,7 +250,7 @@ __device__ __forceinline__ void ring_release(const RingMem& R, const Unit& u, in
 //
 // Spreads 32 entries held by a warp (lane l holds entry i0 + l): broadcast one by one, every lane stores its own copy
 // (bank = lane, no conflicts).  With 16 copies two entries go out per store.  tab1 = the single-copy table.
-template <int LOG_R>
+template <int LOG_R, bool SINGLE = true>
 __device__ __forceinline__ void table_spread(uint32_t* tab, uint32_t* tab1, int i0, uint32_t mine, int lane) {
   constexpr int R = 1 << LOG_R, PER = 32 / R;   // entries per store: lane l writes copy l % R of entry i0 + j + l / R
 #pragma unroll 8
@@ -258,16 +258,19 @@ __device__ __forceinline__ void table_spread(uint32_t* tab, uint32_t* tab1, int 
     const uint32_t v = __shfl_sync(0xffffffffu, mine, j + (lane >> LOG_R));
     tab[(i0 + j) * R + lane] = v;
   }
-  tab1[i0 + lane] = mine;
+  if (SINGLE) tab1[i0 + lane] = mine;
 }
 
-// The whole table, by `nwarps` warps of `nthr` threads (warp, lane = the caller's position among them).
-template <int IDXBITS, int LOG_R>
+// The whole table, by `nwarps` warps (warp, lane = the caller's position among them).  SINGLE = false: no single-copy
+// table (a kernel whose replicated table already holds all 2048 windows has no use for it).
+template <int IDXBITS, int LOG_R, bool SINGLE = true>
 __device__ __forceinline__ void table_fill(const MatDev& M, uint32_t* tab, uint32_t* tab1, int warp, int lane,
                                            int nwarps) {
   constexpr int NIDX = 1 << IDXBITS;
-  for (int i0 = warp * 32; i0 < NIDX; i0 += nwarps * 32) table_spread<LOG_R>(tab, tab1, i0, __ldg(M.tab32 + i0 + lane), lane);
-  for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += nwarps * 32) tab1[idx] = __ldg(M.tab32 + idx);
+  for (int i0 = warp * 32; i0 < NIDX; i0 += nwarps * 32)
+    table_spread<LOG_R, SINGLE>(tab, tab1, i0, __ldg(M.tab32 + i0 + lane), lane);
+  if (SINGLE)
+    for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += nwarps * 32) tab1[idx] = __ldg(M.tab32 + idx);
 }
 
 // ------------------------------------------------------------------------------------------------ chain reader
@@ -297,10 +300,12 @@ struct GroupChain {
   }
   // next table entry; tab = replicated table (start of shared memory), lane_off = this lane's byte offset inside the
   // copies of one window, MASK selects the window's address bits
-  template <uint32_t MASK>
+  // RSHIFT > 0: the table has fewer copies than the chains' leading zero bits were laid out for (2^(LOG_R - RSHIFT)
+  // copies): the window is shifted down onto the smaller stride first
+  template <uint32_t MASK, int RSHIFT = 0>
   __device__ __forceinline__ uint32_t sym(const uint8_t* tab, uint32_t lane_off) {
     const uint32_t t = __funnelshift_r(a, b, off);
-    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + ((t & MASK) | lane_off));
+    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + (((t >> RSHIFT) & MASK) | lane_off));
     off = __umulhi(e, 16u) + off;   // e >> 28 = code length
     return e;
   }
