@@ -166,15 +166,22 @@ def test_tensor_memory_gemm_path(lw, tmp_path, ty, n, k):
     wr.close()
     with lw.Bundle(str(tmp_path / "b")) as b:
         assert lw.lib().lw_debug_set(b"wait_limit", 200000) == 0        # a lost signal ends the kernel within a second
-        for m in (1, 9, 16, 17, 33, 48, 64):
+        for m in (1, 8, 9, 16, 17, 33, 48, 64):
             X = rng.standard_normal((m, k)).astype(np.float32)
             ref = orc.gemv_f64(w, X)
-            got = b.matmul("l0.up", X, 3)
+            try:
+                got = b.matmul("l0.up", X, 3)
+            except lw.LwError as e:
+                # the unit of rare codes is several times the usual size: with many rows its staging ring may not fit
+                # beside the activations; the default path then takes the decode + GEMM route by itself
+                assert e.status == -5 and m > 32
+                assert helpers.rel_err(b.matmul("l0.up", X, 0), ref) <= helpers.GEMV_TOL, (ty, m)
+                continue
             assert helpers.rel_err(got, ref) <= helpers.GEMV_TOL, (ty, m)
-            if m > 8:
+            if m >= 8:
                 before = lw.lib().lw_launch_count()
                 auto = b.matmul("l0.up", X, 0)
-                assert np.array_equal(auto, got)                        # the default path for 9 .. 64 rows is this kernel
+                assert np.array_equal(auto, got)                        # the default path for 8 .. 64 rows is this kernel
                 assert lw.lib().lw_launch_count() - before == 2         # the GEMM and the sum of its planes
         assert b.kernel_error() == 0
         lw.lib().lw_debug_set(b"reset", 0)
