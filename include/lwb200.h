@@ -99,6 +99,17 @@ int rt_vocab(void* handle);
 int lw_tp_unique_id(uint8_t* out128);
 int rt_tp_init(void* handle, int rank, int world, const uint8_t* id128);
 
+/* Optional second step: the all-reduces of `o` and `down` over peer memory, fused with the RMSNorm that consumes them
+ * (one kernel per rank writes its partial rows into every rank's exchange buffer with plain NVLink stores, waits for
+ * the other ranks' flags and sums in rank order; no multicast).  rt_tp_peer_export allocates this rank's exchange buffer
+ * and returns its 64-byte CUDA IPC handle; the caller gathers the handles of all ranks (rank-major, world x 64 bytes) and
+ * gives them to rt_tp_peer_open, which maps the peers' buffers.  Without this step the all-reduces are NCCL calls.  The
+ * logits are gathered by NCCL either way.  rt_tp_error reads and clears the runtime's device error word (1: a rank's
+ * flag did not arrive within the poll limit; the pass's logits are then void). */
+int rt_tp_peer_export(void* handle, uint8_t* out64);
+int rt_tp_peer_open(void* handle, const uint8_t* handles, int world);
+int rt_tp_error(void* handle);
+
 /* ---- per-matrix entry points on device pointers (additions) ---------------------------------------------- */
 
 /* Index of a matrix in the handle (>= 0) or -1.  The *_id variants below skip the name lookup. */

@@ -53,6 +53,9 @@ static Nccl g_nccl;
 struct UniqueId { char bytes[128]; };
 constexpr int kNcclFloat = 7, kNcclSum = 0;
 
+// error word of this file's kernels (bit 0: the peer all-reduce gave up waiting for a rank)
+__device__ unsigned int g_rt_error;
+
 struct Runtime {
   int L = 0, D = 0, H = 0, Hk = 0, Dh = 0, I = 0, V = 0;   // heads, FFN width and vocabulary are the LOCAL sizes
   int Tmax = 0, max_batch = 0, pos = 0, window = 0;
@@ -60,6 +63,11 @@ struct Runtime {
   int Vfull = 0, Vmax = 0;           // whole vocabulary; largest shard (ranks may hold 63 or 62 tile rows, say)
   std::vector<int> voff, vcnt;       // first row and rows of every rank's vocabulary shard
   bool time_collectives = false;     // next pass: direct launches with CUDA events around every collective
+  // peer-memory all-reduce (rt_tp_peer_open): every rank's exchange buffer mapped into every other rank
+  void* peer_local = nullptr;                 // this rank's buffer (cudaMalloc; exported with cudaIpcGetMemHandle)
+  void* peer_base[8] = {nullptr};             // the ranks' buffers as seen from this process (own = peer_local)
+  bool peer_ready = false;
+  size_t peer_bytes = 0;
   std::vector<cudaEvent_t> coll_events;
   double collective_us = 0.0;        // time inside collectives during the last such pass
   int collective_calls = 0;
@@ -190,6 +198,107 @@ __global__ void __launch_bounds__(kNormThreads)
     }
   } else {
     for (int k = threadIdx.x; k < D; k += blockDim.x) orow[k] = hr[k] * r * g[k];
+  }
+}
+
+// ---------------------------------------------------------------------------------- all-reduce fused with the norm
+//
+// Tensor-parallel ranks hold partial outputs of the row-parallel matrices (o, down); their sum is the residual the next
+// RMSNorm adds.  Instead of a library all-reduce followed by the norm kernel, ONE kernel per rank does both over peer
+// memory (one-shot, all-to-all): every rank stores its partial row into its slot of EVERY rank's exchange buffer (plain
+// stores through NVLink), publishes a flag per destination (release at system scope), waits until the flags of all ranks
+// have arrived in its own buffer, adds the slots in rank order (every rank adds the same numbers in the same order: the
+// ranks' results are identical, as after an all-reduce) and goes on with the norm.  At one token the payload is 16 KB per
+// rank and destination: the cost is latency, and this is two NVLink traversals (data, then flag) instead of a library
+// call's protocol.  Only ordinary loads and stores touch peer memory - no multicast of any kind.
+//
+// Exchange buffer of a rank: [kPeerMaxBlocks epoch counters][flags: 2 parities x kPeerMaxBlocks x 8 ranks][slots:
+// 2 parities x 8 ranks x kPeerMaxBlocks rows x D floats].  Block j (token row j) keeps its own epoch: the number of
+// all-reduces it has taken part in; slot and flag parity = epoch & 1, so a rank that is one all-reduce ahead never
+// overwrites data a slower rank still reads (it cannot be two ahead: it needs the slower rank's contribution first).
+// The wait is bounded: after `limit` polls the block sets the device error word and continues with what it has.
+constexpr int kPeerMaxBlocks = 8, kPeerMaxRanks = 8;
+struct PeerView {
+  float* slots[kPeerMaxRanks];       // rank p's slot area, as mapped here
+  uint32_t* flags[kPeerMaxRanks];    // rank p's flag area
+  uint32_t* epoch;                   // this rank's epoch counters
+  int world, rank, D;
+};
+__host__ __device__ constexpr size_t peer_flag_words() { return 2 * kPeerMaxBlocks * kPeerMaxRanks; }
+__host__ __device__ inline size_t peer_slot_floats(int D) { return static_cast<size_t>(2) * kPeerMaxRanks * kPeerMaxBlocks * D; }
+
+__global__ void __launch_bounds__(kNormThreads)
+    k_allreduce_rmsnorm(PeerView P, const float* __restrict__ part, float* __restrict__ h, const float* __restrict__ g,
+                        float* __restrict__ out, float eps, unsigned int* err, uint32_t limit) {
+  dep_begin();
+  __shared__ float red[33];
+  __shared__ uint32_t s_epoch;
+  const int j = blockIdx.x, D = P.D;
+  if (threadIdx.x == 0) s_epoch = P.epoch[j];
+  __syncthreads();
+  const uint32_t e = s_epoch, parity = e & 1u;
+  const size_t row = (static_cast<size_t>(parity) * kPeerMaxRanks * kPeerMaxBlocks + static_cast<size_t>(j)) * D;   // + rank * kPeerMaxBlocks * D
+  // 1. my partial row into my slot of every rank's buffer
+  const float* mine = part + static_cast<size_t>(j) * D;
+  for (int k = threadIdx.x * 4; k < D; k += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(mine + k);
+    for (int p = 0; p < P.world; ++p)
+      *reinterpret_cast<float4*>(P.slots[p] + row + static_cast<size_t>(P.rank) * kPeerMaxBlocks * D + k) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  // 2. publish: flag (parity, block j, source rank) of every destination := e + 1
+  const size_t flag_at = (static_cast<size_t>(parity) * kPeerMaxBlocks + j) * kPeerMaxRanks;
+  if (threadIdx.x < P.world) {
+    uint32_t* dst = P.flags[threadIdx.x] + flag_at + P.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(e + 1u) : "memory");
+  }
+  // 3. wait for every rank's flag in my own buffer
+  if (threadIdx.x < P.world) {
+    const uint32_t* src = P.flags[P.rank] + flag_at + threadIdx.x;
+    bool ok = false;
+    for (uint32_t i = 0; i < limit && !ok; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+      ok = v == e + 1u;
+    }
+    if (!ok) atomicOr(err, 1u);
+  }
+  __syncthreads();
+  // 4. sum in rank order + residual, then the norm (as k_rmsnorm)
+  float* hr = h + static_cast<size_t>(j) * D;
+  float* orow = out + static_cast<size_t>(j) * D;
+  const float* my_slots = P.slots[P.rank] + row;
+  float ss = 0.f;
+  for (int k = threadIdx.x * 4; k < D; k += blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(hr + k);
+    for (int r = 0; r < P.world; ++r) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(my_slots + static_cast<size_t>(r) * kPeerMaxBlocks * D + k));
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(hr + k) = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) {
+      red[32] = rsqrtf(t / D + eps);
+      P.epoch[j] = e + 1u;
+    }
+  }
+  __syncthreads();
+  const float r = red[32];
+  for (int k = threadIdx.x * 4; k < D; k += blockDim.x * 4) {
+    const float4 hv = *reinterpret_cast<const float4*>(hr + k);
+    const float4 g4 = *reinterpret_cast<const float4*>(g + k);
+    *reinterpret_cast<float4*>(orow + k) = make_float4(hv.x * r * g4.x, hv.y * r * g4.y, hv.z * r * g4.z, hv.w * r * g4.w);
   }
 }
 
@@ -534,6 +643,9 @@ void runtime_free(Model* M) {
   for (auto& kv : R->graph_exec) cudaGraphExecDestroy(kv.second);
   if (R->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(R->comm);
   if (R->stream) cudaStreamDestroy(R->stream);
+  for (int p = 0; p < kPeerMaxRanks; ++p)
+    if (R->peer_base[p] && R->peer_base[p] != R->peer_local) cudaIpcCloseMemHandle(R->peer_base[p]);
+  if (R->peer_local) cudaFree(R->peer_local);
   if (R->h_ids) cudaFreeHost(R->h_ids);
   for (void* p : R->owned) cudaFree(p);
   delete R;
@@ -576,6 +688,47 @@ static int nccl_check(int r, const char* what) {
 
 // The device work of one pass over m <= max_batch tokens (ids and position already in R->h_ids): everything is
 // enqueued on `st`, nothing here depends on host-side values that change from pass to pass except `nchunks`.
+static PeerView peer_view(const Runtime* R) {
+  PeerView P;
+  for (int p = 0; p < kPeerMaxRanks; ++p) {
+    uint8_t* base = static_cast<uint8_t*>(p < R->tp_world ? R->peer_base[p] : nullptr);
+    P.flags[p] = base ? reinterpret_cast<uint32_t*>(base + kPeerMaxBlocks * 4) : nullptr;
+    P.slots[p] = base ? reinterpret_cast<float*>(base + 4096) : nullptr;
+  }
+  P.epoch = static_cast<uint32_t*>(R->peer_local);
+  P.world = R->tp_world;
+  P.rank = R->tp_rank;
+  P.D = R->D;
+  return P;
+}
+
+// h += (sum over ranks of) `res`, out = rmsnorm(h) * g: the norm kernel; with tensor parallelism the ranks' partial
+// `res` are summed first - over peer memory inside the same kernel, or by an NCCL all-reduce in front of it.
+static int norm_residual(Model* M, Runtime* R, int m, const float* res, bool res_is_partial, const float* g, cudaStream_t st,
+                         const char* what) {
+  (void)M;
+  if (res && res_is_partial && R->tp_world > 1) {
+    if (R->peer_ready && m <= kPeerMaxBlocks && R->D % 4 == 0) {
+      CollTimer t(R, st);
+      unsigned int* err = nullptr;
+      if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_rt_error) != cudaSuccess) return cuda_fail("error word", cudaGetLastError());
+      launch_dep(k_allreduce_rmsnorm, dim3(m), dim3(kNormThreads), st, peer_view(R), res, R->h, g, R->xn, R->eps, err,
+                 uint32_t(1) << 22);
+      return kOk;
+    }
+    if (!R->comm) {
+      set_error("tensor-parallel bundle without a communicator: call rt_tp_init");
+      return kErrArg;
+    }
+    CollTimer t(R, st);
+    const int rc = nccl_check(g_nccl.AllReduce(res, const_cast<float*>(res), static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum,
+                                               R->comm, st), what);
+    if (rc) return rc;
+  }
+  launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, res, g, R->xn, R->D, R->eps);
+  return kOk;
+}
+
 static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunks, cudaStream_t st) {
   cudaError_t e = cudaMemcpyAsync(R->ids, R->h_ids, (R->max_batch + 1) * sizeof(int), cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) return cuda_fail("ids upload", e);
@@ -584,9 +737,9 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
   else k_embed8<<<m, 256, 0, st>>>(R->ids, R->embed8, R->embed_rs, R->embed_rsub, R->h, R->D, R->embed_groups);
   const size_t QKV = static_cast<size_t>(R->H + 2 * R->Hk) * R->Dh;
   const float* pending = nullptr;   // output of the previous block, added to h by the next norm
-  int rc;
+  int rc = kOk;
   for (int l = 0; l < R->L; ++l) {
-    launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, pending, R->ln1[l], R->xn, R->D, R->eps);
+    if ((rc = norm_residual(M, R, m, pending, true, R->ln1[l], st, "all-reduce (down)"))) return rc;
     if (R->m_qkv[l] >= 0) {
       if ((rc = linear_device(M, M->mats[R->m_qkv[l]], R->xn, false, m, R->qkv, static_cast<int>(QKV), st))) return rc;
     } else if (m == 1) {   // one token: q, k and v read the same activations - one launch where their plans agree
@@ -622,13 +775,7 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     }
     launch_dep(k_attn_combine, dim3(R->H, m), dim3(128), st, R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
-    if (R->comm) {
-      CollTimer t(R, st);
-      if ((rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum, R->comm, st),
-                           "all-reduce (o)")))
-        return rc;
-    }
-    launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, R->o, R->ln2[l], R->xn, R->D, R->eps);
+    if ((rc = norm_residual(M, R, m, R->o, true, R->ln2[l], st, "all-reduce (o)"))) return rc;
     if (m == 1) {          // one token: gate and up in one launch
       const int idx[2] = {R->m_gate[l], R->m_up[l]};
       const float* xs[2] = {R->xn, R->xn};
@@ -641,15 +788,9 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     const size_t ng = static_cast<size_t>(m) * R->I;
     launch_dep(k_silu_mul, dim3(static_cast<unsigned>((ng + 255) / 256)), dim3(256), st, R->g, R->u, ng);
     if ((rc = linear_device(M, M->mats[R->m_down[l]], R->g, false, m, R->o, R->D, st))) return rc;
-    if (R->comm) {
-      CollTimer t(R, st);
-      if ((rc = nccl_check(g_nccl.AllReduce(R->o, R->o, static_cast<size_t>(m) * R->D, kNcclFloat, kNcclSum, R->comm, st),
-                           "all-reduce (down)")))
-        return rc;
-    }
-    pending = R->o;
+    pending = R->o;   // the ranks' partial outputs of `down`: summed by the next norm
   }
-  launch_dep(k_rmsnorm, dim3(m), dim3(kNormThreads), st, R->h, pending, R->lnf, R->xn, R->D, R->eps);
+  if ((rc = norm_residual(M, R, m, pending, true, R->lnf, st, "all-reduce (down)"))) return rc;
   const int rows = all_logits ? m : 1;
   const float* xlast = all_logits ? R->xn : R->xn + static_cast<size_t>(m - 1) * R->D;
   if ((rc = linear_device(M, M->mats[R->m_head], xlast, false, rows, R->logits, R->V, st))) return rc;
@@ -838,6 +979,72 @@ int rt_tp_init(void* handle, int rank, int world, const uint8_t* id128) {
   if (rc) return rc;
   R->tp_rank = rank;
   return kOk;
+}
+
+int rt_tp_peer_export(void* handle, uint8_t* out64) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt || !out64) return kErrArg;
+  Runtime* R = M->rt;
+  if (const int rc = check_device(M)) return rc;
+  if (R->tp_world < 2 || R->tp_world > kPeerMaxRanks || R->max_batch < 1) {
+    set_error("rt_tp_peer_export: needs a shard of 2..8 ranks");
+    return kErrArg;
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  if (!R->peer_local) {
+    R->peer_bytes = 4096 + peer_slot_floats(R->D) * sizeof(float);
+    cudaError_t e = cudaMalloc(&R->peer_local, R->peer_bytes);
+    if (e != cudaSuccess) return cuda_fail("cudaMalloc (exchange buffer)", e);
+    if ((e = cudaMemset(R->peer_local, 0, R->peer_bytes)) != cudaSuccess) return cuda_fail("cudaMemset (exchange buffer)", e);
+  }
+  cudaIpcMemHandle_t hnd;
+  const cudaError_t e = cudaIpcGetMemHandle(&hnd, R->peer_local);
+  if (e != cudaSuccess) return cuda_fail("cudaIpcGetMemHandle", e);
+  std::memcpy(out64, &hnd, 64);
+  return kOk;
+}
+
+int rt_tp_peer_open(void* handle, const uint8_t* handles, int world) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt || !handles) return kErrArg;
+  Runtime* R = M->rt;
+  if (const int rc = check_device(M)) return rc;
+  if (world != R->tp_world || !R->peer_local) {
+    set_error("rt_tp_peer_open: call rt_tp_peer_export first; world must match the shard");
+    return kErrArg;
+  }
+  for (int p = 0; p < world; ++p) {
+    if (p == R->tp_rank) {
+      R->peer_base[p] = R->peer_local;
+      continue;
+    }
+    cudaIpcMemHandle_t hnd;
+    std::memcpy(&hnd, handles + 64 * p, 64);
+    const cudaError_t e = cudaIpcOpenMemHandle(&R->peer_base[p], hnd, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      R->peer_base[p] = nullptr;
+      return cuda_fail("cudaIpcOpenMemHandle", e);
+    }
+  }
+  cudaDeviceSynchronize();
+  // captured passes hold the NCCL form of the all-reduce: drop them
+  for (auto& kv : R->graph_exec) cudaGraphExecDestroy(kv.second);
+  R->graph_exec.clear();
+  R->graph_seen.clear();
+  R->peer_ready = true;
+  return kOk;
+}
+
+int rt_tp_error(void* handle) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt) return kErrArg;
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_rt_error, sizeof v) != cudaSuccess) return cuda_fail("read error word", cudaGetLastError());
+  if (v) {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_rt_error, &z, sizeof z);
+  }
+  return static_cast<int>(v);
 }
 
 }  // extern "C"

@@ -241,6 +241,17 @@ class Bundle(_Handle):
     def tp_init(self, rank, world, unique_id):
         nat.check(nat.lib().rt_tp_init(self._h, rank, world, (C.c_uint8 * 128).from_buffer_copy(unique_id)))
 
+    def tp_peer_export(self):
+        buf = (C.c_uint8 * 64)()
+        nat.check(nat.lib().rt_tp_peer_export(self._h, buf))
+        return bytes(buf)
+
+    def tp_peer_open(self, handles, world):
+        nat.check(nat.lib().rt_tp_peer_open(self._h, (C.c_uint8 * (64 * world)).from_buffer_copy(handles), world))
+
+    def tp_error(self):
+        return nat.lib().rt_tp_error(self._h)
+
     def cpu_decode(self, name, threads=0):
         inf = self.info(name)
         cols = inf["K"] // 2 if inf["paired"] else inf["K"]

@@ -21,9 +21,26 @@ def broadcast_id(rank, group=None, device=None):
     return bytes(buf.cpu().numpy().tobytes())
 
 
-def open_shard(path, rank, world, max_ctx=4096, max_batch=8, group=None, device=None):
-    """Opens this rank's shard bundle on the current CUDA device and joins the tensor-parallel communicator."""
+def gather_bytes(mine, world, group=None, device=None):
+    """Every rank's byte string (all of one length), rank-major, through the torch.distributed group."""
+    import torch
+    import torch.distributed as dist
+    t = torch.frombuffer(bytearray(mine), dtype=torch.uint8).to(device or "cpu")
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t, group=group)
+    return b"".join(bytes(p.cpu().numpy().tobytes()) for p in parts)
+
+
+def open_shard(path, rank, world, max_ctx=4096, max_batch=8, group=None, device=None, peer=None):
+    """Opens this rank's shard bundle on the current CUDA device and joins the tensor-parallel communicator.
+    peer (default: on unless LW_TP_PEER=0): the all-reduces run over peer memory fused with the following norm
+    (rt_tp_peer_export / rt_tp_peer_open) instead of as NCCL calls."""
+    import os
     b = Bundle(path, max_ctx=max_ctx, max_batch=max_batch)
     if world > 1:
         b.tp_init(rank, world, broadcast_id(rank, group, device))
+        if peer is None:
+            peer = os.environ.get("LW_TP_PEER", "1") != "0"
+        if peer:
+            b.tp_peer_open(gather_bytes(b.tp_peer_export(), world, group, device), world)
     return b

@@ -55,14 +55,17 @@ def test_shards_tile_the_full_model(tmp_path):
 
 
 @pytest.mark.gpu
-def test_two_rank_forward_matches_one_gpu(tmp_path):
+@pytest.mark.parametrize("peer", ["1", "0"])
+def test_two_rank_forward_matches_one_gpu(tmp_path, peer):
+    """peer = 1: all-reduces over peer memory fused with the norm; 0: NCCL all-reduces."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     helpers.build_library()
     import lazyweights_b200 as lw
     from lazyweights_b200 import modelgen
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29741", WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29741" if peer == "1" else "29743", WORLD_SIZE="2",
+               NCCL_NVLS_ENABLE="0", LW_TP_PEER=peer)
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(tmp_path)],
                               env=dict(env, RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
              for r in range(2)]

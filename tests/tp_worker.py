@@ -25,7 +25,7 @@ def main():
     b = tp.open_shard(path, rank, world, max_ctx=64, max_batch=8)
     logits = b.forward(ids, all_logits=True)
     step = b.forward(ids[:1])                      # one more single-token pass (m = 1 path through the collectives)
-    assert b.kernel_error() == 0
+    assert b.kernel_error() == 0 and b.tp_error() == 0
     np.save(os.path.join(out, "logits%d.npy" % rank), logits)
     np.save(os.path.join(out, "step%d.npy" % rank), step)
     dist.barrier()
