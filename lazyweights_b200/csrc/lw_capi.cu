@@ -215,6 +215,11 @@ static int finish_model(Model* M) {
     const cudaError_t e = cudaMalloc(&M->d_partials, need * sizeof(float));
     if (e != cudaSuccess) return cuda_fail("cudaMalloc (partials)", e);
     M->partial_floats = need;
+    // range factors of the rows of fp32 activations on the fp16 paths: here, not on first use, so that a pass that is
+    // being captured into a graph never allocates
+    const cudaError_t e2 = cudaMalloc(&M->d_row_scale, 4096 * sizeof(float));
+    if (e2 != cudaSuccess) return cuda_fail("cudaMalloc (row factors)", e2);
+    M->row_scale_floats = 4096;
   }
   return kOk;
 }
@@ -280,10 +285,14 @@ static int linear_decode_gemm(Model* M, Matrix& mx, const void* x, bool x_half, 
                               cudaStream_t st) {
   int rc;
   const __half* x16 = static_cast<const __half*>(x);
+  const float* unscale = nullptr;
   if (!x_half) {
     if ((rc = grow(&M->d_x16, &M->x16_halfs, static_cast<size_t>(m) * mx.K, "cudaMalloc (fp16 activations)"))) return rc;
-    if ((rc = launch_to_half(static_cast<const float*>(x), M->d_x16, static_cast<size_t>(m) * mx.K, st))) return rc;
+    if ((rc = grow(&M->d_row_scale, &M->row_scale_floats, static_cast<size_t>(2) * m, "cudaMalloc (row factors)"))) return rc;
+    if ((rc = launch_row_scales(static_cast<const float*>(x), m, mx.K, M->d_row_scale, st))) return rc;
+    if ((rc = launch_to_half_rows(static_cast<const float*>(x), M->d_x16, m, mx.K, M->d_row_scale, st))) return rc;
     x16 = M->d_x16;
+    unscale = M->d_row_scale + m;
   }
   const int NT = mx.N / kTileRows;
   const size_t row_halfs = static_cast<size_t>(kTileRows) * mx.K;
@@ -295,7 +304,7 @@ static int linear_decode_gemm(Model* M, Matrix& mx, const void* x, bool x_half, 
     const int tr1 = std::min(NT, tr0 + chunk);
     if ((rc = launch_decode_weights_rows(mx.dev, M->d_w16, tr0, tr1, st))) return rc;
     if ((rc = launch_gemm_tc(x16, M->d_w16, y + static_cast<size_t>(tr0) * kTileRows, m, (tr1 - tr0) * kTileRows, mx.K,
-                             ldy, M->d_partials, M->partial_floats, st)))
+                             ldy, M->d_partials, M->partial_floats, unscale, st)))
       return rc;
   }
   return kOk;
@@ -312,7 +321,9 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   // go to tensor memory, never to DRAM); more rows, or shapes that kernel does not take, decode to fp16 weights in DRAM
   // and a tensor-core GEMM over them (the decode is paid once however many rows follow).  path 3 forces the tcgen05 kernel.
   if (path == 3 || (path == 0 && m >= debug_knobs().t5_min_rows && m <= 64)) {
-    const int rc = launch_gemm_coded(mx.dev, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, st);
+    if (!x_half)
+      if (const int rc = grow(&M->d_row_scale, &M->row_scale_floats, 128, "cudaMalloc (row factors)")) return rc;
+    const int rc = launch_gemm_coded(mx.dev, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, M->d_row_scale, st);
     if (rc != kErrTooLarge || path == 3) return rc;
   }
   if (path == 2 || (path == 0 && m > 16)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);

@@ -50,7 +50,7 @@ static bool plan_t5(const MatDev& M, int m, T5Plan& p) {
 }
 
 template <int FMT, int G, int IDXBITS>
-static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
+static int launch_t(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err, cudaStream_t st,
                     int* terms) {
   T5Plan p;
   if (!plan_t5<FMT>(M, m, p)) return kErrTooLarge;
@@ -68,6 +68,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float
   a.x = X;
   a.planes = planes;
   a.x_is_half = x_is_half;
+  a.row_scale = row_scale;
   a.m = m;
   a.ntok = p.ntok;
   a.r.err = err;
@@ -89,23 +90,23 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float
 }
 
 template <int FMT, int G>
-static int launch_i(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
+static int launch_i(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err, cudaStream_t st,
                     int* terms) {
-  if (M.index_bits == 10) return launch_t<FMT, G, 10>(M, X, x_is_half, m, planes, err, st, terms);
-  return launch_t<FMT, G, 11>(M, X, x_is_half, m, planes, err, st, terms);
+  if (M.index_bits == 10) return launch_t<FMT, G, 10>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+  return launch_t<FMT, G, 11>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
 }
 
 template <int FMT>
-static int launch_g(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
+static int launch_g(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err, cudaStream_t st,
                     int* terms) {
   switch (M.group) {
-    case 3: return launch_i<FMT, 3>(M, X, x_is_half, m, planes, err, st, terms);
-    case 4: return launch_i<FMT, 4>(M, X, x_is_half, m, planes, err, st, terms);
+    case 3: return launch_i<FMT, 3>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    case 4: return launch_i<FMT, 4>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
   }
   if constexpr (!is_paired(FMT)) {
     switch (M.group) {
-      case 5: return launch_i<FMT, 5>(M, X, x_is_half, m, planes, err, st, terms);
-      case 6: return launch_i<FMT, 6>(M, X, x_is_half, m, planes, err, st, terms);
+      case 5: return launch_i<FMT, 5>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+      case 6: return launch_i<FMT, 6>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
     }
   }
   set_kernel_error_text("gemm (tcgen05)", "no kernel for this group size");
@@ -117,17 +118,17 @@ size_t gemm_t5_plane_floats(const MatDev& M, int m) { return static_cast<size_t>
 // planes[K / 512][m][N] = partial products of the column sets; *terms = K / 512.  kErrTooLarge (nothing launched) where
 // this kernel cannot take the product: more than 64 rows, tile rows not a multiple of four, K not a multiple of 512, or
 // too little shared memory left for the staging ring (the 2048-window table with many rows).
-int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
+int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err, cudaStream_t st,
                    int* terms) {
   if (!err || !planes || !terms) {
     set_kernel_error_text("gemm (tcgen05)", "null argument");
     return kErrTooLarge;
   }
   switch (M.fmt) {
-    case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, m, planes, err, st, terms);
-    case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, m, planes, err, st, terms);
-    case kFmtIQ4XS: return launch_g<kFmtIQ4XS>(M, X, x_is_half, m, planes, err, st, terms);
-    case kFmtQ6K: return launch_g<kFmtQ6K>(M, X, x_is_half, m, planes, err, st, terms);
+    case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    case kFmtIQ4XS: return launch_g<kFmtIQ4XS>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    case kFmtQ6K: return launch_g<kFmtQ6K>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
   }
   return kErrTooLarge;
 }

@@ -43,6 +43,7 @@ struct GemmT5Args {
   RingArgs r;          // r.nsets = K / 512 column sets; r.tr0 / r.ntr unused (all tile rows)
   const void* x;       // activations [m][K], fp16 or fp32
   float* planes;       // P[K / 512][m][N]
+  const float* row_scale;   // fp32 x only (else null): factor per row that keeps it inside fp16's range
   int x_is_half;
   int m;               // tokens (rows of x), 1 .. ntok
   int ntok;            // N of the MMA: m rounded up to a multiple of 16
@@ -247,7 +248,9 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
         } else {
           const float4 f0 = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(A.x) + src));
           const float4 f1 = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(A.x) + src) + 1);
-          v = make_uint4(pack_half2(f0.x, f0.y), pack_half2(f0.z, f0.w), pack_half2(f1.x, f1.y), pack_half2(f1.z, f1.w));
+          const float rs = A.row_scale ? A.row_scale[n] : 1.f;   // not __ldg: written by the kernel just before
+          v = make_uint4(pack_half2(f0.x * rs, f0.y * rs), pack_half2(f0.z * rs, f0.w * rs), pack_half2(f1.x * rs, f1.y * rs),
+                         pack_half2(f1.z * rs, f1.w * rs));
         }
       }
       *reinterpret_cast<uint4*>(xs + (n >> 3) * (kT5SetK / 8 * 128) + kc * 128 + (n & 7) * 16) = v;

@@ -14,14 +14,45 @@ namespace lw {
 
 constexpr int kGemmRows = 64, kGemmTokens = 32, kGemmK = 64, kGemmPad = 8;
 
-__global__ void k_to_half(const float* __restrict__ src, __half* __restrict__ dst, size_t n) {
-  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (i < n) dst[i] = __float2half_rn(src[i]);
+// fp32 activations enter the tensor cores as fp16, whose largest finite value is 65504: a row with larger entries
+// (the input of a down projection can be the product of two unnormalised projections) would turn into infinities and
+// the product into NaN.  Each row therefore gets a power-of-two factor that brings its largest |x| to at most 2^15 -
+// exactly 1 for every row that already fits, so ordinary inputs are converted bit for bit as before - and the
+// product's rows are multiplied by the inverse afterwards (exact: both are powers of two).
+// scales[r] = factor of row r, scales[m + r] = its inverse.  One block per row.
+__global__ void __launch_bounds__(256) k_row_scales(const float* __restrict__ X, int K, int m, float* __restrict__ scales) {
+  __shared__ float part[8];
+  const int r = blockIdx.x;
+  const float* x = X + static_cast<size_t>(r) * K;
+  float amax = 0.f;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(x[k]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, part[w]);
+    int e = 0;
+    if (amax > 32768.f && amax <= 3.0e38f) {   // frexp: amax = f 2^e with f in [0.5, 1)
+      frexpf(amax, &e);
+      e -= 15;
+    }
+    scales[r] = ldexpf(1.f, -e);
+    scales[m + r] = ldexpf(1.f, e);
+  }
+}
+
+// dst[r][k] = half(src[r][k] * scales[r]); grid (ceil(K / 256), m)
+__global__ void k_to_half_rows(const float* __restrict__ src, __half* __restrict__ dst, int K,
+                               const float* __restrict__ scales) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+  if (k < K) dst[static_cast<size_t>(r) * K + k] = __float2half_rn(src[static_cast<size_t>(r) * K + k] * scales[r]);
 }
 
 __global__ void __launch_bounds__(128)
     k_gemm_tc(const __half* __restrict__ X, const __half* __restrict__ W, float* __restrict__ Y, int m, int K, int ldy,
-              int kspan, size_t zstride) {
+              int kspan, size_t zstride, const float* __restrict__ unscale) {
   __shared__ __align__(16) __half ws[kGemmRows][kGemmK + kGemmPad];
   __shared__ __align__(16) __half xs[kGemmTokens][kGemmK + kGemmPad];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -77,7 +108,7 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int tok = m0 + nb * 8 + 2 * t + (j & 1), row = n0 + warp * 16 + g + (j >> 1) * 8;
-      if (tok < m) Y[static_cast<size_t>(tok) * ldy + row] = acc[nb][j];
+      if (tok < m) Y[static_cast<size_t>(tok) * ldy + row] = unscale ? acc[nb][j] * unscale[tok] : acc[nb][j];
     }
 }
 

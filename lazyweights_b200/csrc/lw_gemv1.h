@@ -27,10 +27,11 @@ int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* p
 int launch_decode_codes_ring(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st);
 
 // Decode + tcgen05 GEMM for up to 64 rows (lw_gemm_t5.cuh): planes[K / 512][m][N] of partial products, *terms = K / 512,
-// to be added by the caller; kErrTooLarge (nothing launched) where this kernel cannot take the product.
+// to be added by the caller; kErrTooLarge (nothing launched) where this kernel cannot take the product.  row_scale (may
+// be null): factor per row of X applied before the conversion to fp16; the caller multiplies the sums by the inverse.
 size_t gemm_t5_plane_floats(const MatDev& M, int m);
-int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, int m, float* planes, unsigned int* err, cudaStream_t st,
-                   int* terms);
+int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes,
+                   unsigned int* err, cudaStream_t st, int* terms);
 
 // fp16 weights of tile rows tr0 .. tr1 - 1 on the batch-1 kernel's decoder (lw_decw.cuh); kErrTooLarge (nothing
 // launched) where it cannot take the matrix.

@@ -172,7 +172,9 @@ namespace lw {
 
 // Y[j, n] = sum over the `terms` partial rows of P[term, j, n], added in term order (no atomics: results do not
 // depend on scheduling).  One thread per four consecutive outputs: 16-byte loads, eight terms in flight.
-__global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int terms) {
+// unscale (may be null): factor per output row j, applied to the finished sum.
+__global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ Y, int m, int N, int ldy, int terms,
+                               const float* __restrict__ unscale = nullptr) {
   pdl_trigger();   // launched as a programmatic dependent of the kernel that writes P (see lw_device.cuh)
   pdl_wait();
   const int quads = N / 4, i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -192,6 +194,13 @@ __global__ void k_sum_partials(const float* __restrict__ P, float* __restrict__ 
       acc.z += v[u].z;
       acc.w += v[u].w;
     }
+  }
+  if (unscale) {
+    const float f = unscale[j];
+    acc.x *= f;
+    acc.y *= f;
+    acc.z *= f;
+    acc.w *= f;
   }
   float* y = Y + static_cast<size_t>(j) * ldy + n;
   y[0] = acc.x;
@@ -372,22 +381,34 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
     // measured: waiting early pays for small products (Q4_K 4096 x 4096, 8 rows: 26 -> 20 us) and costs on large ones
     // (Q6_K 14336 x 4096, 8 rows: 78 -> 88 us), so only up to 16 MB of partial products
     cfg.numAttrs = static_cast<size_t>(terms) * m * M.N * 4 <= (size_t(16) << 20) ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, k_sum_partials, static_cast<const float*>(partials), Y, m, M.N, ldy, terms);
+    cudaLaunchKernelEx(&cfg, k_sum_partials, static_cast<const float*>(partials), Y, m, M.N, ldy, terms,
+                       static_cast<const float*>(nullptr));
   }
   return check_launch("k_sum_partials");
 }
 
 // Y[m, N] = X . W^T for up to 64 rows on the tcgen05 path: planes of partial products, then their ordered sum.
+// row_scale: 2 m floats of device scratch for the per-row range factors of fp32 activations (k_row_scales); unused and
+// may be null when X is fp16.
 int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
-                      size_t scratch_floats, cudaStream_t st) {
+                      size_t scratch_floats, float* row_scale, cudaStream_t st) {
   if (!gemv1_usable(M) || M.K % 512 || scratch_floats < gemm_t5_plane_floats(M, m)) {
     set_kernel_error_text("gemm (tcgen05)", "matrix not laid out for it, K not a multiple of 512, or scratch too small");
     return kErrTooLarge;
   }
+  if (!x_is_half && !row_scale) {
+    set_kernel_error_text("gemm (tcgen05)", "fp32 activations need scratch for their per-row factors");
+    return kErrArg;
+  }
   int terms = 0;
-  const int rc = launch_gemm_t5(M, X, x_is_half, m, scratch, error_word(), st, &terms);
+  if (!x_is_half) {
+    const int rc = launch_row_scales(static_cast<const float*>(X), m, M.K, row_scale, st);
+    if (rc) return rc;
+  }
+  const int rc = launch_gemm_t5(M, X, x_is_half, x_is_half ? nullptr : row_scale, m, scratch, error_word(), st, &terms);
   if (rc) return rc;
-  k_sum_partials<<<(m * (M.N / 4) + 127) / 128, 128, 0, st>>>(scratch, Y, m, M.N, ldy, terms);
+  k_sum_partials<<<(m * (M.N / 4) + 127) / 128, 128, 0, st>>>(scratch, Y, m, M.N, ldy, terms,
+                                                             x_is_half ? nullptr : row_scale + m);
   return check_launch("k_sum_partials");
 }
 
@@ -496,14 +517,21 @@ extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_i
 
 namespace lw {
 
-int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st) {
-  k_to_half<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(src, dst, n);
-  return check_launch("k_to_half");
+int launch_row_scales(const float* X, int m, int K, float* scales, cudaStream_t st) {
+  k_row_scales<<<m, 256, 0, st>>>(X, K, m, scales);
+  return check_launch("k_row_scales");
+}
+
+// dst = fp16 of src [m, K] with row r multiplied by scales[r] (launch_row_scales)
+int launch_to_half_rows(const float* src, __half* dst, int m, int K, const float* scales, cudaStream_t st) {
+  k_to_half_rows<<<dim3((K + 255) / 256, m), 256, 0, st>>>(src, dst, K, scales);
+  return check_launch("k_to_half_rows");
 }
 
 // Y[m, rows] (row stride ldy, starting at column col0) = X[m, K] . W[rows, K]^T on the tensor cores
+// unscale (may be null): per-token factor applied to the finished products (inverse of the activations' range factors)
 int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, float* partials,
-                   size_t partial_capacity, cudaStream_t st) {
+                   size_t partial_capacity, const float* unscale, cudaStream_t st) {
   if (m < 1 || rows % kGemmRows || K % kGemmK) {
     set_kernel_error_text("gemm_tc", "shape must be a multiple of 64 rows x 64 columns");
     return kErrArg;
@@ -513,13 +541,13 @@ int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, 
   while (ks > 1 && (K % (ks * kGemmK) || static_cast<size_t>(ks) * m * rows > partial_capacity || !partials)) ks /= 2;
   dim3 grid(rows / kGemmRows, (m + kGemmTokens - 1) / kGemmTokens, ks);
   if (ks == 1) {
-    k_gemm_tc<<<grid, 128, 0, st>>>(X, W, Y, m, K, ldy, K, 0);
+    k_gemm_tc<<<grid, 128, 0, st>>>(X, W, Y, m, K, ldy, K, 0, unscale);
     return check_launch("k_gemm_tc");
   }
-  k_gemm_tc<<<grid, 128, 0, st>>>(X, W, partials, m, K, rows, K / ks, static_cast<size_t>(m) * rows);
+  k_gemm_tc<<<grid, 128, 0, st>>>(X, W, partials, m, K, rows, K / ks, static_cast<size_t>(m) * rows, nullptr);
   int rc = check_launch("k_gemm_tc");
   if (rc) return rc;
-  k_sum_partials<<<(m * (rows / 4) + 127) / 128, 128, 0, st>>>(partials, Y, m, rows, ldy, ks);
+  k_sum_partials<<<(m * (rows / 4) + 127) / 128, 128, 0, st>>>(partials, Y, m, rows, ldy, ks, unscale);
   return check_launch("k_sum_partials");
 }
 

@@ -46,9 +46,12 @@ int launch_decode_weights(const MatDev& M, __half* out, cudaStream_t st);
 // Only tile rows tr0 .. tr1 - 1 (64 matrix rows each); `out` receives those rows, [ (tr1 - tr0) * 64, K ].
 int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st);
 // fp32 -> fp16 copy, and Y[m, rows] = X[m, K] . W[rows, K]^T (fp16 in, fp32 out, tensor cores) for the decode + GEMM path.
-int launch_to_half(const float* src, __half* dst, size_t n, cudaStream_t st);
+// fp32 activations on their way to fp16: scales[r] = a power of two that brings row r inside fp16's range (1 unless the
+// row holds values above 2^15), scales[m + r] = its inverse, to be applied to row r of the product.
+int launch_row_scales(const float* X, int m, int K, float* scales, cudaStream_t st);
+int launch_to_half_rows(const float* src, __half* dst, int m, int K, const float* scales, cudaStream_t st);
 int launch_gemm_tc(const __half* X, const __half* W, float* Y, int m, int rows, int K, int ldy, float* partials,
-                   size_t partial_capacity, cudaStream_t st);
+                   size_t partial_capacity, const float* unscale, cudaStream_t st);
 // Y[j, n] (row stride ldy) = sum_k X[j, k] W[n, k] for m <= 8 rows of X (fp16 or fp32, row-major [m, K]).
 // `partials` (partial_capacity floats) must hold gemv_partial_floats(M, m) floats.  `clean_epoch` (may be null) is the
 // caller's per-matrix note of when the matrix's tile-row counters were last known to be zero: after a kernel reported
@@ -58,9 +61,10 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
                 size_t partial_capacity, cudaStream_t st, unsigned int* clean_epoch = nullptr);
 // Y[m, N] = X[m, K] . W^T for 1 <= m <= 64 with the decode + tcgen05 kernel (lw_gemm_t5.cuh): the decoded weights go
 // from registers to tensor memory, never to DRAM.  `scratch` holds the K / 512 planes of partial products.  Returns
-// kErrTooLarge, with nothing launched, where that kernel cannot take the product.
+// kErrTooLarge, with nothing launched, where that kernel cannot take the product.  row_scale: 2 m floats of device
+// scratch for launch_row_scales (fp32 activations only).
 int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
-                      size_t scratch_floats, cudaStream_t st);
+                      size_t scratch_floats, float* row_scale, cudaStream_t st);
 
 // n one-row products y_j = W_j x_j (each with its own scratch of gemv_partial_floats(M_j, 1) floats); in one launch
 // where the matrices share a format and decode plan, one by one otherwise.

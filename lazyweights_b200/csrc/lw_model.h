@@ -51,6 +51,8 @@ struct Model {
   size_t pin_floats = 0;
   __half *d_w16 = nullptr, *d_x16 = nullptr;   // decode + GEMM path: decoded weights of a chunk of tile rows, fp16 x
   size_t w16_halfs = 0, x16_halfs = 0;
+  float* d_row_scale = nullptr;   // per-row range factors of fp32 activations headed for fp16 (2 floats per row)
+  size_t row_scale_floats = 0;
   size_t resident_bytes = 0;
   long long coded_bytes = 0, side_bytes = 0;
   Runtime* rt = nullptr;
@@ -66,6 +68,7 @@ struct Model {
     if (h_pin) cudaFreeHost(h_pin);
     if (d_w16) cudaFree(d_w16);
     if (d_x16) cudaFree(d_x16);
+    if (d_row_scale) cudaFree(d_row_scale);
     if (fd >= 0) close(fd);
   }
 };

@@ -182,6 +182,32 @@ def test_tensor_memory_gemm_path(lw, tmp_path, ty, n, k):
                 before = lw.lib().lw_launch_count()
                 auto = b.matmul("l0.up", X, 0)
                 assert np.array_equal(auto, got)                        # the default path for 8 .. 64 rows is this kernel
-                assert lw.lib().lw_launch_count() - before == 2         # the GEMM and the sum of its planes
+                assert lw.lib().lw_launch_count() - before == 3         # range factors of fp32 rows, the GEMM, the sum of its planes
         assert b.kernel_error() == 0
         lw.lib().lw_debug_set(b"reset", 0)
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q4_K", 256, 2048), ("Q6_K", 512, 1024)])
+def test_rows_beyond_half_range(lw, tmp_path, ty, n, k):
+    """fp32 activations far outside fp16's range (the input of a down projection in an unnormalised model) through the
+    paths that feed the tensor cores fp16: every row is brought into range by a power of two and the product scaled
+    back, so the result is finite and as accurate as for ordinary rows; rows that fit are converted as they are."""
+    rng = np.random.default_rng(n * 7 + k)
+    q, side = orc.synth_codes(ty, n, k, rng), orc.synth_side(ty, n, k, rng)
+    w = orc.dequant(ty, q, side)
+    wr = lw.bundle.Writer(str(tmp_path / "b"))
+    wr.add_kquant("l0.down", ty, q, side)
+    wr.close()
+    with lw.Bundle(str(tmp_path / "b")) as b:
+        for m in (8, 33, 70):
+            X = rng.standard_normal((m, k)).astype(np.float32)
+            X[0] *= 3.0e5                                               # every entry of this row overflows fp16
+            X[1, 5] = -7.0e7                                            # one outlier
+            X[m - 1] *= 1.0e-3
+            ref = orc.gemv_f64(w, X)
+            for path in (0, 2) + ((3,) if m <= 64 else ()):
+                got = b.matmul("l0.down", X, path)
+                assert np.isfinite(got).all(), (ty, m, path)
+                for r in range(m):                                      # row by row: the rows differ by 1e11 in size
+                    assert helpers.rel_err(got[r], ref[r]) <= helpers.GEMV_TOL, (ty, m, path, r)
+        assert b.kernel_error() == 0
