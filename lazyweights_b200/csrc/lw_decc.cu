@@ -23,12 +23,12 @@ static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned in
     const int rc = launch_t<FMT, G, IDXBITS, EXPAND>(M, out, tr0, mid, err, st);
     return rc ? rc : launch_t<FMT, G, IDXBITS, EXPAND>(M, out, mid, tr1, err, st);
   }
-  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 + ring_fixed_bytes(max_units) + kRingSlackWords * 4;
+  const size_t fixed = (size_t(1) << (M.index_bits + ring_log_copies(M.index_bits) + 2)) + kLutSize * 4 + ring_fixed_bytes(max_units) + kRingSlackWords * 4;
   if (fixed + static_cast<size_t>(buf_words) * 4 > kSmemLimit) return kErrTooLarge;
   const int slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed) / (buf_words * 4)));
   const int warps = std::max(1, std::min(std::min(kRingMaxWarps, max_units), max_units <= slots ? slots : slots * 3 / 4));
   const size_t smem = fixed + static_cast<size_t>(slots) * buf_words * 4;
-  auto kernel = k_decode_codes_ring<FMT, G, IDXBITS, kRingLogCopies, EXPAND>;
+  auto kernel = k_decode_codes_ring<FMT, G, IDXBITS, ring_log_copies(IDXBITS), EXPAND>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return note_launch("cudaFuncSetAttribute(k_decode_codes_ring)");
   DeccArgs a = {};

@@ -74,8 +74,8 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
     if (got == 0) break;
     if (got < 0) return;
     GroupChain ca, cb;
-    ca.init(u.buf + lane);
-    cb.init(u.buf + u.second * 32u + lane);
+    ca.init(u.buf + lane, kRingLogCopies - LOG_R);
+    cb.init(u.buf + u.second * 32u + lane, kRingLogCopies - LOG_R);
     uint8_t* oa = A.out + (static_cast<size_t>(u.tr) * kTileRows + lane) * A.row_bytes +
                   (static_cast<size_t>(u.j) * kTileSyms + u.seg * USYM) * OUT_PER_SYM;
     uint8_t* ob = oa + static_cast<size_t>(32) * A.row_bytes;
@@ -113,8 +113,8 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
         for (int c = 0; c < PER; ++c) {
           uint32_t ea, eb;
           if (u.cls == 2) {
-            ea = ca.slow_sym(tab1, static_cast<uint32_t>(M.pad));
-            eb = cb.slow_sym(tab1, static_cast<uint32_t>(M.pad));
+            ea = ca.slow_sym(tab1, LOG_R + 2);
+            eb = cb.slow_sym(tab1, LOG_R + 2);
           } else {
             ca.begin();
             cb.begin();

@@ -23,13 +23,13 @@ static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
     const int rc = launch_t<FMT, G, IDXBITS>(M, out, tr0, mid, err, st);
     return rc ? rc : launch_t<FMT, G, IDXBITS>(M, out + static_cast<size_t>(mid - tr0) * kTileRows * M.K, mid, tr1, err, st);
   }
-  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 + 2 * kGemv1MaxSlots * 8 +
+  const size_t fixed = (size_t(1) << (M.index_bits + ring_log_copies(M.index_bits) + 2)) + kLutSize * 4 + 2 * kGemv1MaxSlots * 8 +
                        kGemv1MaxSlots * 4 + 16 + max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
   if (fixed + static_cast<size_t>(buf_words) * 4 > kSmemLimit) return kErrTooLarge;
   const int slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (buf_words * 4)));
   const int warps = std::max(1, std::min(std::min(kGemv1MaxWarps, max_units), max_units <= slots ? slots : slots * 3 / 4));
   const size_t smem = fixed + static_cast<size_t>(slots) * buf_words * 4;
-  auto kernel = k_decw<FMT, G, IDXBITS, kGemv1LogCopies>;
+  auto kernel = k_decw<FMT, G, IDXBITS, ring_log_copies(IDXBITS)>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return note_launch("cudaFuncSetAttribute(k_decw)");
   DecwArgs a = {};

@@ -82,8 +82,8 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
     side_a.load(buf + lines * 32u - SIDEW, lane);
     side_b.load(buf + lines * 32u - SIDEW, lane + 32);
     GroupChain ca, cb;
-    ca.init(buf + lane);
-    cb.init(buf + second * 32u + lane);
+    ca.init(buf + lane, kRingLogCopies - LOG_R);
+    cb.init(buf + second * 32u + lane, kRingLogCopies - LOG_R);
     __half* oa = A.out + (static_cast<size_t>(tr - RA.tr0) * kTileRows + lane) * M.K + static_cast<size_t>(tc) * TW +
                  seg * (TW / SPLIT);
     __half* ob = oa + static_cast<size_t>(32) * M.K;
@@ -149,8 +149,8 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
           for (int c = 0; c < PER; ++c) {
             uint32_t ea, eb;
             if (cls == 2) {
-              ea = ca.slow_sym(tab1, static_cast<uint32_t>(M.pad));
-              eb = cb.slow_sym(tab1, static_cast<uint32_t>(M.pad));
+              ea = ca.slow_sym(tab1, LOG_R + 2);
+              eb = cb.slow_sym(tab1, LOG_R + 2);
             } else {
               ca.begin();
               cb.begin();

@@ -160,7 +160,6 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
   static_assert(TU % kT5Teams == 0 && KU % 16 == 0 && GW % 16 == 0, "team-units are dealt evenly; steps stay inside a sub-block");
   constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
-  constexpr int RSHIFT = kRingLogCopies - LOG_R;
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
   extern __shared__ __align__(128) uint8_t smem[];
   uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
@@ -345,8 +344,8 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
         side_a.load(buf + lines * 32u - SIDEW, lane);
         side_b.load(buf + lines * 32u - SIDEW, lane + 32);
         GroupChain ca, cb;
-        ca.init(buf + lane);
-        cb.init(buf + second * 32u + lane);
+        ca.init(buf + lane, kRingLogCopies - LOG_R);
+        cb.init(buf + second * 32u + lane, kRingLogCopies - LOG_R);
         // One unit: STEPS times sixteen weights of rows l (chain a) and l + 32 (chain b) -> one A slot each.  CLS = the
         // unit's class: 0 groups of G symbols per refill check (fully unrolled, the phase of the groups is static),
         // 1 the window normalised per symbol (exact for any data), 2 symbol by symbol through the single-copy table.
@@ -368,8 +367,8 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
                   ca.begin();
                   cb.begin();
                 }
-                ea = ca.template sym<MASK, RSHIFT>(smem, lane_off);
-                eb = cb.template sym<MASK, RSHIFT>(smem, lane_off);
+                ea = ca.template sym<MASK>(smem, lane_off);
+                eb = cb.template sym<MASK>(smem, lane_off);
                 if (f % G == G - 1 || f == STEPS * SYM16 - 1) {
                   ca.end();
                   cb.end();
@@ -377,13 +376,13 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
               } else if constexpr (CLS == 1) {
                 ca.begin();
                 cb.begin();
-                ea = ca.template sym<MASK, RSHIFT>(smem, lane_off);
-                eb = cb.template sym<MASK, RSHIFT>(smem, lane_off);
+                ea = ca.template sym<MASK>(smem, lane_off);
+                eb = cb.template sym<MASK>(smem, lane_off);
                 ca.end();
                 cb.end();
               } else {
-                ea = ca.slow_sym(tab1, static_cast<uint32_t>(M.pad));
-                eb = cb.slow_sym(tab1, static_cast<uint32_t>(M.pad));
+                ea = ca.slow_sym(tab1, LOG_R + 2);
+                eb = cb.slow_sym(tab1, LOG_R + 2);
               }
               if (PAIR) {
                 w[c] = pack_half2(__fsub_rn(__fmul_rn(s_a, entry_value(ea, 0)), o_a), __fsub_rn(__fmul_rn(s_a, entry_value(ea, 1)), o_a));

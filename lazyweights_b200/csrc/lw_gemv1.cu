@@ -39,6 +39,7 @@ static const Gemv1Env& gemv1_env() {
 // units than its list holds (the caller then covers the rows in several launches).
 template <int FMT>
 static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits, int avail_blocks = 0) {
+  const int log_copies = ring_log_copies(index_bits);
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT);
   constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
   p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
@@ -60,7 +61,7 @@ static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits, i
   // LW_GEMV1_RING=16 where 36 staging buffers still fit (measured: no difference on the bench matrix).
   size_t fixed = 0;
   for (p.tile_ring_log2 = gemv1_env().ring >= 16 ? 4 : 3; p.tile_ring_log2 >= 3; --p.tile_ring_log2) {
-    fixed = (size_t(1) << (index_bits + M.pad)) + kLutSize * 4 +
+    fixed = (size_t(1) << (index_bits + log_copies + 2)) + kLutSize * 4 +
             static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * (TW / sub_width(FMT))) * 4 +
             2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + (size_t(1) << p.tile_ring_log2) * (8 + SPLIT * kTileRows * 4) +
             p.max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
@@ -158,7 +159,7 @@ static int launch_batch_t(int n, const MatDev* const* mats, const void* const* x
   cudaGetDevice(&dev);
   size_t& configured = configured_per_device[dev & 63];
   if (smem > configured) {
-    if (cudaFuncSetAttribute(k_gemv1_batch<FMT, G, IDXBITS, kGemv1LogCopies>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(k_gemv1_batch<FMT, G, IDXBITS, ring_log_copies(IDXBITS)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kSmemLimit)) != cudaSuccess)
       return note_launch("cudaFuncSetAttribute(k_gemv1_batch)");
     configured = kSmemLimit;
@@ -166,7 +167,7 @@ static int launch_batch_t(int n, const MatDev* const* mats, const void* const* x
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
   launch_config(cfg, attr, B->first[n], threads, smem, st, gemv1_env().pdl != 0);
-  cudaLaunchKernelEx(&cfg, k_gemv1_batch<FMT, G, IDXBITS, kGemv1LogCopies>, *B);
+  cudaLaunchKernelEx(&cfg, k_gemv1_batch<FMT, G, IDXBITS, ring_log_copies(IDXBITS)>, *B);
   return note_launch("k_gemv1_batch");
 }
 
@@ -268,7 +269,7 @@ static int launch_i(const MatDev& M, const void* X, bool x_is_half, float* P, fl
   }();
   if (use_limit && M.cmp_tab) return launch_t<FMT, G, 10, kGemv1LogCopies, kReaderLimit>(M, X, x_is_half, P, Y, err, st);
   if (M.index_bits == 10) return launch_t<FMT, G, 10, kGemv1LogCopies>(M, X, x_is_half, P, Y, err, st);
-  return launch_t<FMT, G, 11, kGemv1LogCopies>(M, X, x_is_half, P, Y, err, st);
+  return launch_t<FMT, G, 11, ring_log_copies(11)>(M, X, x_is_half, P, Y, err, st);
 }
 
 template <int FMT>
@@ -291,7 +292,7 @@ static int launch_g(const MatDev& M, const void* X, bool x_is_half, float* P, fl
 bool gemv1_usable(const MatDev& M) {
   const bool fmt_ok = M.fmt >= kFmtQ4K && M.fmt <= kFmtIQ4XS;
   const int gmax = is_paired(M.fmt) ? 4 : 6;
-  return fmt_ok && (M.index_bits == 10 || M.index_bits == 11) && M.pad == kGemv1LogCopies + 2 && M.split == default_split(M.fmt) && M.unit_slow && M.row_done && M.group >= 3 &&
+  return fmt_ok && (M.index_bits == 10 || M.index_bits == 11) && M.pad == kRingLogCopies + 2 && M.split == default_split(M.fmt) && M.unit_slow && M.row_done && M.group >= 3 &&
          M.group <= gmax;
 }
 
@@ -313,3 +314,15 @@ int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P, float
 }
 
 }  // namespace lw
+
+#ifdef LW_GEMV1_PROFILE
+extern "C" int lw_debug_prof(unsigned long long* out, int reset) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out, lw::g_gemv1_prof, sizeof(unsigned long long) * 8) != cudaSuccess) return -1;
+  if (reset) {
+    unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaMemcpyToSymbol(lw::g_gemv1_prof, z, sizeof z);
+  }
+  return 0;
+}
+#endif

@@ -225,6 +225,13 @@ static __device__ __noinline__ void row_sum(const float* p, unsigned int terms, 
   if (lane < 16) reinterpret_cast<float4*>(y)[lane] = acc;
 }
 
+#ifdef LW_GEMV1_PROFILE
+// Built with -DLW_GEMV1_PROFILE, every consumer warp adds up the clock cycles it spends in the phases of its loop; the
+// sums over all warps land here: [0] prologue, [1] drawing a unit and waiting for its copy, [2] decoding, [3] handing
+// the buffer back and meeting the tile's other segments, [4] units, [5] final row sums, [6] whole loop, [7] warps.
+// Read with lw_debug_prof (same build only).  Off by default: the clock reads cost a few instructions per unit.
+__device__ unsigned long long g_gemv1_prof[8];
+#endif
 constexpr int kGemv1MaxTileRing = 16;   // tiles whose segments a block may be combining at one time (8 or 16)
 
 // The work of one block: block `bidx` of the `nblocks` blocks that share matrix M.
@@ -260,6 +267,10 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
   S.init(M, RA, SPLIT, bidx, nblocks);
   const int set = S.set, ncol = S.ncol, nmine = S.nmine;
   pdl_trigger();   // the next kernel of the stream may be set up while this one runs (it waits before it reads)
+#ifdef LW_GEMV1_PROFILE
+  const long long prof_t0 = clock64();
+  long long prof_wait = 0, prof_dec = 0, prof_tail = 0, prof_units = 0;
+#endif
   const bool consumer = warp < A.helpers;   // takes part in the prologue; warps >= RA.warps leave after it
   const int nthr = A.helpers * 32;
 
@@ -407,12 +418,23 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
       cnt_tr = kNone;
     }
   };
+#ifdef LW_GEMV1_PROFILE
+  const long long prof_t1 = clock64();
+#endif
 #pragma unroll 1
   for (;;) {
     Unit u;
+#ifdef LW_GEMV1_PROFILE
+    const long long pfa = clock64();
+#endif
     const int got = ring_draw(RA, RM, nmine, lane, u);
     if (got == 0) break;
     if (got < 0) return;
+#ifdef LW_GEMV1_PROFILE
+    const long long pfb = clock64();
+    prof_wait += pfb - pfa;
+    ++prof_units;
+#endif
     const uint32_t j = u.j, seg = u.seg, tr = u.tr, cls = u.cls;
     const int tc = set + RA.nsets * static_cast<int>(j);
     const uint32_t* xt = xq + static_cast<size_t>(j) * kTileSyms + seg * USYM;
@@ -423,8 +445,8 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
     side_a.load(buf + u.lines * 32u - SIDEW, lane);
     side_b.load(buf + u.lines * 32u - SIDEW, lane + 32);
     GroupChain ca, cb;
-    ca.init(buf + lane);
-    cb.init(buf + u.second * 32u + lane);
+    ca.init(buf + lane, kRingLogCopies - LOG_R);
+    cb.init(buf + u.second * 32u + lane, kRingLogCopies - LOG_R);
     float tot_a = 0.f, tot_b = 0.f;
     // scales of sub-block jj applied to its exact integer sums; the previous unit is counted on the way (see above)
     auto finish_sub = [&](const int jj, int acc_a, int acc_b) {
@@ -482,10 +504,14 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
         if (cls == 1)
           sub_block<2, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
         else
-          sub_block_slow<SPG, PAIR>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG, acc_a, acc_b);
+          sub_block_slow<SPG, PAIR>(ca, cb, tab1, LOG_R + 2, xt + jj * SPG, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
     }
+#ifdef LW_GEMV1_PROFILE
+    const long long pfc = clock64();
+    prof_dec += pfc - pfb;
+#endif
     ring_release(RM, u, lane);
     // the unit's totals meet those of the tile's other segments in shared memory
     constexpr int LOG_SPLIT = SPLIT == 4 ? 2 : SPLIT == 2 ? 1 : 0;
@@ -516,9 +542,27 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
       prow[lane + 32] = pb;
       cnt_tr = tr;
     }
+#ifdef LW_GEMV1_PROFILE
+    prof_tail += clock64() - pfc;
+#endif
   }
+#ifdef LW_GEMV1_PROFILE
+  const long long prof_t2 = clock64();
+#endif
   count();
   resolve();
+#ifdef LW_GEMV1_PROFILE
+  if (lane == 0) {
+    atomicAdd(&g_gemv1_prof[0], static_cast<unsigned long long>(prof_t1 - prof_t0));
+    atomicAdd(&g_gemv1_prof[1], static_cast<unsigned long long>(prof_wait));
+    atomicAdd(&g_gemv1_prof[2], static_cast<unsigned long long>(prof_dec));
+    atomicAdd(&g_gemv1_prof[3], static_cast<unsigned long long>(prof_tail));
+    atomicAdd(&g_gemv1_prof[4], static_cast<unsigned long long>(prof_units));
+    atomicAdd(&g_gemv1_prof[5], static_cast<unsigned long long>(clock64() - prof_t2));
+    atomicAdd(&g_gemv1_prof[6], static_cast<unsigned long long>(prof_t2 - prof_t1));
+    atomicAdd(&g_gemv1_prof[7], 1ull);
+  }
+#endif
 }
 
 template <int FMT, int G, int IDXBITS, int LOG_R, int READER = kReaderTable>

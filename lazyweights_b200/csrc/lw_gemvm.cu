@@ -35,7 +35,7 @@ static bool plan_gemvm(const MatDev& M, int ntr, GemvmPlan& p) {
   }
   p.max_units = (p.max_units + 1) & ~1;
   if (p.max_units > debug_knobs().max_units) return false;
-  const size_t fixed = (size_t(1) << (M.index_bits + M.pad)) + kLutSize * 4 +
+  const size_t fixed = (size_t(1) << (M.index_bits + ring_log_copies(M.index_bits) + 2)) + kLutSize * 4 +
                        static_cast<size_t>(p.cols_per_set) * (kTileSyms + (has_offset ? 2 : 1) * NSB) * MR * 4 +
                        2 * kGemv1MaxSlots * 8 + kGemv1MaxSlots * 4 + 16 + p.max_units * sizeof(UnitMeta) +
                        kRingSlackWords * 4;
@@ -61,7 +61,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, int m, float
     }
     chunks = std::min(NT, std::max(chunks + 1, chunks * p.max_units / debug_knobs().max_units));
   }
-  auto kernel = k_gemvm<FMT, G, IDXBITS, kGemv1LogCopies, MR>;
+  auto kernel = k_gemvm<FMT, G, IDXBITS, ring_log_copies(IDXBITS), MR>;
   static size_t configured_per_device[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
     side_a.load(buf + lines * 32u - SIDEW, lane);
     side_b.load(buf + lines * 32u - SIDEW, lane + 32);
     GroupChain ca, cb;
-    ca.init(buf + lane);
-    cb.init(buf + second * 32u + lane);
+    ca.init(buf + lane, kRingLogCopies - LOG_R);
+    cb.init(buf + second * 32u + lane, kRingLogCopies - LOG_R);
     float tot_a[MR], tot_b[MR];
 #pragma unroll
     for (int r = 0; r < MR; ++r) tot_a[r] = tot_b[r] = 0.f;
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
         if (cls == 1)
           sub_block_m<2, SPG, MASK, MR>(ca, cb, smem, lane_off, xt + jj * SPG * MR, jj * SPG, jj == 3, acc_a, acc_b);
         else
-          sub_block_slow_m<SPG, MR>(ca, cb, tab1, static_cast<uint32_t>(M.pad), xt + jj * SPG * MR, acc_a, acc_b);
+          sub_block_slow_m<SPG, MR>(ca, cb, tab1, LOG_R + 2, xt + jj * SPG * MR, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
     }

@@ -298,16 +298,20 @@ int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, i
 static uint8_t scan_chain(const uint16_t* rel, int n, int quad) {
   uint8_t bad = 0;
   for (int g = kScanMinG; g <= kScanMaxG; ++g) {
-    uint32_t bp = 0;
     bool ok = true;
-    for (int q0 = 0; q0 < n && ok; q0 += quad)
-      for (int i = q0; i < q0 + quad && ok; i += g) {
-        const int last = std::min(i + g, q0 + quad) - 1;   // last symbol of the group
-        if (rel[last] - rel[i] > 31) ok = false;
-        bp += rel[last + 1] - rel[i];
-        if (bp >= 64) ok = false;
-        if (bp >= 32) bp -= 32;
-      }
+    // a kernel that keeps fewer copies of its table starts reading one bit into the chain's pad (lw_ring.cuh,
+    // GroupChain::init): a group must be exact from either starting offset
+    for (uint32_t bp0 = 0; bp0 < 2 && ok; ++bp0) {
+      uint32_t bp = bp0;
+      for (int q0 = 0; q0 < n && ok; q0 += quad)
+        for (int i = q0; i < q0 + quad && ok; i += g) {
+          const int last = std::min(i + g, q0 + quad) - 1;   // last symbol of the group
+          if (rel[last] - rel[i] > 31) ok = false;
+          bp += rel[last + 1] - rel[i];
+          if (bp >= 64) ok = false;
+          if (bp >= 32) bp -= 32;
+        }
+    }
     if (!ok) bad |= static_cast<uint8_t>(1u << (g - kScanMinG));
   }
   return bad;

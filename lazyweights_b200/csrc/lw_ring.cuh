@@ -21,7 +21,14 @@
 
 namespace lw {
 
-constexpr int kRingLogCopies = 4;        // 16 copies of the decode table: 64 KB (1024 windows) or 128 KB (2048)
+constexpr int kRingLogCopies = 4;        // the layout's pad allows up to 16 copies of the decode table
+// Copies a kernel keeps: 16 of a 1024-window table, 8 of a 2048-window table - 64 KB either way.  With 16 copies of the
+// large table (128 KB) too few staging buffers fit beside it, and a block is left with 10 consumer warps instead of 28:
+// measured on a paired 4-bit matrix, the decode loop then waits on its own dependency chain (2.5 warps per scheduler).
+#ifndef LW_LOG_COPIES_11
+#define LW_LOG_COPIES_11 3
+#endif
+__host__ __device__ constexpr int ring_log_copies(int index_bits) { return index_bits == 11 ? LW_LOG_COPIES_11 : kRingLogCopies; }
 constexpr int kRingMaxWarps = 28;        // consumer warps; up to four more warps produce
 constexpr int kRingMaxSlots = 64;        // staging buffers in the ring
 constexpr int kRingMaxUnits = 1024;      // work units one block can be dealt in one launch
@@ -286,12 +293,15 @@ struct GroupChain {
   const uint32_t* p;
   uint32_t w0, w1, w2, bp;   // three stream words; bp = bits consumed so far (its low five bits place the window)
   uint32_t a, b, off;        // window normalised to bp, offset inside the group
-  __device__ __forceinline__ void init(const uint32_t* chain_words) {
+  // bp0: pad bits to skip.  A chain is laid out with kRingLogCopies + 2 leading zero bits; a kernel whose table has
+  // fewer copies (2^LOG_R) wants the window LOG_R + 2 bits up in the shifted word, i.e. starts kRingLogCopies - LOG_R
+  // bits into the pad.
+  __device__ __forceinline__ void init(const uint32_t* chain_words, uint32_t bp0 = 0) {
     w0 = chain_words[0];
     w1 = chain_words[32];
     w2 = chain_words[64];
     p = chain_words + 96;
-    bp = 0;
+    bp = bp0;
   }
   __device__ __forceinline__ void begin() {
     a = __funnelshift_r(w0, w1, bp);
@@ -300,12 +310,10 @@ struct GroupChain {
   }
   // next table entry; tab = replicated table (start of shared memory), lane_off = this lane's byte offset inside the
   // copies of one window, MASK selects the window's address bits
-  // RSHIFT > 0: the table has fewer copies than the chains' leading zero bits were laid out for (2^(LOG_R - RSHIFT)
-  // copies): the window is shifted down onto the smaller stride first
-  template <uint32_t MASK, int RSHIFT = 0>
+  template <uint32_t MASK>
   __device__ __forceinline__ uint32_t sym(const uint8_t* tab, uint32_t lane_off) {
     const uint32_t t = __funnelshift_r(a, b, off);
-    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + (((t >> RSHIFT) & MASK) | lane_off));
+    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + ((t & MASK) | lane_off));
     off = __umulhi(e, 16u) + off;   // e >> 28 = code length
     return e;
   }

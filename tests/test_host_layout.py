@@ -15,9 +15,13 @@ def _funnel(lo, hi, s):
 
 
 def _replay_chain(words, base, lane, lut, pad, index_bits, nsym, group, cls):
-    """symbols of one chain, decoded the way the kernel does for unit class `cls` (lw_gemv1.cuh: GroupChain)"""
+    """symbols of one chain, decoded the way the kernel does for unit class `cls` (lw_ring.cuh: GroupChain).  The
+    kernel keeps 16 copies of a 1024-window table and 8 of a 2048-window one; with 8 it starts one bit into the
+    chain's pad, which puts the window one bit lower in the shifted word."""
     w = lambda i: int(words[base + 32 * i + lane])
-    w0, w1, w2, nxt, bp = w(0), w(1), w(2), 3, 0
+    bp0 = 1 if index_bits == 11 else 0
+    pad -= bp0
+    w0, w1, w2, nxt, bp = w(0), w(1), w(2), 3, bp0
     out = []
     if cls == 2:                                   # symbol by symbol, single-copy table of all 2048 windows
         for _ in range(nsym):
