@@ -235,6 +235,24 @@ long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int K
                          long long side_bytes, int* info, uint32_t* group_base, long long group_base_cap,
                          uint32_t* words, long long words_cap, uint8_t* unit_class, long long unit_class_cap);
 
+/* Pair layout.  For Q6_K and Q5_K matrices whose K is a multiple of 512 the loader keeps a second device layout
+ * that only products of ONE activation row read (lw_linear / lw_linear_batch / lw_linear_static / rt_forward with one
+ * token): two adjacent codes of a row are one symbol of a prefix code built from the matrix's own pair counts (at most
+ * 12 bits for pairs of 6-bit codes, 11 for pairs of 5-bit codes), so that the kernel does one table lookup per two
+ * weights, as it does for the 4-bit formats whose bundle symbols are pairs already.  The decoded codes are the same;
+ * device memory holds the matrix twice (LW_PAIRS=0 in the environment at load: no pair layouts).  No reference
+ * counterpart: the reference's kernel decodes these formats one symbol per weight (kernels/llmrt.cu:972-1024).
+ * lw_matrix_pair_bytes: bytes of the pair layout that one product reads (0: the matrix has none).
+ * lw_host_pairs: host only, builds the layout from decoded codes [N, K] (one per weight; fmt LW_FMT_Q6_K or
+ * LW_FMT_Q5_K) for inspection and CPU replay tests.  info[0..7] = column segments per tile row, pad bits per chain,
+ * symbols per group, index bits of the table, entries of group_base, longest code, words of scales behind every unit,
+ * longest unit in words; table = [1 << index bits] entries length << 28 | value of the second weight << 8 | value of
+ * the first (signed bytes).  Returns the number of layout words; arrays are filled if their capacity suffices. */
+long long lw_matrix_pair_bytes(void* handle, int id);
+long long lw_host_pairs(const uint8_t* codes, int N, int K, int fmt, const uint8_t* side, long long side_bytes, int* info,
+                        uint32_t* table, long long table_cap, uint32_t* group_base, long long group_base_cap,
+                        uint32_t* words, long long words_cap);
+
 /* ---- diagnostics ------------------------------------------------------------------------------------------ */
 
 /* Message of the last failure on the calling thread. */

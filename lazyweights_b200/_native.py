@@ -47,6 +47,9 @@ _SIGNATURES = {
     "lw_matrix_make_twin": (C.c_int, [C.c_void_p, C.c_int]),
     "lw_matrix_drop_twin": (C.c_int, [C.c_void_p, C.c_int]),
     "lw_matrix_twin_bytes": (C.c_longlong, [C.c_void_p, C.c_int]),
+    "lw_matrix_pair_bytes": (C.c_longlong, [C.c_void_p, C.c_int]),
+    "lw_host_pairs": (C.c_longlong, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.POINTER(C.c_int),
+                                     C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong]),
     "lw_linear_twin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "lw_decode_weights": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "lw_decode_codes": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),

@@ -14,7 +14,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblwb200.so")
-SOURCES = ["lw_host.cpp", "lw_blocks.cpp", "lw_kernels.cu", "lw_gemv1.cu", "lw_gemvm.cu", "lw_decw.cu", "lw_decc.cu", "lw_gemm_t5.cu", "lw_capi.cu", "lw_runtime.cu"]
+SOURCES = ["lw_host.cpp", "lw_blocks.cpp", "lw_pairs.cpp", "lw_kernels.cu", "lw_gemv1.cu", "lw_gemvm.cu", "lw_decw.cu", "lw_decc.cu", "lw_gemm_t5.cu", "lw_capi.cu", "lw_runtime.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC,-O3,-Wall,-pthread", "-Xptxas", "-v"]
 

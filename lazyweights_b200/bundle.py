@@ -72,6 +72,25 @@ def host_layout(blob, N, Ks, fmt="none", side=None):
                 max_unit_words=info[7], group_base=gb, words=words, unit_class=uc)
 
 
+def host_pairs(codes, fmt, side):
+    """The pair layout of Q6_K / Q5_K codes [N, K] (one per weight), built on the host (no GPU): dict with split, pad,
+    group, index_bits, max_len, unit_side_words, max_unit_words and the arrays table, group_base, words (uint32)."""
+    q = np.ascontiguousarray(codes, np.uint8)
+    s = np.ascontiguousarray(side, np.uint8).reshape(-1)
+    info = (C.c_int * 8)()
+    args = (q.ctypes.data_as(C.c_void_p), q.shape[0], q.shape[1], nat.FMT[fmt], s.ctypes.data_as(C.c_void_p), s.size, info)
+    n = nat.lib().lw_host_pairs(*args, None, 0, None, 0, None, 0)
+    if n < 0:
+        nat.check(int(n))
+    tab, gb, words = np.zeros(1 << info[3], np.uint32), np.zeros(info[4], np.uint32), np.zeros(n, np.uint32)
+    n = nat.lib().lw_host_pairs(*args, tab.ctypes.data_as(C.c_void_p), tab.size, gb.ctypes.data_as(C.c_void_p), gb.size,
+                                words.ctypes.data_as(C.c_void_p), words.size)
+    if n < 0:
+        nat.check(int(n))
+    return dict(split=info[0], pad=info[1], group=info[2], index_bits=info[3], max_len=info[5], unit_side_words=info[6],
+                max_unit_words=info[7], table=tab, group_base=gb, words=words)
+
+
 def decode_huf8(blob, N, K):
     """blob -> uint8 [N, K] symbols, decoded by the CUDA kernel."""
     from .runtime import CodedMatrix

@@ -44,6 +44,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Host-side result of validating, indexing and re-laying out one blob: everything that goes to the device.
 struct HostImage {
+  PairImage pair;   // fmt == kFmtNone: the matrix has no pair layout
   std::vector<uint16_t> lut;
   std::vector<uint32_t> fat, symtab, cmp, group_base, words;
   std::vector<uint8_t> unit_slow;
@@ -81,7 +82,19 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   GroupScan scan;
   scan.quad_syms = 4 * sub_syms(mx.fmt);
   const bool grouped = mx.fmt != kFmtNone && split == default_split(mx.fmt);
-  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, nullptr, grouped ? &scan : nullptr))) return rc;
+  // Q6_K / Q5_K rows of whole 512-weight tiles also get a pair layout for the one-row product (LW_PAIRS=0: none); it
+  // is built from the decoded codes, which the same walk writes out
+  static const bool pairs_wanted = [] {
+    const char* e = getenv("LW_PAIRS");
+    return !(e && e[0] == '0');
+  }();
+  const bool pairs = pairs_wanted && grouped && pair_layout_of(mx.fmt) != kFmtNone && mx.K % 512 == 0 && side;
+  std::vector<uint8_t> codes;
+  if (pairs) codes.resize(static_cast<size_t>(mx.N) * mx.Ks);
+  if ((rc = walk_blob(v, *tab, split, threads, &chain_start, &lane_end, pairs ? codes.data() : nullptr, grouped ? &scan : nullptr)))
+    return rc;
+  if (pairs && (rc = build_pairs(codes.data(), mx.N, mx.K, mx.fmt, side, threads, im.pair))) return rc;
+  codes = std::vector<uint8_t>();
   // The batch-1 kernel's table: 1024 windows (codes up to 10 bits; units that hold a longer code are decoded symbol
   // by symbol) or 2048, 16 copies each; and the group size: units where groups of g symbols are not exact fall back
   // to groups of two.  Estimated cost per symbol: 8.3 instructions + 10 per group; groups of two cost about 22
@@ -138,6 +151,49 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
   return kOk;
 }
 
+// The pair layout as a second device image with a descriptor of its own.
+static int upload_pairs(Matrix& mx, const PairImage& p) {
+  const size_t off_gb = align_up(p.tab32.size() * 4, 256);
+  const size_t off_words = align_up(off_gb + p.group_base.size() * 4, 256);
+  const size_t off_cls = align_up(off_words + p.words.size() * 4, 256);
+  const size_t off_done = off_cls + align_up(p.unit_class.size(), 256);
+  const size_t total = off_done + align_up(static_cast<size_t>(mx.N / kTileRows) * kRowDoneStride * 4, 256);
+  cudaError_t e = cudaMalloc(&mx.d_pair, total);
+  if (e != cudaSuccess) return cuda_fail("cudaMalloc (pair layout)", e);
+  uint8_t* d = static_cast<uint8_t*>(mx.d_pair);
+  if ((e = cudaMemset(d + off_cls, 0, total - off_cls)) != cudaSuccess ||
+      (e = cudaMemcpy(d, p.tab32.data(), p.tab32.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_gb, p.group_base.data(), p.group_base.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_words, p.words.data(), p.words.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (e = cudaMemcpy(d + off_cls, p.unit_class.data(), p.unit_class.size(), cudaMemcpyHostToDevice)) != cudaSuccess)
+    return cuda_fail("cudaMemcpy (pair layout)", e);
+  MatDev& P = mx.pair;
+  P = MatDev{};
+  P.tab32 = reinterpret_cast<const uint32_t*>(d);
+  P.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
+  P.words = reinterpret_cast<const uint32_t*>(d + off_words);
+  P.unit_slow = d + off_cls;
+  P.row_done = reinterpret_cast<unsigned int*>(d + off_done);
+  P.index_bits = p.index_bits;
+  P.group = p.group;
+  P.N = mx.N;
+  P.K = mx.K;
+  P.Ks = mx.K / 2;
+  P.KT = p.KT;
+  P.T = p.T;
+  P.fmt = p.fmt;
+  P.split = p.split;
+  P.reader = 0;
+  P.pad = p.pad;
+  P.max_len = p.max_len;
+  P.max_tile_words = p.max_tile_words;
+  P.max_unit_words = p.max_unit_words;
+  mx.pair_bytes = (p.words.size() - kTailWords) * 4;
+  mx.pair_epoch = 0;
+  mx.device_bytes += total;
+  return kOk;
+}
+
 static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, size_t side_nbytes) {
   const int rc_side = check_side(mx, side, side_nbytes);
   if (rc_side) return rc_side;
@@ -189,7 +245,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   mx.dev.split = im.split;
   mx.dev.max_tile_words = im.max_tile;
   mx.dev.max_unit_words = im.max_unit;
-  return kOk;
+  return im.pair.fmt != kFmtNone && mx.dev.group ? upload_pairs(mx, im.pair) : kOk;
 }
 
 // Validates, indexes, re-lays out and uploads one blob.  Ks = symbols per row.
@@ -233,15 +289,18 @@ static Matrix* matrix_by_id(void* h, int id) {
   return &M->mats[id];
 }
 
-const MatDev* matrix_descriptor(void* handle, int id) {
+static bool reads_pairs(const Matrix& mx, int m) { return m == 1 && mx.d_pair && debug_knobs().pairs; }
+
+const MatDev* matrix_descriptor(void* handle, int id, bool one_row) {
   Matrix* mx = matrix_by_id(handle, id);
   if (!mx || check_device(static_cast<Model*>(handle))) return nullptr;
-  return &mx->dev;
+  return reads_pairs(*mx, one_row ? 1 : 0) ? &mx->pair : &mx->dev;
 }
 
-unsigned int* matrix_clean_epoch(void* handle, int id) {
+unsigned int* matrix_clean_epoch(void* handle, int id, bool one_row) {
   Matrix* mx = matrix_by_id(handle, id);
-  return mx ? &mx->clean_epoch : nullptr;
+  if (!mx) return nullptr;
+  return reads_pairs(*mx, one_row ? 1 : 0) ? &mx->pair_epoch : &mx->clean_epoch;
 }
 
 int check_device(const Model* M) {
@@ -330,9 +389,10 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   const size_t xe = x_half ? 2 : 4;
   for (int r0 = 0; r0 < m; r0 += 8) {
     const int mm = std::min(8, m - r0);
-    const int rc = launch_gemv(mx.dev, static_cast<const uint8_t*>(x) + static_cast<size_t>(r0) * mx.K * xe, x_half,
+    const bool pr = reads_pairs(mx, mm);
+    const int rc = launch_gemv(pr ? mx.pair : mx.dev, static_cast<const uint8_t*>(x) + static_cast<size_t>(r0) * mx.K * xe, x_half,
                                mm, y + static_cast<size_t>(r0) * ldy, ldy, M->d_partials, M->partial_floats, st,
-                               &mx.clean_epoch);
+                               pr ? &mx.pair_epoch : &mx.clean_epoch);
     if (rc) return rc;
   }
   return kOk;
@@ -353,10 +413,10 @@ int linear_batch_device(Model* M, int n, const int* mat_index, const float* cons
     }
     const size_t need = (gemv_partial_floats(mx.dev, 1) + 63) & ~size_t(63);
     if (off + need > M->partial_floats) return kErrTooLarge;
-    mats[j] = &mx.dev;
+    mats[j] = reads_pairs(mx, 1) ? &mx.pair : &mx.dev;
     xv[j] = xs[j];
     partials[j] = M->d_partials + off;
-    epochs[j] = &mx.clean_epoch;
+    epochs[j] = reads_pairs(mx, 1) ? &mx.pair_epoch : &mx.clean_epoch;
     off += need;
   }
   return launch_gemv_batch(n, mats, xv, false, ys, partials, st, epochs);
@@ -388,6 +448,7 @@ int lw_debug_set(const char* key, long long value) {
   else if (s == "wait_limit" && value >= 1 && value <= (1ll << 30)) k.wait_limit = static_cast<uint32_t>(value);
   else if (s == "drop_unit" && value >= -1 && value < 1024) k.drop_unit = static_cast<int>(value);
   else if (s == "t5_min_rows" && value >= 1 && value <= 65) k.t5_min_rows = static_cast<int>(value);
+  else if (s == "pairs" && (value == 0 || value == 1)) k.pairs = static_cast<int>(value);
   else if (s == "reset") k = DebugKnobs();
   else {
     set_error("lw_debug_set: unknown key or value out of range (%s)", key);
@@ -586,9 +647,9 @@ int lw_linear_batch(int n, void* const* handles, const int* ids, const void* con
         set_error("lw_linear_batch: the products of one handle need more scratch than the handle holds");
         return kErrTooLarge;
       }
-      mats[j] = &mx->dev;
+      mats[j] = reads_pairs(*mx, 1) ? &mx->pair : &mx->dev;
       partials[j] = M->d_partials + off;
-      epochs[j] = &mx->clean_epoch;
+      epochs[j] = reads_pairs(*mx, 1) ? &mx->pair_epoch : &mx->clean_epoch;
       off += need;
     }
     const int rc = launch_gemv_batch(c, mats, xs_dev + i0, x_is_half != 0, ys_dev + i0, partials, st, epochs);
@@ -917,6 +978,37 @@ long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int K
   if (unit_class && unit_class_cap >= static_cast<long long>(im.unit_slow.size()) && !im.unit_slow.empty())
     std::memcpy(unit_class, im.unit_slow.data(), im.unit_slow.size());
   return static_cast<long long>(im.words.size());
+}
+
+long long lw_host_pairs(const uint8_t* codes, int N, int K, int fmt, const uint8_t* side, long long side_bytes_n, int* info,
+                        uint32_t* table, long long table_cap, uint32_t* group_base, long long group_base_cap,
+                        uint32_t* words, long long words_cap) {
+  if (!codes || !info || !side || side_bytes_n != static_cast<long long>(N) * (K / 256) * side_bytes(fmt)) {
+    set_error("lw_host_pairs: bad argument");
+    return kErrArg;
+  }
+  PairImage p;
+  const int rc = build_pairs(codes, N, K, fmt, side, default_threads(), p);
+  if (rc) return rc;
+  info[0] = p.split;
+  info[1] = p.pad;
+  info[2] = p.group;
+  info[3] = p.index_bits;
+  info[4] = static_cast<int>(p.group_base.size());
+  info[5] = p.max_len;
+  info[6] = unit_side_words(p.fmt);
+  info[7] = static_cast<int>(p.max_unit_words);
+  if (table && table_cap >= static_cast<long long>(p.tab32.size())) std::memcpy(table, p.tab32.data(), p.tab32.size() * 4);
+  if (group_base && group_base_cap >= static_cast<long long>(p.group_base.size()))
+    std::memcpy(group_base, p.group_base.data(), p.group_base.size() * 4);
+  if (words && words_cap >= static_cast<long long>(p.words.size())) std::memcpy(words, p.words.data(), p.words.size() * 4);
+  return static_cast<long long>(p.words.size());
+}
+
+long long lw_matrix_pair_bytes(void* handle, int id) {
+  Matrix* mx = matrix_by_id(handle, id);
+  if (!mx) return -1;
+  return mx->d_pair ? static_cast<long long>(mx->pair_bytes) : 0;
 }
 
 int lw_validate_bundle(const char* dir) {

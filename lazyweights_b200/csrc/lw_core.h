@@ -28,11 +28,22 @@ constexpr int kBlobAlign = 256;
 constexpr int kTailWords = 512;   // zero words after the last group: read-ahead of the last chains lands here
 
 // Block formats of the side bytes (reference: kernels/llmrt.cu:113-121, scripts/a2_kq_bundle.py:41-42).
-enum Format : int { kFmtNone = 0, kFmtQ4K = 1, kFmtQ5K = 2, kFmtQ6K = 3, kFmtIQ4XS = 4 };
+// kFmtQ6KP / kFmtQ5KP are not bundle formats: they name the pair layouts that the loader builds for Q6_K / Q5_K matrices
+// (lw::build_pairs: two adjacent codes become one symbol of a code of its own, so that the one-row kernel does one
+// table lookup per two weights, as it does for the formats whose symbols are pairs already).  Geometry as Q4_K: tiles of
+// 64 rows x 256 symbols = 512 weights.
+enum Format : int { kFmtNone = 0, kFmtQ4K = 1, kFmtQ5K = 2, kFmtQ6K = 3, kFmtIQ4XS = 4, kFmtQ6KP = 5, kFmtQ5KP = 6 };
 
 constexpr int side_bytes(int f) { return f == kFmtQ6K ? 18 : f == kFmtIQ4XS ? 8 : 16; }
-constexpr int sub_width(int f) { return f == kFmtQ6K ? 16 : 32; }
-constexpr bool is_paired(int f) { return f == kFmtQ4K || f == kFmtIQ4XS; }
+constexpr int sub_width(int f) { return (f == kFmtQ6K || f == kFmtQ6KP) ? 16 : 32; }
+constexpr bool is_paired(int f) { return f == kFmtQ4K || f == kFmtIQ4XS || f == kFmtQ6KP || f == kFmtQ5KP; }
+constexpr bool is_pair_layout(int f) { return f == kFmtQ6KP || f == kFmtQ5KP; }
+constexpr int pair_layout_of(int f) { return f == kFmtQ6K ? kFmtQ6KP : f == kFmtQ5K ? kFmtQ5KP : kFmtNone; }
+// Longest code a pair layout's own code may have = index bits of its table: 1024 pairs of 5-bit codes fit 11 bits; the
+// 4096 pairs of 6-bit codes need 12, but a matrix in which at most 2048 different pairs occur gets an 11-bit code where
+// that costs under one per cent of size (the 2048-window table has twice the copies for the same shared memory: fewer
+// bank conflicts per lookup).
+constexpr int pair_code_bits_max(int f) { return f == kFmtQ6KP ? 12 : 11; }
 // Column segments per tile row of the device layout: more segments = shorter chains = more of them in flight for the
 // same staging memory; a segment must hold whole quads of sub-blocks (four 32-weight sub-blocks of Q5_K = 128 symbols).
 constexpr int default_split(int f) { return f == kFmtNone ? 1 : f == kFmtQ5K ? 2 : 4; }
@@ -41,7 +52,11 @@ constexpr int default_split(int f) { return f == kFmtNone ? 1 : f == kFmtQ5K ? 2
 //   Q6_K    word[r] = the four int8 scales;                      half[2 * 64 + r] = fp16 d
 //   IQ4_XS  word[r] = the four 6-bit scales (one per byte);      half[2 * 64 + r] = fp16 d
 //   Q4_K / Q5_K  word[r] = fp16 d | fp16 dmin << 16; word[64 + r] = the four 6-bit scales; word[128 + r] = the mins
-constexpr int unit_side_words(int f) { return f == kFmtNone ? 0 : (f == kFmtQ6K || f == kFmtIQ4XS) ? 96 : 192; }
+//   Q6KP    word[r], word[64 + r] = the eight int8 scales of the unit's 128 weights; half[4 * 64 + r] = fp16 d
+//   Q5KP    as Q5_K
+constexpr int unit_side_words(int f) {
+  return f == kFmtNone ? 0 : f == kFmtQ6KP ? 160 : (f == kFmtQ6K || f == kFmtIQ4XS) ? 96 : 192;
+}
 // Symbols per sub-block (one scale), and per quad of sub-blocks
 constexpr int sub_syms(int f) { return is_paired(f) ? sub_width(f) / 2 : sub_width(f); }
 

@@ -41,7 +41,7 @@ template <int FMT>
 static bool plan_gemv1(const MatDev& M, int ntr, Gemv1Plan& p, int index_bits, int avail_blocks = 0) {
   const int log_copies = ring_log_copies(index_bits);
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT);
-  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K || FMT == kFmtQ5KP;
   p.nsets = (M.KT + kMaxStagedColumns - 1) / kMaxStagedColumns;
   p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
   // a chain reader looks up to three words past its chain; for all buffers but the last that lands in the next buffer
@@ -181,17 +181,23 @@ static int launch_batch_i(int n, const MatDev* const* mats, const void* const* x
 template <int FMT>
 static int launch_batch_g(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
                           float* const* ys, unsigned int* err, cudaStream_t st) {
-  switch (mats[0]->group) {
-    case 3: return launch_batch_i<FMT, 3>(n, mats, xs, x_is_half, partials, ys, err, st);
-    case 4: return launch_batch_i<FMT, 4>(n, mats, xs, x_is_half, partials, ys, err, st);
-  }
-  if constexpr (!is_paired(FMT)) {
+  if constexpr (is_pair_layout(FMT)) {   // groups of three; the table of the layout's own code, 2048 or 4096 windows
+    if constexpr (pair_code_bits_max(FMT) == 12)
+      if (mats[0]->index_bits == 12) return launch_batch_t<FMT, 3, 12>(n, mats, xs, x_is_half, partials, ys, err, st);
+    return launch_batch_t<FMT, 3, 11>(n, mats, xs, x_is_half, partials, ys, err, st);
+  } else {
     switch (mats[0]->group) {
-      case 5: return launch_batch_i<FMT, 5>(n, mats, xs, x_is_half, partials, ys, err, st);
-      case 6: return launch_batch_i<FMT, 6>(n, mats, xs, x_is_half, partials, ys, err, st);
+      case 3: return launch_batch_i<FMT, 3>(n, mats, xs, x_is_half, partials, ys, err, st);
+      case 4: return launch_batch_i<FMT, 4>(n, mats, xs, x_is_half, partials, ys, err, st);
     }
+    if constexpr (!is_paired(FMT)) {
+      switch (mats[0]->group) {
+        case 5: return launch_batch_i<FMT, 5>(n, mats, xs, x_is_half, partials, ys, err, st);
+        case 6: return launch_batch_i<FMT, 6>(n, mats, xs, x_is_half, partials, ys, err, st);
+      }
+    }
+    return kErrTooLarge;
   }
-  return kErrTooLarge;
 }
 
 int launch_gemv1_batch(int n, const MatDev* const* mats, const void* const* xs, bool x_is_half, float* const* partials,
@@ -212,6 +218,8 @@ int launch_gemv1_batch(int n, const MatDev* const* mats, const void* const* xs, 
     case kFmtQ4K: return launch_batch_g<kFmtQ4K>(n, mats, xs, x_is_half, partials, ys, err, st);
     case kFmtQ5K: return launch_batch_g<kFmtQ5K>(n, mats, xs, x_is_half, partials, ys, err, st);
     case kFmtIQ4XS: return launch_batch_g<kFmtIQ4XS>(n, mats, xs, x_is_half, partials, ys, err, st);
+    case kFmtQ6KP: return launch_batch_g<kFmtQ6KP>(n, mats, xs, x_is_half, partials, ys, err, st);
+    case kFmtQ5KP: return launch_batch_g<kFmtQ5KP>(n, mats, xs, x_is_half, partials, ys, err, st);
     default: return launch_batch_g<kFmtQ6K>(n, mats, xs, x_is_half, partials, ys, err, st);
   }
 }
@@ -274,22 +282,31 @@ static int launch_i(const MatDev& M, const void* X, bool x_is_half, float* P, fl
 
 template <int FMT>
 static int launch_g(const MatDev& M, const void* X, bool x_is_half, float* P, float* Y, unsigned int* err, cudaStream_t st) {
-  if (M.reader == 1) return launch_t<FMT, 3, 10, kGemv1LogCopies, kReaderFixed>(M, X, x_is_half, P, Y, err, st);
-  switch (M.group) {
-    case 3: return launch_i<FMT, 3>(M, X, x_is_half, P, Y, err, st);
-    case 4: return launch_i<FMT, 4>(M, X, x_is_half, P, Y, err, st);
-  }
-  if constexpr (!is_paired(FMT)) {
+  if constexpr (is_pair_layout(FMT)) {
+    if constexpr (pair_code_bits_max(FMT) == 12)
+      if (M.index_bits == 12) return launch_t<FMT, 3, 12, ring_log_copies(12)>(M, X, x_is_half, P, Y, err, st);
+    return launch_t<FMT, 3, 11, ring_log_copies(11)>(M, X, x_is_half, P, Y, err, st);
+  } else {
+    if (M.reader == 1) return launch_t<FMT, 3, 10, kGemv1LogCopies, kReaderFixed>(M, X, x_is_half, P, Y, err, st);
     switch (M.group) {
-      case 5: return launch_i<FMT, 5>(M, X, x_is_half, P, Y, err, st);
-      case 6: return launch_i<FMT, 6>(M, X, x_is_half, P, Y, err, st);
+      case 3: return launch_i<FMT, 3>(M, X, x_is_half, P, Y, err, st);
+      case 4: return launch_i<FMT, 4>(M, X, x_is_half, P, Y, err, st);
     }
+    if constexpr (!is_paired(FMT)) {
+      switch (M.group) {
+        case 5: return launch_i<FMT, 5>(M, X, x_is_half, P, Y, err, st);
+        case 6: return launch_i<FMT, 6>(M, X, x_is_half, P, Y, err, st);
+      }
+    }
+    set_kernel_error_text("gemv1", "no kernel for this group size");
+    return kErrArg;
   }
-  set_kernel_error_text("gemv1", "no kernel for this group size");
-  return kErrArg;
 }
 
 bool gemv1_usable(const MatDev& M) {
+  if (is_pair_layout(M.fmt))
+    return (M.index_bits == 11 || M.index_bits == pair_code_bits_max(M.fmt)) && M.pad == kRingLogCopies + 2 && M.split == default_split(M.fmt) && M.unit_slow && M.row_done &&
+           M.group == 3 && M.reader == 0;
   const bool fmt_ok = M.fmt >= kFmtQ4K && M.fmt <= kFmtIQ4XS;
   const int gmax = is_paired(M.fmt) ? 4 : 6;
   return fmt_ok && (M.index_bits == 10 || M.index_bits == 11) && M.pad == kRingLogCopies + 2 && M.split == default_split(M.fmt) && M.unit_slow && M.row_done && M.group >= 3 &&
@@ -309,6 +326,8 @@ int launch_gemv1(const MatDev& M, const void* X, bool x_is_half, float* P, float
     case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, P, Y, err, st);
     case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, P, Y, err, st);
     case kFmtIQ4XS: return launch_g<kFmtIQ4XS>(M, X, x_is_half, P, Y, err, st);
+    case kFmtQ6KP: return launch_g<kFmtQ6KP>(M, X, x_is_half, P, Y, err, st);
+    case kFmtQ5KP: return launch_g<kFmtQ5KP>(M, X, x_is_half, P, Y, err, st);
     default: return launch_g<kFmtQ6K>(M, X, x_is_half, P, Y, err, st);
   }
 }

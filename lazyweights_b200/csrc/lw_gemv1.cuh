@@ -40,8 +40,8 @@ __device__ __forceinline__ int mac_result(int acc) {
 // sub-block's activation words (one per symbol: the int16 pair of a paired symbol's two weights, or one int16 in the
 // low half).  `first` = index of the sub-block's first symbol within its quad (fixes the phase of the groups); `last`:
 // the quad ends with this sub-block.
-template <int G, int SPG, uint32_t MASK, bool PAIR>
-__device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const uint8_t* tab, uint32_t lane_off,
+template <int G, int SPG, uint32_t MASK, bool PAIR, class CH>
+__device__ __forceinline__ void sub_block(CH& ca, CH& cb, const uint8_t* tab, uint32_t lane_off,
                                           const uint32_t* xq, const int first, const bool last, int& acc_a,
                                           int& acc_b) {
   uint4 x = make_uint4(0u, 0u, 0u, 0u);
@@ -64,8 +64,8 @@ __device__ __forceinline__ void sub_block(GroupChain& ca, GroupChain& cb, const 
   }
 }
 
-template <int SPG, bool PAIR>
-__device__ __forceinline__ void sub_block_slow(GroupChain& ca, GroupChain& cb, const uint32_t* tab32, uint32_t pad,
+template <int SPG, bool PAIR, class CH>
+__device__ __forceinline__ void sub_block_slow(CH& ca, CH& cb, const uint32_t* tab32, uint32_t pad,
                                                const uint32_t* xq, int& acc_a, int& acc_b) {
 #pragma unroll 2
   for (int c = 0; c < SPG; ++c) {
@@ -243,9 +243,12 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
   constexpr int GW = sub_width(FMT), SPG = sub_syms(FMT), SIDEW = unit_side_words(FMT);
   constexpr int NSU = TW / GW / SPLIT;                            // sub-blocks per unit
   constexpr int USYM = kTileSyms / SPLIT;                         // symbols (= activation words) per chain
-  static_assert(NSU == 4, "a unit is one quad of sub-blocks");
-  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  static_assert(NSU == 4 || NSU == 8, "a unit is four sub-blocks (eight of the 16-weight sub-blocks of a Q6_K pair layout)");
+  constexpr bool PAIR_LAYOUT = is_pair_layout(FMT);
+  static_assert(!PAIR_LAYOUT || READER == kReaderTable, "pair layouts are read through their table");
+  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K || FMT == kFmtQ5KP;
   constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;              // windows, copies of the table
+  constexpr bool SINGLE = NIDX <= kLutSize;                       // a single-copy table of all 2048 windows beside it
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
   // the table area: the replicated Huffman table; or, for the other readers, [256][32] grid values (+ [12][32] offsets)
   constexpr int kReplicatedTableBytes = READER == kReaderTable ? NIDX * R * 4 : NIDX * R * 4 >= 34 * 1024 ? NIDX * R * 4 : 34 * 1024;
@@ -333,10 +336,10 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
 #pragma unroll
     for (int i = 0; i < TAB_PRE; ++i) {
       const int i0 = (i * A.helpers + warp) * 32;
-      if (i0 < NIDX) table_spread<LOG_R>(tab, tab1, i0, tab_pre[i], lane);
+      if (i0 < NIDX) table_spread<LOG_R, SINGLE>(tab, tab1, i0, tab_pre[i], lane);
     }
     for (int i0 = (TAB_PRE * A.helpers + warp) * 32; i0 < NIDX; i0 += A.helpers * 32)
-      table_spread<LOG_R>(tab, tab1, i0, __ldg(M.tab32 + i0 + lane), lane);
+      table_spread<LOG_R, SINGLE>(tab, tab1, i0, __ldg(M.tab32 + i0 + lane), lane);
 #pragma unroll
     for (int i = 0; i < T1_PRE; ++i) {
       const int idx = NIDX + i * nthr + static_cast<int>(threadIdx.x);
@@ -444,7 +447,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
     UnitSide<FMT> side_a, side_b;
     side_a.load(buf + u.lines * 32u - SIDEW, lane);
     side_b.load(buf + u.lines * 32u - SIDEW, lane + 32);
-    GroupChain ca, cb;
+    typename ChainOf<PAIR_LAYOUT>::type ca, cb;
     ca.init(buf + lane, kRingLogCopies - LOG_R);
     cb.init(buf + u.second * 32u + lane, kRingLogCopies - LOG_R);
     float tot_a = 0.f, tot_b = 0.f;
@@ -469,7 +472,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
     // The common class has its four sub-blocks to itself, so that its code is contiguous: 28 warps at different
     // program counters share the instruction cache (`no_instruction` stalls were 0.9 per issued instruction with the
     // fallback bodies interleaved).
-    if (READER == kReaderFixed) {
+    if constexpr (READER == kReaderFixed) {
       constexpr int NW = SPG * (FMT == kFmtQ5K ? 5 : FMT == kFmtQ6K ? 6 : 8) / 32;   // words per sub-block and chain
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
@@ -478,7 +481,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
                                   static_cast<uint32_t>(lane) << 2, xt + jj * SPG, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
-    } else if (READER == kReaderLimit) {
+    } else if constexpr (READER == kReaderLimit) {
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         int acc_a = 0, acc_b = 0;
@@ -490,19 +493,19 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
                                              jj * SPG, jj == 3, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
-    } else if (cls == 0) {
+    } else if (PAIR_LAYOUT || cls == 0) {   // a pair layout has no other class
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
+      for (int jj = 0; jj < NSU; ++jj) {
         int acc_a = 0, acc_b = 0;
-        sub_block<G, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+        sub_block<G, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == NSU - 1, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
-    } else {
+    } else if constexpr (!PAIR_LAYOUT) {
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
+      for (int jj = 0; jj < NSU; ++jj) {
         int acc_a = 0, acc_b = 0;
         if (cls == 1)
-          sub_block<2, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == 3, acc_a, acc_b);
+          sub_block<2, SPG, MASK, PAIR>(ca, cb, smem, lane_off, xt + jj * SPG, jj * SPG, jj == NSU - 1, acc_a, acc_b);
         else
           sub_block_slow<SPG, PAIR>(ca, cb, tab1, LOG_R + 2, xt + jj * SPG, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
@@ -514,7 +517,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
 #endif
     ring_release(RM, u, lane);
     // the unit's totals meet those of the tile's other segments in shared memory
-    constexpr int LOG_SPLIT = SPLIT == 4 ? 2 : SPLIT == 2 ? 1 : 0;
+    constexpr int LOG_SPLIT = SPLIT == 8 ? 3 : SPLIT == 4 ? 2 : SPLIT == 2 ? 1 : 0;
     static_assert((1 << LOG_SPLIT) == SPLIT, "power of two");
     const uint32_t tl = static_cast<uint32_t>(u.k) >> LOG_SPLIT, ts = tl & (ring - 1), tgen = tl >> A.tile_ring_log2;
     if (!wait_released(tile_free + ts, tgen, RA.err, RA.wait_limit)) return;   // the ring slot's previous tile has been handed back

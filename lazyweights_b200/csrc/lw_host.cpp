@@ -411,9 +411,13 @@ int walk_blob(const BlobView& v, const HuffTable& tab, int split, int threads, s
 // sc / mn: one value per byte; dd: fp16 d (low half) and fp16 dmin (reference block formulas: kernels/llmrt.cu:126-149).
 static void unit_scales(int fmt, const uint8_t* side_row, int tc, int seg, int split, uint32_t* sc, uint32_t* mn,
                         uint32_t* dd) {
-  const int sb = side_bytes(fmt);
   const int subs_per_tile = (is_paired(fmt) ? 512 : 256) / sub_width(fmt);
-  const int sub0 = tc * subs_per_tile + seg * (subs_per_tile / split);   // first sub-block, counted along the row
+  unit_scales_at(fmt, side_row, tc * subs_per_tile + seg * (subs_per_tile / split), sc, mn, dd);
+}
+
+// The same for the four sub-blocks sub0 .. sub0 + 3, counted along the row (they must lie in one super-block).
+void unit_scales_at(int fmt, const uint8_t* side_row, int sub0, uint32_t* sc, uint32_t* mn, uint32_t* dd) {
+  const int sb = side_bytes(fmt);
   const int per_block = 256 / sub_width(fmt);                            // sub-blocks per super-block
   const uint8_t* blk = side_row + static_cast<size_t>(sub0 / per_block) * sb;
   const int j0 = sub0 % per_block;

@@ -71,6 +71,32 @@ int relayout(const BlobView& v, int split, int pad, const std::vector<uint32_t>&
              std::vector<uint32_t>& words, uint32_t* max_unit_words, uint32_t* max_tile_words, int fmt = kFmtNone,
              const uint8_t* side = nullptr);
 
+// Scales of four consecutive sub-blocks sub0 .. sub0 + 3 of one row (sub-blocks counted along the row; all four inside
+// one 256-weight super-block): sc / mn one value per byte, dd = fp16 d (low half) and fp16 dmin.
+void unit_scales_at(int fmt, const uint8_t* side_row, int sub0, uint32_t* sc, uint32_t* mn, uint32_t* dd);
+
+// ---- pair layout (lw_pairs.cpp)
+// A second device layout for Q6_K / Q5_K matrices, read by the one-row product only: two adjacent codes of a row become
+// one symbol, the pairs get a length-limited prefix code of their own (12 bits for pairs of 6-bit codes, 11 for pairs of
+// 5-bit codes; the code is built from the matrix's pair counts like the bundle's code is from its symbol counts), and
+// the rows are laid out like a paired format's: tiles of 64 rows x 256 pair symbols, four column segments, chains of
+// 64 symbols interleaved by lane, the unit's scales behind its second group.  The kernel then does one table lookup
+// and one dp2a per two weights.  The decoded codes are identical by construction; what changes is the entropy code
+// that device memory holds (its size is within a per cent of the bundle's: pairs cost no more bits than two singles).
+struct PairImage {
+  int fmt = kFmtNone;                  // kFmtQ6KP or kFmtQ5KP
+  int index_bits = 0, group = 3, split = 4, pad = 6, KT = 0, T = 0, max_len = 0;
+  std::vector<uint32_t> tab32;         // [1 << index_bits] length << 28 | value of the second weight << 8 | of the first
+  std::vector<uint32_t> group_base;    // [T * 8 + 1]
+  std::vector<uint32_t> words;         // interleaved chain words + unit scales (+ zero tail)
+  std::vector<uint8_t> unit_class;     // [T * 4], all 0: groups of three are exact for codes of at most 12 bits
+  uint32_t max_unit_words = 0, max_tile_words = 0;
+  long long code_bits = 0;             // bits of all pair codes (without padding)
+};
+// sym = decoded codes [N, K] (one per weight), fmt = kFmtQ6K or kFmtQ5K, side = the matrix's side bytes.
+// K must be a multiple of 512 and N of 64.
+int build_pairs(const uint8_t* sym, int N, int K, int fmt, const uint8_t* side, int threads, PairImage& out);
+
 // ---- bundle directory (reference: lazyweights/bundle.py:114-148)
 struct TensorEntry {
   std::string name, enc;

@@ -492,7 +492,7 @@ static int static_partials(float** out) {
 extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_is_half, int m, float* y_dev,
                                 void* stream) {
   using namespace lw;
-  const MatDev* M = matrix_descriptor(handle, id);
+  const MatDev* M = matrix_descriptor(handle, id, m == 1);
   if (!M) return kErrGeneric;
   if (!x_dev || !y_dev || m < 1 || m > 8) {
     set_kernel_error_text("lw_linear_static", "bad argument (m must be 1..8)");
@@ -512,7 +512,7 @@ extern "C" int lw_linear_static(void* handle, int id, const void* x_dev, int x_i
   const int rc = static_partials(&scratch);
   if (rc) return rc;
   return launch_gemv(*M, x_dev, x_is_half != 0, m, y_dev, M->N, scratch, kStaticPartialFloats,
-                     static_cast<cudaStream_t>(stream), matrix_clean_epoch(handle, id));
+                     static_cast<cudaStream_t>(stream), matrix_clean_epoch(handle, id, m == 1));
 }
 
 namespace lw {

@@ -80,8 +80,10 @@ int launch_wait_probe(unsigned int limit, int* gave_up);
 void set_kernel_error_text(const char* what, const char* detail);
 // Device descriptor of matrix `id` of a handle (implemented next to the handle type), or null; and that matrix's
 // clean-epoch note (see launch_gemv).
-const MatDev* matrix_descriptor(void* handle, int id);
-unsigned int* matrix_clean_epoch(void* handle, int id);
+// one_row: the descriptor (and its counter epoch) a product of ONE activation row reads - the matrix's pair layout
+// where it has one
+const MatDev* matrix_descriptor(void* handle, int id, bool one_row = false);
+unsigned int* matrix_clean_epoch(void* handle, int id, bool one_row = false);
 // Kernels launched by this library since it was loaded.
 long long launch_count();
 

@@ -29,6 +29,12 @@ struct Matrix {
   MatDev twin{};
   size_t twin_bytes = 0;          // chain words + unit scales: what one product of the twin reads
   unsigned int twin_epoch = 0;
+  // pair layout (lw::build_pairs; Q6_K / Q5_K with K a multiple of 512): what the one-row product reads instead of
+  // `dev` - the other kernels keep reading the bundle's own code
+  void* d_pair = nullptr;
+  MatDev pair{};
+  size_t pair_bytes = 0;
+  unsigned int pair_epoch = 0;
 };
 
 struct Runtime;   // decoder state, defined in lw_runtime.cu
@@ -61,6 +67,7 @@ struct Model {
     for (auto& m : mats) {
       if (m.d_block) cudaFree(m.d_block);
       if (m.d_twin) cudaFree(m.d_twin);
+      if (m.d_pair) cudaFree(m.d_pair);
     }
     if (d_partials) cudaFree(d_partials);
     if (d_x) cudaFree(d_x);

@@ -22,13 +22,17 @@
 namespace lw {
 
 constexpr int kRingLogCopies = 4;        // the layout's pad allows up to 16 copies of the decode table
-// Copies a kernel keeps: 16 of a 1024-window table, 8 of a 2048-window table - 64 KB either way.  With 16 copies of the
+// Copies a kernel keeps: 16 of a 1024-window table, 8 of a 2048-window table, 4 of a 4096-window table (pair layouts)
+// - 64 KB either way.  (Measured on the pair layout of Q6_K, 14336 x 4096: 8 copies of its 4096-window table = 128 KB
+// leave 10 consumer warps, 23.3 instead of 20.1 us per product; so do units of half the size with either table.)  With 16 copies of the
 // large table (128 KB) too few staging buffers fit beside it, and a block is left with 10 consumer warps instead of 28:
 // measured on a paired 4-bit matrix, the decode loop then waits on its own dependency chain (2.5 warps per scheduler).
 #ifndef LW_LOG_COPIES_11
 #define LW_LOG_COPIES_11 3
 #endif
-__host__ __device__ constexpr int ring_log_copies(int index_bits) { return index_bits == 11 ? LW_LOG_COPIES_11 : kRingLogCopies; }
+__host__ __device__ constexpr int ring_log_copies(int index_bits) {
+  return index_bits == 12 ? 2 : index_bits == 11 ? LW_LOG_COPIES_11 : kRingLogCopies;   // 64 KB in every case
+}
 constexpr int kRingMaxWarps = 28;        // consumer warps; up to four more warps produce
 constexpr int kRingMaxSlots = 64;        // staging buffers in the ring
 constexpr int kRingMaxUnits = 1024;      // work units one block can be dealt in one launch
@@ -340,18 +344,69 @@ struct GroupChain {
   }
 };
 
+// The reader of the pair layouts (lw::build_pairs): every group starts by loading its three words from the chain at
+// the word its bit position has reached - no refill, no branch, nothing kept between groups but the position - so a
+// group may use up any number of words.  What remains of the grouping rule is that its last symbol starts within 31
+// bits of its first: always true for groups of three symbols of at most 12 bits.  (Measured on the 11-bit codes of
+// the bundle formats this reader is a few per cent slower than GroupChain: two more shared-memory loads per group.  A
+// variant of GroupChain that holds a fourth word and refills up to twice per group was measured on the pair layout too:
+// 119 M instead of 81 M instructions for eight 14336 x 4096 products, 22.4 instead of 18.3 us each.)
+struct ReloadChain {
+  const uint32_t* base;
+  uint32_t bp;
+  uint32_t a, b, off;
+  __device__ __forceinline__ void init(const uint32_t* chain_words, uint32_t bp0 = 0) {
+    base = chain_words;
+    bp = bp0;
+  }
+  __device__ __forceinline__ void begin() {
+    const uint32_t* q = base + (bp >> 5) * 32u;
+    const uint32_t w0 = q[0], w1 = q[32], w2 = q[64];
+    a = __funnelshift_r(w0, w1, bp);
+    b = __funnelshift_r(w1, w2, bp);
+    off = 0;
+  }
+  template <uint32_t MASK>
+  __device__ __forceinline__ uint32_t sym(const uint8_t* tab, uint32_t lane_off) {
+    const uint32_t t = __funnelshift_r(a, b, off);
+    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + ((t & MASK) | lane_off));
+    off = __umulhi(e, 16u) + off;
+    return e;
+  }
+  __device__ __forceinline__ void end() { bp += off; }
+  __device__ __forceinline__ uint32_t slow_sym(const uint32_t* tab32, uint32_t pad) {
+    const uint32_t* q = base + (bp >> 5) * 32u;
+    const uint32_t e = tab32[(__funnelshift_r(q[0], q[32], bp) >> pad) & (kLutSize - 1)];
+    bp += e >> 28;
+    return e;
+  }
+};
+
+template <bool RELOAD>
+struct ChainOf {
+  using type = GroupChain;
+};
+template <>
+struct ChainOf<true> {
+  using type = ReloadChain;
+};
+
 // Scales of the unit's two rows (row `lane` and row `lane + 32`), read from the block that follows the unit's chain
 // words in its staging buffer (layout: lw::unit_side_words).  sub(j) = (scale, offset) of sub-block j (a constant
 // after unrolling): weight = scale * f(code) - offset, every operation rounded separately in float32 (llama.cpp's
 // block formulas; reference: scripts/a2_kq_bundle.py:50-68, kernels/llmrt.cu:126-149).
 template <int FMT>
 struct UnitSide {
-  uint32_t sc, mn, dd;
+  uint32_t sc, mn, dd;   // Q6KP: mn = scales of sub-blocks 4..7
   __device__ __forceinline__ void load(const uint32_t* sb, int row) {
-    if (FMT == kFmtQ4K || FMT == kFmtQ5K) {
+    if (FMT == kFmtQ4K || FMT == kFmtQ5K || FMT == kFmtQ5KP) {
       dd = sb[row];
       sc = sb[64 + row];
       mn = sb[128 + row];
+    } else if (FMT == kFmtQ6KP) {
+      sc = sb[row];
+      mn = sb[64 + row];
+      dd = reinterpret_cast<const uint16_t*>(sb)[256 + row];
     } else {
       sc = sb[row];
       dd = reinterpret_cast<const uint16_t*>(sb)[128 + row];
@@ -359,8 +414,8 @@ struct UnitSide {
     }
   }
   __device__ __forceinline__ void sub(int j, float& s, float& o) const {
-    const uint32_t q = (sc >> (8 * j)) & 255u;
-    if (FMT == kFmtQ6K) {
+    const uint32_t q = ((FMT == kFmtQ6KP && j >= 4 ? mn : sc) >> (8 * (j & 3))) & 255u;
+    if (FMT == kFmtQ6K || FMT == kFmtQ6KP) {
       s = __fmul_rn(half_bits_to_float(dd), static_cast<float>(static_cast<int8_t>(q)));
       o = 0.f;
     } else if (FMT == kFmtIQ4XS) {

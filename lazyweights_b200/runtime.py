@@ -114,6 +114,10 @@ class _Handle:
     def twin_bytes(self, name):
         return int(nat.lib().lw_matrix_twin_bytes(self._h, self.matrix_id(name)))
 
+    def pair_bytes(self, name):
+        """Bytes of the matrix's pair layout that a one-row product reads (0: the matrix has none)."""
+        return int(nat.lib().lw_matrix_pair_bytes(self._h, self.matrix_id(name)))
+
     def linear_twin(self, name, x, out=None):
         """y[N] = W x for one activation row, read from the twin (make_twin first)."""
         torch = _torch()

@@ -22,7 +22,7 @@ def lw():
     assert pkg.lib().lw_kernel_error() == 0
 
 
-@pytest.mark.parametrize("ty,n,k", [("Q6_K", 4096, 1024), ("Q4_K", 2048, 4096), ("Q5_K", 4096, 2048)])
+@pytest.mark.parametrize("ty,n,k", [("Q6_K", 4096, 2048), ("Q4_K", 2048, 4096), ("Q5_K", 4096, 2048)])
 def test_products_over_several_launches(lw, ty, n, k):
     """With the per-block unit list capped at a few units a product runs as many launches over ranges of tile rows,
     the way a matrix with more tile rows than one list holds does; results must not change."""
@@ -35,7 +35,7 @@ def test_products_over_several_launches(lw, ty, n, k):
         before = lw.lib().lw_launch_count()
         mat.linear("m", x[0])
         one = lw.lib().lw_launch_count() - before
-        assert lw.lib().lw_debug_set(b"max_units", 4) == 0                # 256 or 512 tiles, at most 148 or 296 per launch
+        assert lw.lib().lw_debug_set(b"max_units", 4) == 0                # 256 or 512 tiles (of 512 weights for the one-row product), at most 148 per launch
         before = lw.lib().lw_launch_count()
         got1 = mat.linear("m", x[0]).cpu().numpy()
         assert lw.lib().lw_launch_count() - before > one                  # really several launches

@@ -41,9 +41,14 @@ def test_twin_equals_coded_product(lw, ty, n, k):
         assert mat.twin_bytes("m") >= n * k * bits // 8                  # fixed-width codes plus the unit scales
         for dt in (np.float16, np.float32):
             x = torch.from_numpy(rng.standard_normal(k).astype(dt)).cuda()
+            # the twin has the unit structure of the bundle's own code: same sums in the same order (a Q5_K / Q6_K
+            # matrix with whole 512-weight tiles is otherwise read through its pair layout, whose units are wider)
+            assert lw.lib().lw_debug_set(b"pairs", 0) == 0
             coded = mat.linear("m", x).cpu().numpy()
+            assert lw.lib().lw_debug_set(b"pairs", 1) == 0
             twin = mat.linear_twin("m", x).cpu().numpy()[0]
             assert np.array_equal(twin, coded)
+            assert helpers.rel_err(mat.linear("m", x).cpu().numpy(), coded) <= 1e-5
             assert helpers.rel_err(twin, orc.gemv_f64(w, x.cpu().numpy().astype(np.float32)[None])[0]) <= helpers.GEMV_TOL
         mat.drop_twin("m")
         with pytest.raises(lw.LwError):
@@ -81,6 +86,7 @@ def test_limit_register_decoder_equals_table_decoder(lw, tmp_path):
     for mode in ("table", "limit"):
         env = dict(os.environ)
         env.pop("LW_GEMV1_LOOKUP", None)
+        env["LW_PAIRS"] = "0"   # both decoders read the bundle's own code (a pair layout has its own table reader)
         if mode == "limit":
             env["LW_GEMV1_LOOKUP"] = "limit"
         path = str(tmp_path / (mode + ".npz"))
@@ -210,4 +216,45 @@ def test_rows_beyond_half_range(lw, tmp_path, ty, n, k):
                 assert np.isfinite(got).all(), (ty, m, path)
                 for r in range(m):                                      # row by row: the rows differ by 1e11 in size
                     assert helpers.rel_err(got[r], ref[r]) <= helpers.GEMV_TOL, (ty, m, path, r)
+        assert b.kernel_error() == 0
+
+
+@pytest.mark.parametrize("ty,n,k,narrow", [("Q6_K", 512, 1024, False), ("Q5_K", 256, 2048, False), ("Q6_K", 192, 1536, False),
+                                            ("Q6_K", 256, 1024, True)])
+def test_pair_layout_product(lw, tmp_path, ty, n, k, narrow):
+    """Q6_K / Q5_K matrices whose rows are whole 512-weight tiles carry a pair layout that the one-row products read
+    (two weights per table lookup): same product as through the bundle's own code, both against the oracle; single
+    launch, batched launch and the allocation-free entry point."""
+    import torch
+    rng = np.random.default_rng(n + 3 * k)
+    q, side = orc.synth_codes(ty, n, k, rng), orc.synth_side(ty, n, k, rng)
+    hi = 31 if ty == "Q5_K" else 63
+    if narrow:   # few different pairs: the pair code fits 11 bits and the kernel keeps 8 copies of a 2048-window table
+        q = np.clip(np.rint(rng.normal(32.0, 1.5, q.shape)), 0, 63).astype(np.uint8)
+    else:
+        q[:64, :256] = rng.integers(0, hi + 1, (64, 256))               # rare pairs: the longest codes of the pair code
+    w = orc.dequant(ty, q, side)
+    wr = lw.bundle.Writer(str(tmp_path / "b"))
+    wr.add_kquant("a", ty, q, side)
+    wr.add_kquant("b", ty, q[::-1].copy(), side[::-1].copy())
+    wr.close()
+    with lw.Bundle(str(tmp_path / "b")) as b:
+        assert b.pair_bytes("a") > 0
+        for dt in (np.float32, np.float16):
+            x = rng.standard_normal(k).astype(dt)
+            xd = torch.from_numpy(x).cuda()
+            ref = orc.gemv_f64(w, x.astype(np.float32)[None])[0]
+            y_pair = b.linear("a", xd).cpu().numpy()
+            assert lw.lib().lw_debug_set(b"pairs", 0) == 0
+            y_code = b.linear("a", xd).cpu().numpy()
+            assert lw.lib().lw_debug_set(b"pairs", 1) == 0
+            assert helpers.rel_err(y_pair, ref) <= helpers.GEMV_TOL and helpers.rel_err(y_code, ref) <= helpers.GEMV_TOL
+            assert helpers.rel_err(y_pair, y_code) <= 1e-5              # same integer sums, another order of float adds
+        x = torch.from_numpy(rng.standard_normal(k).astype(np.float32)).cuda()
+        ya, yb = (torch.empty(n, dtype=torch.float32, device="cuda") for _ in range(2))
+        lw.ProductBatch([(b, "a", x, ya), (b, "b", x, yb)]).launch()
+        assert np.array_equal(ya.cpu().numpy(), b.linear("a", x).cpu().numpy())
+        assert helpers.rel_err(yb.cpu().numpy(), orc.gemv_f64(w[::-1], x.cpu().numpy()[None])[0]) <= helpers.GEMV_TOL
+        X = rng.standard_normal((3, k)).astype(np.float32)              # more rows: the bundle's code, as before
+        assert helpers.rel_err(b.matmul("a", X), orc.gemv_f64(w, X)) <= helpers.GEMV_TOL
         assert b.kernel_error() == 0

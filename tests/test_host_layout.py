@@ -125,3 +125,93 @@ def test_unit_scales_follow_the_chains(ty, n, k):
                     s, o = d * (b - (32 if ty == "IQ4_XS" else 0)), np.zeros(4, np.float32)
                 assert np.array_equal(s.astype(np.float32), s_ref[tr * 64 + r, sub0:sub0 + 4])
                 assert np.array_equal(o.astype(np.float32), o_ref[tr * 64 + r, sub0:sub0 + 4])
+
+
+def _replay_pair_chain(words, base, lane, table, pad, index_bits, nsym, group):
+    """pair symbols (value bytes) of one chain of a pair layout, read the way the kernel's reload reader does: every
+    group loads three words at the word its bit position has reached; the reader starts 4 - log2(copies) bits into
+    the pad (4 copies of a 4096-window table, 8 of a 2048-window one)"""
+    bp0 = 4 - (2 if index_bits == 12 else 3)                     # 4096 windows: 4 copies; 2048: 8 copies
+    shift = pad - bp0
+    bp, out = bp0, []
+    a = b = off = 0
+    for i in range(nsym):
+        if i % group == 0:
+            q = base + 32 * (bp >> 5) + lane
+            w0, w1, w2 = int(words[q]), int(words[q + 32]), int(words[q + 64])
+            a, b, off = _funnel(w0, w1, bp), _funnel(w1, w2, bp), 0
+        assert off < 32
+        e = int(table[(_funnel(a, b, off) >> shift) & ((1 << index_bits) - 1)])
+        assert e >> 28, "window without a code"
+        out.append(e & 0xFFFF)
+        off += e >> 28
+        if i % group == group - 1 or i == nsym - 1:
+            bp += off
+    return out
+
+
+@pytest.mark.parametrize("ty,n,k", [("Q6_K", 128, 1024), ("Q5_K", 64, 512), ("Q6_K", 64, 1536)])
+def test_pair_layout_replayed_on_cpu(ty, n, k):
+    """The pair layout of Q6_K / Q5_K: every chain decodes (on the CPU, with the kernel's bit arithmetic) to the value
+    bytes of its row's code pairs, and the scales behind every unit are the oracle's sub-block scales."""
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=5 + n + k)
+    _tail_block(ty, q, rng, slice(0, 64), slice(64, 192))         # long codes back to back in one unit
+    q[32:40, :] = rng.integers(0, 64 if ty == "Q6_K" else 32, (8, k))   # rows of rare pairs: the longest codes
+    lay = lw.bundle.host_pairs(q, ty, side)
+    L = lay["index_bits"]                                         # rows of rare pairs: more than 2048 different pairs
+    assert L == (12 if ty == "Q6_K" else 11)
+    assert lay["split"] == 4 and lay["pad"] == 6 and lay["group"] == 3 and lay["max_len"] <= L
+    bias = 32 if ty == "Q6_K" else 0
+    KT = k // 512
+    for t in range((n // 64) * KT):
+        tr, tc = divmod(t, KT)
+        for seg in range(4):
+            for half in range(2):
+                base = int(lay["group_base"][t * 8 + 2 * seg + half])
+                for lane in range(0, 32, 3):
+                    got = _replay_pair_chain(lay["words"], base, lane, lay["table"], 6, L, 64, 3)
+                    row = tr * 64 + half * 32 + lane
+                    c = q[row, tc * 512 + seg * 128: tc * 512 + (seg + 1) * 128].astype(np.int64) - bias
+                    want = ((c[0::2] & 255) | ((c[1::2] & 255) << 8)).tolist()
+                    assert got == want, (t, seg, half, lane)
+    # scales: rows r of unit (t, seg) against the oracle's per-sub-block scales
+    sc, mn = orc.sub_scales(ty, side.reshape(n * k // 256, -1))          # [blocks, sub-blocks]
+    sc, mn = sc.reshape(n, -1), mn.reshape(n, -1)                         # [row, sub-block along the row]
+    nsub = 8 if ty == "Q6_K" else 4
+    sw = lay["unit_side_words"]
+    for t in range((n // 64) * KT):
+        tr, tc = divmod(t, KT)
+        for seg in range(4):
+            end = int(lay["group_base"][t * 8 + 2 * seg + 2])             # the scales are the unit's last words
+            sd = lay["words"][end - sw:end]
+            for r in (0, 17, 63):
+                row = tr * 64 + r
+                sub0 = (tc * 512 + seg * 128) // (16 if ty == "Q6_K" else 32)
+                if ty == "Q6_K":
+                    d = np.frombuffer(sd.tobytes(), np.float16)[256 + r].astype(np.float32)
+                    ints = np.frombuffer(np.array([sd[r], sd[64 + r]], np.uint32).tobytes(), np.int8).astype(np.float32)
+                    got = d * ints
+                    assert np.array_equal(got, sc[row, sub0:sub0 + nsub]), (t, seg, r)
+                else:
+                    dd = np.frombuffer(np.array([sd[r]], np.uint32).tobytes(), np.float16).astype(np.float32)
+                    s6 = np.frombuffer(np.array([sd[64 + r]], np.uint32).tobytes(), np.uint8).astype(np.float32)
+                    m6 = np.frombuffer(np.array([sd[128 + r]], np.uint32).tobytes(), np.uint8).astype(np.float32)
+                    assert np.array_equal(dd[0] * s6, sc[row, sub0:sub0 + nsub]), (t, seg, r)
+                    assert np.array_equal(dd[1] * m6, mn[row, sub0:sub0 + nsub]), (t, seg, r)
+
+
+def test_pair_code_width_follows_the_data():
+    """Pairs of 6-bit codes get an 11-bit code when at most 2048 different pairs occur and the limit costs little
+    (here: codes from a narrow spread), else a 12-bit one; the layout replays to the same codes."""
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    q, side, sym, w, rng = helpers.seeded_case("Q6_K", 64, 1024, seed=3)
+    q = np.clip(np.rint(rng.normal(32.0, 1.5, q.shape)), 0, 63).astype(np.uint8)
+    lay = lw.bundle.host_pairs(q, "Q6_K", side)
+    assert lay["index_bits"] == 11 and lay["max_len"] <= 11
+    for lane in (0, 9, 31):
+        got = _replay_pair_chain(lay["words"], int(lay["group_base"][3]), lane, lay["table"], 6, 11, 64, 3)
+        c = q[32 + lane, 128:256].astype(np.int64) - 32
+        assert got == ((c[0::2] & 255) | ((c[1::2] & 255) << 8)).tolist()
