@@ -41,7 +41,7 @@ constexpr bool is_pair_layout(int f) { return f == kFmtQ6KP || f == kFmtQ5KP; }
 constexpr int pair_layout_of(int f) { return f == kFmtQ6K ? kFmtQ6KP : f == kFmtQ5K ? kFmtQ5KP : kFmtNone; }
 // Longest code a pair layout's own code may have = index bits of its table: 1024 pairs of 5-bit codes fit 11 bits; the
 // 4096 pairs of 6-bit codes need 12, but a matrix in which at most 2048 different pairs occur gets an 11-bit code where
-// that costs under one per cent of size (the 2048-window table has twice the copies for the same shared memory: fewer
+// that costs at most a fifth more code bits (the 2048-window table has twice the copies for the same shared memory: fewer
 // bank conflicts per lookup).
 constexpr int pair_code_bits_max(int f) { return f == kFmtQ6KP ? 12 : 11; }
 // Column segments per tile row of the device layout: more segments = shorter chains = more of them in flight for the

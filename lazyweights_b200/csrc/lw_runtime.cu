@@ -76,6 +76,7 @@ struct Runtime {
   float *h = nullptr, *xn = nullptr, *att = nullptr, *o = nullptr, *qkv = nullptr, *g = nullptr, *u = nullptr;
   float *logits = nullptr, *logits_all = nullptr, *cosv = nullptr, *sinv = nullptr, *lnf = nullptr;
   float* attn_part = nullptr;   // [max_batch][H][max_chunks][Dh + 2]
+  unsigned int* attn_done = nullptr;   // [max_batch][H] chunk blocks finished per (token, head group); zero between passes
   int max_chunks = 1;
   int* ids = nullptr;          // device: max_batch token ids, then the position of the pass (read by the kernels, so
                                // that a captured graph replays at any position, as kernels/llmrt.cu:1308 does)
@@ -330,133 +331,222 @@ __global__ void k_rope_cache(float* __restrict__ qkv, const float* __restrict__ 
 }
 
 // Causal attention, split over the context so that a long context fills the GPU (one query token of one head is a
-// single reduction otherwise).  k_attn_part: block (head, token, chunk of kAttnChunk positions) -> the chunk's score
-// maximum, its sum of exponentials and the unnormalised weighted sum of v; k_attn_combine merges the chunks of one
-// (head, token) with the usual running-maximum rescaling.  Per-query arithmetic does not depend on how many tokens the
-// pass carries.
-constexpr int kAttnChunk = 128, kAttnThreads = 256, kAttnMaxDh = 128;
+// single reduction otherwise).  k_attn: block (group of query heads, token, chunk of kAttnChunk positions) -> the chunk's
+// score maximum, its sum of exponentials and the unnormalised weighted sum of v; the block that finishes LAST for a
+// (head group, token) merges the chunks with the usual running-maximum rescaling (a counter per (token, head group)
+// that the last block sets back to zero), so no second kernel and no wait: every block but one just leaves.  Per-query
+// arithmetic does not depend on how many tokens the pass carries, nor on which block happens to be last (the merge
+// always runs over the chunks in order).  Chunks of 64 positions: 256 blocks for a context of 2048 and 8 kv heads
+// (with 128 positions and a separate merge kernel attention took 0.51 of 3.51 ms per token of the 7B-shaped model).
+constexpr int kAttnChunk = 64, kAttnThreads = 256, kAttnMaxDh = 128;
 constexpr int kAttnStride = kAttnMaxDh / 2 + 1;   // words per staged row: odd, so 32 consecutive rows hit 32 banks
 
 // GH query heads that share one kv head (grouped-query attention) per block: the chunk's keys, then its values, are
 // staged once in shared memory (16-byte loads) and serve all of them.
 template <int GH>
 __global__ void __launch_bounds__(kAttnThreads)
-    k_attn_part(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
-                float* __restrict__ part, const int* __restrict__ posp, int H, int Hk, int Dh, int Tmax, float scale,
-                int window, int max_chunks) {
+    k_attn(const float* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc,
+           float* __restrict__ part, float* __restrict__ att, unsigned int* __restrict__ done,
+           const int* __restrict__ posp, int H, int Hk, int Dh, int Tmax, float scale, int window, int max_chunks) {
   dep_begin();
   __shared__ uint32_t kv[kAttnChunk * kAttnStride];
   __shared__ float qs[GH][kAttnMaxDh];
   __shared__ float sc[GH][kAttnChunk];
-  constexpr int HT = GH >= 2 ? GH / 2 : 1;   // heads per thread: the two halves of the block split the heads
+  __shared__ unsigned int s_last;
+  constexpr int SLOTS = kAttnThreads / kAttnChunk;          // head slots of the score phase (4)
+  constexpr int HS = (GH + SLOTS - 1) / SLOTS;              // heads per slot (1)
+  constexpr int HV = GH >= 2 ? GH / 2 : 1;                  // heads per thread of the value phase: two halves of the block
   const int head0 = blockIdx.x * GH, j = blockIdx.y, c = blockIdx.z, kh = head0 / (H / Hk), last = *posp + j;
   const int lo = window > 0 ? max(0, last - window + 1) : 0;
   const int p0 = lo + c * kAttnChunk, n = min(kAttnChunk, last + 1 - p0);
-  auto out_of = [&](int h) { return part + ((static_cast<size_t>(j) * H + head0 + h) * max_chunks + c) * (Dh + 2); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto out_of = [&](int h, int chunk) { return part + ((static_cast<size_t>(j) * H + head0 + h) * max_chunks + chunk) * (Dh + 2); };
   if (n <= 0) {   // chunk beyond this token's causal range
     if (threadIdx.x < GH) {
-      float* out = out_of(threadIdx.x);
+      float* out = out_of(threadIdx.x, c);
       out[0] = -INFINITY;
       out[1] = 0.f;
     }
-    return;
-  }
-  const float* q = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head0) * Dh;
-  for (int i = threadIdx.x; i < GH * Dh; i += kAttnThreads) qs[i / Dh][i % Dh] = q[i];
-  const int cpr = Dh / 8;   // 16-byte pieces per row
-  auto stage = [&](const __half* src) {
-    for (int idx = threadIdx.x; idx < kAttnChunk * cpr; idx += kAttnThreads) {
-      const int t = idx / cpr, ch = idx - t * cpr;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (t < n) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * Dh) + ch);
-      uint32_t* d = kv + t * kAttnStride + ch * 4;
-      d[0] = v.x;
-      d[1] = v.y;
-      d[2] = v.z;
-      d[3] = v.w;
-    }
-  };
-  stage(kc + (static_cast<size_t>(kh) * Tmax + p0) * Dh);
-  __syncthreads();
-  const int t = threadIdx.x & (kAttnChunk - 1), hp = threadIdx.x / kAttnChunk, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (hp * HT < GH) {   // scores of position t against this thread's heads
-    float acc[HT];
+  } else {
+    const float* q = qkv + static_cast<size_t>(j) * (H + 2 * Hk) * Dh + static_cast<size_t>(head0) * Dh;
+    for (int i = threadIdx.x; i < GH * Dh; i += kAttnThreads) qs[i / Dh][i % Dh] = q[i];
+    const int cpr = Dh / 8;   // 16-byte pieces per row
+    auto stage = [&](const __half* src) {
+      for (int idx = threadIdx.x; idx < kAttnChunk * cpr; idx += kAttnThreads) {
+        const int t = idx / cpr, ch = idx - t * cpr;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (t < n) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * Dh) + ch);
+        uint32_t* d = kv + t * kAttnStride + ch * 4;
+        d[0] = v.x;
+        d[1] = v.y;
+        d[2] = v.z;
+        d[3] = v.w;
+      }
+    };
+    stage(kc + (static_cast<size_t>(kh) * Tmax + p0) * Dh);
+    // the chunk's values are requested now and parked in registers while the scores are computed: their DRAM latency
+    // hides behind the score phase instead of following it
+    constexpr int VPT = kAttnChunk * (kAttnMaxDh / 8) / kAttnThreads;   // 16-byte pieces per thread (4)
+    uint4 vreg[VPT];
+    {
+      const __half* vsrc = vc + (static_cast<size_t>(kh) * Tmax + p0) * Dh;
 #pragma unroll
-    for (int h = 0; h < HT; ++h) acc[h] = 0.f;
-    const uint32_t* kr = kv + t * kAttnStride;
-    for (int w = 0; w < Dh / 2; ++w) {
-      const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kr + w));
-#pragma unroll
-      for (int h = 0; h < HT; ++h) {
-        const float2 qq = *reinterpret_cast<const float2*>(&qs[hp * HT + h][2 * w]);
-        acc[h] = fmaf(qq.x, kk.x, acc[h]);
-        acc[h] = fmaf(qq.y, kk.y, acc[h]);
+      for (int u = 0; u < VPT; ++u) {
+        const int idx = threadIdx.x + u * kAttnThreads, t = idx / cpr, ch = idx - t * cpr;
+        vreg[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (idx < kAttnChunk * cpr && t < n) vreg[u] = __ldg(reinterpret_cast<const uint4*>(vsrc + static_cast<size_t>(t) * Dh) + ch);
       }
     }
+    __syncthreads();
+    {   // scores of position t against the heads of this thread's slot
+      const int t = threadIdx.x & (kAttnChunk - 1), slot = threadIdx.x / kAttnChunk;
+      if (slot * HS < GH) {
+        float acc[HS];
 #pragma unroll
-    for (int h = 0; h < HT; ++h) sc[hp * HT + h][t] = t < n ? acc[h] * scale : -INFINITY;
+        for (int h = 0; h < HS; ++h) acc[h] = 0.f;
+        const uint32_t* kr = kv + t * kAttnStride;
+        for (int w = 0; w < Dh / 2; ++w) {
+          const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kr + w));
+#pragma unroll
+          for (int h = 0; h < HS; ++h) {
+            if (slot * HS + h < GH) {
+              const float2 qq = *reinterpret_cast<const float2*>(&qs[slot * HS + h][2 * w]);
+              acc[h] = fmaf(qq.x, kk.x, acc[h]);
+              acc[h] = fmaf(qq.y, kk.y, acc[h]);
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < HS; ++h)
+          if (slot * HS + h < GH) sc[slot * HS + h][t] = t < n ? acc[h] * scale : -INFINITY;
+      }
+    }
+    __syncthreads();
+    if (warp < GH) {   // one warp per head: maximum, exponentials, their sum
+      constexpr int PER = kAttnChunk / 32;
+      float s4[PER], mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        s4[i] = sc[warp][lane + 32 * i];
+        mx = fmaxf(mx, s4[i]);
+      }
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const float e = __expf(s4[i] - mx);   // exp(-inf) = 0 for the positions past n
+        sc[warp][lane + 32 * i] = e;
+        sum += e;
+      }
+      for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane == 0) {
+        float* out = out_of(warp, c);
+        out[0] = mx;
+        out[1] = sum;
+      }
+    }
+    __syncthreads();   // scores final, keys no longer needed
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int idx = threadIdx.x + u * kAttnThreads, t = idx / cpr, ch = idx - t * cpr;
+      if (idx < kAttnChunk * cpr) {
+        uint32_t* d = kv + t * kAttnStride + ch * 4;
+        d[0] = vreg[u].x;
+        d[1] = vreg[u].y;
+        d[2] = vreg[u].z;
+        d[3] = vreg[u].w;
+      }
+    }
+    __syncthreads();
+    const int t = threadIdx.x & (kAttnMaxDh - 1), hp = threadIdx.x / kAttnMaxDh;   // t = output dimension
+    if (hp * HV < GH && t < Dh) {
+      float acc[HV];
+#pragma unroll
+      for (int h = 0; h < HV; ++h) acc[h] = 0.f;
+      const __half* vcol = reinterpret_cast<const __half*>(kv) + t;
+      for (int p = 0; p < n; ++p) {
+        const float v = __half2float(vcol[p * (2 * kAttnStride)]);
+#pragma unroll
+        for (int h = 0; h < HV; ++h) acc[h] = fmaf(sc[hp * HV + h][p], v, acc[h]);
+      }
+#pragma unroll
+      for (int h = 0; h < HV; ++h) out_of(hp * HV + h, c)[2 + t] = acc[h];
+    }
+  }
+  // the last block of this (token, head group) merges all chunks
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* cnt = done + static_cast<size_t>(j) * gridDim.x + blockIdx.x;
+    const unsigned int old = atomicAdd(cnt, 1u);
+    s_last = old == gridDim.z - 1 ? 1u : 0u;
+    if (s_last) *cnt = 0u;   // ready for the next pass
   }
   __syncthreads();
-  if (warp < GH) {   // one warp per head: maximum, exponentials, their sum
-    float s4[4], mx = -INFINITY;
+  if (!s_last) return;
+  __threadfence();
+  // Merge.  The chunks' maxima and sums first (one load per thread), the weights exp(m_c - max) by one warp per head,
+  // then every output sums its chunks with the loads of 16 chunks in flight at a time (they are L2 round trips: one
+  // after the other, as a plain loop over the chunks issues them, they took longer than the attention itself).
+  const int nchunks = gridDim.z;
+  float* wgt = reinterpret_cast<float*>(kv);              // [GH][nchunks] weights (the staging area is free now)
+  float* sums = wgt + GH * nchunks;                        // [GH][nchunks]
+  float* tot_s = qs[0];                                    // [GH]
+  constexpr int kMergeMax = kAttnChunk * kAttnStride / (2 * GH);   // chunks whose weights fit the staging area
+  if (nchunks <= kMergeMax) {
+    for (int i = threadIdx.x; i < GH * nchunks; i += kAttnThreads) {
+      const int h = i / nchunks, ch = i - h * nchunks;
+      const float* pc = out_of(h, ch);
+      wgt[i] = __ldcg(pc);
+      sums[i] = __ldcg(pc + 1);
+    }
+    __syncthreads();
+    if (warp < GH) {
+      float mx = -INFINITY;
+      for (int ch = lane; ch < nchunks; ch += 32) mx = fmaxf(mx, wgt[warp * nchunks + ch]);
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float tot = 0.f;
+      for (int ch = lane; ch < nchunks; ch += 32) {
+        const float sm = sums[warp * nchunks + ch];
+        const float w = sm > 0.f ? __expf(wgt[warp * nchunks + ch] - mx) : 0.f;
+        wgt[warp * nchunks + ch] = w;
+        tot += sm * w;
+      }
+      for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      if (lane == 0) tot_s[warp] = tot;
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < GH * Dh; o += kAttnThreads) {
+      const int h = o / Dh, d = o - h * Dh;
+      const float* col = out_of(h, 0) + 2 + d;
+      const float* w = wgt + h * nchunks;
+      float a = 0.f;
+      for (int c0 = 0; c0 < nchunks; c0 += 16) {
+        float v[16];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      s4[i] = sc[warp][lane + 32 * i];
-      mx = fmaxf(mx, s4[i]);
-    }
-    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
+        for (int u = 0; u < 16; ++u) v[u] = c0 + u < nchunks ? __ldcg(col + static_cast<size_t>(c0 + u) * (Dh + 2)) : 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float e = __expf(s4[i] - mx);   // exp(-inf) = 0 for the positions past n
-      sc[warp][lane + 32 * i] = e;
-      sum += e;
+        for (int u = 0; u < 16; ++u) a = fmaf(c0 + u < nchunks ? w[c0 + u] : 0.f, v[u], a);   // in chunk order
+      }
+      att[static_cast<size_t>(j) * H * Dh + static_cast<size_t>(head0 + h) * Dh + d] = a / tot_s[h];
     }
-    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) {
-      float* out = out_of(warp);
-      out[0] = mx;
-      out[1] = sum;
-    }
+    return;
   }
-  __syncthreads();   // scores final, keys no longer needed
-  stage(vc + (static_cast<size_t>(kh) * Tmax + p0) * Dh);
-  __syncthreads();
-  if (hp * HT < GH && t < Dh) {   // t is now the output dimension
-    float acc[HT];
-#pragma unroll
-    for (int h = 0; h < HT; ++h) acc[h] = 0.f;
-    const __half* vcol = reinterpret_cast<const __half*>(kv) + t;
-    for (int p = 0; p < n; ++p) {
-      const float v = __half2float(vcol[p * (2 * kAttnStride)]);
-#pragma unroll
-      for (int h = 0; h < HT; ++h) acc[h] = fmaf(sc[hp * HT + h][p], v, acc[h]);
+  for (int o = threadIdx.x; o < GH * Dh; o += kAttnThreads) {   // very long contexts: chunk by chunk
+    const int h = o / Dh, d = o - h * Dh;
+    float mx = -INFINITY;
+    for (int ch = 0; ch < nchunks; ++ch) mx = fmaxf(mx, __ldcg(out_of(h, ch)));
+    float tot = 0.f, a = 0.f;
+    for (int ch = 0; ch < nchunks; ++ch) {
+      const float* pc = out_of(h, ch);
+      const float sum = __ldcg(pc + 1);
+      if (sum > 0.f) {
+        const float w = __expf(__ldcg(pc) - mx);
+        tot += sum * w;
+        a += __ldcg(pc + 2 + d) * w;
+      }
     }
-#pragma unroll
-    for (int h = 0; h < HT; ++h) out_of(hp * HT + h)[2 + t] = acc[h];
-  }
-}
-
-__global__ void k_attn_combine(const float* __restrict__ part, float* __restrict__ att, int H, int Dh, int nchunks,
-                               int max_chunks) {
-  dep_begin();
-  const int head = blockIdx.x, j = blockIdx.y;
-  const float* p = part + (static_cast<size_t>(j) * H + head) * max_chunks * (Dh + 2);
-  float mx = -INFINITY;
-  for (int c = 0; c < nchunks; ++c) mx = fmaxf(mx, p[static_cast<size_t>(c) * (Dh + 2)]);
-  float tot = 0.f;
-  for (int c = 0; c < nchunks; ++c) {
-    const float* pc = p + static_cast<size_t>(c) * (Dh + 2);
-    tot += pc[1] * __expf(pc[0] - mx);
-  }
-  const float inv = 1.f / tot;
-  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
-    float a = 0.f;
-    for (int c = 0; c < nchunks; ++c) {
-      const float* pc = p + static_cast<size_t>(c) * (Dh + 2);
-      if (pc[1] > 0.f) a += pc[2 + d] * __expf(pc[0] - mx);
-    }
-    att[static_cast<size_t>(j) * H * Dh + static_cast<size_t>(head) * Dh + d] = a * inv;
+    att[static_cast<size_t>(j) * H * Dh + static_cast<size_t>(head0 + h) * Dh + d] = a / tot;
   }
 }
 
@@ -570,9 +660,12 @@ int runtime_init(Model* M, int max_ctx, int max_batch) {
       (rc = dalloc(R, &R->logits, B * R->Vmax)) || (rc = dalloc(R, &R->logits_all, B * R->Vmax * R->tp_world)) ||
       (rc = dalloc(R, &R->ids, B + 1)) ||
       (rc = dalloc(R, &R->attn_part, B * R->H * ((R->Tmax + kAttnChunk - 1) / kAttnChunk) * (R->Dh + 2))) ||
+      (rc = dalloc(R, &R->attn_done, B * R->H)) ||
       (rc = dalloc(R, &R->kc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)) ||
       (rc = dalloc(R, &R->vc, static_cast<size_t>(R->L) * R->Hk * R->Tmax * R->Dh)))
     return rc;
+  if (cudaMemset(R->attn_done, 0, B * R->H * sizeof(unsigned int)) != cudaSuccess)
+    return cuda_fail("cudaMemset (attention counters)", cudaGetLastError());
   if (cudaMallocHost(reinterpret_cast<void**>(&R->h_ids), (B + 1) * sizeof(int)) != cudaSuccess)
     return cuda_fail("cudaMallocHost (ids)", cudaGetLastError());
   if (cudaStreamCreateWithFlags(&R->stream, cudaStreamNonBlocking) != cudaSuccess)
@@ -761,19 +854,15 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
     {
       const int group = R->H / R->Hk;
       if (group % 4 == 0)
-        launch_dep(k_attn_part<4>, dim3(R->H / 4, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
-                                                                           R->Dh, R->Tmax, R->attn_scale, R->window,
-                                                                           R->max_chunks);
+        launch_dep(k_attn<4>, dim3(R->H / 4, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, R->att, R->attn_done,
+                   posp, R->H, R->Hk, R->Dh, R->Tmax, R->attn_scale, R->window, R->max_chunks);
       else if (group % 2 == 0)
-        launch_dep(k_attn_part<2>, dim3(R->H / 2, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
-                                                                           R->Dh, R->Tmax, R->attn_scale, R->window,
-                                                                           R->max_chunks);
+        launch_dep(k_attn<2>, dim3(R->H / 2, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, R->att, R->attn_done,
+                   posp, R->H, R->Hk, R->Dh, R->Tmax, R->attn_scale, R->window, R->max_chunks);
       else
-        launch_dep(k_attn_part<1>, dim3(R->H, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, posp, R->H, R->Hk,
-                                                                       R->Dh, R->Tmax, R->attn_scale, R->window,
-                                                                       R->max_chunks);
+        launch_dep(k_attn<1>, dim3(R->H, m, nchunks), dim3(kAttnThreads), st, R->qkv, kc, vc, R->attn_part, R->att, R->attn_done,
+                   posp, R->H, R->Hk, R->Dh, R->Tmax, R->attn_scale, R->window, R->max_chunks);
     }
-    launch_dep(k_attn_combine, dim3(R->H, m), dim3(128), st, R->attn_part, R->att, R->H, R->Dh, nchunks, R->max_chunks);
     if ((rc = linear_device(M, M->mats[R->m_o[l]], R->att, false, m, R->o, R->D, st))) return rc;
     if ((rc = norm_residual(M, R, m, R->o, true, R->ln2[l], st, "all-reduce (o)"))) return rc;
     if (m == 1) {          // one token: gate and up in one launch
