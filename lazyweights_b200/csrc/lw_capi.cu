@@ -799,8 +799,11 @@ int rt_test_matmul(void* handle, const char* name, const float* X, int m, float*
   std::memcpy(M->h_pin, X, nx * 4);
   if ((e = cudaMemcpyAsync(M->d_x, M->h_pin, nx * 4, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess)
     return cuda_fail("rt_test_matmul copy in", e);
-  int rc = linear_device(M, mx, M->d_x, false, m, M->d_y, mx.N, nullptr, path);
-  if (!rc && (e = cudaMemcpyAsync(M->h_pin + nx, M->d_y, ny * 4, cudaMemcpyDeviceToHost, nullptr)) != cudaSuccess)
+  // A small result is written by the kernels straight into the pinned buffer (it is mapped into the device's address
+  // space): no copy-back to enqueue and wait for.  Large results go through device memory and one copy.
+  const bool direct = ny * 4 <= (size_t(1) << 20);
+  int rc = linear_device(M, mx, M->d_x, false, m, direct ? M->h_pin + nx : M->d_y, mx.N, nullptr, path);
+  if (!rc && !direct && (e = cudaMemcpyAsync(M->h_pin + nx, M->d_y, ny * 4, cudaMemcpyDeviceToHost, nullptr)) != cudaSuccess)
     rc = cuda_fail("rt_test_matmul copy back", e);
   if ((e = cudaStreamSynchronize(nullptr)) != cudaSuccess && !rc) rc = cuda_fail("rt_test_matmul", e);
   if (!rc) std::memcpy(Y, M->h_pin + nx, ny * 4);
