@@ -86,6 +86,14 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
 /* Position bookkeeping.  Replace rt_reset, rt_set_window, rt_set_pos, rt_pos, rt_vocab, kernels/llmrt.cu:2269-2274:
  * rt_set_pos only rewinds (the KV cache below the new position is kept); rt_set_window sets a sliding attention
  * window (0 = none). */
+/* Greedy decoding without a round trip per token (no counterpart in the reference, whose generation loops pick every
+ * token on the host with `argmax`, kernels/llmrt.cu:2663, 2816-2820, 3065-3070): n one-token passes starting with `first_token` at the current
+ * position; the arg-max of each pass (lowest id among equal logits, like a host arg-max) is taken on the device and
+ * becomes the token of the next pass; out[i] = token chosen by pass i.  The position advances by n.  Equivalent to n
+ * calls of rt_forward with an arg-max in between.  With tensor parallelism every rank calls it with the same arguments.
+ * Returns 0, -1 on context overflow, or a negative status. */
+int rt_decode_greedy(void* handle, int first_token, int n, int* out);
+
 void rt_reset(void* handle);
 void rt_set_window(void* handle, int w);
 void rt_set_pos(void* handle, int p);

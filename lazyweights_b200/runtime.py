@@ -225,6 +225,16 @@ class Bundle(_Handle):
         nat.check(rc)
         return out
 
+    def decode_greedy(self, first_token, n):
+        """rt_decode_greedy: n greedy one-token passes without a host round trip per token; returns the n chosen tokens
+        (int32).  The same tokens as n calls of forward() with np.argmax in between."""
+        out = np.empty(n, np.int32)
+        rc = nat.lib().rt_decode_greedy(self._h, int(first_token), int(n), out.ctypes.data_as(C.c_void_p))
+        if rc == -1:
+            raise IndexError("context overflow")
+        nat.check(rc)
+        return out
+
     def reset(self):
         nat.lib().rt_reset(self._h)
 

@@ -9,11 +9,14 @@ the position is rewound to pos0 + 1 + accepted with rt_set_pos (:3144-3159).  Th
 import numpy as np
 
 
-def greedy(bundle, prompt, n_new):
-    """Plain greedy decoding: returns the generated ids."""
+def greedy(bundle, prompt, n_new, on_device=False):
+    """Plain greedy decoding: returns the generated ids.  on_device: the tokens after the first are chosen by the
+    runtime itself (rt_decode_greedy: no round trip per token); the ids are the same."""
     bundle.reset()
     tok = int(np.argmax(bundle.forward(np.asarray(prompt, np.int32))))
     out = [tok]
+    if on_device and n_new > 1:
+        return out + [int(t) for t in bundle.decode_greedy(tok, n_new - 1)]
     while len(out) < n_new:
         tok = int(np.argmax(bundle.forward(np.array([tok], np.int32))))
         out.append(tok)

@@ -100,6 +100,17 @@ def test_prompt_lookup_equals_greedy(tmp_path):
         assert passes <= 24 and accepted >= 0
         cached, passes_c, accepted_c = speculate.prompt_lookup(b, prompt, 24, n_draft=7, drafter="ngramcache")
         assert cached == plain and passes_c <= 24 and accepted_c >= 0
+        # the same tokens when the runtime picks them itself, pass after pass without the host (80 tokens: the passes
+        # cross a boundary of the attention's 64-position chunks, i.e. more than one captured graph)
+        long_plain = speculate.greedy(b, prompt, 80)
+        assert long_plain[:24] == plain
+        pos = b.pos
+        assert speculate.greedy(b, prompt, 80, on_device=True) == long_plain
+        assert b.pos == pos
+        with pytest.raises(IndexError):
+            b.decode_greedy(1, 128)                                       # beyond the context: refused, nothing launched
+        with pytest.raises(lw.LwError):
+            b.decode_greedy(SHAPE["vocab"], 1)
 
 
 def test_bundle_built_from_a_gguf_runs(tmp_path):
