@@ -305,7 +305,7 @@ static int launch_g(const MatDev& M, const void* X, bool x_is_half, float* P, fl
 
 bool gemv1_usable(const MatDev& M) {
   if (is_pair_layout(M.fmt))
-    return (M.index_bits == 11 || M.index_bits == pair_code_bits_max(M.fmt)) && M.pad == kRingLogCopies + 2 && M.split == default_split(M.fmt) && M.unit_slow && M.row_done &&
+    return (M.index_bits == 11 || M.index_bits == pair_code_bits_max(M.fmt)) && M.pad == pair_pad_bits(M.index_bits) && M.split == default_split(M.fmt) && M.unit_slow && M.row_done &&
            M.group == 3 && M.reader == 0;
   const bool fmt_ok = M.fmt >= kFmtQ4K && M.fmt <= kFmtIQ4XS;
   const int gmax = is_paired(M.fmt) ? 4 : 6;

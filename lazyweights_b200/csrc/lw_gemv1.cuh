@@ -447,7 +447,7 @@ __device__ __forceinline__ void gemv1_block(const MatDev& M, const Gemv1Args& A,
     UnitSide<FMT> side_a, side_b;
     side_a.load(buf + u.lines * 32u - SIDEW, lane);
     side_b.load(buf + u.lines * 32u - SIDEW, lane + 32);
-    typename ChainOf<PAIR_LAYOUT>::type ca, cb;
+    typename ChainOf<PAIR_LAYOUT, IDXBITS>::type ca, cb;
     ca.init(buf + lane, kRingLogCopies - LOG_R);
     cb.init(buf + u.second * 32u + lane, kRingLogCopies - LOG_R);
     float tot_a = 0.f, tot_b = 0.f;

@@ -106,7 +106,6 @@ int build_pairs(const uint8_t* sym, int N, int K, int fmt, const uint8_t* side, 
   int L = pair_code_bits_max(pf);
   const int Ks = K / 2, KT = Ks / kTileSyms, NT = N / kTileRows, T = NT * KT;
   const int split = default_split(pf), G = 2 * split, seg_syms = kTileSyms / split;
-  constexpr int pad = 6;
   const uint32_t side_words = unit_side_words(pf);
   out = PairImage();
   out.fmt = pf;
@@ -175,6 +174,10 @@ int build_pairs(const uint8_t* sym, int N, int K, int fmt, const uint8_t* side, 
     }
   }
   out.index_bits = L;
+  // an 11-bit code is laid out without pad bits (its reader loads two words per group: lw_ring.cuh), a 12-bit code
+  // with the six the table's address bits want
+  const int pad = L == 11 ? 0 : 6;
+  out.pad = pad;
   std::vector<int> order;
   for (int p = 0; p < NP; ++p)
     if (len[p]) order.push_back(p);

@@ -382,14 +382,58 @@ struct ReloadChain {
   }
 };
 
-template <bool RELOAD>
+// Pair layouts with an 11-bit code are laid out WITHOUT pad bits: three symbols of at most 11 bits need 33 bits after
+// the bit position, which the two words a group starts in always hold (position mod 32 <= 31, 31 + 33 = 64), so a group
+// loads two words instead of three; the price is one instruction per lookup (the window is shifted up onto the table's
+// address bits instead of being read where the pad put it) in a kernel whose issue slots are half empty and whose
+// shared-memory pipe is full.
+struct ReloadChain2 {
+  const uint32_t* base;
+  uint32_t bp;
+  uint32_t a, b, off;
+  __device__ __forceinline__ void init(const uint32_t* chain_words, uint32_t = 0) {
+    base = chain_words;
+    bp = 0;
+  }
+  __device__ __forceinline__ void begin() {
+    const uint32_t* q = base + (bp >> 5) * 32u;
+    const uint32_t w0 = q[0], w1 = q[32];
+    a = __funnelshift_r(w0, w1, bp);
+    b = w1 >> (bp & 31u);
+    off = 0;
+  }
+  template <uint32_t MASK>
+  __device__ __forceinline__ uint32_t sym(const uint8_t* tab, uint32_t lane_off) {
+    constexpr int SH = __builtin_ctz(MASK);
+    const uint32_t t = __funnelshift_r(a, b, off);
+    const uint32_t e = *reinterpret_cast<const uint32_t*>(tab + (((t << SH) & MASK) | lane_off));
+    off = __umulhi(e, 16u) + off;
+    return e;
+  }
+  __device__ __forceinline__ void end() { bp += off; }
+  __device__ __forceinline__ uint32_t slow_sym(const uint32_t* tab32, uint32_t) {
+    const uint32_t* q = base + (bp >> 5) * 32u;
+    const uint32_t e = tab32[__funnelshift_r(q[0], q[32], bp) & (kLutSize - 1)];
+    bp += e >> 28;
+    return e;
+  }
+};
+
+// The reader of a kernel instantiation: pair layouts by the width of their code, everything else GroupChain.
+template <bool PAIR_LAYOUT, int IDXBITS>
 struct ChainOf {
   using type = GroupChain;
 };
 template <>
-struct ChainOf<true> {
+struct ChainOf<true, 12> {
   using type = ReloadChain;
 };
+template <>
+struct ChainOf<true, 11> {
+  using type = ReloadChain2;
+};
+// zero bits at the start of every chain of a pair layout
+__host__ __device__ constexpr int pair_pad_bits(int index_bits) { return index_bits == 11 ? 0 : kRingLogCopies + 2; }
 
 // Scales of the unit's two rows (row `lane` and row `lane + 32`), read from the block that follows the unit's chain
 // words in its staging buffer (layout: lw::unit_side_words).  sub(j) = (scale, offset) of sub-block j (a constant

@@ -128,18 +128,23 @@ def test_unit_scales_follow_the_chains(ty, n, k):
 
 
 def _replay_pair_chain(words, base, lane, table, pad, index_bits, nsym, group):
-    """pair symbols (value bytes) of one chain of a pair layout, read the way the kernel's reload reader does: every
-    group loads three words at the word its bit position has reached; the reader starts 4 - log2(copies) bits into
-    the pad (4 copies of a 4096-window table, 8 of a 2048-window one)"""
-    bp0 = 4 - (2 if index_bits == 12 else 3)                     # 4096 windows: 4 copies; 2048: 8 copies
+    """pair symbols (value bytes) of one chain of a pair layout, read the way the kernel's reload readers do.  A
+    12-bit code (pad 6, 4 copies of a 4096-window table): every group loads three words at the word its bit position has
+    reached and starts 4 - log2(copies) bits into the pad.  An 11-bit code is laid out without pad: a group loads two
+    words, which always hold the 33 bits three symbols can take."""
+    two_words = pad == 0
+    bp0 = 0 if two_words else 4 - 2
     shift = pad - bp0
     bp, out = bp0, []
     a = b = off = 0
     for i in range(nsym):
         if i % group == 0:
             q = base + 32 * (bp >> 5) + lane
-            w0, w1, w2 = int(words[q]), int(words[q + 32]), int(words[q + 64])
-            a, b, off = _funnel(w0, w1, bp), _funnel(w1, w2, bp), 0
+            w0, w1 = int(words[q]), int(words[q + 32])
+            if two_words:
+                a, b, off = _funnel(w0, w1, bp), w1 >> (bp & 31), 0
+            else:
+                a, b, off = _funnel(w0, w1, bp), _funnel(w1, int(words[q + 64]), bp), 0
         assert off < 32
         e = int(table[(_funnel(a, b, off) >> shift) & ((1 << index_bits) - 1)])
         assert e >> 28, "window without a code"
@@ -162,7 +167,7 @@ def test_pair_layout_replayed_on_cpu(ty, n, k):
     lay = lw.bundle.host_pairs(q, ty, side)
     L = lay["index_bits"]                                         # rows of rare pairs: more than 2048 different pairs
     assert L == (12 if ty == "Q6_K" else 11)
-    assert lay["split"] == 4 and lay["pad"] == 6 and lay["group"] == 3 and lay["max_len"] <= L
+    assert lay["split"] == 4 and lay["pad"] == (0 if L == 11 else 6) and lay["group"] == 3 and lay["max_len"] <= L
     bias = 32 if ty == "Q6_K" else 0
     KT = k // 512
     for t in range((n // 64) * KT):
@@ -171,7 +176,7 @@ def test_pair_layout_replayed_on_cpu(ty, n, k):
             for half in range(2):
                 base = int(lay["group_base"][t * 8 + 2 * seg + half])
                 for lane in range(0, 32, 3):
-                    got = _replay_pair_chain(lay["words"], base, lane, lay["table"], 6, L, 64, 3)
+                    got = _replay_pair_chain(lay["words"], base, lane, lay["table"], lay["pad"], L, 64, 3)
                     row = tr * 64 + half * 32 + lane
                     c = q[row, tc * 512 + seg * 128: tc * 512 + (seg + 1) * 128].astype(np.int64) - bias
                     want = ((c[0::2] & 255) | ((c[1::2] & 255) << 8)).tolist()
@@ -210,8 +215,8 @@ def test_pair_code_width_follows_the_data():
     q, side, sym, w, rng = helpers.seeded_case("Q6_K", 64, 1024, seed=3)
     q = np.clip(np.rint(rng.normal(32.0, 1.5, q.shape)), 0, 63).astype(np.uint8)
     lay = lw.bundle.host_pairs(q, "Q6_K", side)
-    assert lay["index_bits"] == 11 and lay["max_len"] <= 11
+    assert lay["index_bits"] == 11 and lay["max_len"] <= 11 and lay["pad"] == 0
     for lane in (0, 9, 31):
-        got = _replay_pair_chain(lay["words"], int(lay["group_base"][3]), lane, lay["table"], 6, 11, 64, 3)
+        got = _replay_pair_chain(lay["words"], int(lay["group_base"][3]), lane, lay["table"], lay["pad"], 11, 64, 3)
         c = q[32 + lane, 128:256].astype(np.int64) - 32
         assert got == ((c[0::2] & 255) | ((c[1::2] & 255) << 8)).tolist()
