@@ -361,7 +361,9 @@ static int linear_decode_gemm(Model* M, Matrix& mx, const void* x, bool x_half, 
     return rc;
   for (int tr0 = 0; tr0 < NT; tr0 += chunk) {
     const int tr1 = std::min(NT, tr0 + chunk);
-    if ((rc = launch_decode_weights_rows(mx.dev, M->d_w16, tr0, tr1, st))) return rc;
+    rc = reads_pairs(mx, 1) ? launch_decode_weights_rows(mx.pair, M->d_w16, tr0, tr1, st) : kErrTooLarge;   // two weights per lookup
+    if (rc == kErrTooLarge) rc = launch_decode_weights_rows(mx.dev, M->d_w16, tr0, tr1, st);
+    if (rc) return rc;
     if ((rc = launch_gemm_tc(x16, M->d_w16, y + static_cast<size_t>(tr0) * kTileRows, m, (tr1 - tr0) * kTileRows, mx.K,
                              ldy, M->d_partials, M->partial_floats, unscale, st)))
       return rc;
@@ -751,7 +753,10 @@ int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream) {
   if (!mx) return kErrGeneric;
   if (!w_half_dev) return kErrArg;
   if (const int rc = check_device(static_cast<Model*>(handle))) return rc;
-  return launch_decode_weights(mx->dev, static_cast<__half*>(w_half_dev), static_cast<cudaStream_t>(stream));
+  int rc = reads_pairs(*mx, 1) ? launch_decode_weights(mx->pair, static_cast<__half*>(w_half_dev), static_cast<cudaStream_t>(stream))
+                               : kErrTooLarge;
+  if (rc == kErrTooLarge) rc = launch_decode_weights(mx->dev, static_cast<__half*>(w_half_dev), static_cast<cudaStream_t>(stream));
+  return rc;
 }
 
 int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* stream) {

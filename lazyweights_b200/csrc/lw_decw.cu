@@ -58,7 +58,21 @@ static int launch_x(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
 }
 
 template <int FMT>
+static int launch_bundle_code(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st);
+
+template <int FMT>
 static int launch_i(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  if constexpr (is_pair_layout(FMT)) {
+    if constexpr (pair_code_bits_max(FMT) == 12)
+      if (M.index_bits == 12) return launch_t<FMT, 3, 12>(M, out, tr0, tr1, err, st);
+    return launch_t<FMT, 3, 11>(M, out, tr0, tr1, err, st);
+  } else {
+    return launch_bundle_code<FMT>(M, out, tr0, tr1, err, st);
+  }
+}
+
+template <int FMT>
+static int launch_bundle_code(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
   switch (M.group) {
     case 3: return launch_x<FMT, 3>(M, out, tr0, tr1, err, st);
     case 4: return launch_x<FMT, 4>(M, out, tr0, tr1, err, st);
@@ -84,6 +98,8 @@ int launch_decw(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* er
     case kFmtQ5K: return launch_i<kFmtQ5K>(M, out, tr0, tr1, err, st);
     case kFmtIQ4XS: return launch_i<kFmtIQ4XS>(M, out, tr0, tr1, err, st);
     case kFmtQ6K: return launch_i<kFmtQ6K>(M, out, tr0, tr1, err, st);
+    case kFmtQ6KP: return launch_i<kFmtQ6KP>(M, out, tr0, tr1, err, st);
+    case kFmtQ5KP: return launch_i<kFmtQ5KP>(M, out, tr0, tr1, err, st);
   }
   return kErrTooLarge;
 }

@@ -40,7 +40,10 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   constexpr int SPLIT = default_split(FMT);
   constexpr int TW = PAIR ? 2 * kTileSyms : kTileSyms;
   constexpr int GW = sub_width(FMT), SPG = sub_syms(FMT), SIDEW = unit_side_words(FMT);
+  constexpr int NSU = TW / GW / SPLIT;   // sub-blocks per unit: four, or eight 16-weight ones of a Q6_K pair layout
+  constexpr bool PAIR_LAYOUT = is_pair_layout(FMT);
   constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
+  constexpr bool SINGLE = NIDX <= kLutSize;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -67,7 +70,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   }
 
   // 2b. consumers: the tables
-  table_fill<IDXBITS, LOG_R>(M, tab, tab1, warp, lane, RA.warps);
+  table_fill<IDXBITS, LOG_R, SINGLE>(M, tab, tab1, warp, lane, RA.warps);
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
   const uint32_t lane_off = (lane & (R - 1)) << 2;
 #pragma unroll 1
@@ -81,7 +84,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
     UnitSide<FMT> side_a, side_b;
     side_a.load(buf + lines * 32u - SIDEW, lane);
     side_b.load(buf + lines * 32u - SIDEW, lane + 32);
-    GroupChain ca, cb;
+    typename ChainOf<PAIR_LAYOUT, IDXBITS>::type ca, cb;
     ca.init(buf + lane, kRingLogCopies - LOG_R);
     cb.init(buf + second * 32u + lane, kRingLogCopies - LOG_R);
     __half* oa = A.out + (static_cast<size_t>(tr - RA.tr0) * kTileRows + lane) * M.K + static_cast<size_t>(tc) * TW +
@@ -106,10 +109,10 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
         }
       }
     };
-    if (cls == 0) {
+    if (PAIR_LAYOUT || cls == 0) {   // a pair layout has no other class
       // the common class: groups of G symbols per refill check, everything unrolled (the phase of the groups is static)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
+      for (int jj = 0; jj < NSU; ++jj) {
         float s_a, o_a, s_b, o_b;
         side_a.sub(jj, s_a, o_a);
         side_b.sub(jj, s_b, o_b);
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
               cb.begin();
             }
             const uint32_t ea = ca.template sym<MASK>(smem, lane_off), eb = cb.template sym<MASK>(smem, lane_off);
-            if (f % G == G - 1 || f == 4 * SPG - 1) {
+            if (f % G == G - 1 || f == NSU * SPG - 1) {
               ca.end();
               cb.end();
             }
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
           pb.flush(ob + col);
         }
       }
-    } else {
+    } else if constexpr (!PAIR_LAYOUT) {
       // the fallback classes, rolled up: window normalised per symbol (exact for any data), or the single-copy table
 #pragma unroll 1
       for (int jj = 0; jj < 4; ++jj) {

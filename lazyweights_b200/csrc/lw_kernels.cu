@@ -298,6 +298,8 @@ int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaSt
 }
 
 int launch_decode_weights_rows(const MatDev& M, __half* out, int tr0, int tr1, cudaStream_t st) {
+  if (is_pair_layout(M.fmt))   // only the ring kernel reads a pair layout: kErrTooLarge sends the caller to the bundle's code
+    return gemv1_usable(M) ? launch_decw(M, out, tr0, tr1, error_word(), st) : kErrTooLarge;
   if (gemv1_usable(M)) {   // the decoder of the batch-1 kernel, where the layout allows
     const int rc = launch_decw(M, out, tr0, tr1, error_word(), st);
     if (rc != kErrTooLarge) return rc;

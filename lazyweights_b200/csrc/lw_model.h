@@ -29,8 +29,8 @@ struct Matrix {
   MatDev twin{};
   size_t twin_bytes = 0;          // chain words + unit scales: what one product of the twin reads
   unsigned int twin_epoch = 0;
-  // pair layout (lw::build_pairs; Q6_K / Q5_K with K a multiple of 512): what the one-row product reads instead of
-  // `dev` - the other kernels keep reading the bundle's own code
+  // pair layout (lw::build_pairs; Q6_K / Q5_K with K a multiple of 512): what the one-row product and the decode to
+  // fp16 weights read instead of `dev` - the other kernels keep reading the bundle's own code
   void* d_pair = nullptr;
   MatDev pair{};
   size_t pair_bytes = 0;
