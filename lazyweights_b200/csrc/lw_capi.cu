@@ -382,9 +382,14 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   // go to tensor memory, never to DRAM); more rows, or shapes that kernel does not take, decode to fp16 weights in DRAM
   // and a tensor-core GEMM over them (the decode is paid once however many rows follow).  path 3 forces the tcgen05 kernel.
   if (path == 3 || (path == 0 && m >= debug_knobs().t5_min_rows && m <= 64)) {
-    if (!x_half)
+    if (!x_half) {   // range factors of the rows, once for whichever layout takes the product
       if (const int rc = grow(&M->d_row_scale, &M->row_scale_floats, 128, "cudaMalloc (row factors)")) return rc;
-    const int rc = launch_gemm_coded(mx.dev, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, M->d_row_scale, st);
+      if (const int rc = launch_row_scales(static_cast<const float*>(x), m, mx.K, M->d_row_scale, st)) return rc;
+    }
+    int rc = kErrTooLarge;
+    if (reads_pairs(mx, 1))   // two weights per lookup; falls through where the larger units leave no room
+      rc = launch_gemm_coded(mx.pair, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, M->d_row_scale, st);
+    if (rc == kErrTooLarge) rc = launch_gemm_coded(mx.dev, x, x_half, m, y, ldy, M->d_partials, M->partial_floats, M->d_row_scale, st);
     if (rc != kErrTooLarge || path == 3) return rc;
   }
   if (path == 2 || (path == 0 && m > 16)) return linear_decode_gemm(M, mx, x, x_half, m, y, ldy, st);

@@ -9,7 +9,8 @@ namespace lw {
 
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kRingSlackWords = 96;
-constexpr int kT5LogCopies = 3;   // 8 copies of the decode table: 32 KB (1024 windows) or 64 KB (2048)
+// 8 copies of the decode table: 32 KB (1024 windows) or 64 KB (2048); 4 copies of a pair layout's 4096 windows
+constexpr int t5_log_copies(int index_bits) { return index_bits == 12 ? 2 : 3; }
 constexpr int kT5MinSlots = 17;   // sixteen consumer warps hold a unit each; the rest is run-ahead of the copies
 
 struct T5Plan {
@@ -37,7 +38,7 @@ static bool plan_t5(const MatDev& M, int m, T5Plan& p) {
     return false;
   }
   p.buf_words = (M.max_unit_words + 31u) & ~31u;
-  const size_t fixed = (size_t(1) << (M.index_bits + kT5LogCopies + 2)) + (M.index_bits < kMaxLen ? kLutSize * 4 : 0) +
+  const size_t fixed = (size_t(1) << (M.index_bits + t5_log_copies(M.index_bits) + 2)) + (M.index_bits < kMaxLen ? kLutSize * 4 : 0) +
                        static_cast<size_t>(p.ntok) * kT5SetK * 2 +
                        (2 * kT5Teams * kT5ASlots + 4) * 8 + 16 + ring_fixed_bytes(p.max_units) + kRingSlackWords * 4;
   if (fixed + static_cast<size_t>(p.buf_words) * 4 * kT5MinSlots > kSmemLimit) {
@@ -54,7 +55,7 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, const float*
                     int* terms) {
   T5Plan p;
   if (!plan_t5<FMT>(M, m, p)) return kErrTooLarge;
-  auto kernel = k_gemm_t5<FMT, G, IDXBITS, kT5LogCopies>;
+  auto kernel = k_gemm_t5<FMT, G, IDXBITS, t5_log_copies(IDXBITS)>;
   static size_t configured_per_device[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -89,6 +90,10 @@ static int launch_t(const MatDev& M, const void* X, bool x_is_half, const float*
   return note_launch("k_gemm_t5");
 }
 
+template <int FMT>
+static int launch_bundle_code(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err,
+                              cudaStream_t st, int* terms);
+
 template <int FMT, int G>
 static int launch_i(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err, cudaStream_t st,
                     int* terms) {
@@ -99,6 +104,18 @@ static int launch_i(const MatDev& M, const void* X, bool x_is_half, const float*
 template <int FMT>
 static int launch_g(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err, cudaStream_t st,
                     int* terms) {
+  if constexpr (is_pair_layout(FMT)) {   // groups of three pair symbols, the layout's own table
+    if constexpr (pair_code_bits_max(FMT) == 12)
+      if (M.index_bits == 12) return launch_t<FMT, 3, 12>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    return launch_t<FMT, 3, 11>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+  } else {
+    return launch_bundle_code<FMT>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+  }
+}
+
+template <int FMT>
+static int launch_bundle_code(const MatDev& M, const void* X, bool x_is_half, const float* row_scale, int m, float* planes, unsigned int* err,
+                              cudaStream_t st, int* terms) {
   switch (M.group) {
     case 3: return launch_i<FMT, 3>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
     case 4: return launch_i<FMT, 4>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
@@ -129,6 +146,8 @@ int launch_gemm_t5(const MatDev& M, const void* X, bool x_is_half, const float* 
     case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
     case kFmtIQ4XS: return launch_g<kFmtIQ4XS>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
     case kFmtQ6K: return launch_g<kFmtQ6K>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    case kFmtQ6KP: return launch_g<kFmtQ6KP>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
+    case kFmtQ5KP: return launch_g<kFmtQ5KP>(M, X, x_is_half, row_scale, m, planes, err, st, terms);
   }
   return kErrTooLarge;
 }

@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
         UnitSide<FMT> side_a, side_b;
         side_a.load(buf + lines * 32u - SIDEW, lane);
         side_b.load(buf + lines * 32u - SIDEW, lane + 32);
-        GroupChain ca, cb;
+        typename ChainOf<is_pair_layout(FMT), IDXBITS>::type ca, cb;
         ca.init(buf + lane, kRingLogCopies - LOG_R);
         cb.init(buf + second * 32u + lane, kRingLogCopies - LOG_R);
         // One unit: STEPS times sixteen weights of rows l (chain a) and l + 32 (chain b) -> one A slot each.  CLS = the
@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
           }
           return true;
         };
-        if (cls == 0) ok = run_unit(std::integral_constant<int, 0>{});
+        if (is_pair_layout(FMT) || cls == 0) ok = run_unit(std::integral_constant<int, 0>{});   // a pair layout has no other class
         else if (cls == 1 || !SINGLE) ok = run_unit(std::integral_constant<int, 1>{});
         else ok = run_unit(std::integral_constant<int, 2>{});
         if (!ok) break;

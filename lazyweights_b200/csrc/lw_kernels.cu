@@ -390,8 +390,8 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
 }
 
 // Y[m, N] = X . W^T for up to 64 rows on the tcgen05 path: planes of partial products, then their ordered sum.
-// row_scale: 2 m floats of device scratch for the per-row range factors of fp32 activations (k_row_scales); unused and
-// may be null when X is fp16.
+// row_scale: the per-row range factors of fp32 activations and their inverses, 2 m floats filled by launch_row_scales
+// before this call; unused and may be null when X is fp16.
 int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
                       size_t scratch_floats, float* row_scale, cudaStream_t st) {
   if (!gemv1_usable(M) || M.K % 512 || scratch_floats < gemm_t5_plane_floats(M, m)) {
@@ -403,10 +403,6 @@ int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, flo
     return kErrArg;
   }
   int terms = 0;
-  if (!x_is_half) {
-    const int rc = launch_row_scales(static_cast<const float*>(X), m, M.K, row_scale, st);
-    if (rc) return rc;
-  }
   const int rc = launch_gemm_t5(M, X, x_is_half, x_is_half ? nullptr : row_scale, m, scratch, error_word(), st, &terms);
   if (rc) return rc;
   k_sum_partials<<<(m * (M.N / 4) + 127) / 128, 128, 0, st>>>(scratch, Y, m, M.N, ldy, terms,

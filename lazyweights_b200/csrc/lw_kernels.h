@@ -61,8 +61,8 @@ int launch_gemv(const MatDev& M, const void* X, bool x_is_half, int m, float* Y,
                 size_t partial_capacity, cudaStream_t st, unsigned int* clean_epoch = nullptr);
 // Y[m, N] = X[m, K] . W^T for 1 <= m <= 64 with the decode + tcgen05 kernel (lw_gemm_t5.cuh): the decoded weights go
 // from registers to tensor memory, never to DRAM.  `scratch` holds the K / 512 planes of partial products.  Returns
-// kErrTooLarge, with nothing launched, where that kernel cannot take the product.  row_scale: 2 m floats of device
-// scratch for launch_row_scales (fp32 activations only).
+// kErrTooLarge, with nothing launched, where that kernel cannot take the product.  row_scale (fp32 activations only):
+// 2 m floats already filled by launch_row_scales.
 int launch_gemm_coded(const MatDev& M, const void* X, bool x_is_half, int m, float* Y, int ldy, float* scratch,
                       size_t scratch_floats, float* row_scale, cudaStream_t st);
 
