@@ -244,8 +244,8 @@ long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int K
                          uint32_t* words, long long words_cap, uint8_t* unit_class, long long unit_class_cap);
 
 /* Pair layout.  For Q6_K and Q5_K matrices whose K is a multiple of 512 the loader keeps a second device layout
- * that products of ONE activation row (lw_linear / lw_linear_batch / lw_linear_static / rt_forward with one token), the
- * tensor-core kernel for 8..64 rows (where its larger work units fit) and the decode to fp16 weights read: two adjacent codes of a row are one symbol of a prefix code built from the matrix's own pair counts (at most
+ * that every product kernel (one row, 2..8 rows fused, the tensor-core kernel up to 64 rows - where the layout's larger
+ * work units fit their shared memory) and the decode to fp16 weights read: two adjacent codes of a row are one symbol of a prefix code built from the matrix's own pair counts (at most
  * 12 bits for pairs of 6-bit codes, 11 for pairs of 5-bit codes), so that the kernel does one table lookup per two
  * weights, as it does for the 4-bit formats whose bundle symbols are pairs already.  The decoded codes are the same;
  * device memory holds the matrix twice (LW_PAIRS=0 in the environment at load: no pair layouts).  No reference

@@ -43,6 +43,7 @@ struct DebugKnobs {
   uint32_t wait_limit = 1u << 22;  // polls after which a device-side wait gives up
   int drop_unit = -1;              // the producers of block 0 skip the copy of this unit (its consumer's wait runs out)
   int t5_min_rows = 8;             // products of at least this many rows (and at most 64) take the tcgen05 kernel
+  int t5_min_rows_pairs = 9;       // the same for matrices with a pair layout, where the fused kernel wins at eight rows
   int pairs = 1;                   // one-row products read a matrix's pair layout where it has one (0: the bundle's code)
 };
 DebugKnobs& debug_knobs();

@@ -20,7 +20,7 @@ struct GemvmPlan {
 template <int FMT, int MR>
 static bool plan_gemvm(const MatDev& M, int ntr, GemvmPlan& p) {
   constexpr int TW = is_paired(FMT) ? 512 : 256, SPLIT = default_split(FMT), NSB = TW / sub_width(FMT);
-  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  constexpr bool has_offset = FMT == kFmtQ4K || FMT == kFmtQ5K || FMT == kFmtQ5KP;
   const int staged = std::max(1, 8 / MR);   // tile columns whose activations (all rows) one block keeps in shared memory
   p.nsets = (M.KT + staged - 1) / staged;
   p.cols_per_set = (M.KT + p.nsets - 1) / p.nsets;
@@ -128,18 +128,24 @@ static int launch_i(const MatDev& M, const void* X, bool x_is_half, int m, float
 
 template <int FMT>
 static int launch_g(const MatDev& M, const void* X, bool x_is_half, int m, float* P, unsigned int* err, cudaStream_t st) {
-  switch (M.group) {
-    case 3: return launch_i<FMT, 3>(M, X, x_is_half, m, P, err, st);
-    case 4: return launch_i<FMT, 4>(M, X, x_is_half, m, P, err, st);
-  }
-  if constexpr (!is_paired(FMT)) {
+  if constexpr (is_pair_layout(FMT)) {   // groups of three pair symbols, the layout's own table
+    if constexpr (pair_code_bits_max(FMT) == 12)
+      if (M.index_bits == 12) return launch_r<FMT, 3, 12>(M, X, x_is_half, m, P, err, st);
+    return launch_r<FMT, 3, 11>(M, X, x_is_half, m, P, err, st);
+  } else {
     switch (M.group) {
-      case 5: return launch_i<FMT, 5>(M, X, x_is_half, m, P, err, st);
-      case 6: return launch_i<FMT, 6>(M, X, x_is_half, m, P, err, st);
+      case 3: return launch_i<FMT, 3>(M, X, x_is_half, m, P, err, st);
+      case 4: return launch_i<FMT, 4>(M, X, x_is_half, m, P, err, st);
     }
+    if constexpr (!is_paired(FMT)) {
+      switch (M.group) {
+        case 5: return launch_i<FMT, 5>(M, X, x_is_half, m, P, err, st);
+        case 6: return launch_i<FMT, 6>(M, X, x_is_half, m, P, err, st);
+      }
+    }
+    set_kernel_error_text("gemvm", "no kernel for this group size");
+    return kErrArg;
   }
-  set_kernel_error_text("gemvm", "no kernel for this group size");
-  return kErrArg;
 }
 
 size_t gemvm_partial_floats(const MatDev& M, int m) {
@@ -155,6 +161,8 @@ int launch_gemvm(const MatDev& M, const void* X, bool x_is_half, int m, float* P
     case kFmtQ4K: return launch_g<kFmtQ4K>(M, X, x_is_half, m, P, err, st);
     case kFmtQ5K: return launch_g<kFmtQ5K>(M, X, x_is_half, m, P, err, st);
     case kFmtIQ4XS: return launch_g<kFmtIQ4XS>(M, X, x_is_half, m, P, err, st);
+    case kFmtQ6KP: return launch_g<kFmtQ6KP>(M, X, x_is_half, m, P, err, st);
+    case kFmtQ5KP: return launch_g<kFmtQ5KP>(M, X, x_is_half, m, P, err, st);
     default: return launch_g<kFmtQ6K>(M, X, x_is_half, m, P, err, st);
   }
 }

@@ -16,8 +16,8 @@
 namespace lw {
 
 // One sub-block of both chains against MR activation rows.  xs points at the sub-block's operands, [symbol][MR] words.
-template <int G, int SPG, uint32_t MASK, int MR>
-__device__ __forceinline__ void sub_block_m(GroupChain& ca, GroupChain& cb, const uint8_t* tab, uint32_t lane_off,
+template <int G, int SPG, uint32_t MASK, int MR, class CH>
+__device__ __forceinline__ void sub_block_m(CH& ca, CH& cb, const uint8_t* tab, uint32_t lane_off,
                                             const uint32_t* xs, const int first, const bool last, int (&acc_a)[MR],
                                             int (&acc_b)[MR]) {
 #pragma unroll
@@ -47,8 +47,8 @@ __device__ __forceinline__ void sub_block_m(GroupChain& ca, GroupChain& cb, cons
   }
 }
 
-template <int SPG, int MR>
-__device__ __forceinline__ void sub_block_slow_m(GroupChain& ca, GroupChain& cb, const uint32_t* tab32, uint32_t pad,
+template <int SPG, int MR, class CH>
+__device__ __forceinline__ void sub_block_slow_m(CH& ca, CH& cb, const uint32_t* tab32, uint32_t pad,
                                                  const uint32_t* xs, int (&acc_a)[MR], int (&acc_b)[MR]) {
 #pragma unroll 1
   for (int c = 0; c < SPG; ++c) {
@@ -82,10 +82,13 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
   constexpr int GW = sub_width(FMT), SPG = sub_syms(FMT), SIDEW = unit_side_words(FMT);
   constexpr int NSB = TW / GW;                                    // sub-blocks per tile row
   constexpr int USYM = kTileSyms / SPLIT;
-  static_assert(NSB / SPLIT == 4, "a unit is one quad of sub-blocks");
+  constexpr int NSU = NSB / SPLIT;                                // sub-blocks per unit
+  static_assert(NSU == 4 || NSU == 8, "a unit is four sub-blocks (eight of the 16-weight sub-blocks of a Q6_K pair layout)");
   static_assert(MR == 4 || MR == 8, "four or eight rows");
-  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K;
+  constexpr bool PAIR_LAYOUT = is_pair_layout(FMT);
+  constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K || FMT == kFmtQ5KP;
   constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
+  constexpr bool SINGLE = NIDX <= kLutSize;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -116,7 +119,7 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
   }
 
   // 2b. consumers: tables, then the activations of the block's tile columns for all rows
-  table_fill<IDXBITS, LOG_R>(M, tab, tab1, warp, lane, RA.warps);
+  table_fill<IDXBITS, LOG_R, SINGLE>(M, tab, tab1, warp, lane, RA.warps);
   if (A.pdl) pdl_wait();
   constexpr int XB = 8;
   const int per_row = ncol * TW, total = per_row * MR;   // rows >= m are stored as zeros
@@ -171,13 +174,13 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
     const int tc = set + RA.nsets * static_cast<int>(j);
     const int na = static_cast<int>(tr) * kTileRows + lane, nb = na + 32;
     const uint32_t* xt = xq + (static_cast<size_t>(j) * kTileSyms + seg * USYM) * MR;
-    const float* xst = xscale + (static_cast<size_t>(j) * NSB + seg * 4) * MR;
-    const float* xgt = xg + (static_cast<size_t>(j) * NSB + seg * 4) * MR;
+    const float* xst = xscale + (static_cast<size_t>(j) * NSB + seg * NSU) * MR;
+    const float* xgt = xg + (static_cast<size_t>(j) * NSB + seg * NSU) * MR;
     const uint32_t* buf = u.buf;
     UnitSide<FMT> side_a, side_b;
     side_a.load(buf + lines * 32u - SIDEW, lane);
     side_b.load(buf + lines * 32u - SIDEW, lane + 32);
-    GroupChain ca, cb;
+    typename ChainOf<PAIR_LAYOUT, IDXBITS>::type ca, cb;
     ca.init(buf + lane, kRingLogCopies - LOG_R);
     cb.init(buf + second * 32u + lane, kRingLogCopies - LOG_R);
     float tot_a[MR], tot_b[MR];
@@ -201,16 +204,16 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
         }
       }
     };
-    if (cls == 0) {
+    if (PAIR_LAYOUT || cls == 0) {   // a pair layout has no other class
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
+      for (int jj = 0; jj < NSU; ++jj) {
         int acc_a[MR], acc_b[MR];
 #pragma unroll
         for (int r = 0; r < MR; ++r) acc_a[r] = acc_b[r] = 0;
-        sub_block_m<G, SPG, MASK, MR>(ca, cb, smem, lane_off, xt + jj * SPG * MR, jj * SPG, jj == 3, acc_a, acc_b);
+        sub_block_m<G, SPG, MASK, MR>(ca, cb, smem, lane_off, xt + jj * SPG * MR, jj * SPG, jj == NSU - 1, acc_a, acc_b);
         finish_sub(jj, acc_a, acc_b);
       }
-    } else {
+    } else if constexpr (!PAIR_LAYOUT) {
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         int acc_a[MR], acc_b[MR];
