@@ -281,7 +281,8 @@ long long lw_launch_count(void);
  * values make a product run as several launches over ranges of tile rows, the path very tall matrices take),
  * "wait_limit" (polls after which a device-side wait gives up), "drop_unit" (block 0's producers never copy this unit
  * of their list, so the waits for it run out; -1 = none), "t5_min_rows" (1..65: products of at least this many rows,
- * and at most 64, take the decode + tcgen05 kernel; 8 in production), "reset" (all back to the production values). */
+ * and at most 64, take the decode + tcgen05 kernel; 9 in production), "pairs" (0 / 1: product kernels read the bundle's own code even
+ * where a matrix has a pair layout), "reset" (all back to the production values). */
 int lw_debug_set(const char* key, long long value);
 
 /* Launches one warp that waits, `limit` polls each, on a copy barrier nothing completes and on a release counter

@@ -382,9 +382,7 @@ int linear_device(Model* M, Matrix& mx, const void* x, bool x_half, int m, float
   // path 0: up to eight rows the fused decode + product kernels; 9 .. 64 rows the decode + tcgen05 GEMM (decoded weights
   // go to tensor memory, never to DRAM); more rows, or shapes that kernel does not take, decode to fp16 weights in DRAM
   // and a tensor-core GEMM over them (the decode is paid once however many rows follow).  path 3 forces the tcgen05 kernel.
-  // (eight rows of a matrix with a pair layout stay on the fused kernel: measured 49 against 54 us on Q6_K 14336 x 4096)
-  const int t5_from = reads_pairs(mx, 1) ? debug_knobs().t5_min_rows_pairs : debug_knobs().t5_min_rows;
-  if (path == 3 || (path == 0 && m >= t5_from && m <= 64)) {
+  if (path == 3 || (path == 0 && m >= debug_knobs().t5_min_rows && m <= 64)) {
     if (!x_half) {   // range factors of the rows, once for whichever layout takes the product
       if (const int rc = grow(&M->d_row_scale, &M->row_scale_floats, 128, "cudaMalloc (row factors)")) return rc;
       if (const int rc = launch_row_scales(static_cast<const float*>(x), m, mx.K, M->d_row_scale, st)) return rc;
@@ -459,7 +457,7 @@ int lw_debug_set(const char* key, long long value) {
   if (s == "max_units" && value >= 2 && value <= 1024) k.max_units = static_cast<int>(value) & ~1;
   else if (s == "wait_limit" && value >= 1 && value <= (1ll << 30)) k.wait_limit = static_cast<uint32_t>(value);
   else if (s == "drop_unit" && value >= -1 && value < 1024) k.drop_unit = static_cast<int>(value);
-  else if (s == "t5_min_rows" && value >= 1 && value <= 65) k.t5_min_rows = k.t5_min_rows_pairs = static_cast<int>(value);
+  else if (s == "t5_min_rows" && value >= 1 && value <= 65) k.t5_min_rows = static_cast<int>(value);
   else if (s == "pairs" && (value == 0 || value == 1)) k.pairs = static_cast<int>(value);
   else if (s == "reset") k = DebugKnobs();
   else {
