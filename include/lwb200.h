@@ -117,6 +117,11 @@ int rt_tp_init(void* handle, int rank, int world, const uint8_t* id128);
 int rt_tp_peer_export(void* handle, uint8_t* out64);
 int rt_tp_peer_open(void* handle, const uint8_t* handles, int world);
 int rt_tp_error(void* handle);
+/* With tensor parallelism the waits at the end of rt_forward / rt_decode_greedy are bounded: while the pass runs the
+ * library polls ncclCommGetAsyncError, and after `timeout_ms` (default: LW_TP_TIMEOUT_MS in the environment, else
+ * 60000) without completion - a rank never joined the collective - it aborts the communicator, returns LW_ERR_CUDA and
+ * refuses further passes on this handle.  0 restores the default.  No reference counterpart (single GPU). */
+int rt_tp_set_timeout(void* handle, int timeout_ms);
 
 /* ---- per-matrix entry points on device pointers (additions) ---------------------------------------------- */
 
@@ -284,6 +289,10 @@ long long lw_launch_count(void);
  * and at most 64, take the decode + tcgen05 kernel; 9 in production), "pairs" (0 / 1: product kernels read the bundle's own code even
  * where a matrix has a pair layout), "reset" (all back to the production values). */
 int lw_debug_set(const char* key, long long value);
+/* Test hook for the bounded wait above: holds the handle's stream up with a host function that sleeps `ms`
+ * milliseconds (0..5000; the GPU is idle meanwhile) and runs the bounded wait with the handle's timeout: 0 if the
+ * stream drained in time, LW_ERR_CUDA if the wait gave up first. */
+int lw_debug_stream_stall(void* handle, int ms);
 
 /* Launches one warp that waits, `limit` polls each, on a copy barrier nothing completes and on a release counter
  * nothing advances.  Returns 1 (barrier wait gave up) + 2 (counter wait gave up) = 3, or a negative status; the device

@@ -36,6 +36,8 @@ _SIGNATURES = {
     "rt_tp_peer_open": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "rt_tp_error": (C.c_int, [C.c_void_p]),
     "rt_decode_greedy": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "rt_tp_set_timeout": (C.c_int, [C.c_void_p, C.c_int]),
+    "lw_debug_stream_stall": (C.c_int, [C.c_void_p, C.c_int]),
     "lw_matrix_id": (C.c_int, [C.c_void_p, C.c_char_p]),
     "lw_host_layout": (C.c_longlong, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong,
                                       C.POINTER(C.c_int), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,

@@ -10,12 +10,14 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
 #include <sstream>
+#include <thread>
 
 #include "../../include/lwb200.h"
 #include "lw_model.h"
@@ -31,6 +33,8 @@ struct Nccl {
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
   int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
   int (*CommDestroy)(void*) = nullptr;
+  int (*CommGetAsyncError)(void*, int*) = nullptr;   // optional
+  int (*CommAbort)(void*) = nullptr;                 // optional
   const char* (*GetErrorString)(int) = nullptr;
   void* init_rank_sym = nullptr;
   bool load() {
@@ -46,6 +50,8 @@ struct Nccl {
     AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(lib, "ncclAllGather"));
     CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
     GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+    CommGetAsyncError = reinterpret_cast<decltype(CommGetAsyncError)>(dlsym(lib, "ncclCommGetAsyncError"));
+    CommAbort = reinterpret_cast<decltype(CommAbort)>(dlsym(lib, "ncclCommAbort"));
     return GetUniqueId && init_rank_sym && AllReduce && AllGather && CommDestroy;
   }
 };
@@ -82,6 +88,8 @@ struct Runtime {
                                // that a captured graph replays at any position, as kernels/llmrt.cu:1308 does)
   int* h_ids = nullptr;        // pinned host copy of the same
   int* gen = nullptr;          // [Tmax] tokens generated by rt_decode_greedy (device)
+  int wait_timeout_ms = 0;     // rt_tp_set_timeout: overrides LW_TP_TIMEOUT_MS for this handle (0: the default)
+  bool tp_failed = false;      // a guarded wait gave up: the communicator is gone
   cudaStream_t stream = nullptr;
   bool graphs = true;
   std::map<long long, cudaGraphExec_t> graph_exec;
@@ -974,6 +982,47 @@ static int enqueue_pass(Model* M, Runtime* R, int m, bool all_logits, int nchunk
 // One pass: direct launches the first time a shape (tokens, context bucket, all_logits) occurs, captured into a CUDA
 // graph the second time, replayed afterwards (the reference's policy, kernels/llmrt.cu:2294-2341).  The decode + GEMM
 // path (more than eight rows) may allocate scratch, so those passes are never captured.
+// Waits for the runtime's stream like cudaStreamSynchronize, but with tensor parallelism it gives up: a collective
+// whose peer never arrives would otherwise block the host for ever.  While it waits it asks NCCL for asynchronous
+// errors; after `timeout_ms` (LW_TP_TIMEOUT_MS, default 60 s) or on such an error it aborts the communicator (the NCCL
+// kernels then leave the GPU; this file's own peer kernel has bounded waits and leaves by itself) and reports
+// kErrCuda.  The handle is unusable for further tensor-parallel passes after that.
+static int guarded_wait(Runtime* R, const char* what) {
+  if (R->tp_world <= 1) {
+    const cudaError_t e = cudaStreamSynchronize(R->stream);
+    return e == cudaSuccess ? kOk : cuda_fail(what, e);
+  }
+  static const int timeout_ms = [] {
+    const char* e = getenv("LW_TP_TIMEOUT_MS");
+    return e ? std::max(1, atoi(e)) : 60000;
+  }();
+  const int limit = R->wait_timeout_ms > 0 ? R->wait_timeout_ms : timeout_ms;
+  const auto t0 = std::chrono::steady_clock::now();
+  for (unsigned spin = 0;; ++spin) {
+    const cudaError_t q = cudaStreamQuery(R->stream);
+    if (q == cudaSuccess) return kOk;
+    if (q != cudaErrorNotReady) return cuda_fail(what, q);
+    int async = 0;
+    const bool nccl_failed = R->comm && g_nccl.CommGetAsyncError && (spin & 255u) == 255u &&
+                             g_nccl.CommGetAsyncError(R->comm, &async) == 0 && async != 0;
+    const long long waited =
+        std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+    if (nccl_failed || waited > limit) {
+      if (R->comm && g_nccl.CommAbort) {
+        g_nccl.CommAbort(R->comm);
+        R->comm = nullptr;
+      }
+      R->tp_failed = true;
+      if (nccl_failed)
+        set_error("%s: NCCL reports an asynchronous error (%s)", what, g_nccl.GetErrorString ? g_nccl.GetErrorString(async) : "?");
+      else
+        set_error("%s: the pass did not finish within %d ms - a rank is missing", what, limit);
+      return kErrCuda;
+    }
+    if (waited > 2 && (spin & 15u) == 15u) std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
 // greedy (one token, ids_host null): a pass of rt_decode_greedy - token and position are on the device already, the
 // pass ends with the arg-max that prepares the next one, and the host does not wait between passes.
 static int forward_chunk(Model* M, Runtime* R, const int* ids_host, int m, bool all_logits, bool greedy = false) {
@@ -1047,6 +1096,10 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
   }
   Runtime* R = M->rt;
   if (const int rc = check_device(M)) return rc;
+  if (R->tp_failed) {
+    set_error("rt_forward: an earlier tensor-parallel pass gave up waiting for a rank; open the shards again");
+    return kErrCuda;
+  }
   for (int i = 0; i < n; ++i)
     if (ids[i] < 0 || ids[i] >= R->embed_rows) {   // the embedding gather indexes device memory with it
       set_error("rt_forward: token id %d at position %d is outside the embedding's %d rows", ids[i], i, R->embed_rows);
@@ -1070,7 +1123,8 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
     } else {
       stage.resize(static_cast<size_t>(W) * rows * R->Vmax);
       e = cudaMemcpyAsync(stage.data(), R->logits_all, stage.size() * 4, cudaMemcpyDeviceToHost, R->stream);
-      if (e == cudaSuccess) e = cudaStreamSynchronize(R->stream);
+      if (e == cudaSuccess)
+        if (const int rcw = guarded_wait(R, "rt_forward")) return rcw;
       for (int r = 0; r < W && e == cudaSuccess; ++r)
         for (int j = 0; j < rows; ++j)
           std::memcpy(dst + static_cast<size_t>(j) * Vfull + R->voff[r],
@@ -1079,7 +1133,8 @@ int rt_forward(void* handle, const int* ids, int n, float* logits, int all_logit
     }
     if (e != cudaSuccess) return cuda_fail("logits copy", e);
   }
-  if (!logits) cudaStreamSynchronize(R->stream);
+  if (!logits)
+    if (const int rcw = guarded_wait(R, "rt_forward")) return rcw;
   return 0;
 }
 
@@ -1091,6 +1146,10 @@ int rt_decode_greedy(void* handle, int first_token, int n, int* out) {
   }
   Runtime* R = M->rt;
   if (const int rc = check_device(M)) return rc;
+  if (R->tp_failed) {
+    set_error("rt_decode_greedy: an earlier tensor-parallel pass gave up waiting for a rank; open the shards again");
+    return kErrCuda;
+  }
   if (first_token < 0 || first_token >= R->embed_rows) {
     set_error("rt_decode_greedy: token id %d is outside the embedding's %d rows", first_token, R->embed_rows);
     return kErrArg;
@@ -1108,10 +1167,44 @@ int rt_decode_greedy(void* handle, int first_token, int n, int* out) {
     if (const int rc = forward_chunk(M, R, nullptr, 1, false, true)) return rc;
   int* h_gen = R->h_ids + B + 2;
   e = cudaMemcpyAsync(h_gen, R->gen, static_cast<size_t>(n) * sizeof(int), cudaMemcpyDeviceToHost, st);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return cuda_fail("rt_decode_greedy", e);
+  if (const int rcw = guarded_wait(R, "rt_decode_greedy")) return rcw;
   std::memcpy(out, h_gen, static_cast<size_t>(n) * sizeof(int));
   return 0;
+}
+
+int rt_tp_set_timeout(void* handle, int timeout_ms) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt || timeout_ms < 0) return kErrArg;
+  M->rt->wait_timeout_ms = timeout_ms;
+  return 0;
+}
+
+// Test hook: the runtime's stream is held up by a host function that sleeps `ms` milliseconds (the GPU is idle
+// meanwhile), then the guarded wait of a tensor-parallel handle is called: 0 if the stream drained in time, else the
+// status of the give-up path.  For handles without tensor parallelism it only waits.
+int lw_debug_stream_stall(void* handle, int ms) {
+  Model* M = static_cast<Model*>(handle);
+  if (!M || !M->rt || ms < 0 || ms > 5000) return kErrArg;
+  Runtime* R = M->rt;
+  int* arg = new int(ms);
+  const cudaError_t e = cudaLaunchHostFunc(R->stream, [](void* p) {
+    int* q = static_cast<int*>(p);
+    std::this_thread::sleep_for(std::chrono::milliseconds(*q));
+    delete q;
+  }, arg);
+  if (e != cudaSuccess) {
+    delete arg;
+    return cuda_fail("cudaLaunchHostFunc", e);
+  }
+  const int saved_world = R->tp_world;
+  if (saved_world <= 1) R->tp_world = 2;   // exercise the bounded wait on a plain handle too
+  const int rc = guarded_wait(R, "lw_debug_stream_stall");
+  R->tp_world = saved_world;
+  const bool failed = R->tp_failed;
+  if (saved_world <= 1) R->tp_failed = false;   // nothing was lost on a handle without peers
+  cudaStreamSynchronize(R->stream);
+  return rc ? rc : (failed ? kErrCuda : 0);
 }
 
 void rt_reset(void* handle) {

@@ -266,6 +266,16 @@ class Bundle(_Handle):
     def tp_error(self):
         return nat.lib().rt_tp_error(self._h)
 
+    def tp_set_timeout(self, timeout_ms):
+        """Bound (ms) on the wait for a tensor-parallel pass: after it the communicator is aborted and the call fails
+        (0: LW_TP_TIMEOUT_MS or 60 s)."""
+        nat.check(nat.lib().rt_tp_set_timeout(self._h, int(timeout_ms)))
+
+    def debug_stream_stall(self, ms):
+        """Test hook: the stream is held up for `ms` milliseconds by a sleeping host function, then the bounded wait
+        runs; returns 0 if it saw the stream drain, a negative status if it gave up first."""
+        return nat.lib().lw_debug_stream_stall(self._h, int(ms))
+
     def cpu_decode(self, name, threads=0):
         inf = self.info(name)
         cols = inf["K"] // 2 if inf["paired"] else inf["K"]

@@ -105,3 +105,71 @@ def test_uneven_split_over_eight_ranks(tmp_path):
         assert np.array_equal(np.concatenate([p[key][1] for p in parts], axis), full[key][1])
         assert np.array_equal(np.concatenate([p[key][2] for p in parts], axis), full[key][2])   # side bytes too
     assert np.array_equal(np.concatenate([p["lm_head"][1] for p in parts]), full["lm_head"][1])
+
+
+HEARTBEAT_WORKER = r"""
+import sys, time
+sys.path.insert(0, %r)
+import torch.distributed as dist
+from lazyweights_b200.tp import Heartbeat, PeerLost
+rank, port, out = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+store = dist.TCPStore("127.0.0.1", port, 2, rank == 0, timeout=__import__("datetime").timedelta(seconds=20))
+hb = Heartbeat(store, rank, 2, timeout_s=1.0)
+log = []
+for step in range(4):
+    if rank == 1 and step == 2:
+        log.append("left before step 2")          # leaves between steps: nothing of its own is in flight
+        break
+    t0 = time.monotonic()
+    try:
+        hb.before_step(step)
+        log.append("step %%d ok" %% step)
+    except PeerLost as e:
+        log.append("step %%d lost %%s after %%.1f s" %% (e.step, e.missing, time.monotonic() - t0))
+        break
+open(out, "w").write("\n".join(log))
+if rank == 0:
+    time.sleep(0.3)                                # the store lives in rank 0: let the peer finish its last read
+"""
+
+
+def test_rank_that_leaves_between_steps_is_noticed_on_the_host(tmp_path):
+    """Failure detection without a GPU and without a fault: two processes share a TCP store; rank 1 stops after two
+    steps; rank 0 learns of it on the host, within the heartbeat's timeout, before it launches step 2."""
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = HEARTBEAT_WORKER % (ROOT,)
+    procs = [subprocess.Popen([sys.executable, "-c", script, str(r), str(port), str(tmp_path / ("r%d.log" % r))])
+             for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=120) == 0
+    log0 = (tmp_path / "r0.log").read_text().splitlines()
+    log1 = (tmp_path / "r1.log").read_text().splitlines()
+    assert log1 == ["step 0 ok", "step 1 ok", "left before step 2"]
+    assert log0[:2] == ["step 0 ok", "step 1 ok"]
+    assert log0[2].startswith("step 2 lost [1] after 1.")
+
+
+@pytest.mark.gpu
+def test_bounded_wait_gives_up_and_reports(tmp_path):
+    """The wait at the end of a tensor-parallel pass is bounded: with the stream held up by a sleeping host function
+    (the GPU idle, nothing faults) a 100 ms bound gives up and reports, a 2 s bound sees the stream drain."""
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    from lazyweights_b200 import modelgen
+    from tests.test_runtime import SHAPE
+    modelgen.write_model(str(tmp_path / "m"), SHAPE, "Q4_K", "Q4_K", seed=3)
+    with lw.Bundle(str(tmp_path / "m"), max_ctx=64, max_batch=8) as b:
+        b.tp_set_timeout(2000)
+        assert b.debug_stream_stall(300) == 0
+        b.tp_set_timeout(100)
+        assert b.debug_stream_stall(600) == -4                          # gave up after 100 ms
+        from lazyweights_b200 import _native as nat
+        assert "did not finish within 100 ms" in nat.last_error()
+        b.tp_set_timeout(0)
+        ok = b.forward(np.array([1, 2, 3], np.int32))                    # a handle without peers lost nothing
+        assert np.isfinite(ok).all()
