@@ -193,7 +193,8 @@ int lw_linear_twin(void* handle, int id, const void* x_dev, int x_is_half, float
 int lw_decode_weights(void* handle, int id, void* w_half_dev, void* stream);
 
 /* Decoded codes on the device, one per byte [N, K] (expand != 0) or symbols [N, K / (8 / bits)] (expand == 0).
- * out_dev must be 32-byte aligned (32-byte stores). */
+ * out_dev must be 32-byte aligned (32-byte stores).  A matrix with a pair layout (lw_matrix_pair_bytes > 0) is decoded
+ * through it, two codes per table lookup; the bytes written are the same. */
 int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* stream);
 
 /* ---- single matrices without a bundle directory (additions) ---------------------------------------------- */

@@ -292,6 +292,14 @@ static Matrix* matrix_by_id(void* h, int id) {
 // m: rows of the product (1 also stands for the row-count-free users: decode to weights, the tensor-core kernel)
 static bool reads_pairs(const Matrix& mx, int m) { return m >= 1 && m <= 8 && mx.d_pair && debug_knobs().pairs; }
 
+// Codes of one matrix, a byte each (a paired format: a byte per pair unless `expand`). An unpaired format's codes are its
+// symbols, so its pair layout yields two per table lookup; a shape that layout's kernel does not take reads the bundle's code.
+static int decode_codes_of(const Matrix& mx, uint8_t* out, bool expand, cudaStream_t st) {
+  int rc = !mx.paired && reads_pairs(mx, 1) ? launch_decode_codes(mx.pair, out, true, st) : kErrTooLarge;
+  if (rc == kErrTooLarge) rc = launch_decode_codes(mx.dev, out, expand && mx.paired, st);
+  return rc;
+}
+
 const MatDev* matrix_descriptor(void* handle, int id, bool one_row) {
   Matrix* mx = matrix_by_id(handle, id);
   if (!mx || check_device(static_cast<Model*>(handle))) return nullptr;
@@ -772,7 +780,7 @@ int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* st
   if (!mx) return kErrGeneric;
   if (!out_dev) return kErrArg;
   if (const int rc = check_device(static_cast<Model*>(handle))) return rc;
-  return launch_decode_codes(mx->dev, out_dev, expand != 0 && mx->paired, static_cast<cudaStream_t>(stream));
+  return decode_codes_of(*mx, out_dev, expand != 0, static_cast<cudaStream_t>(stream));
 }
 
 int rt_test_matmul(void* handle, const char* name, const float* X, int m, float* Y, int path) {
@@ -834,7 +842,7 @@ int rt_test_decode(void* handle, const char* name, uint8_t* out) {
   uint8_t* d = nullptr;
   cudaError_t e = cudaMalloc(&d, n);
   if (e != cudaSuccess) return cuda_fail("rt_test_decode buffer", e);
-  int rc = launch_decode_codes(mx.dev, d, mx.paired, nullptr);
+  int rc = decode_codes_of(mx, d, true, nullptr);
   if (!rc && (e = cudaMemcpy(out, d, n, cudaMemcpyDeviceToHost)) != cudaSuccess) rc = cuda_fail("rt_test_decode copy", e);
   cudaFree(d);
   return rc;
@@ -902,7 +910,7 @@ double rt_gpu_decode_all(void* handle, int reps) {
   for (int r = 0; r < reps && ok; ++r) {
     cudaEventRecord(e0);
     for (auto& mx : M->mats)
-      if (launch_decode_codes(mx.dev, scratch, mx.paired, nullptr)) ok = false;
+      if (decode_codes_of(mx, scratch, true, nullptr)) ok = false;
     cudaEventRecord(e1);
     if (cudaEventSynchronize(e1) != cudaSuccess) ok = false;
     float ms = 0;

@@ -24,10 +24,11 @@ static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned in
     return rc ? rc : launch_t<FMT, G, IDXBITS, EXPAND>(M, out, mid, tr1, err, st);
   }
   const size_t fixed = (size_t(1) << (M.index_bits + ring_log_copies(M.index_bits) + 2)) + kLutSize * 4 + ring_fixed_bytes(max_units) + kRingSlackWords * 4;
-  if (fixed + static_cast<size_t>(buf_words) * 4 > kSmemLimit) return kErrTooLarge;
-  const int slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed) / (buf_words * 4)));
+  const size_t buf_bytes = static_cast<size_t>(buf_words) * 4;
+  if (fixed + buf_bytes > kSmemLimit) return kErrTooLarge;
+  const int slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed) / buf_bytes));
   const int warps = std::max(1, std::min(std::min(kRingMaxWarps, max_units), max_units <= slots ? slots : slots * 3 / 4));
-  const size_t smem = fixed + static_cast<size_t>(slots) * buf_words * 4;
+  const size_t smem = fixed + slots * buf_bytes;
   auto kernel = k_decode_codes_ring<FMT, G, IDXBITS, ring_log_copies(IDXBITS), EXPAND>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return note_launch("cudaFuncSetAttribute(k_decode_codes_ring)");
@@ -51,6 +52,9 @@ static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned in
   return note_launch("k_decode_codes_ring");
 }
 
+template <int FMT>
+static int launch_bundle_code(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st);
+
 template <int FMT, int G, int IDXBITS>
 static int launch_e(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st) {
   const int NT = M.N / kTileRows;
@@ -68,6 +72,18 @@ static int launch_x(const MatDev& M, uint8_t* out, bool expand, unsigned int* er
 
 template <int FMT>
 static int launch_i(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st) {
+  if constexpr (is_pair_layout(FMT)) {
+    const int NT = M.N / kTileRows;
+    if constexpr (pair_code_bits_max(FMT) == 12)
+      if (M.index_bits == 12) return launch_t<FMT, 3, 12, true>(M, out, 0, NT, err, st);
+    return launch_t<FMT, 3, 11, true>(M, out, 0, NT, err, st);
+  } else {
+    return launch_bundle_code<FMT>(M, out, expand, err, st);
+  }
+}
+
+template <int FMT>
+static int launch_bundle_code(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st) {
   switch (M.group) {
     case 3: return launch_x<FMT, 3>(M, out, expand, err, st);
     case 4: return launch_x<FMT, 4>(M, out, expand, err, st);
@@ -83,12 +99,14 @@ static int launch_i(const MatDev& M, uint8_t* out, bool expand, unsigned int* er
 
 // Returns kErrTooLarge where this kernel cannot take the matrix (the caller then uses the warp-per-tile kernel).
 int launch_decode_codes_ring(const MatDev& M, uint8_t* out, bool expand, unsigned int* err, cudaStream_t st) {
-  if (!err || !M.symtab32 || !gemv1_usable(M) || M.reader != 0 || M.KT > 255) return kErrTooLarge;
+  if (!err || (!M.symtab32 && !is_pair_layout(M.fmt)) || !gemv1_usable(M) || M.reader != 0 || M.KT > 255) return kErrTooLarge;
   switch (M.fmt) {
     case kFmtQ4K: return launch_i<kFmtQ4K>(M, out, expand, err, st);
     case kFmtQ5K: return launch_i<kFmtQ5K>(M, out, expand, err, st);
     case kFmtIQ4XS: return launch_i<kFmtIQ4XS>(M, out, expand, err, st);
     case kFmtQ6K: return launch_i<kFmtQ6K>(M, out, expand, err, st);
+    case kFmtQ6KP: return launch_i<kFmtQ6KP>(M, out, expand, err, st);   // always one code per byte
+    case kFmtQ5KP: return launch_i<kFmtQ5KP>(M, out, expand, err, st);
   }
   return kErrTooLarge;
 }

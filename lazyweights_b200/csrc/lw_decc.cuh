@@ -16,10 +16,6 @@ struct DeccArgs {
 
 struct BytePack {
   uint32_t w[8];
-  __device__ __forceinline__ void clear() {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = 0u;
-  }
   __device__ __forceinline__ void flush(uint8_t* dst) const {
     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
                  "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
@@ -35,7 +31,13 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
   constexpr int PER = EXPAND ? 16 : 32;                            // symbols per 32-byte store
   constexpr int OUT_PER_SYM = EXPAND ? 2 : 1;
   static_assert(!EXPAND || is_paired(FMT), "only paired symbols expand");
+  // a pair layout (two codes of an unpaired format per symbol) is always written one code per byte; its table holds
+  // grid values, from which the codes follow: Q6_K stores code - 32 (so code = low six bits with bit 5 flipped),
+  // Q5_K the code itself
+  constexpr bool PAIR_LAYOUT = is_pair_layout(FMT);
+  static_assert(!PAIR_LAYOUT || EXPAND, "a pair layout is written expanded");
   constexpr int NIDX = 1 << IDXBITS, R = 1 << LOG_R;
+  constexpr bool SINGLE = NIDX <= kLutSize;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -44,6 +46,15 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
   RingMem RM;
   RM.carve(tab1 + kLutSize, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the table's loads are issued before the block sets up its list, so that their latency is paid once and overlapped
+  const uint32_t* src = PAIR_LAYOUT ? M.tab32 : M.symtab32;
+  constexpr int TAB_PRE = 8;
+  uint32_t tab_pre[TAB_PRE];
+#pragma unroll
+  for (int i = 0; i < TAB_PRE; ++i) {
+    const int i0 = (i * RA.warps + warp) * 32;
+    tab_pre[i] = warp < RA.warps && i0 < NIDX ? __ldg(src + i0 + lane) : 0u;
+  }
   BlockShare S;
   S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);
   const int nmine = S.nmine;
@@ -56,16 +67,40 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
     return;
   }
   // the symbol table, replicated like the value table of the other kernels
-  for (int i0 = warp * 32; i0 < NIDX; i0 += RA.warps * 32) table_spread<LOG_R>(tab, tab1, i0, __ldg(M.symtab32 + i0 + lane), lane);
-  for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += RA.warps * 32) tab1[idx] = __ldg(M.symtab32 + idx);
+#pragma unroll
+  for (int i = 0; i < TAB_PRE; ++i) {
+    const int i0 = (i * RA.warps + warp) * 32;
+    if (i0 < NIDX) table_spread<LOG_R, SINGLE>(tab, tab1, i0, tab_pre[i], lane);
+  }
+  for (int i0 = (TAB_PRE * RA.warps + warp) * 32; i0 < NIDX; i0 += RA.warps * 32)
+    table_spread<LOG_R, SINGLE>(tab, tab1, i0, __ldg(src + i0 + lane), lane);
+  for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += RA.warps * 32) tab1[idx] = __ldg(src + idx);
   asm volatile("bar.sync 1, %0;" ::"r"(RA.warps * 32) : "memory");
   const uint32_t lane_off = (lane & (R - 1)) << 2;
-  auto put = [&](BytePack& p, int c, uint32_t e) {   // symbol c of the current 32 bytes
-    const uint32_t sym = e & 255u;
-    if (EXPAND)
-      p.w[c / 2] |= ((sym & 15u) | ((sym >> 4) << 8)) << (16 * (c % 2));
-    else
-      p.w[c / 4] |= sym << (8 * (c % 4));
+  // Symbol c of the current 32 bytes.  Bytes are placed with byte permutes (one instruction per symbol, c is a constant
+  // after unrolling); the first symbol of a word just sets it, its upper bytes are replaced by the symbols that follow.
+  // Table entries are length << 28 | payload with zero bits between, so byte 1 of a symbol entry is zero.
+  auto put = [&](BytePack& p, int c, uint32_t e) {
+    if constexpr (PAIR_LAYOUT) {          // two code bytes per entry
+      uint32_t& w = p.w[c / 2];
+      if (c % 2 == 0) {
+        w = e;
+      } else {
+        w = __byte_perm(w, e, 0x5410);
+        if (FMT == kFmtQ6KP) w = (w & 0x3F3F3F3Fu) ^ 0x20202020u;   // the table holds code - 32
+      }
+    } else if constexpr (EXPAND) {        // a pair symbol to two 4-bit codes, low nibble first
+      uint32_t& w = p.w[c / 2];
+      if (c % 2 == 0) {
+        w = e;
+      } else {
+        w = __byte_perm(w, e, 0x5410);    // [s0, 0, s1, 0]
+        w = (w | (w << 4)) & 0x0F0F0F0Fu;
+      }
+    } else {
+      uint32_t& w = p.w[c / 4];
+      w = c % 4 == 0 ? e : __byte_perm(w, e, c % 4 == 1 ? 0x3240 : c % 4 == 2 ? 0x3410 : 0x4210);
+    }
   };
 #pragma unroll 1
   for (;;) {
@@ -73,18 +108,16 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
     const int got = ring_draw(RA, RM, nmine, lane, u);
     if (got == 0) break;
     if (got < 0) return;
-    GroupChain ca, cb;
+    typename ChainOf<PAIR_LAYOUT, IDXBITS>::type ca, cb;
     ca.init(u.buf + lane, kRingLogCopies - LOG_R);
     cb.init(u.buf + u.second * 32u + lane, kRingLogCopies - LOG_R);
     uint8_t* oa = A.out + (static_cast<size_t>(u.tr) * kTileRows + lane) * A.row_bytes +
                   (static_cast<size_t>(u.j) * kTileSyms + u.seg * USYM) * OUT_PER_SYM;
     uint8_t* ob = oa + static_cast<size_t>(32) * A.row_bytes;
-    if (u.cls == 0) {
+    if (PAIR_LAYOUT || u.cls == 0) {   // a pair layout has no other class
 #pragma unroll
       for (int c0 = 0; c0 < USYM; c0 += PER) {
         BytePack pa, pb;
-        pa.clear();
-        pb.clear();
 #pragma unroll
         for (int c = 0; c < PER; ++c) {
           const int f = c0 + c;
@@ -103,12 +136,10 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
         pa.flush(oa + c0 * OUT_PER_SYM);
         pb.flush(ob + c0 * OUT_PER_SYM);
       }
-    } else {
+    } else if constexpr (!PAIR_LAYOUT) {
 #pragma unroll 1
       for (int c0 = 0; c0 < USYM; c0 += PER) {
         BytePack pa, pb;
-        pa.clear();
-        pb.clear();
 #pragma unroll
         for (int c = 0; c < PER; ++c) {
           uint32_t ea, eb;

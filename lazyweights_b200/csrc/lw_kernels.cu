@@ -280,6 +280,8 @@ int launch_decode_codes(const MatDev& M, uint8_t* out, bool expand_pairs, cudaSt
     set_kernel_error_text("decode_codes", "the output must be 32-byte aligned");
     return kErrArg;
   }
+  if (is_pair_layout(M.fmt))   // only the ring kernel reads a pair layout: kErrTooLarge sends the caller to the bundle's code
+    return gemv1_usable(M) ? launch_decode_codes_ring(M, out, true, error_word(), st) : kErrTooLarge;
   if (gemv1_usable(M) && M.symtab32) {   // the shared decoder, where the layout allows
     const int rc = launch_decode_codes_ring(M, out, expand_pairs, error_word(), st);
     if (rc != kErrTooLarge) return rc;

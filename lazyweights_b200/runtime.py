@@ -131,21 +131,27 @@ class _Handle:
                                            int(x2.dtype == torch.float16), C.c_void_p(y.data_ptr()), C.c_void_p(st)))
         return y
 
-    def decode_weights(self, name):
-        """fp16 CUDA tensor [N, K] of the dequantised weights."""
+    def decode_weights(self, name, out=None):
+        """fp16 CUDA tensor [N, K] of the dequantised weights (`out`: a contiguous tensor of that shape to fill)."""
         torch = _torch()
         inf = self.info(name)
-        w = torch.empty((inf["N"], inf["K"]), dtype=torch.float16, device="cuda")
+        w = out if out is not None else torch.empty((inf["N"], inf["K"]), dtype=torch.float16, device="cuda")
+        if w.dtype != torch.float16 or tuple(w.shape) != (inf["N"], inf["K"]) or not w.is_cuda or not w.is_contiguous():
+            raise ValueError("decode_weights wants a contiguous CUDA fp16 [%d, %d] tensor" % (inf["N"], inf["K"]))
         st = torch.cuda.current_stream().cuda_stream
         nat.check(nat.lib().lw_decode_weights(self._h, self.matrix_id(name), C.c_void_p(w.data_ptr()), C.c_void_p(st)))
         return w
 
-    def decode_codes(self, name, expand=True):
-        """uint8 CUDA tensor: codes [N, K] (expand) or symbols [N, K / 2] of a paired matrix."""
+    def decode_codes(self, name, expand=True, out=None):
+        """uint8 CUDA tensor: codes [N, K] (expand) or symbols [N, K / 2] of a paired matrix (`out`: a contiguous tensor
+        of that shape to fill)."""
         torch = _torch()
         inf = self.info(name)
         cols = inf["K"] if (expand or not inf["paired"]) else inf["K"] // 2
-        out = torch.empty((inf["N"], cols), dtype=torch.uint8, device="cuda")
+        if out is None:
+            out = torch.empty((inf["N"], cols), dtype=torch.uint8, device="cuda")
+        if out.dtype != torch.uint8 or tuple(out.shape) != (inf["N"], cols) or not out.is_cuda or not out.is_contiguous():
+            raise ValueError("decode_codes wants a contiguous CUDA uint8 [%d, %d] tensor" % (inf["N"], cols))
         st = torch.cuda.current_stream().cuda_stream
         nat.check(nat.lib().lw_decode_codes(self._h, self.matrix_id(name), C.c_void_p(out.data_ptr()), int(expand),
                                             C.c_void_p(st)))

@@ -261,4 +261,8 @@ def test_pair_layout_product(lw, tmp_path, ty, n, k, narrow):
         assert helpers.rel_err(yb.cpu().numpy(), orc.gemv_f64(w[::-1], x.cpu().numpy()[None])[0]) <= helpers.GEMV_TOL
         X = rng.standard_normal((3, k)).astype(np.float32)              # the several-row kernel reads the pair layout too
         assert helpers.rel_err(b.matmul("a", X), orc.gemv_f64(w, X)) <= helpers.GEMV_TOL
+        assert np.array_equal(b.decode("a"), q)                         # decode to codes: two codes per lookup,
+        assert lw.lib().lw_debug_set(b"pairs", 0) == 0
+        assert np.array_equal(b.decode("a"), q)                         # and through the bundle's own code
+        assert lw.lib().lw_debug_set(b"pairs", 1) == 0
         assert b.kernel_error() == 0
