@@ -46,15 +46,9 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
   RingMem RM;
   RM.carve(tab1 + kLutSize, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the table's loads are issued before the block sets up its list, so that their latency is paid once and overlapped
   const uint32_t* src = PAIR_LAYOUT ? M.tab32 : M.symtab32;
-  constexpr int TAB_PRE = 8;
-  uint32_t tab_pre[TAB_PRE];
-#pragma unroll
-  for (int i = 0; i < TAB_PRE; ++i) {
-    const int i0 = (i * RA.warps + warp) * 32;
-    tab_pre[i] = warp < RA.warps && i0 < NIDX ? __ldg(src + i0 + lane) : 0u;
-  }
+  TableLoad<IDXBITS, LOG_R, SINGLE> table;
+  table.issue(src, warp, lane, RA.warps);
   BlockShare S;
   S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);
   const int nmine = S.nmine;
@@ -67,14 +61,7 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
     return;
   }
   // the symbol table, replicated like the value table of the other kernels
-#pragma unroll
-  for (int i = 0; i < TAB_PRE; ++i) {
-    const int i0 = (i * RA.warps + warp) * 32;
-    if (i0 < NIDX) table_spread<LOG_R, SINGLE>(tab, tab1, i0, tab_pre[i], lane);
-  }
-  for (int i0 = (TAB_PRE * RA.warps + warp) * 32; i0 < NIDX; i0 += RA.warps * 32)
-    table_spread<LOG_R, SINGLE>(tab, tab1, i0, __ldg(src + i0 + lane), lane);
-  for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += RA.warps * 32) tab1[idx] = __ldg(src + idx);
+  table.finish(src, tab, tab1, warp, lane, RA.warps);
   asm volatile("bar.sync 1, %0;" ::"r"(RA.warps * 32) : "memory");
   const uint32_t lane_off = (lane & (R - 1)) << 2;
   // Symbol c of the current 32 bytes.  Bytes are placed with byte permutes (one instruction per symbol, c is a constant

@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   RingMem RM;
   RM.carve(tab1 + kLutSize, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  TableLoad<IDXBITS, LOG_R, SINGLE> table;
+  table.issue(M.tab32, warp, lane, RA.warps);
   BlockShare S;
   S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);   // one column set (nsets = 1): there are no activations to stage
   const int nmine = S.nmine;
@@ -70,7 +72,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   }
 
   // 2b. consumers: the tables
-  table_fill<IDXBITS, LOG_R, SINGLE>(M, tab, tab1, warp, lane, RA.warps);
+  table.finish(M.tab32, tab, tab1, warp, lane, RA.warps);
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
   const uint32_t lane_off = (lane & (R - 1)) << 2;
 #pragma unroll 1

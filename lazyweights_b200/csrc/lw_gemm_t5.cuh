@@ -178,6 +178,8 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
   RingMem RM;
   RM.carve(tmem_slot + 4, RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  TableLoad<IDXBITS, LOG_R, SINGLE> table;
+  table.issue(M.tab32, warp, lane, kT5Consumers);
   const int NT = M.N / kTileRows, NRG = NT / 4;                   // row groups of four tile rows
   const int set = blockIdx.x % RA.nsets, bi = blockIdx.x / RA.nsets;
   const int nb_set = (gridDim.x - set + RA.nsets - 1) / RA.nsets;
@@ -256,7 +258,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) k_gemm_t5(const __grid_constant
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads xs through the async proxy
   }
-  if (warp < kT5Consumers) table_fill<IDXBITS, LOG_R, SINGLE>(M, tab, tab1, warp, lane, kT5Consumers);
+  if (warp < kT5Consumers) table.finish(M.tab32, tab, tab1, warp, lane, kT5Consumers);
   if (warp < kT5Consumers || warp == kT5Consumers + kT5Producers)
     asm volatile("bar.sync 1, %0;" ::"r"((kT5Consumers + 1) * 32) : "memory");
 

@@ -100,6 +100,8 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
   RingMem RM;
   RM.carve(xg + (HAS_OFFSET ? RA.cols_per_set * NSB * MR : 0), RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  TableLoad<IDXBITS, LOG_R, SINGLE> table;   // the matrix is not written by the kernel before: no need to wait for it
+  table.issue(M.tab32, warp, lane, RA.warps);
   BlockShare S;
   S.init(M, RA, SPLIT, blockIdx.x, gridDim.x);
   const int set = S.set, ncol = S.ncol, nmine = S.nmine;
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(gemvm_threads(MR), 1) k_gemvm(MatDev M, GemvmA
   }
 
   // 2b. consumers: tables, then the activations of the block's tile columns for all rows
-  table_fill<IDXBITS, LOG_R, SINGLE>(M, tab, tab1, warp, lane, RA.warps);
+  table.finish(M.tab32, tab, tab1, warp, lane, RA.warps);
   if (A.pdl) pdl_wait();
   constexpr int XB = 8;
   const int per_row = ncol * TW, total = per_row * MR;   // rows >= m are stored as zeros

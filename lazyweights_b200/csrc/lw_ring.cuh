@@ -284,6 +284,33 @@ __device__ __forceinline__ void table_fill(const MatDev& M, uint32_t* tab, uint3
     for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += nwarps * 32) tab1[idx] = __ldg(M.tab32 + idx);
 }
 
+// The same in two steps, for kernels that have set-up to do between them: issue() starts up to PRE loads per lane right
+// at the kernel's start (their latency, a DRAM miss for the first block that touches the table, then overlaps the unit
+// list's own loads and barriers), finish() spreads them and loads whatever a small block has left.
+template <int IDXBITS, int LOG_R, bool SINGLE = true, int PRE = 8>
+struct TableLoad {
+  static constexpr int NIDX = 1 << IDXBITS;
+  uint32_t pre[PRE];
+  __device__ __forceinline__ void issue(const uint32_t* src, int warp, int lane, int nwarps) {
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const int i0 = (i * nwarps + warp) * 32;
+      pre[i] = warp < nwarps && i0 < NIDX ? __ldg(src + i0 + lane) : 0u;
+    }
+  }
+  __device__ __forceinline__ void finish(const uint32_t* src, uint32_t* tab, uint32_t* tab1, int warp, int lane, int nwarps) const {
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const int i0 = (i * nwarps + warp) * 32;
+      if (i0 < NIDX) table_spread<LOG_R, SINGLE>(tab, tab1, i0, pre[i], lane);
+    }
+    for (int i0 = (PRE * nwarps + warp) * 32; i0 < NIDX; i0 += nwarps * 32)
+      table_spread<LOG_R, SINGLE>(tab, tab1, i0, __ldg(src + i0 + lane), lane);
+    if (SINGLE)
+      for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += nwarps * 32) tab1[idx] = __ldg(src + idx);
+  }
+};
+
 // ------------------------------------------------------------------------------------------------ chain reader
 //
 // Refills are checked once per group of G symbols: the 64-bit window is normalised to the chain's bit position when a
