@@ -1,7 +1,10 @@
 // Instantiations and launcher of the decode-to-codes kernel on the shared decoder; see lw_decc.cuh.
 #include "lw_gemv1.h"
 
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstdlib>
 
 #include "lw_decc.cuh"
 
@@ -10,8 +13,8 @@ namespace lw {
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kRingSlackWords = 96;
 
-template <int FMT, int G, int IDXBITS, bool EXPAND>
-static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+template <int FMT, int G, int IDXBITS, bool EXPAND, bool TILE_OUT>
+static int launch_o(const MatDev& M, uint8_t* out, const CUtensorMap& tm, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
   constexpr int SPLIT = default_split(FMT);
   const uint32_t buf_words = (M.max_unit_words + 31u) & ~31u;
   const int tiles = (tr1 - tr0) * M.KT;
@@ -20,16 +23,20 @@ static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned in
   if (max_units > kRingMaxUnits) {   // more tile rows than one block's list holds: two halves
     const int mid = tr0 + (tr1 - tr0) / 2;
     if (mid == tr0) return kErrTooLarge;
-    const int rc = launch_t<FMT, G, IDXBITS, EXPAND>(M, out, tr0, mid, err, st);
-    return rc ? rc : launch_t<FMT, G, IDXBITS, EXPAND>(M, out, mid, tr1, err, st);
+    const int rc = launch_o<FMT, G, IDXBITS, EXPAND, TILE_OUT>(M, out, tm, tr0, mid, err, st);
+    return rc ? rc : launch_o<FMT, G, IDXBITS, EXPAND, TILE_OUT>(M, out, tm, mid, tr1, err, st);
   }
   const size_t fixed = (size_t(1) << (M.index_bits + ring_log_copies(M.index_bits) + 2)) + kLutSize * 4 + ring_fixed_bytes(max_units) + kRingSlackWords * 4;
   const size_t buf_bytes = static_cast<size_t>(buf_words) * 4;
   if (fixed + buf_bytes > kSmemLimit) return kErrTooLarge;
-  const int slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed) / buf_bytes));
+  // with TILE_OUT every consumer warp also has a 2 KB area for its rows' bytes: about three consumers per four buffers
+  const size_t stage = TILE_OUT ? WarpTileStage::kBytes : 0;
+  int slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed) / (buf_bytes + stage * 3 / 4)));
   const int warps = std::max(1, std::min(std::min(kRingMaxWarps, max_units), max_units <= slots ? slots : slots * 3 / 4));
-  const size_t smem = fixed + slots * buf_bytes;
-  auto kernel = k_decode_codes_ring<FMT, G, IDXBITS, ring_log_copies(IDXBITS), EXPAND>;
+  slots = static_cast<int>(std::min<size_t>(kRingMaxSlots, (kSmemLimit - fixed - warps * stage) / buf_bytes));
+  if (slots < 1) return kErrTooLarge;
+  const size_t smem = fixed + warps * stage + slots * buf_bytes;
+  auto kernel = k_decode_codes_ring<FMT, G, IDXBITS, ring_log_copies(IDXBITS), EXPAND, TILE_OUT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return note_launch("cudaFuncSetAttribute(k_decode_codes_ring)");
   DeccArgs a = {};
@@ -48,8 +55,23 @@ static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned in
   a.r.ntr = tr1 - tr0;
   a.out = out;
   a.row_bytes = EXPAND ? 2 * M.Ks : M.Ks;
-  kernel<<<blocks, (warps + 2) * 32, smem, st>>>(M, a);
+  kernel<<<blocks, (warps + 2) * 32, smem, st>>>(M, a, tm);
   return note_launch("k_decode_codes_ring");
+}
+
+static bool tile_out_wanted() {
+  static const bool v = !(getenv("LW_TILE_OUT") && atoi(getenv("LW_TILE_OUT")) == 0);
+  return v;
+}
+
+template <int FMT, int G, int IDXBITS, bool EXPAND>
+static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  alignas(64) CUtensorMap tm = {};
+  if (tile_out_wanted() && make_row_tile_map(&tm, out, EXPAND ? 2 * static_cast<size_t>(M.Ks) : M.Ks, M.N)) {
+    const int rc = launch_o<FMT, G, IDXBITS, EXPAND, true>(M, out, tm, tr0, tr1, err, st);
+    if (rc != kErrTooLarge) return rc;
+  }
+  return launch_o<FMT, G, IDXBITS, EXPAND, false>(M, out, tm, tr0, tr1, err, st);
 }
 
 template <int FMT>

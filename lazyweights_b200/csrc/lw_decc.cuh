@@ -23,8 +23,11 @@ struct BytePack {
   }
 };
 
-template <int FMT, int G, int IDXBITS, int LOG_R, bool EXPAND>
-__global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_constant__ MatDev M, const __grid_constant__ DeccArgs A) {
+// TILE_OUT: the bytes leave through shared memory and the tensor-copy engine (WarpTileStage; TM = the output's tensor map)
+// instead of 32-byte stores
+template <int FMT, int G, int IDXBITS, int LOG_R, bool EXPAND, bool TILE_OUT>
+__global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_constant__ MatDev M, const __grid_constant__ DeccArgs A,
+                                                               const __grid_constant__ CUtensorMap TM) {
   const RingArgs& RA = A.r;
   constexpr int SPLIT = default_split(FMT);
   constexpr int USYM = kTileSyms / SPLIT;                          // symbols per chain
@@ -40,11 +43,12 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
   constexpr bool SINGLE = NIDX <= kLutSize;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
   uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);
+  uint8_t* stage0 = reinterpret_cast<uint8_t*>(tab1 + kLutSize);   // [warps][2 KB] when TILE_OUT; 1024-byte aligned
   RingMem RM;
-  RM.carve(tab1 + kLutSize, RA);
+  RM.carve(stage0 + (TILE_OUT ? RA.warps * WarpTileStage::kBytes : 0), RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t* src = PAIR_LAYOUT ? M.tab32 : M.symtab32;
   TableLoad<IDXBITS, LOG_R, SINGLE> table;
@@ -89,12 +93,29 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
       w = c % 4 == 0 ? e : __byte_perm(w, e, c % 4 == 1 ? 0x3240 : c % 4 == 2 ? 0x3410 : 0x4210);
     }
   };
+  WarpTileStage stage;
+  stage.init(stage0 + (TILE_OUT ? warp * WarpTileStage::kBytes : 0), lane);
+  // 32 bytes of each of the unit's rows: piece `it` of the unit; oa / ob: the unit's first byte in rows lane, lane + 32
+  auto out32 = [&](const Unit& u, int it, const BytePack& pa, const BytePack& pb, uint8_t* oa, uint8_t* ob) {
+    if constexpr (TILE_OUT) {
+      stage.reuse(lane);
+      stage.put(0, pa.w);
+      stage.put(1, pb.w);
+      stage.send(&TM, (u.j * kTileSyms + u.seg * USYM) * OUT_PER_SYM + it * 32, u.tr * kTileRows, lane);
+    } else {
+      pa.flush(oa + it * 32);
+      pb.flush(ob + it * 32);
+    }
+  };
 #pragma unroll 1
   for (;;) {
     Unit u;
     const int got = ring_draw(RA, RM, nmine, lane, u);
     if (got == 0) break;
-    if (got < 0) return;
+    if (got < 0) {
+      if (TILE_OUT) stage.drain(lane);
+      return;
+    }
     typename ChainOf<PAIR_LAYOUT, IDXBITS>::type ca, cb;
     ca.init(u.buf + lane, kRingLogCopies - LOG_R);
     cb.init(u.buf + u.second * 32u + lane, kRingLogCopies - LOG_R);
@@ -120,8 +141,7 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
           put(pa, c, ea);
           put(pb, c, eb);
         }
-        pa.flush(oa + c0 * OUT_PER_SYM);
-        pb.flush(ob + c0 * OUT_PER_SYM);
+        out32(u, c0 / PER, pa, pb, oa, ob);
       }
     } else if constexpr (!PAIR_LAYOUT) {
 #pragma unroll 1
@@ -144,12 +164,12 @@ __global__ void __launch_bounds__(1024, 1) k_decode_codes_ring(const __grid_cons
           put(pa, c, ea);
           put(pb, c, eb);
         }
-        pa.flush(oa + c0 * OUT_PER_SYM);
-        pb.flush(ob + c0 * OUT_PER_SYM);
+        out32(u, c0 / PER, pa, pb, oa, ob);
       }
     }
     ring_release(RM, u, lane);
   }
+  if (TILE_OUT) stage.drain(lane);
 }
 
 }  // namespace lw

@@ -1,7 +1,10 @@
 // Instantiations and launcher of the decode-to-weights kernel; see lw_decw.cuh.
 #include "lw_gemv1.h"
 
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstdlib>
 
 #include "lw_decw.cuh"
 
@@ -10,8 +13,13 @@ namespace lw {
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kRingSlackWords = 96;
 
-template <int FMT, int G, int IDXBITS>
-static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+static bool tile_out_wanted() {
+  static const bool v = !(getenv("LW_TILE_OUT") && atoi(getenv("LW_TILE_OUT")) == 0);
+  return v;
+}
+
+template <int FMT, int G, int IDXBITS, bool TILE_OUT>
+static int launch_o(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
   constexpr int SPLIT = default_split(FMT);
   const uint32_t buf_words = (M.max_unit_words + 31u) & ~31u;
   const int tiles = (tr1 - tr0) * M.KT;
@@ -20,16 +28,23 @@ static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
   if (max_units > kGemv1MaxUnits) {   // more tile rows than one block's list holds: two halves
     const int mid = tr0 + (tr1 - tr0) / 2;
     if (mid == tr0) return kErrTooLarge;
-    const int rc = launch_t<FMT, G, IDXBITS>(M, out, tr0, mid, err, st);
-    return rc ? rc : launch_t<FMT, G, IDXBITS>(M, out + static_cast<size_t>(mid - tr0) * kTileRows * M.K, mid, tr1, err, st);
+    const int rc = launch_o<FMT, G, IDXBITS, TILE_OUT>(M, out, tr0, mid, err, st);
+    return rc ? rc : launch_o<FMT, G, IDXBITS, TILE_OUT>(M, out + static_cast<size_t>(mid - tr0) * kTileRows * M.K, mid, tr1, err, st);
   }
   const size_t fixed = (size_t(1) << (M.index_bits + ring_log_copies(M.index_bits) + 2)) + kLutSize * 4 + 2 * kGemv1MaxSlots * 8 +
                        kGemv1MaxSlots * 4 + 16 + max_units * sizeof(UnitMeta) + kRingSlackWords * 4;
-  if (fixed + static_cast<size_t>(buf_words) * 4 > kSmemLimit) return kErrTooLarge;
-  const int slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (buf_words * 4)));
+  const size_t buf_bytes = static_cast<size_t>(buf_words) * 4;
+  if (fixed + buf_bytes > kSmemLimit) return kErrTooLarge;
+  // with TILE_OUT every consumer warp also has a 2 KB area for its rows' weights: about three consumers per four buffers
+  alignas(64) CUtensorMap tm = {};
+  if (TILE_OUT && !make_row_tile_map(&tm, out, static_cast<size_t>(M.K) * 2, static_cast<size_t>(tr1 - tr0) * kTileRows)) return kErrTooLarge;
+  const size_t stage = TILE_OUT ? WarpTileStage::kBytes : 0;
+  int slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed) / (buf_bytes + stage * 3 / 4)));
   const int warps = std::max(1, std::min(std::min(kGemv1MaxWarps, max_units), max_units <= slots ? slots : slots * 3 / 4));
-  const size_t smem = fixed + static_cast<size_t>(slots) * buf_words * 4;
-  auto kernel = k_decw<FMT, G, IDXBITS, ring_log_copies(IDXBITS)>;
+  slots = static_cast<int>(std::min<size_t>(kGemv1MaxSlots, (kSmemLimit - fixed - warps * stage) / buf_bytes));
+  if (slots < 1) return kErrTooLarge;
+  const size_t smem = fixed + warps * stage + slots * buf_bytes;
+  auto kernel = k_decw<FMT, G, IDXBITS, ring_log_copies(IDXBITS), TILE_OUT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return note_launch("cudaFuncSetAttribute(k_decw)");
   DecwArgs a = {};
@@ -47,8 +62,17 @@ static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
   a.r.tr0 = tr0;
   a.r.ntr = tr1 - tr0;
   a.out = out;
-  kernel<<<blocks, (warps + 2) * 32, smem, st>>>(M, a);
+  kernel<<<blocks, (warps + 2) * 32, smem, st>>>(M, a, tm);
   return note_launch("k_decw");
+}
+
+template <int FMT, int G, int IDXBITS>
+static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
+  if (tile_out_wanted()) {
+    const int rc = launch_o<FMT, G, IDXBITS, true>(M, out, tr0, tr1, err, st);
+    if (rc != kErrTooLarge) return rc;
+  }
+  return launch_o<FMT, G, IDXBITS, false>(M, out, tr0, tr1, err, st);
 }
 
 template <int FMT, int G>

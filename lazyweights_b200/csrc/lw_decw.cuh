@@ -33,8 +33,11 @@ __device__ __forceinline__ float grid_of_entry(uint32_t e, int which) {
   return static_cast<float>(static_cast<int>(static_cast<int8_t>((e >> (8 * which)) & 255u)));
 }
 
-template <int FMT, int G, int IDXBITS, int LOG_R>
-__global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
+// TILE_OUT: the weights leave through shared memory and the tensor-copy engine (WarpTileStage; TM = the tensor map of the
+// launch's output rows) instead of 32-byte stores
+template <int FMT, int G, int IDXBITS, int LOG_R, bool TILE_OUT>
+__global__ void __launch_bounds__(1024, 1) k_decw(const __grid_constant__ MatDev M, const __grid_constant__ DecwArgs A,
+                                                  const __grid_constant__ CUtensorMap TM) {
   const RingArgs& RA = A.r;
   constexpr bool PAIR = is_paired(FMT);
   constexpr int SPLIT = default_split(FMT);
@@ -46,11 +49,12 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   constexpr bool SINGLE = NIDX <= kLutSize;
   constexpr uint32_t MASK = static_cast<uint32_t>(NIDX - 1) << (LOG_R + 2);
   constexpr int kReplicatedTableBytes = NIDX * R * 4;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint32_t* tab = reinterpret_cast<uint32_t*>(smem);
   uint32_t* tab1 = reinterpret_cast<uint32_t*>(smem + kReplicatedTableBytes);
+  uint8_t* stage0 = reinterpret_cast<uint8_t*>(tab1 + kLutSize);   // [warps][2 KB] when TILE_OUT; 1024-byte aligned
   RingMem RM;
-  RM.carve(tab1 + kLutSize, RA);
+  RM.carve(stage0 + (TILE_OUT ? RA.warps * WarpTileStage::kBytes : 0), RA);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   TableLoad<IDXBITS, LOG_R, SINGLE> table;
   table.issue(M.tab32, warp, lane, RA.warps);
@@ -75,12 +79,17 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
   table.finish(M.tab32, tab, tab1, warp, lane, RA.warps);
   asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
   const uint32_t lane_off = (lane & (R - 1)) << 2;
+  WarpTileStage stage;
+  stage.init(stage0 + (TILE_OUT ? warp * WarpTileStage::kBytes : 0), lane);
 #pragma unroll 1
   for (;;) {
     Unit u;
     const int got = ring_draw(RA, RM, nmine, lane, u);
     if (got == 0) break;
-    if (got < 0) return;
+    if (got < 0) {
+      if (TILE_OUT) stage.drain(lane);
+      return;
+    }
     const uint32_t tc = u.j, seg = u.seg, tr = u.tr, cls = u.cls, lines = u.lines, second = u.second;
     const uint32_t* buf = u.buf;
     UnitSide<FMT> side_a, side_b;
@@ -94,14 +103,32 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
     __half* ob = oa + static_cast<size_t>(32) * M.K;
     // symbols per 32-byte store: eight paired symbols (two weights each) or sixteen single ones
     constexpr int PER = PAIR ? 8 : 16;
+    // sixteen weights of each of the unit's rows, from column `col` of the unit
+    auto out16 = [&](int col, const HalfPack& pa, const HalfPack& pb) {
+      if constexpr (TILE_OUT) {
+        stage.reuse(lane);
+        stage.put(0, pa.w);
+        stage.put(1, pb.w);
+        stage.send(&TM, (static_cast<int>(tc) * TW + static_cast<int>(seg) * (TW / SPLIT) + col) * 2, static_cast<int>(tr - RA.tr0) * kTileRows, lane);
+      } else {
+        pa.flush(oa + col);
+        pb.flush(ob + col);
+      }
+    };
     // weights of one decoded symbol pair (chains a and b) into the two packs
+    // s * f(q) - o, each operation rounded; formats without offsets have o = 0 and x - 0 = x exactly, so they skip it
+    constexpr bool HAS_OFFSET = FMT == kFmtQ4K || FMT == kFmtQ5K || FMT == kFmtQ5KP;
+    auto weight = [&](float s, float o, uint32_t e, int which) {
+      const float p = __fmul_rn(s, grid_of_entry(e, which));
+      return HAS_OFFSET ? __fsub_rn(p, o) : p;
+    };
     auto emit = [&](int c, uint32_t ea, uint32_t eb, float s_a, float o_a, float s_b, float o_b, HalfPack& pa, HalfPack& pb) {
       if (PAIR) {
-        pa.put(c, __fsub_rn(__fmul_rn(s_a, grid_of_entry(ea, 0)), o_a), __fsub_rn(__fmul_rn(s_a, grid_of_entry(ea, 1)), o_a));
-        pb.put(c, __fsub_rn(__fmul_rn(s_b, grid_of_entry(eb, 0)), o_b), __fsub_rn(__fmul_rn(s_b, grid_of_entry(eb, 1)), o_b));
+        pa.put(c, weight(s_a, o_a, ea, 0), weight(s_a, o_a, ea, 1));
+        pb.put(c, weight(s_b, o_b, eb, 0), weight(s_b, o_b, eb, 1));
       } else {   // two consecutive symbols make one half2: the even one waits (as float bits) for the odd one
-        const float wa = __fsub_rn(__fmul_rn(s_a, grid_of_entry(ea, 0)), o_a);
-        const float wb = __fsub_rn(__fmul_rn(s_b, grid_of_entry(eb, 0)), o_b);
+        const float wa = weight(s_a, o_a, ea, 0);
+        const float wb = weight(s_b, o_b, eb, 0);
         if (c % 2 == 0) {
           pa.w[c / 2] = __float_as_uint(wa);
           pb.w[c / 2] = __float_as_uint(wb);
@@ -135,9 +162,7 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
             }
             emit(c, ea, eb, s_a, o_a, s_b, o_b, pa, pb);
           }
-          const int col = jj * GW + (PAIR ? 2 * c0 : c0);
-          pa.flush(oa + col);
-          pb.flush(ob + col);
+          out16(jj * GW + (PAIR ? 2 * c0 : c0), pa, pb);
         }
       }
     } else if constexpr (!PAIR_LAYOUT) {
@@ -166,14 +191,13 @@ __global__ void __launch_bounds__(1024, 1) k_decw(MatDev M, DecwArgs A) {
             }
             emit(c, ea, eb, s_a, o_a, s_b, o_b, pa, pb);
           }
-          const int col = jj * GW + (PAIR ? 2 * c0 : c0);
-          pa.flush(oa + col);
-          pb.flush(ob + col);
+          out16(jj * GW + (PAIR ? 2 * c0 : c0), pa, pb);
         }
       }
     }
     ring_release(RM, u, lane);
   }
+  if (TILE_OUT) stage.drain(lane);
 }
 
 }  // namespace lw

@@ -18,6 +18,9 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include "lw_ring.cuh"
 #include "lw_gemv1.h"
 
@@ -232,6 +235,24 @@ static int check_launch(const char* what) {
 }
 
 int note_launch(const char* what) { return check_launch(what); }
+
+bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t rows) {
+  static const PFN_cuTensorMapEncodeTiled encode = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess || found != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    (void)cudaGetLastError();
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  }();
+  if (!encode || (reinterpret_cast<uintptr_t>(base) & 15u) || row_bytes % 32 || rows % kTileRows) return false;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {32, kTileRows};
+  const cuuint32_t estr[2] = {1, 1};
+  return encode(static_cast<CUtensorMap*>(tensor_map), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 // SMs of the current device (cached per device: a process may hold handles on several).
 int sm_count() {

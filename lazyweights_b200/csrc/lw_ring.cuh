@@ -17,6 +17,7 @@
 // is known to be in the phase the parity wait assumes.  Every wait is bounded: a warp that gives up sets the device
 // error word and leaves.
 #pragma once
+#include <cuda.h>
 #include "lw_device.cuh"
 
 namespace lw {
@@ -308,6 +309,50 @@ struct TableLoad {
       table_spread<LOG_R, SINGLE>(tab, tab1, i0, __ldg(src + i0 + lane), lane);
     if (SINGLE)
       for (int idx = NIDX + warp * 32 + lane; idx < kLutSize; idx += nwarps * 32) tab1[idx] = __ldg(src + idx);
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ tile stores
+//
+// Output of the decode-only kernels.  A lane owns two rows of a tile, so a plain store instruction of a warp touches 32
+// different lines and passes the load/store pipe once per line - the pipe the table lookups already fill.  Instead a
+// warp collects 32 bytes of each of its 64 rows in shared memory (2 KB, two 16-byte stores per lane and row) and one lane
+// hands the 64 x 32-byte box to the tensor-copy engine (cp.async.bulk.tensor shared -> global, no multicast, this GPU's
+// own memory), which writes whole sectors without the load/store pipe.  The tensor map (built on the host per output
+// buffer, bytes as elements: [rows][row bytes]) uses the 32-byte swizzle: the 16-byte half of a row is exchanged where
+// address bit 7 is set, which is exactly what spreads the lanes' 16-byte stores over all banks.
+// wait_group is a hardware wait on the issuing lane's own copies, not a spin on memory.
+struct WarpTileStage {
+  static constexpr int kBytes = 2048;
+  uint32_t base, row_a, swz;   // shared addresses: the warp's area (1024-byte aligned), this lane's first row
+  __device__ __forceinline__ void init(const void* warp_area, int lane) {
+    base = smem_addr(warp_area);
+    row_a = base + lane * 32;          // row lane; row lane + 32 is 1024 bytes further (same address bit 7)
+    swz = ((lane >> 2) & 1) * 16;
+  }
+  // the box sent last has been read: the area may be written again
+  __device__ __forceinline__ void reuse(int lane) const {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+  }
+  __device__ __forceinline__ void put(int second, const uint32_t (&w)[8]) const {
+    const uint32_t a = row_a + second * 1024;
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a + swz), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a + (16u ^ swz)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  }
+  // x: byte column (a multiple of 32), y: first of the 64 rows
+  __device__ __forceinline__ void send(const void* tensor_map, int x, int y, int lane) const {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tensor_map), "r"(x), "r"(y), "r"(base)
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  // before the warp exits: its copies are complete
+  __device__ __forceinline__ void drain(int lane) const {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 };
 
