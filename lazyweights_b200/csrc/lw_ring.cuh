@@ -317,7 +317,7 @@ struct TableLoad {
 // Output of the decode-only kernels.  A lane owns two rows of a tile, so a plain store instruction of a warp touches 32
 // different lines and passes the load/store pipe once per line - the pipe the table lookups already fill.  Instead a
 // warp collects 32 bytes of each of its 64 rows in shared memory (2 KB, two 16-byte stores per lane and row) and one lane
-// hands the 64 x 32-byte box to the tensor-copy engine (cp.async.bulk.tensor shared -> global, no multicast, this GPU's
+// hands the 64 x 32-byte box to the tensor-copy engine (cp.async.bulk.tensor shared -> global, a plain store of this GPU's
 // own memory), which writes whole sectors without the load/store pipe.  The tensor map (built on the host per output
 // buffer, bytes as elements: [rows][row bytes]) uses the 32-byte swizzle: the 16-byte half of a row is exchanged where
 // address bit 7 is set, which is exactly what spreads the lanes' 16-byte stores over all banks.
