@@ -19,7 +19,7 @@ struct DecwArgs {
 struct HalfPack {
   uint32_t w[8];
   __device__ __forceinline__ void put(int i, float lo, float hi) {   // halfs 2 i, 2 i + 1 of the current sixteen
-    const __half2 h = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
+    const __half2 h = __floats2half2_rn(lo, hi);   // one conversion instruction for both, each rounded to nearest even
     w[i] = *reinterpret_cast<const uint32_t*>(&h);
   }
   __device__ __forceinline__ void flush(__half* dst) const {

@@ -105,6 +105,35 @@ def test_limit_register_decoder_equals_table_decoder(lw, tmp_path):
         assert helpers.rel_err(outs["limit"][key], orc.gemv_f64(w, x[None])[0]) <= helpers.GEMV_TOL
 
 
+DECODE_WORKER = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, %r)
+import lazyweights_b200 as lw
+from tests import helpers
+from oracle import lw_oracle as orc
+for ty, n, k in %r:
+    q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=3 * n + k)
+    blob, _, _ = lw.bundle.encode_huf8(sym)
+    with lw.CodedMatrix(blob, n, sym.shape[1], ty, side) as mat:
+        assert np.array_equal(mat.decode_codes("m", expand=True).cpu().numpy(), q), ty
+        assert np.array_equal(mat.decode_codes("m", expand=False).cpu().numpy(), sym), ty
+        got = mat.decode_weights("m").cpu().numpy()
+        assert np.array_equal(got.view(np.uint16), w.astype(np.float16).view(np.uint16)), ty
+assert lw.lib().lw_kernel_error() == 0
+print("ok")
+"""
+
+
+def test_decode_kernels_with_plain_stores(lw):
+    """The decode kernels normally send their rows through shared memory and tensor copies; LW_TILE_OUT=0 (read once per
+    process) keeps the 32-byte stores, which are also what a driver without the tensor-map encoder gets.  Same bits."""
+    shapes = [("Q4_K", 128, 1024), ("Q5_K", 128, 1024), ("Q6_K", 192, 1536), ("IQ4_XS", 64, 2560), ("Q6_K", 64, 256)]
+    env = dict(os.environ)
+    env["LW_TILE_OUT"] = "0"
+    r = subprocess.run([sys.executable, "-c", DECODE_WORKER % (ROOT, shapes)], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
 def test_batched_launch_equals_single_products(lw, tmp_path):
     """lw_linear_batch: several products in one launch (same format and plan), mixed formats (launched one by one),
     several matrices of one handle; results equal the single-product entry point's bit for bit."""
