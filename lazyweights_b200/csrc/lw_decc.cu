@@ -4,7 +4,6 @@
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdlib>
 
 #include "lw_decc.cuh"
 
@@ -59,15 +58,10 @@ static int launch_o(const MatDev& M, uint8_t* out, const CUtensorMap& tm, int tr
   return note_launch("k_decode_codes_ring");
 }
 
-static bool tile_out_wanted() {
-  static const bool v = !(getenv("LW_TILE_OUT") && atoi(getenv("LW_TILE_OUT")) == 0);
-  return v;
-}
-
 template <int FMT, int G, int IDXBITS, bool EXPAND>
 static int launch_t(const MatDev& M, uint8_t* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
   alignas(64) CUtensorMap tm = {};
-  if (tile_out_wanted() && make_row_tile_map(&tm, out, EXPAND ? 2 * static_cast<size_t>(M.Ks) : M.Ks, M.N)) {
+  if (tile_output_enabled() && make_row_tile_map(&tm, out, EXPAND ? 2 * static_cast<size_t>(M.Ks) : M.Ks, M.N)) {
     const int rc = launch_o<FMT, G, IDXBITS, EXPAND, true>(M, out, tm, tr0, tr1, err, st);
     if (rc != kErrTooLarge) return rc;
   }

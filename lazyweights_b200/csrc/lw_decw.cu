@@ -4,7 +4,6 @@
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdlib>
 
 #include "lw_decw.cuh"
 
@@ -12,11 +11,6 @@ namespace lw {
 
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kRingSlackWords = 96;
-
-static bool tile_out_wanted() {
-  static const bool v = !(getenv("LW_TILE_OUT") && atoi(getenv("LW_TILE_OUT")) == 0);
-  return v;
-}
 
 template <int FMT, int G, int IDXBITS, bool TILE_OUT>
 static int launch_o(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
@@ -68,7 +62,7 @@ static int launch_o(const MatDev& M, __half* out, int tr0, int tr1, unsigned int
 
 template <int FMT, int G, int IDXBITS>
 static int launch_t(const MatDev& M, __half* out, int tr0, int tr1, unsigned int* err, cudaStream_t st) {
-  if (tile_out_wanted()) {
+  if (tile_output_enabled()) {
     const int rc = launch_o<FMT, G, IDXBITS, true>(M, out, tr0, tr1, err, st);
     if (rc != kErrTooLarge) return rc;
   }

@@ -51,6 +51,8 @@ DebugKnobs& debug_knobs();
 // Tensor map (a CUtensorMap, 128 bytes, 64-byte aligned) over an output buffer seen as bytes [rows][row_bytes] with boxes of
 // 64 rows x 32 bytes and the 32-byte swizzle; false where the driver does not offer the encoder or refuses the shape.
 bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t rows);
+// False with LW_TILE_OUT=0 in the environment (read once): the decode kernels then keep their 32-byte stores.
+bool tile_output_enabled();
 int note_launch(const char* what);   // counts a launch and returns the status of cudaGetLastError
 int sm_count();
 

@@ -236,6 +236,11 @@ static int check_launch(const char* what) {
 
 int note_launch(const char* what) { return check_launch(what); }
 
+bool tile_output_enabled() {
+  static const bool on = !(getenv("LW_TILE_OUT") && atoi(getenv("LW_TILE_OUT")) == 0);
+  return on;
+}
+
 bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t rows) {
   static const PFN_cuTensorMapEncodeTiled encode = [] {
     void* fn = nullptr;
