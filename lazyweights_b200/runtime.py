@@ -13,6 +13,15 @@ import numpy as np
 from . import _native as nat
 
 
+def _address(a):
+    """Address of a contiguous NumPy array's first byte.  `a.ctypes.data_as(...)` costs 4 us, twice per host-buffer call of
+    60 us; a ctypes view of the buffer costs 0.6 us (writable arrays only, hence the fallback)."""
+    try:
+        return C.addressof(C.c_char.from_buffer(a))
+    except (TypeError, ValueError, BufferError):
+        return a.ctypes.data
+
+
 def _torch():
     import torch
     return torch
@@ -165,8 +174,7 @@ class _Handle:
         if X.shape[1] != inf["K"]:
             raise ValueError("X has %d columns, the matrix %d" % (X.shape[1], inf["K"]))
         Y = np.empty((X.shape[0], inf["N"]), np.float32)
-        nat.check(nat.lib().rt_test_matmul(self._h, name.encode(), X.ctypes.data_as(C.c_void_p), X.shape[0],
-                                           Y.ctypes.data_as(C.c_void_p), path))
+        nat.check(nat.lib().rt_test_matmul(self._h, name.encode(), _address(X), X.shape[0], _address(Y), path))
         return Y
 
     def decode(self, name):
