@@ -80,3 +80,17 @@ def test_debug_switch_arguments():
     assert L.lw_debug_set(b"wait_limit", 1000) == 0 and L.lw_debug_set(b"wait_limit", 0) == -2
     assert L.lw_debug_set(b"drop_unit", 3) == 0 and L.lw_debug_set(b"nonsense", 1) == -2
     assert L.lw_debug_set(b"reset", 0) == 0
+
+
+def test_array_addresses_of_the_host_buffer_calls():
+    """The host-buffer wrappers hand NumPy arrays to the C ABI by address; the quick route (a ctypes view of the buffer)
+    and its fallback for read-only arrays must give the address NumPy itself reports."""
+    import numpy as np
+    helpers.build_library()
+    from lazyweights_b200 import runtime
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    assert runtime._address(a) == a.ctypes.data
+    assert runtime._address(a[1:]) == a.ctypes.data + 16            # a contiguous view starts at its own first byte
+    frozen = a.copy()
+    frozen.setflags(write=False)
+    assert runtime._address(frozen) == frozen.ctypes.data
