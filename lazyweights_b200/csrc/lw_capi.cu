@@ -232,6 +232,7 @@ static int upload_matrix(Matrix& mx, const HostImage& im, const uint8_t* side, s
   mx.dev.max_len = im.max_len;
   mx.dev.group_base = reinterpret_cast<const uint32_t*>(d + off_gb);
   mx.dev.words = reinterpret_cast<const uint32_t*>(d + off_words);
+  tile_output_warm();
   mx.dev.side = side_nbytes ? d + off_side : nullptr;
   mx.dev.unit_slow = im.unit_slow.empty() ? nullptr : d + off_slow;
   mx.dev.group = im.unit_slow.empty() ? 0 : im.group;

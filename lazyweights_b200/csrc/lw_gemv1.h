@@ -53,6 +53,9 @@ DebugKnobs& debug_knobs();
 bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t rows);
 // False with LW_TILE_OUT=0 in the environment (read once): the decode kernels then keep their 32-byte stores.
 bool tile_output_enabled();
+// Looks the tensor-map encoder up now (done when a matrix is loaded, so that a first decode inside a stream capture makes
+// no such call).
+void tile_output_warm();
 int note_launch(const char* what);   // counts a launch and returns the status of cudaGetLastError
 int sm_count();
 

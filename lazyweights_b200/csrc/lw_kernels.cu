@@ -241,7 +241,9 @@ bool tile_output_enabled() {
   return on;
 }
 
-bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t rows) {
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against the driver library); null where
+// the driver does not offer it.
+static PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
   static const PFN_cuTensorMapEncodeTiled encode = [] {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
@@ -250,6 +252,13 @@ bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t ro
     (void)cudaGetLastError();
     return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
   }();
+  return encode;
+}
+
+void tile_output_warm() { (void)tensor_map_encoder(); }
+
+bool make_row_tile_map(void* tensor_map, void* base, size_t row_bytes, size_t rows) {
+  const PFN_cuTensorMapEncodeTiled encode = tensor_map_encoder();
   if (!encode || (reinterpret_cast<uintptr_t>(base) & 15u) || row_bytes % 32 || rows % kTileRows) return false;
   const cuuint64_t dims[2] = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_bytes};

@@ -134,6 +134,35 @@ def test_decode_kernels_with_plain_stores(lw):
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
 
 
+def test_decode_kernels_replayed_from_a_graph(lw):
+    """Both decode kernels captured into a CUDA graph (their tensor maps travel as kernel parameters) and replayed into
+    cleared buffers: same bits as the oracle."""
+    import torch
+    for ty, n, k in (("Q6_K", 256, 1024), ("Q4_K", 128, 1024)):
+        q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=11 * n + k)
+        blob, _, _ = lw.bundle.encode_huf8(sym)
+        with lw.CodedMatrix(blob, n, sym.shape[1], ty, side) as mat:
+            codes = torch.empty((n, k), dtype=torch.uint8, device="cuda")
+            halves = torch.empty((n, k), dtype=torch.float16, device="cuda")
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                mat.decode_codes("m", expand=True, out=codes)              # first calls outside the capture
+                mat.decode_weights("m", out=halves)
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    mat.decode_codes("m", expand=True, out=codes)
+                    mat.decode_weights("m", out=halves)
+                codes.zero_()
+                halves.zero_()
+                g.replay()
+                stream.synchronize()
+            assert np.array_equal(codes.cpu().numpy(), q), ty
+            assert np.array_equal(halves.cpu().numpy().view(np.uint16), w.astype(np.float16).view(np.uint16)), ty
+            del g
+        assert lw.lib().lw_kernel_error() == 0
+
+
 def test_batched_launch_equals_single_products(lw, tmp_path):
     """lw_linear_batch: several products in one launch (same format and plan), mixed formats (launched one by one),
     several matrices of one handle; results equal the single-product entry point's bit for bit."""
