@@ -1,8 +1,10 @@
 // Decode to codes with the batch-1 kernel's decoder (lw_ring.cuh: replicated 32-bit table, grouped refills chosen from
 // the data, producer warps feeding a ring of staging buffers): the role of k_decode_hufi, kernels/llmrt.cu:767-806.
-// The table here maps a window to the SYMBOL itself (length << 28 | symbol; lw::MatDev::symtab32), not to grid values.
-// A lane writes the symbols of its two rows 32 bytes at a time: 32 symbols, or 16 paired symbols expanded to one 4-bit
-// code per byte (low nibble first, kernels/llmrt.cu:798-800).  Included by lw_decc.cu.
+// The table here maps a window to the SYMBOL itself (length << 28 | symbol; lw::MatDev::symtab32), not to grid values;
+// a pair layout's table already holds two codes per entry.  A lane produces the bytes of its two rows 32 at a time: 32
+// symbols, or 16 paired symbols expanded to one 4-bit code per byte (low nibble first, kernels/llmrt.cu:798-800), or 16
+// pair symbols of two codes.  They leave through the warp's staging area and a 2-D tensor copy (WarpTileStage,
+// lw_ring.cuh) or, without it, as one 32-byte store per lane and row.  Included by lw_decc.cu.
 #pragma once
 #include "lw_ring.cuh"
 

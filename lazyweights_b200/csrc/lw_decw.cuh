@@ -2,8 +2,9 @@
 // table, grouped refills chosen from the data, unit scales staged with the chains, producer warps feeding a ring of
 // staging buffers, units drawn from a shared counter.  Instead of dot products every decoded grid value becomes
 // w = s * f(q) - o in float32 (product and difference rounded separately, llama.cpp's block formulas; reference:
-// scripts/a2_kq_bundle.py:50-68) and one __float2half_rn; a lane writes the weights of its two rows 32 bytes at a time.
-// Included by lw_decw.cu.
+// scripts/a2_kq_bundle.py:50-68) and one round to fp16; a lane produces the weights of its two rows 32 bytes at a time,
+// which leave through the warp's staging area and a 2-D tensor copy (WarpTileStage, lw_ring.cuh) or, without it, as one
+// 32-byte store per lane and row.  Included by lw_decw.cu.
 #pragma once
 #include "lw_gemv1.cuh"
 
@@ -14,8 +15,9 @@ struct DecwArgs {
   __half* out;      // [ntr * 64][K]
 };
 
-// Collects sixteen weights of one chain and stores them as one 32-byte piece (a whole sector: a lane writes to its
-// own row, so every store instruction touches 32 different lines, and 16-byte pieces paid for a full sector each).
+// Collects sixteen weights of one chain: one 32-byte piece of a row.  flush() is the plain-store form (a whole sector:
+// a lane writes to its own row, so every store instruction touches 32 different lines, and 16-byte pieces paid for a
+// full sector each).
 struct HalfPack {
   uint32_t w[8];
   __device__ __forceinline__ void put(int i, float lo, float hi) {   // halfs 2 i, 2 i + 1 of the current sixteen
