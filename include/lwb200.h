@@ -249,6 +249,12 @@ long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int K
                          long long side_bytes, int* info, uint32_t* group_base, long long group_base_cap,
                          uint32_t* words, long long words_cap, uint8_t* unit_class, long long unit_class_cap);
 
+/* The decode table of that layout, lut[2048] = symbol | length << 8 per 11-bit window: the blob's own table, or, where
+ * the loader re-coded the matrix with a shorter length limit (LW_RECODE), the table of the code the device holds.
+ * Returns the longest code length (negative status on error).  No reference counterpart. */
+int lw_host_layout_table(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
+                         long long side_bytes, uint16_t* lut);
+
 /* Pair layout.  For Q6_K and Q5_K matrices whose K is a multiple of 512 the loader keeps a second device layout
  * that every product kernel (one row, 2..8 rows fused, the tensor-core kernel up to 64 rows - where the layout's larger
  * work units fit their shared memory) and the decode to fp16 weights read: two adjacent codes of a row are one symbol of a prefix code built from the matrix's own pair counts (at most

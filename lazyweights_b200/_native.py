@@ -42,6 +42,7 @@ _SIGNATURES = {
     "lw_host_layout": (C.c_longlong, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong,
                                       C.POINTER(C.c_int), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                                       C.c_void_p, C.c_longlong]),
+    "lw_host_layout_table": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
     "lw_matrix_plan": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_double)]),
     "lw_matrix_info": (C.c_int, [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 3 + [C.POINTER(C.c_longlong)] * 3),
     "lw_linear": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

@@ -54,7 +54,8 @@ def cpu_decode_huf8(blob, N, K, threads=0):
 
 def host_layout(blob, N, Ks, fmt="none", side=None):
     """The device layout of one blob, built on the host (no GPU): dict with split, pad, group, index_bits,
-    unit_side_words, max_unit_words and the arrays group_base (uint32), words (uint32), unit_class (uint8)."""
+    unit_side_words, max_unit_words, max_len and the arrays group_base (uint32), words (uint32), unit_class (uint8), lut
+    (uint16[2048]: the decode table of the code the layout holds - the blob's own unless the loader re-coded it)."""
     b, bp = _u8(np.frombuffer(blob, np.uint8))
     s = np.ascontiguousarray(side, np.uint8).reshape(-1) if side is not None else np.zeros(0, np.uint8)
     sp = s.ctypes.data_as(C.c_void_p) if s.size else None
@@ -68,8 +69,12 @@ def host_layout(blob, N, Ks, fmt="none", side=None):
                                  uc.ctypes.data_as(C.c_void_p), uc.size)
     if n < 0:
         nat.check(int(n))
+    lut = np.zeros(2048, np.uint16)
+    max_len = nat.lib().lw_host_layout_table(bp, b.size, N, Ks, nat.FMT[fmt], sp, s.size, lut.ctypes.data_as(C.c_void_p))
+    if max_len < 0:
+        nat.check(int(max_len))
     return dict(split=info[0], pad=info[1], group=info[2], index_bits=info[3], unit_side_words=info[6],
-                max_unit_words=info[7], group_base=gb, words=words, unit_class=uc)
+                max_unit_words=info[7], group_base=gb, words=words, unit_class=uc, lut=lut, max_len=int(max_len))
 
 
 def host_pairs(codes, fmt, side):

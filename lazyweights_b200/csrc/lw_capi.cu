@@ -63,14 +63,31 @@ static int check_side(const Matrix& mx, const uint8_t* side, size_t side_nbytes)
   return kOk;
 }
 
+// Matrices with a block format whose bundle code uses 11-bit words are re-coded at load with the same rule limited to
+// 10 bits (LW_RECODE=0, read at every load: keep the bundle's own code).  The symbols are the same; the device then holds
+// a code whose 1024-window table fits sixteen times where the 2048-window table fits eight times, and shared-memory
+// bank conflicts are what bounds the product kernels (Q4_K 4096 x 4096: 4.5 instead of 5.1 us per product).
+static bool recode_wanted() {
+  const char* e = getenv("LW_RECODE");
+  return !(e && e[0] == '0');
+}
+
 static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, const uint8_t* side, size_t side_nbytes,
-                          int threads, HostImage& im) {
+                          int threads, HostImage& im, bool may_recode = true) {
   BlobView v;
   int rc = make_view(blob, nbytes, mx.N, mx.Ks, v);
   if (rc) return rc;
   if ((rc = check_side(mx, side, side_nbytes))) return rc;
   auto tab = std::make_unique<HuffTable>();
   if ((rc = table_from_lut(v.lut(), *tab))) return rc;
+  if (may_recode && recode_wanted() && mx.fmt != kFmtNone && tab->max_len > 10) {
+    // validate and decode the bundle's blob, encode the symbols again with the shorter limit, lay that blob out
+    std::vector<uint8_t> symbols(static_cast<size_t>(mx.N) * mx.Ks), shorter;
+    if ((rc = walk_blob(v, *tab, default_split(mx.fmt), threads, nullptr, nullptr, symbols.data(), nullptr))) return rc;
+    if ((rc = encode_huf8(symbols.data(), mx.N, mx.Ks, shorter, nullptr, 10, threads))) return rc;
+    symbols = std::vector<uint8_t>();
+    return prepare_matrix(mx, shorter.data(), shorter.size(), side, side_nbytes, threads, im, false);
+  }
   const int split = default_split(mx.fmt);
   std::vector<uint32_t> chain_start, lane_end;
   im.fat.resize(kLutSize);
@@ -948,7 +965,7 @@ long long lw_encode_huf8(const uint8_t* sym, int N, int Ks, uint8_t* out, long l
   }
   std::vector<uint8_t> blob;
   int64_t bits = 0;
-  const int rc = encode_huf8(sym, N, Ks, blob, &bits);
+  const int rc = encode_huf8(sym, N, Ks, blob, &bits, kMaxLen, default_threads());   // the bytes do not depend on the threads
   if (rc) return rc;
   if (nbits) *nbits = bits;
   if (out && cap >= static_cast<long long>(blob.size())) std::memcpy(out, blob.data(), blob.size());
@@ -1003,6 +1020,29 @@ long long lw_host_layout(const uint8_t* blob, long long blob_bytes, int N, int K
   if (unit_class && unit_class_cap >= static_cast<long long>(im.unit_slow.size()) && !im.unit_slow.empty())
     std::memcpy(unit_class, im.unit_slow.data(), im.unit_slow.size());
   return static_cast<long long>(im.words.size());
+}
+
+int lw_host_layout_table(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
+                         long long side_bytes, uint16_t* lut) {
+  if (!blob || blob_bytes <= 0 || !lut || fmt < kFmtNone || fmt > kFmtIQ4XS) {
+    set_error("lw_host_layout_table: bad argument");
+    return kErrArg;
+  }
+  Matrix mx;
+  mx.name = "m";
+  mx.N = N;
+  mx.Ks = Ks;
+  mx.fmt = fmt;
+  mx.paired = is_paired(fmt);
+  mx.K = mx.paired ? 2 * Ks : Ks;
+  std::vector<uint8_t> copy(static_cast<size_t>(blob_bytes) + 16, 0);   // the walk reads 8 bytes at a time
+  std::memcpy(copy.data(), blob, static_cast<size_t>(blob_bytes));
+  HostImage im;
+  const int rc = prepare_matrix(mx, copy.data(), static_cast<size_t>(blob_bytes), side,
+                                static_cast<size_t>(std::max(0ll, side_bytes)), default_threads(), im);
+  if (rc) return rc;
+  std::memcpy(lut, im.lut.data(), 2 * kLutSize);
+  return im.max_len;
 }
 
 long long lw_host_pairs(const uint8_t* codes, int N, int K, int fmt, const uint8_t* side, long long side_bytes_n, int* info,

@@ -4,6 +4,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <array>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -96,13 +97,14 @@ void huffman_depths(const int64_t counts[256], int depth[256]) {
   }
 }
 
-void limited_lengths(const int64_t counts[256], uint8_t len[256]) {
+void limited_lengths(const int64_t counts[256], uint8_t len[256], int limit) {
+  limit = std::max(8, std::min(limit, kMaxLen));
   int depth[256];
   for (int shift = 0;; ++shift) {
     int64_t scaled[256];
     for (int s = 0; s < 256; ++s) scaled[s] = counts[s] > 0 ? std::max<int64_t>(counts[s] >> shift, 1) : 0;
     huffman_depths(scaled, depth);
-    if (*std::max_element(depth, depth + 256) <= kMaxLen) break;
+    if (*std::max_element(depth, depth + 256) <= limit) break;
   }
   for (int s = 0; s < 256; ++s) len[s] = static_cast<uint8_t>(depth[s]);
 }
@@ -230,16 +232,38 @@ int make_view(const uint8_t* blob, size_t nbytes, int N, int Ks, BlobView& v) {
   return kOk;
 }
 
-int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits) {
+int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits, int limit, int threads) {
   if (N <= 0 || Ks <= 0 || N % kTileRows || Ks % kTileSyms) {
     set_error("matrix of %d x %d symbols is not a multiple of 64 x 256", N, Ks);
     return kErrArg;
   }
+  const int KT = Ks / kTileSyms, NT = N / kTileRows, T = NT * KT;
+  threads = std::max(1, std::min(threads, T));
+  // counts, per range of tiles
+  std::vector<std::array<int64_t, 256>> part(threads);
+  for (auto& h : part) h.fill(0);
+  auto tile_range = [&](int w, int& t0, int& t1) {
+    t0 = static_cast<int>(static_cast<int64_t>(T) * w / threads);
+    t1 = static_cast<int>(static_cast<int64_t>(T) * (w + 1) / threads);
+  };
+  auto tile_row = [&](int t, int lane, int half) {
+    return sym + (static_cast<size_t>(t / KT) * kTileRows + half * 32 + lane) * Ks + static_cast<size_t>(t % KT) * kTileSyms;
+  };
+  parallel_for(threads, threads, [&](int w) {
+    int t0, t1;
+    tile_range(w, t0, t1);
+    auto& h = part[w];
+    for (int t = t0; t < t1; ++t)
+      for (int r = 0; r < kTileRows; ++r) {
+        const uint8_t* row = tile_row(t, r & 31, r >> 5);
+        for (int c = 0; c < kTileSyms; ++c) ++h[row[c]];
+      }
+  });
   int64_t hist[256] = {0};
-  const size_t total_sym = static_cast<size_t>(N) * Ks;
-  for (size_t i = 0; i < total_sym; ++i) ++hist[sym[i]];
+  for (auto& h : part)
+    for (int s = 0; s < 256; ++s) hist[s] += h[s];
   uint8_t len[256];
-  limited_lengths(hist, len);
+  limited_lengths(hist, len, limit);
   HuffTable tab;
   table_from_lengths(len, tab);
   uint32_t rcode[256] = {0};
@@ -257,36 +281,57 @@ int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, i
     set_error("payload of %llu bits does not fit 32-bit lane offsets", static_cast<unsigned long long>(total));
     return kErrTooLarge;
   }
-  const int KT = Ks / kTileSyms, NT = N / kTileRows, T = NT * KT;
   const size_t nwords = (total + 31) / 32 + 2;
   const size_t head = 2 * kLutSize + static_cast<size_t>(T) * kLanes * 4;
   blob.assign(head + nwords * 4, 0);
   std::memcpy(blob.data(), tab.lut, 2 * kLutSize);
   uint32_t* starts = reinterpret_cast<uint32_t*>(blob.data() + 2 * kLutSize);
   uint32_t* words = reinterpret_cast<uint32_t*>(blob.data() + head);
-  uint64_t acc = 0, pos = 0;   // acc holds the bits of the current 32-bit word and beyond
-  size_t wi = 0;
-  int fill = 0;
-  for (int tr = 0; tr < NT; ++tr)
-    for (int tc = 0; tc < KT; ++tc)
+  // where every range of tiles starts in the stream: the bits of the ranges before it
+  std::vector<uint64_t> range_bits(threads + 1, 0);
+  for (int w = 0; w < threads; ++w) {
+    uint64_t b = 0;
+    for (int s = 0; s < 256; ++s) b += static_cast<uint64_t>(part[w][s]) * len[s];
+    range_bits[w + 1] = range_bits[w] + b;
+  }
+  // Lanes follow one another bit by bit, so two ranges can share a word: whole words are stored, the first and the last
+  // word of a range are OR-ed in atomically (the words start as zero and the ranges' bits are disjoint).
+  parallel_for(threads, threads, [&](int w) {
+    int t0, t1;
+    tile_range(w, t0, t1);
+    if (t0 == t1) return;
+    uint64_t pos = range_bits[w];
+    size_t wi = pos >> 5;
+    const size_t first = wi, last = (range_bits[w + 1] - 1) >> 5;
+    int fill = static_cast<int>(pos & 31);
+    uint64_t acc = 0;   // the bits of word wi and beyond, bit `fill` is the next free one
+    auto put = [&](uint32_t v) {
+      if (wi == first || wi == last)
+        __atomic_fetch_or(words + wi, v, __ATOMIC_RELAXED);
+      else
+        words[wi] = v;
+      ++wi;
+    };
+    for (int t = t0; t < t1; ++t)
       for (int lane = 0; lane < kLanes; ++lane) {
-        starts[(static_cast<size_t>(tr) * KT + tc) * kLanes + lane] = static_cast<uint32_t>(pos);
+        starts[static_cast<size_t>(t) * kLanes + lane] = static_cast<uint32_t>(pos);
         for (int half = 0; half < 2; ++half) {
-          const uint8_t* row = sym + (static_cast<size_t>(tr) * kTileRows + half * 32 + lane) * Ks + tc * kTileSyms;
+          const uint8_t* row = tile_row(t, lane, half);
           for (int c = 0; c < kTileSyms; ++c) {
             const int s = row[c], l = len[s];
             acc |= static_cast<uint64_t>(rcode[s]) << fill;
             fill += l;
             pos += l;
             if (fill >= 32) {
-              words[wi++] = static_cast<uint32_t>(acc);
+              put(static_cast<uint32_t>(acc));
               acc >>= 32;
               fill -= 32;
             }
           }
         }
       }
-  if (fill) words[wi++] = static_cast<uint32_t>(acc);
+    if (fill) put(static_cast<uint32_t>(acc));
+  });
   if (nbits) *nbits = static_cast<int64_t>(total);
   return kOk;
 }

@@ -19,7 +19,8 @@ int last_status();
 
 // ---- tables (reference: lazyweights/huffman.py:8-26, lazyweights/lanecodecs.py:28-62, lazyweights/bundle.py:46-54)
 void huffman_depths(const int64_t counts[256], int depth[256]);
-void limited_lengths(const int64_t counts[256], uint8_t len[256]);
+// limit: the longest code allowed (the bundle format's own is kMaxLen = 11; any limit >= 8 fits 256 symbols)
+void limited_lengths(const int64_t counts[256], uint8_t len[256], int limit = kMaxLen);
 void table_from_lengths(const uint8_t len[256], HuffTable& t);
 // Recovers lengths from a stored table and checks that the table is exactly the canonical one for those lengths.
 int table_from_lut(const uint16_t* lut, HuffTable& t);
@@ -43,7 +44,9 @@ int build_twin(const uint8_t* sym, int N, int Ks, int fmt, const uint8_t* side, 
                std::vector<uint32_t>& group_base, std::vector<uint32_t>& words, uint32_t* unit_words);
 
 // ---- blob (reference: lazyweights/bundle.py:57-106, kernels/llmrt.cu:2513-2541)
-int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits);
+// limit / threads: the code's longest word (kMaxLen = the bundle format's own rule, whose blobs are byte-identical to the
+// reference encoder's) and the threads that pack tile ranges side by side (the result does not depend on them).
+int encode_huf8(const uint8_t* sym, int N, int Ks, std::vector<uint8_t>& blob, int64_t* nbits, int limit = kMaxLen, int threads = 1);
 int make_view(const uint8_t* blob, size_t nbytes, int N, int Ks, BlobView& v);
 
 // Walks every lane once.  chain_start[(t * 32 + l) * (2 * split) + g] = absolute bit offset at which chain g of the

@@ -136,6 +136,7 @@ def test_batch1_grouped_and_symbol_by_symbol_units(lw, monkeypatch, ty, n, k, fo
     """The batch-1 kernel decodes groups of symbols per refill where the loader proved that exact and single symbols
     elsewhere; both kinds of work unit, every group size and both table widths must give the oracle's product."""
     import torch
+    monkeypatch.setenv("LW_RECODE", "0")   # the bundle's own code: 11-bit words, hence symbol-by-symbol units under a 10-bit table
     q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=n * 7 + k)
     # one work unit full of codes from the tails of the distribution (long codes, many bits per group)
     tails = {"Q4_K": [0, 1, 2, 14, 15], "IQ4_XS": [0, 1, 2, 14, 15], "Q5_K": [0, 1, 2, 3, 4, 5, 27, 28, 29, 30, 31],

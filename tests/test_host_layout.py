@@ -1,6 +1,8 @@
 """The load-time device layout, checked on the CPU: the batch-1 kernel's grouped bit arithmetic is replayed in Python
 on the words the host produced, unit by unit, with the unit class the host assigned; it must return every symbol.
 Also: the scales stored behind every work unit equal the oracle's sub-block scales."""
+import os
+
 import numpy as np
 import pytest
 
@@ -56,9 +58,13 @@ def _tail_block(ty, q, rng, rows, cols):
 
 @pytest.mark.parametrize("ty,n,k", [("Q6_K", 128, 512), ("Q4_K", 64, 1024), ("Q5_K", 64, 512), ("IQ4_XS", 64, 1024)])
 @pytest.mark.parametrize("force", [None, ("max", "10"), ("max", "11"), ("3", "11")])
-def test_grouped_decoder_replayed_on_cpu(monkeypatch, ty, n, k, force):
+@pytest.mark.parametrize("recode", ["1", "0"])
+def test_grouped_decoder_replayed_on_cpu(monkeypatch, ty, n, k, force, recode):
+    """recode 1: the loader's default, the matrix re-coded with words of at most 10 bits where the bundle's code has
+    11-bit words; 0: the bundle's own code (whose long words make symbol-by-symbol units under a 10-bit table)."""
     helpers.build_library()
     import lazyweights_b200 as lw
+    monkeypatch.setenv("LW_RECODE", recode)
     q, side, sym, w, rng = helpers.seeded_case(ty, n, k, seed=17 + n + k)
     _tail_block(ty, q, rng, slice(0, 64), slice(64, 128))        # long codes back to back in one unit
     sym = orc.symbols_of(ty, q)
@@ -68,7 +74,12 @@ def test_grouped_decoder_replayed_on_cpu(monkeypatch, ty, n, k, force):
         monkeypatch.setenv("LW_GEMV1_IDX", force[1])
     blob, _, _ = lw.bundle.encode_huf8(sym)
     lay = lw.bundle.host_layout(blob, n, sym.shape[1], ty, side)
-    lut = np.frombuffer(blob, np.uint16, 2048)
+    lut = lay["lut"]                                              # the blob's table, or the re-coded layout's
+    own = np.frombuffer(blob, np.uint16, 2048)
+    if recode == "0" or (own >> 8).max() <= 10:
+        assert np.array_equal(lut, own) and lay["max_len"] == (own >> 8).max()
+    else:
+        assert lay["max_len"] <= 10 and (lut >> 8).max() <= 10 and not np.array_equal(lut, own)
     split, pad, group, ib = lay["split"], lay["pad"], lay["group"], lay["index_bits"]
     assert group >= 3 and ib in (10, 11) and pad == 6 and split == (2 if ty == "Q5_K" else 4)
     if force:
