@@ -200,7 +200,10 @@ int lw_decode_codes(void* handle, int id, uint8_t* out_dev, int expand, void* st
 /* ---- single matrices without a bundle directory (additions) ---------------------------------------------- */
 
 /* Builds a one-matrix handle from a blob in host memory (N rows, Ks symbols per row), an optional side tensor and
- * its block format.  The matrix has id 0.  Released by rt_close. */
+ * its block format.  The matrix has id 0.  Released by rt_close.
+ * What the device holds (here and in rt_open) is the loader's business: a block-format matrix whose code has 11-bit
+ * words is re-coded with words of at most 10 bits (LW_RECODE=0 in the environment: not), Q6_K / Q5_K matrices also get a
+ * pair layout (below).  Decoded symbols, products and the byte counts lw_matrix_info reports for the bundle do not change. */
 void* lw_matrix_create(const uint8_t* blob, long long blob_bytes, int N, int Ks, int fmt, const uint8_t* side,
                        long long side_bytes);
 
