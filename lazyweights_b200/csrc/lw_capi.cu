@@ -84,9 +84,10 @@ static int prepare_matrix(const Matrix& mx, const uint8_t* blob, size_t nbytes, 
     // validate and decode the bundle's blob, encode the symbols again with the shorter limit, lay that blob out
     std::vector<uint8_t> symbols(static_cast<size_t>(mx.N) * mx.Ks), shorter;
     if ((rc = walk_blob(v, *tab, default_split(mx.fmt), threads, nullptr, nullptr, symbols.data(), nullptr))) return rc;
-    if ((rc = encode_huf8(symbols.data(), mx.N, mx.Ks, shorter, nullptr, 10, threads))) return rc;
+    rc = encode_huf8(symbols.data(), mx.N, mx.Ks, shorter, nullptr, 10, threads);
     symbols = std::vector<uint8_t>();
-    return prepare_matrix(mx, shorter.data(), shorter.size(), side, side_nbytes, threads, im, false);
+    if (rc == kOk) return prepare_matrix(mx, shorter.data(), shorter.size(), side, side_nbytes, threads, im, false);
+    if (rc != kErrTooLarge) return rc;   // a payload at the format's 2^32-bit limit: the bundle's own code stays
   }
   const int split = default_split(mx.fmt);
   std::vector<uint32_t> chain_start, lane_end;
