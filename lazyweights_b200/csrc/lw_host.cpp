@@ -8,6 +8,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <queue>
@@ -37,6 +38,10 @@ int note_status(int rc) {
 int last_status() { return g_status; }
 
 int default_threads() {
+  if (const char* e = getenv("LW_THREADS")) {   // host threads of the loader and the host codec (read at every use)
+    const int n = atoi(e);
+    if (n >= 1) return std::min(n, 256);
+  }
   unsigned n = std::thread::hardware_concurrency();
   return n ? static_cast<int>(n) : 1;
 }

@@ -138,3 +138,19 @@ def test_gpu_entry_points_fail_loudly_without_device(lwlib, golden_dir, tmp_path
     w.close()
     with pytest.raises(lwlib.LwError):
         runtime.Bundle(str(tmp_path / "b"))
+
+
+def test_encoder_bytes_do_not_depend_on_the_threads(monkeypatch):
+    """The encoder packs ranges of tiles side by side (LW_THREADS host threads) and ORs the words two ranges share:
+    one thread, a few, and more threads than tiles must give the same bytes."""
+    helpers.build_library()
+    import lazyweights_b200 as lw
+    rng = np.random.default_rng(8)
+    sym = np.clip(np.rint(rng.laplace(100.0, 6.0, (192, 768))), 0, 255).astype(np.uint8)   # 3 x 3 tiles, long and short words
+    blobs = []
+    for threads in ("1", "2", "5", "64"):
+        monkeypatch.setenv("LW_THREADS", threads)
+        blob, _, bits = lw.bundle.encode_huf8(sym)
+        blobs.append(bytes(blob))
+    assert all(b == blobs[0] for b in blobs[1:])
+    assert np.array_equal(orc.decode_huf8(blobs[0], *sym.shape), sym)
